@@ -1,0 +1,266 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes driver for the C oracle (``oracle/ocnn_oracle.c``).
+
+The oracle restates the reference's CPU algorithms for the octree hot path.  Only tests, the
+smoke check and the benchmark's CPU-baseline leg import this module; the shipped CUDA library
+never does.  ``OctreeView`` is a small numpy reader of the octree wire format used by the tests to
+slice properties out of a buffer, whichever implementation produced it.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+c_float_p = ctypes.POINTER(ctypes.c_float)
+c_int_p = ctypes.POINTER(ctypes.c_int32)
+c_u8_p = ctypes.POINTER(ctypes.c_uint8)
+
+PROPS = ['key', 'child', 'neigh', 'feature', 'label', 'split']
+
+
+def build():
+  """Compile the C oracle in place (gcc only; a second or so)."""
+  subprocess.check_call(['make', '-s', '-C', _HERE, 'port'])
+
+
+def lib():
+  global _LIB
+  if _LIB is None:
+    path = os.path.join(_HERE, 'libocnn_oracle.so')
+    src = os.path.join(_HERE, 'ocnn_oracle.c')
+    if not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(src):
+      build()
+    L = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+    L.oc_points2octree.restype = ctypes.c_long
+    L.oc_points2octree.argtypes = [ctypes.c_char_p] + [ctypes.c_int] * 7 + [
+        ctypes.c_float, ctypes.c_float, c_float_p, c_u8_p, ctypes.c_long]
+    L.oc_octree_batch.restype = ctypes.c_long
+    L.oc_octree_batch.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.c_int, c_u8_p,
+                                  ctypes.c_long]
+    L.oc_morton.restype = ctypes.c_uint64
+    L.oc_morton.argtypes = [ctypes.c_uint64] * 3 + [ctypes.c_int]
+    L.oc_ni_table.restype = ctypes.c_int
+    L.oc_ni_table.argtypes = [c_int_p, c_int_p]
+    L.oc_calc_neigh_full.argtypes = [c_int_p, ctypes.c_int, ctypes.c_int]
+    L.oc_calc_neigh_split.argtypes = [c_int_p, c_int_p, c_int_p, ctypes.c_int]
+    L.oc_octree2col.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 4 + [c_int_p, c_int_p]
+    L.oc_octree_conv.restype = ctypes.c_long
+    L.oc_octree_conv.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p, ctypes.c_char_p,
+                                 ctypes.c_int, ctypes.c_int, ctypes.c_int, c_int_p, ctypes.c_int]
+    L.oc_max_pool.argtypes = [c_float_p, ctypes.c_int, c_int_p, c_float_p, ctypes.c_int,
+                              ctypes.c_int]
+    L.oc_pad.argtypes = [c_float_p, ctypes.c_int, ctypes.c_int, c_float_p, ctypes.c_int, c_int_p,
+                         ctypes.c_float]
+    L.oc_depad.argtypes = [c_float_p, ctypes.c_int, ctypes.c_int, c_float_p, ctypes.c_int,
+                           c_int_p]
+    _LIB = L
+  return _LIB
+
+
+def _fp(a):
+  return None if a is None else a.ctypes.data_as(c_float_p)
+
+
+def _ip(a):
+  return None if a is None else a.ctypes.data_as(c_int_p)
+
+
+def _f32(a):
+  return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+  return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _bytes(a):
+  return np.ascontiguousarray(a, dtype=np.uint8).tobytes()
+
+
+# -- wire formats --------------------------------------------------------------------------
+def points_new(pts, normals=None, feats=None, labels=None):
+  """Points buffer: 88-byte PointsInfo header then xyz / normal / feature / label arrays,
+  point-major float32 (octree/octree/points_info.h:8-40, points.cpp:96-150)."""
+  pts = _f32(pts).reshape(-1, 3)
+  n = pts.shape[0]
+  blocks = [pts]
+  channels = [3, 0, 0, 0]
+  flags = 1
+  for i, arr in enumerate((normals, feats, labels), start=1):
+    if arr is None:
+      blocks.append(None)
+      continue
+    arr = _f32(arr).reshape(n, -1)
+    channels[i] = arr.shape[1]
+    flags |= 1 << i
+    blocks.append(arr)
+  hdr = np.zeros(88, dtype=np.uint8)
+  hdr[:12] = np.frombuffer(b'_POINTS_1.0_', dtype=np.uint8)
+  ints = hdr[16:].view(np.int32)
+  ints[0] = n
+  ints[1] = flags
+  ints[2:6] = channels
+  dis = 88
+  for i in range(5):
+    ints[10 + i] = dis
+    if i < 4:
+      dis += 4 * n * channels[i]
+  payload = b''.join(b.tobytes() for b in blocks if b is not None)
+  return np.concatenate([hdr, np.frombuffer(payload, dtype=np.uint8)])
+
+
+class OctreeView:
+  """Read-only numpy view of an octree buffer (single or merged batch)."""
+
+  def __init__(self, buf):
+    self.buf = np.ascontiguousarray(buf, dtype=np.uint8)
+    b = self.buf
+    self.magic = bytes(b[:12])
+    self.key_bits = 64 if self.magic == b'_OCTREE_2.0_' else 32
+    i32 = lambda off, n=1: b[off:off + 4 * n].view(np.int32)
+    self.batch_size = int(i32(16)[0])
+    self.depth = int(i32(20)[0])
+    self.full_depth = int(i32(24)[0])
+    self.nnum = i32(48, 16).copy()
+    self.nnum_cum = i32(112, 16).copy()
+    self.nnum_nempty = i32(176, 16).copy()
+    self.content_flags = int(i32(240)[0])
+    self.channels = i32(244, 16).copy()
+    self.locations = i32(308, 16).copy()
+    self.ptr_dis = i32(652, 16).copy()
+    self.sizeof_octree = int(self.ptr_dis[6])
+
+  def has(self, prop):
+    return self.channels[PROPS.index(prop)] != 0
+
+  def prop(self, prop, d):
+    """Array of property `prop` at level d: key uint32/uint64 [n], child int32 [n],
+    neigh int32 [n/8, 64], feature float32 [C, n], label/split float32 [n]."""
+    p = PROPS.index(prop)
+    ch = int(self.channels[p])
+    assert ch != 0, prop
+    esz = self.key_bits // 8 if prop == 'key' else 4
+    off = int(self.ptr_dis[p])
+    if self.locations[p] == -1:
+      off += int(self.nnum_cum[d]) * ch * esz
+    else:
+      assert d == self.locations[p]
+    n = int(self.nnum[d])
+    raw = self.buf[off:off + n * ch * esz]
+    if prop == 'key':
+      return raw.view(np.uint64 if esz == 8 else np.uint32)
+    if prop in ('child',):
+      return raw.view(np.int32)
+    if prop == 'neigh':
+      return raw.view(np.int32).reshape(-1, 64)
+    if prop == 'feature':
+      return raw.view(np.float32).reshape(ch, n)
+    return raw.view(np.float32)
+
+
+# -- oracle calls --------------------------------------------------------------------------
+def _sized(call):
+  n = call(None, 0)
+  if n < 0:
+    raise ValueError('oracle call failed (%d)' % n)
+  out = np.zeros(n, dtype=np.uint8)
+  m = call(out.ctypes.data_as(c_u8_p), n)
+  assert m == n
+  return out
+
+
+def points2octree(points, depth, full_depth=2, node_dis=False, split_label=False,
+                  save_pts=False, key_bits=32, bbox=None, adp_depth=4, th_normal=0.1,
+                  th_distance=2.0):
+  pbuf = _bytes(points)
+  bb = None if bbox is None else _f32(bbox)
+  return _sized(lambda o, c: lib().oc_points2octree(
+      pbuf, depth, full_depth, int(node_dis), int(split_label), int(save_pts), key_bits,
+      adp_depth, th_normal, th_distance, _fp(bb), o, c))
+
+
+def octree_batch(octrees):
+  bufs = [_bytes(o) for o in octrees]
+  arr = (ctypes.c_char_p * len(bufs))(*bufs)
+  return _sized(lambda o, c: lib().oc_octree_batch(arr, len(bufs), o, c))
+
+
+def morton(x, y, z, depth):
+  return int(lib().oc_morton(int(x), int(y), int(z), depth))
+
+
+def ni_table(ksize):
+  ks = _i32(ksize)
+  n = lib().oc_ni_table(_ip(ks), None)
+  if n < 0:
+    raise ValueError('unsupported kernel size %s' % (list(ksize),))
+  out = np.empty(n, np.int32)
+  lib().oc_ni_table(_ip(ks), _ip(out))
+  return out
+
+
+def calc_neigh_full(depth, batch_size):
+  out = np.empty(batch_size * (8 ** depth) * 8, dtype=np.int32)
+  lib().oc_calc_neigh_full(_ip(out), depth, batch_size)
+  return out
+
+
+def calc_neigh_split(neigh, child, nnum_child, fill=-7):
+  neigh, child = _i32(neigh), _i32(child)
+  out = np.full(nnum_child * 8, fill, dtype=np.int32)
+  lib().oc_calc_neigh_split(_ip(out), _ip(neigh), _ip(child), child.size)
+  return out
+
+
+def octree2col(data, neigh, ksize, stride, height):
+  data, neigh = _f32(data), _i32(neigh)
+  channel = data.shape[0]
+  ni = ni_table(ksize)
+  kdim = int(np.prod(ksize))
+  col = np.empty((channel, kdim, height), np.float32)
+  lib().oc_octree2col(_fp(col), _fp(data), channel, height, kdim, stride, _ip(neigh), _ip(ni))
+  return col
+
+
+def octree_conv(data, weights, octree, depth, num_output, ksize, stride):
+  data, weights = _f32(data), _f32(weights)
+  ks = _i32(ksize)
+  obuf = _bytes(octree)
+  cin = data.shape[0]
+  n = lib().oc_octree_conv(None, 0, _fp(data), _fp(weights), obuf, depth, cin, num_output,
+                           _ip(ks), stride)
+  if n < 0:
+    raise ValueError('unsupported convolution')
+  top = np.zeros((num_output, n // num_output), np.float32)
+  lib().oc_octree_conv(_fp(top), n, _fp(data), _fp(weights), obuf, depth, cin, num_output,
+                       _ip(ks), stride)
+  return top
+
+
+def max_pool(btm):
+  btm = _f32(btm)
+  channel, btm_h = btm.shape
+  top_h = btm_h // 8
+  top = np.empty((channel, top_h), np.float32)
+  mask = np.empty((channel, top_h), np.int32)
+  lib().oc_max_pool(_fp(top), top_h, _ip(mask), _fp(btm), btm_h, channel)
+  return top, mask
+
+
+def pad(x, child, val=0.0):
+  x, child = _f32(x), _i32(child)
+  channel, hx = x.shape
+  y = np.empty((channel, child.size), np.float32)
+  lib().oc_pad(_fp(y), child.size, channel, _fp(x), hx, _ip(child), val)
+  return y
+
+
+def depad(y, child, hx):
+  y, child = _f32(y), _i32(child)
+  channel = y.shape[0]
+  x = np.zeros((channel, hx), np.float32)
+  lib().oc_depad(_fp(x), hx, channel, _fp(y), child.size, _ip(child))
+  return x

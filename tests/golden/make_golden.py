@@ -1,0 +1,98 @@
+"""Generate tests/golden/reference_vectors.npz from the reference's own CPU code.
+
+Run in a container that has the reference checkout (it is compiled unmodified by
+``make -C oracle ref``):
+
+    python tests/golden/make_golden.py
+
+Every array written here is an input fed to, or an output produced by, the reference
+(``oracle/_ref/libocnn_ref{32,64}.so``); nothing is computed by this repository's own oracle or
+CUDA code.  The fixtures let the oracle be pinned on machines where the reference is absent.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, 'o-cnn_b200'))
+
+from oracle import ref  # noqa: E402
+from ocnn_harness import synth  # noqa: E402
+
+KERNELS = [[3, 3, 3], [2, 2, 2], [3, 1, 1], [1, 3, 1], [1, 1, 3], [3, 3, 1], [3, 1, 3], [1, 3, 3],
+           [1, 1, 1]]
+
+
+def main():
+  out = {}
+  rng = np.random.default_rng(20240)
+  for kb in (32, 64):
+    R = ref.get(kb)
+    tag = 'k%d_' % kb
+    for name in ('octree_1', 'octree_2'):
+      out[tag + name] = R.octree_sample(name)
+    out[tag + 'merge_samples_12'] = R.octree_batch([out[tag + 'octree_1'], out[tag + 'octree_2']])
+    out[tag + 'merge_samples_11'] = R.octree_batch([out[tag + 'octree_1']] * 2)
+
+    # one cloud with every supported signal, two flag combinations
+    if kb == 32:
+      p, q = synth.primitive_union(250, 11)
+      out['a_xyz'], out['a_normal'] = p, q
+      out['a_feat'] = rng.normal(size=(250, 2)).astype(np.float32)
+      out['a_label'] = rng.integers(-1, 4, size=250).astype(np.float32)
+    pts = R.points_new(out['a_xyz'], out['a_normal'], out['a_feat'], out['a_label'])
+    if kb == 32:
+      out['a_points'] = pts
+    out[tag + 'a_octree'] = R.points2octree(pts, 5, 2)
+    out[tag + 'a_octree_flags'] = R.points2octree(pts, 5, 2, node_dis=True, split_label=True,
+                                                  save_pts=True)
+    pts_nn = R.points_new(out['a_xyz'], None, out['a_feat'])
+    out[tag + 'a_octree_nonormal'] = R.points2octree(pts_nn, 4, 1, node_dis=True)
+
+    # a merged batch of three clouds and the operators on it
+    singles = []
+    for i in range(3):
+      if kb == 32:
+        p, q = synth.primitive_union(120 + 30 * i, 21 + i)
+        out['b%d_xyz' % i], out['b%d_normal' % i] = p, q
+      singles.append(R.points2octree(R.points_new(out['b%d_xyz' % i], out['b%d_normal' % i]), 4, 2))
+      out[tag + 'b%d_octree' % i] = singles[-1]
+    merged = R.octree_batch(singles)
+    out[tag + 'b_merged'] = merged
+    if kb == 32:
+      info = R.octree_info(merged)
+      d = 4
+      H, Hne = int(info['nnum'][d]), int(info['nnum_nempty'][d])
+      out['b_x'] = rng.uniform(-1, 1, size=(3, H)).astype(np.float32)
+      out['b_xne'] = rng.uniform(-1, 1, size=(3, Hne)).astype(np.float32)
+      for ks in KERNELS:
+        kd = int(np.prod(ks))
+        name = ''.join(map(str, ks))
+        out['b_w' + name] = rng.normal(scale=0.2, size=(5, 3 * kd)).astype(np.float32)
+        for stride in (1, 2):
+          out['b_conv%s_s%d' % (name, stride)] = R.octree_conv(
+              out['b_x'], out['b_w' + name], merged, d, 5, ks, stride)
+      neigh = merged[info['ptr_dis']['neigh'] + 32 * int(info['nnum_cum'][d]):][:32 * H].view(np.int32)
+      child = merged[info['ptr_dis']['child'] + 4 * int(info['nnum_cum'][d]):][:4 * H].view(np.int32)
+      out['b_col311_s1'] = R.octree2col(out['b_x'], neigh, [3, 1, 1], 1, H)
+      out['b_col222_s2'] = R.octree2col(out['b_x'], neigh, [2, 2, 2], 2, H // 8)
+      top, mask = R.max_pool(out['b_x'])
+      out['b_pool'], out['b_pool_mask'] = top, mask
+      out['b_pad'] = R.pad_forward(out['b_xne'], child, 0.25)
+      out['b_depad'] = R.pad_backward(out['b_x'], child, Hne)
+      for dd in (1, 2, 3):
+        out['neigh_full_d%d_b2' % dd] = R.calc_neigh_full(dd, 2)
+      parent, dis = R.neigh_tables()
+      out['tbl_parent'], out['tbl_dis'] = parent, dis
+      for ks in KERNELS:
+        out['tbl_ni' + ''.join(map(str, ks))] = R.ni_table(ks)
+
+  path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'reference_vectors.npz')
+  np.savez_compressed(path, **out)
+  print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
+
+
+if __name__ == '__main__':
+  main()

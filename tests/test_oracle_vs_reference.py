@@ -1,0 +1,137 @@
+"""Differential test: the C oracle against the reference's own CPU code compiled unmodified
+(oracle/_ref, built by `make -C oracle ref` where the reference checkout exists).  Bit-exact on
+every output.  Skipped where the compiled reference is absent; the committed fixtures
+(test_oracle_golden.py) pin the oracle there."""
+import numpy as np
+import pytest
+
+from conftest import same_bits
+from oracle import oracle as oc
+from oracle import ref
+from ocnn_harness import synth
+
+pytestmark = pytest.mark.skipif(not (ref.available(32) and ref.available(64)),
+                                reason='compiled reference (oracle/_ref) not present')
+
+KERNELS = [[3, 3, 3], [2, 2, 2], [3, 1, 1], [1, 3, 1], [1, 1, 3], [3, 3, 1], [3, 1, 3], [1, 3, 3],
+           [1, 1, 1]]
+
+
+@pytest.fixture(scope='module', params=[32, 64])
+def batch(request):
+  kb = request.param
+  R = ref.get(kb)
+  rng = np.random.default_rng(3 + kb)
+  singles_r, singles_o = [], []
+  for i in range(3):
+    p, q = synth.primitive_union(4000 + 500 * i, 70 + i)
+    f = rng.normal(size=(p.shape[0], 2)).astype(np.float32)
+    pr, po = R.points_new(p, q, f), oc.points_new(p, q, f)
+    assert same_bits(pr, po)
+    singles_r.append(R.points2octree(pr, 6, 2))
+    singles_o.append(oc.points2octree(po, 6, 2, key_bits=kb))
+    assert same_bits(singles_r[-1], singles_o[-1])
+  return kb, R, R.octree_batch(singles_r), oc.octree_batch(singles_o)
+
+
+@pytest.mark.parametrize('kb', [32, 64])
+@pytest.mark.parametrize('flags', [(0, 0, 0), (1, 1, 0), (1, 0, 1), (0, 1, 1)])
+def test_build_flags(kb, flags):
+  R = ref.get(kb)
+  nd, sl, sp = flags
+  rng = np.random.default_rng(17)
+  p, q = synth.primitive_union(6000, 5, jitter_frac=0.05, jitter_sigma=0.005)
+  f = rng.normal(size=(p.shape[0], 3)).astype(np.float32)
+  lab = rng.integers(-1, 6, size=p.shape[0]).astype(np.float32)
+  for normals in (q, None):
+    pts = oc.points_new(p, normals, f, lab)
+    for depth, full in ((7, 2), (4, 3), (3, 3), (5, 1)):
+      a = R.points2octree(pts, depth, full, node_dis=nd, split_label=sl, save_pts=sp)
+      b = oc.points2octree(pts, depth, full, node_dis=nd, split_label=sl, save_pts=sp,
+                           key_bits=kb)
+      assert same_bits(a, b), (depth, full, normals is None)
+
+
+def test_build_deep_64bit():
+  R = ref.get(64)
+  p, q, c = synth.indoor_scene(20000, 5000)
+  pts = oc.points_new(p, q, c)
+  assert same_bits(R.points2octree(pts, 9, 2), oc.points2octree(pts, 9, 2, key_bits=64))
+  assert same_bits(R.points2octree(pts, 12, 3, node_dis=True),
+                   oc.points2octree(pts, 12, 3, node_dis=True, key_bits=64))
+
+
+def test_degenerate_clouds():
+  for kb in (32, 64):
+    R = ref.get(kb)
+    one = oc.points_new([0.3, -0.2, 0.1], [0.0, 0.0, 1.0])
+    assert same_bits(R.points2octree(one, 5, 2), oc.points2octree(one, 5, 2, key_bits=kb))
+    # all points in one cell, cancelling normals (falls back to the first point's normal)
+    p = np.tile(np.array([[0.5, 0.5, 0.5]], np.float32), (4, 1))
+    q = np.array([[1, 0, 0], [-1, 0, 0], [0, 1, 0], [0, -1, 0]], np.float32)
+    same = oc.points_new(p, q)
+    assert same_bits(R.points2octree(same, 6, 2), oc.points2octree(same, 6, 2, key_bits=kb))
+    single = R.points2octree(one, 5, 2)
+    assert same_bits(R.octree_batch([single]), oc.octree_batch([single]))
+
+
+def test_merge(batch):
+  kb, R, merged_r, merged_o = batch
+  assert same_bits(merged_r, merged_o)
+  info = R.octree_info(merged_o)
+  v = oc.OctreeView(merged_o)
+  assert info['key_bits'] == kb and info['sizeof_octree'] == merged_o.size == v.sizeof_octree
+  assert np.array_equal(info['nnum'], v.nnum) and np.array_equal(info['nnum_cum'], v.nnum_cum)
+  assert np.array_equal(info['nnum_nempty'], v.nnum_nempty)
+  for i, p in enumerate(oc.PROPS):
+    assert info['channel'][p] == v.channels[i]
+    if v.channels[i]:
+      assert info['ptr_dis'][p] == v.ptr_dis[i] and info['location'][p] == v.locations[i]
+
+
+def test_neighbour_tables(batch):
+  kb, R, merged_r, _ = batch
+  v = oc.OctreeView(merged_r)
+  for d in (1, 2, 3):
+    assert np.array_equal(R.calc_neigh_full(d, 3), oc.calc_neigh_full(d, 3))
+  for d in range(3, 7):
+    a = R.calc_neigh_split(v.prop('neigh', d - 1), v.prop('child', d - 1), int(v.nnum[d]))
+    b = oc.calc_neigh_split(v.prop('neigh', d - 1), v.prop('child', d - 1), int(v.nnum[d]))
+    assert np.array_equal(a, b)
+  for ks in KERNELS:
+    assert np.array_equal(R.ni_table(ks), oc.ni_table(ks))
+
+
+@pytest.mark.parametrize('ks', KERNELS)
+@pytest.mark.parametrize('stride', [1, 2])
+def test_conv_and_octree2col(batch, ks, stride):
+  kb, R, merged_r, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(sum(ks) * 10 + stride)
+  for d in (6, 4):
+    H = int(v.nnum[d])
+    cin, cout = 3, 5
+    x = rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)
+    w = rng.normal(size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
+    assert same_bits(R.octree_conv(x, w, merged_r, d, cout, ks, stride),
+                     oc.octree_conv(x, w, merged_o, d, cout, ks, stride))
+    hc = H if stride == 1 else H // 8
+    assert same_bits(R.octree2col(x, v.prop('neigh', d), ks, stride, hc),
+                     oc.octree2col(x, v.prop('neigh', d), ks, stride, hc))
+
+
+def test_pool_pad_depad(batch):
+  kb, R, _, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(8)
+  for d in (6, 5, 3):
+    H, Hne = int(v.nnum[d]), int(v.nnum_nempty[d])
+    x = rng.uniform(-1, 1, size=(4, H)).astype(np.float32)
+    x[0, :16] = 1.0            # ties: the first maximum must win
+    x[1, 8:16] = np.nan        # NaN never wins a '>' comparison
+    a, b = R.max_pool(x), oc.max_pool(x)
+    assert same_bits(a[0], b[0]) and same_bits(a[1], b[1])
+    child = v.prop('child', d)
+    xs = rng.uniform(-1, 1, size=(4, Hne)).astype(np.float32)
+    assert same_bits(R.pad_forward(xs, child, 0.5), oc.pad(xs, child, 0.5))
+    assert same_bits(R.pad_backward(x, child, Hne), oc.depad(x, child, Hne))
