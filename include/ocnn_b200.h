@@ -1,0 +1,245 @@
+/* ocnn_b200 — C ABI of the B200 (sm_100a) implementation of O-CNN's octree hot path.
+ *
+ * This is the drop-in boundary: a framework binding (the reference's pytorch/cpp extension, its
+ * TensorFlow op library, ...) links libocnn_b200.so and calls these entry points where it used to
+ * call the `*_gpu` functions of the reference's octree library.  Each declaration cites the
+ * reference interface it replaces (paths relative to the microsoft/O-CNN checkout).
+ *
+ * Conventions
+ *  - Plain pointers and sizes only.  Pointers named *_dev are device pointers, *_host host pointers.
+ *  - `stream` is a cudaStream_t passed as void*; every kernel is enqueued on it and, unless a
+ *    function says otherwise, nothing synchronises.  The library never allocates device memory:
+ *    scratch is passed in by the caller (sizes from the *_workspace_bytes functions).
+ *  - Every function returns an ocnn_status; ocnn_last_error() gives the message of the last
+ *    failure on the calling thread.  Nothing aborts the process (the reference's CHECK macros do,
+ *    octree/octree/logs.h:46-49).
+ *  - There is no CPU implementation behind these entry points: without a CUDA device they fail
+ *    with OCNN_ERR_CUDA.
+ */
+#ifndef OCNN_B200_H_
+#define OCNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ocnn_status {
+  OCNN_OK = 0,
+  OCNN_ERR_INVALID = 1,      /* bad argument / malformed header / size mismatch            */
+  OCNN_ERR_UNSUPPORTED = 2,  /* valid request the library does not implement                */
+  OCNN_ERR_CUDA = 3,         /* a CUDA runtime call failed                                  */
+  OCNN_ERR_CAPACITY = 4,     /* caller-provided buffer or workspace too small               */
+  OCNN_ERR_DEVICE = 5        /* a kernel reported an internal error through its status word */
+} ocnn_status;
+
+typedef enum ocnn_dtype { OCNN_F32 = 0, OCNN_BF16 = 1 } ocnn_dtype;
+
+/* Memory layout of a data tensor of C channels over H octree nodes.
+ * OCNN_CHANNEL_MAJOR is the reference's [1,C,H,1] contiguous tensor (data[c*H + h],
+ * octree/octree/octree_nn.cu:125).  OCNN_NODE_MAJOR is data[h*C + c] — the same logical tensor
+ * in torch's channels_last memory format. */
+typedef enum ocnn_layout { OCNN_CHANNEL_MAJOR = 0, OCNN_NODE_MAJOR = 1 } ocnn_layout;
+
+const char* ocnn_last_error(void);
+/* Library version and the compute capability it was compiled for (100 = sm_100a). */
+int ocnn_version(void);
+int ocnn_compiled_arch(void);
+/* Number of CUDA kernels this library has launched so far in this process (all threads). */
+long long ocnn_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Octree wire format (host side).  Replaces OctreeInfo / OctreeParser,
+ * octree/octree/octree_info.h:12-116, octree_info.cpp:157-167,254-268, octree_parser.h:13-83.
+ * The reference copies the 716-byte header device->host inside every operator call
+ * (octree_parser.cu:4-15); here the binding parses it once and passes pointers.
+ * ------------------------------------------------------------------------------------------ */
+#define OCNN_HEADER_BYTES 720   /* sizeof(OctreeInfo)=716 rounded up to the first block offset */
+#define OCNN_MAX_DEPTH 16
+
+enum { OCNN_PROP_KEY = 0, OCNN_PROP_CHILD = 1, OCNN_PROP_NEIGH = 2, OCNN_PROP_FEATURE = 3,
+       OCNN_PROP_LABEL = 4, OCNN_PROP_SPLIT = 5, OCNN_PROP_COUNT = 6 };
+
+typedef struct ocnn_octree_meta {
+  int32_t key_bits;            /* 32 ("_OCTREE_1.0_") or 64 ("_OCTREE_2.0_")                  */
+  int32_t batch_size, depth, full_depth;
+  int32_t is_adaptive, key2xyz, has_node_dis, save_pts;
+  int32_t nnum[OCNN_MAX_DEPTH];          /* nodes per level over the whole batch              */
+  int32_t nnum_cum[OCNN_MAX_DEPTH + 2];  /* prefix sums; [depth+1] = total, [depth+2] = cap.   */
+  int32_t nnum_nempty[OCNN_MAX_DEPTH];   /* non-empty nodes per level                         */
+  int32_t channels[OCNN_PROP_COUNT];     /* 0 = property absent                               */
+  int32_t locations[OCNN_PROP_COUNT];    /* -1 = every level, d = only level d                */
+  int64_t ptr_dis[OCNN_PROP_COUNT + 1];  /* byte offset of each property block; [6] = size    */
+} ocnn_octree_meta;
+
+/* Parse and validate the first OCNN_HEADER_BYTES of an octree buffer held in host memory
+ * (OctreeInfo::check_format, octree_info.cpp:80-116). */
+int ocnn_parse_header(const void* header_host, size_t nbytes, ocnn_octree_meta* meta);
+/* Byte offset of property `prop` at level `depth`, or -1 when absent
+ * (OctreeInfo::ptr_dis, octree_info.cpp:157-167). */
+int64_t ocnn_prop_offset(const ocnn_octree_meta* meta, int prop, int depth);
+
+/* ------------------------------------------------------------------------------------------
+ * octree_pad / octree_depad.  Replace pad_forward_gpu / pad_backward_gpu,
+ * octree/octree/octree_nn.cu:65-106 (bindings: pytorch/cpp/octree_pad.cpp:6-60).
+ *   pad  : y[.,h] = child[h] < 0 ? val : x[., child[h]]      x: [C,Hx] -> y: [C,Hy]
+ *   depad: x[., child[h]] = y[.,h] for child[h] >= 0         y: [C,Hy] -> x: [C,Hx]
+ * child_dev = the child array of the level (Hy ints).  depad writes every row of x when child is
+ * an octree child array (its non-negative entries enumerate 0..Hx-1).
+ * ------------------------------------------------------------------------------------------ */
+int ocnn_octree_pad(const void* x_dev, void* y_dev, const int32_t* child_dev, int channels,
+                    int hx, int hy, float val, int dtype, int layout, void* stream);
+int ocnn_octree_depad(const void* y_dev, void* x_dev, const int32_t* child_dev, int channels,
+                      int hx, int hy, int dtype, int layout, void* stream);
+
+/* octree_max_pool.  Replaces octree_max_pool_gpu, octree/octree/octree_nn.cu:258-290
+ * (binding: pytorch/cpp/octree_pool.cpp:6-34).  Per channel and sibling group: the maximum
+ * (first one wins, NaN never wins) and the absolute bottom row of it.  btm: [C, 8*top_h],
+ * top and mask: [C, top_h] in the same layout as the data. */
+int ocnn_octree_max_pool(const void* btm_dev, void* top_dev, int32_t* mask_dev, int channels,
+                         int top_h, int dtype, int layout, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Neighbour table.  Replace calc_neigh_gpu (both overloads), octree/octree/octree_nn.cu:331-413,
+ * and the CPU loop of merge_octrees that the PyTorch path actually runs
+ * (octree/octree/merge_octrees.cpp:184-197 -> octree_nn.cpp:357-424).
+ * ------------------------------------------------------------------------------------------ */
+/* Full level `depth` of `batch` octrees: batch * 8^depth * 8 ints. */
+int ocnn_calc_neigh_full(int32_t* neigh_dev, int depth, int batch, void* stream);
+/* Level d from level d-1: neigh_dev / child_dev describe the nnum_parent nodes of level d-1;
+ * neigh_child_dev receives one 64-int block per non-empty parent. */
+int ocnn_calc_neigh_split(int32_t* neigh_child_dev, const int32_t* neigh_dev,
+                          const int32_t* child_dev, int nnum_parent, void* stream);
+/* All levels 1..depth of a merged octree buffer in device memory (its Child blocks must be
+ * filled in); `meta` is the parsed header of that buffer. */
+int ocnn_calc_neigh(void* octree_dev, const ocnn_octree_meta* meta, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * octree2col (compatibility/test operator; the convolution below never materialises it).
+ * Replaces octree2col_gpu, octree/octree/octree_nn.cu:110-159 (binding:
+ * pytorch/cpp/octree2col.cpp:47-83).  data: [C, octree_h] fp32 channel-major;
+ * col: [C, K, h_out]; stride 1: h_out = octree_h; stride 2: h_out = octree_h / 8.
+ * ------------------------------------------------------------------------------------------ */
+int ocnn_octree2col(const float* data_dev, float* col_dev, const int32_t* neigh_dev,
+                    int channels, int h_out, const int kernel_size[3], int stride, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Octree convolution, forward.  Replaces OctreeBaseConv::forward_gpu_gemm
+ * (octree/octree/octree_conv.cpp:276-298: octree2col_gpu + cublasSgemm through
+ * pytorch/cpp/octree_conv.cpp:30-45) with one implicit-GEMM kernel: no im2col workspace.
+ *
+ *   y[co, h] = sum_{ci, t} w[co, ci*K + t] * x[ci, nbr(h, t)]        (taps with no neighbour = 0)
+ *   stride 1: h over the h_out = nnum[d] nodes, nbr(h,t) = neigh[(h>>3)*64 + ni[(h&7)*K + t]]
+ *   stride 2: h over the h_out = nnum[d]/8 sibling groups, nbr(h,t) = neigh[h*64 + ni[t]]
+ *   kernel 1x1x1 stride 1: nbr(h) = h and neigh_dev may be NULL.
+ *
+ * x: h_in rows (nnum[d]); weights: fp32 [Cout, Cin*K] exactly as the reference module holds them
+ * (pytorch/ocnn/octree_conv.py:90).  dtype/layout describe x and y.  OCNN_F32 computes in fp32 FMA
+ * (parity path, rel 1e-5); OCNN_BF16 data uses the tensor-core path where the shape allows
+ * (node-major, Cin % 8 == 0, packed weights) and an fp32-accumulating SIMT kernel otherwise.
+ *
+ * Optional fused epilogue (all NULL/0 for the plain reference operator):
+ *   y = act( scale[co] * acc + bias[co] + residual[co,h] ),  act = ReLU when relu != 0.
+ * This is how an inference BatchNorm / ReLU / skip connection that follows the convolution in the
+ * reference's modules (pytorch/ocnn/modules.py:23-36,110-139) is applied without another pass.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ocnn_conv_epilogue {
+  const float* scale_dev;     /* [Cout] or NULL (= 1)  */
+  const float* bias_dev;      /* [Cout] or NULL (= 0)  */
+  const void* residual_dev;   /* same dtype/layout/shape as y, or NULL */
+  int32_t relu;
+} ocnn_conv_epilogue;
+
+int ocnn_octree_conv(const void* x_dev, const float* weights_dev, void* y_dev,
+                     const int32_t* neigh_dev, int h_in, int h_out, int cin, int cout,
+                     const int kernel_size[3], int stride, int dtype, int layout,
+                     const ocnn_conv_epilogue* epilogue, void* stream);
+
+/* Tensor-core path: weights packed once per layer into bf16 K-major tiles. */
+size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3]);
+int ocnn_conv_pack_weights(const float* weights_dev, void* packed_dev, int cin, int cout,
+                           const int kernel_size[3], void* stream);
+/* x, y: bf16 node-major ([h, C]); cin % 8 == 0, cout % 8 == 0, cout <= 256.
+ * status_dev: one int32 in device memory, zero before the call; a kernel that gives up on a
+ * bounded wait writes a non-zero code there instead of hanging. */
+int ocnn_octree_conv_tc(const void* x_dev, const void* packed_weights_dev, void* y_dev,
+                        const int32_t* neigh_dev, int h_in, int h_out, int cin, int cout,
+                        const int kernel_size[3], int stride,
+                        const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * points -> octree, batched, on the device.  Replaces Octree::build
+ * (octree/octree/octree.cpp:74-121, binding pytorch/cpp/point2octree.cpp:5-34) and, when
+ * `merged` is set, the merge_octrees call that follows it in the reference pipeline
+ * (octree/octree/merge_octrees.cpp:7-15, binding pytorch/cpp/octree_batch.cpp:5-22): the output
+ * is bit-identical to building each cloud with the reference and merging the results.
+ *
+ * Two calls, because the output size depends on the data:
+ *   1. ocnn_octree_build_plan: sorts and counts on `stream`, then SYNCHRONISES that stream once
+ *      and fills `meta` (node counts, block offsets, total size in meta->ptr_dis[6]).
+ *   2. ocnn_octree_build_emit: writes the header and every block into out_dev
+ *      (>= meta->ptr_dis[6] bytes), including the neighbour table when merged; the header
+ *      bytes are also returned in header_host_out so the caller need not read them back.
+ * The workspace must stay untouched between the two calls.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ocnn_build_params {
+  int32_t depth, full_depth;
+  int32_t key_bits;        /* 32 (depth <= 8, batch <= 255) or 64                               */
+  int32_t merged;          /* 0: single octree (batch must be 1, no Neigh); 1: merged batch     */
+  int32_t node_dis, split_label, save_pts;   /* as Points2Octree, pytorch/ocnn/transforms.py:10-25 */
+  int32_t adp_depth;       /* recorded in the header only                                       */
+  float th_normal, th_distance;              /* recorded in the header only                     */
+  float bbmin[3], bbmax[3];                  /* points2octree always uses [-1,1]^3               */
+} ocnn_build_params;
+
+typedef struct ocnn_points_batch {
+  int32_t batch;                   /* number of clouds                                          */
+  const int32_t* offsets_host;     /* [batch+1] running point counts: cloud b has             */
+                                   /* offsets[b+1]-offsets[b] points                            */
+  /* Host arrays of `batch` device pointers, one per cloud, point-major float32 as in the      */
+  /* reference's Points buffer (octree/octree/points_info.h:8-40); every cloud of a batch has   */
+  /* the same set of properties.                                                               */
+  const float* const* xyz_dev;     /* each [n_b,3]                                              */
+  const float* const* normal_dev;  /* each [n_b,3], or NULL for the whole batch                 */
+  const float* const* feature_dev; /* each [n_b,feature_channels], or NULL                      */
+  int32_t feature_channels;
+  const float* const* label_dev;   /* each [n_b], or NULL                                       */
+} ocnn_points_batch;
+
+size_t ocnn_octree_build_workspace_bytes(int64_t total_points, int batch, int depth,
+                                         int full_depth);
+int ocnn_octree_build_plan(const ocnn_points_batch* points, const ocnn_build_params* params,
+                           void* workspace_dev, size_t workspace_bytes, ocnn_octree_meta* meta,
+                           void* stream);
+int ocnn_octree_build_emit(const ocnn_points_batch* points, const ocnn_build_params* params,
+                           const ocnn_octree_meta* meta, void* workspace_dev,
+                           size_t workspace_bytes, void* out_dev, size_t out_bytes,
+                           void* header_host_out /* OCNN_HEADER_BYTES or NULL */, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * octree_batch: merge already-built octrees held in device memory.  Replaces merge_octrees
+ * (octree/octree/merge_octrees.cpp:7-198, binding pytorch/cpp/octree_batch.cpp:5-22).
+ * headers_host: `batch` parsed headers; octrees_dev: `batch` device pointers (host array).
+ * ocnn_octree_batch_meta computes the merged header; ocnn_octree_batch fills out_dev
+ * (merged->ptr_dis[6] bytes) including the neighbour table.
+ * ------------------------------------------------------------------------------------------ */
+int ocnn_octree_batch_meta(const ocnn_octree_meta* headers_host, int batch,
+                           ocnn_octree_meta* merged);
+size_t ocnn_octree_batch_workspace_bytes(int batch, int depth);
+int ocnn_octree_batch(const void* const* octrees_dev, const ocnn_octree_meta* headers_host,
+                      const void* first_header_host, int batch, const ocnn_octree_meta* merged,
+                      void* workspace_dev, size_t workspace_bytes, void* out_dev,
+                      void* header_host_out /* OCNN_HEADER_BYTES or NULL */, void* stream);
+
+/* Feature block of the finest level (fp32 [C, nnum] channel-major, as stored in the octree) to the
+ * bf16 node-major tensor [nnum, c_pad] the tensor-core convolution reads (channels >= C are 0).
+ * Replaces the octree_property('feature') copy, pytorch/cpp/octree_property.cpp:89-97. */
+int ocnn_feature_to_node_major(const float* feature_dev, void* out_dev, int channels, int c_pad,
+                               int nnum, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* OCNN_B200_H_ */

@@ -1,0 +1,79 @@
+// Shared helpers of the ocnn_b200 CUDA library: status/error plumbing, launch geometry and the
+// arithmetic forms of the reference's neighbour lookup tables.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/ocnn_b200.h"
+
+namespace ocnn {
+
+// ---- error reporting -------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+// Count of kernels this library has launched in this process (ocnn_launch_count()).
+void note_launches(int n);
+
+#define OCNN_CUDA_OK(expr)                                                              \
+  do {                                                                                  \
+    cudaError_t err__ = (expr);                                                         \
+    if (err__ != cudaSuccess)                                                           \
+      return ::ocnn::fail(OCNN_ERR_CUDA, "%s: %s (%s:%d)", #expr, cudaGetErrorString(err__), \
+                          __FILE__, __LINE__);                                          \
+  } while (0)
+
+#define OCNN_LAUNCH_OK(what) OCNN_LAUNCHES_OK(what, 1)
+
+#define OCNN_LAUNCHES_OK(what, count)                                                   \
+  do {                                                                                  \
+    ::ocnn::note_launches(count);                                                       \
+    cudaError_t err__ = cudaPeekAtLastError();                                          \
+    if (err__ != cudaSuccess)                                                           \
+      return ::ocnn::fail(OCNN_ERR_CUDA, "launch of %s failed: %s", what,               \
+                          cudaGetErrorString(err__));                                   \
+  } while (0)
+
+#define OCNN_REQUIRE(cond, ...)                                  \
+  do {                                                           \
+    if (!(cond)) return ::ocnn::fail(OCNN_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+// ---- launch geometry --------------------------------------------------------------------------
+constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs
+
+inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Grid for a grid-stride kernel: enough blocks to cover `work` items, capped at a whole number of
+// waves over the 148 SMs.
+inline int grid_for(long long work, int threads, int blocks_per_sm = 8) {
+  long long need = (work + threads - 1) / threads;
+  long long cap = (long long)kSMs * blocks_per_sm;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+// ---- neighbour index arithmetic ---------------------------------------------------------------
+// Position, inside the 4x4x4 neighbour block of a sibling group, of the cell at offset
+// (tx-1, ty-1, tz-1) from octant o of that group, tap = tx*9 + ty*3 + tz.  This is the closed
+// form of the reference's ni table for the 3x3x3 kernel
+// (NeighHelper::init_neigh_index, octree/octree/octree_nn.cpp:22-37).
+__host__ __device__ __forceinline__ int ni333(int octant, int tap) {
+  const int ox = octant >> 2, oy = (octant >> 1) & 1, oz = octant & 1;
+  const int tx = tap / 9, ty = (tap / 3) % 3, tz = tap % 3;
+  return ((tx + ox) << 4) | ((ty + oy) << 2) | (tz + oz);
+}
+
+// The taps of the 3x3x3 neighbourhood that each supported kernel shape uses
+// (octree/octree/octree_nn.cpp:7-19).  Returns the tap count or -1.
+struct TapList {
+  int count;
+  signed char tap[27];
+};
+TapList taps_for_kernel(const int kernel_size[3]);
+
+}  // namespace ocnn

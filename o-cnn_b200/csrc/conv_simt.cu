@@ -1,0 +1,195 @@
+// Octree convolution as one implicit-GEMM kernel on the CUDA cores (fp32 FMA accumulation).
+//
+// This is the parity path (fp32 in/out, rel 1e-5 against the reference's octree2col + SGEMM) and
+// the general path for shapes the tensor-core kernel does not take (Cin % 8 != 0, channel-major
+// data).  The neighbour gather is done while staging the A tile in shared memory, so the
+// 27x-inflated column matrix of the reference (octree/octree/octree_conv.cpp:276-298) never
+// exists in HBM.
+//
+// Tile: 64 nodes x 64 output channels per CTA, 256 threads, 4x4 outputs per thread, K walked in
+// slices of 16 over the flattened (channel, tap) index.  Channel-major data walks K as
+// ci*K + t (the reference's weight column order); node-major data walks t*Cin + ci so that one
+// slice reads 16 contiguous channels of a neighbour row.
+#include "common.cuh"
+
+namespace ocnn {
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16, THREADS = 256;
+
+struct ConvArgs {
+  const void* x;
+  const float* w;
+  void* y;
+  const int* neigh;
+  int h_in, h_out, cin, cout, K, stride, identity;
+  const float* scale;
+  const float* bias;
+  const void* residual;
+  int relu;
+  signed char tap[27];
+};
+
+__device__ __forceinline__ float ld(const float* p, long long i) { return p[i]; }
+__device__ __forceinline__ float ld(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st(float* p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void st(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
+
+template <typename T, int LAYOUT>
+__global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  __shared__ int nbr[27][BM];
+
+  const T* __restrict__ x = static_cast<const T*>(a.x);
+  const int tid = threadIdx.x;
+  const int h0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int KD = a.cin * a.K;
+
+  // neighbour rows of this tile's nodes, one entry per (tap, node)
+  for (int e = tid; e < a.K * BM; e += THREADS) {
+    const int t = e / BM, m = e % BM;
+    const int h = h0 + m;
+    int p = -1;
+    if (h < a.h_out) {
+      if (a.identity) {
+        p = h;
+      } else {
+        const int tap = a.tap[t];
+        const long long at = a.stride == 2 ? ((long long)h << 6) + ni333(0, tap)
+                                           : ((long long)(h >> 3) << 6) + ni333(h & 7, tap);
+        p = a.neigh[at];
+      }
+    }
+    nbr[t][m] = p;
+  }
+  __syncthreads();
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  const int tm = tid % 16, tn = tid / 16;
+
+  for (int k0 = 0; k0 < KD; k0 += BK) {
+#pragma unroll
+    for (int r = 0; r < (BK * BM) / THREADS; ++r) {
+      const int e = tid + THREADS * r;
+      int m, kl;
+      if (LAYOUT == OCNN_CHANNEL_MAJOR) { m = e % BM; kl = e / BM; } else { kl = e % BK; m = e / BK; }
+      const int kk = k0 + kl;
+      float v = 0.f;
+      if (kk < KD) {
+        int ci, t;
+        if (LAYOUT == OCNN_CHANNEL_MAJOR) { ci = kk / a.K; t = kk % a.K; } else { t = kk / a.cin; ci = kk % a.cin; }
+        const int p = nbr[t][m];
+        if (p >= 0)
+          v = LAYOUT == OCNN_CHANNEL_MAJOR ? ld(x, (long long)ci * a.h_in + p)
+                                           : ld(x, (long long)p * a.cin + ci);
+      }
+      As[kl][m] = v;
+    }
+#pragma unroll
+    for (int r = 0; r < (BK * BN) / THREADS; ++r) {
+      const int e = tid + THREADS * r;
+      const int kl = e % BK, n = e / BK;
+      const int kk = k0 + kl, co = n0 + n;
+      float v = 0.f;
+      if (kk < KD && co < a.cout) {
+        int col = kk;
+        if (LAYOUT != OCNN_CHANNEL_MAJOR) col = (kk % a.cin) * a.K + kk / a.cin;
+        v = a.w[(long long)co * KD + col];
+      }
+      Bs[kl][n] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kl = 0; kl < BK; ++kl) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kl][tm * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[kl][tn * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+  T* __restrict__ y = static_cast<T*>(a.y);
+  const T* __restrict__ res = static_cast<const T*>(a.residual);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int co = n0 + tn * 4 + j;
+    if (co >= a.cout) continue;
+    const float sc = a.scale ? a.scale[co] : 1.f;
+    const float bi = a.bias ? a.bias[co] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int h = h0 + tm * 4 + i;
+      if (h >= a.h_out) continue;
+      const long long at = LAYOUT == OCNN_CHANNEL_MAJOR ? (long long)co * a.h_out + h
+                                                        : (long long)h * a.cout + co;
+      float v = acc[i][j] * sc + bi;
+      if (res) v += ld(res, at);
+      if (a.relu) v = fmaxf(v, 0.f);
+      st(y, at, v);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace ocnn
+
+extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const int32_t* neigh,
+                                int h_in, int h_out, int cin, int cout, const int kernel_size[3],
+                                int stride, int dtype, int layout, const ocnn_conv_epilogue* ep,
+                                void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv: null kernel size");
+  OCNN_REQUIRE(stride == 1 || stride == 2, "ocnn_octree_conv: stride must be 1 or 2 (got %d)", stride);
+  const TapList tl = taps_for_kernel(kernel_size);
+  if (tl.count < 0)
+    return fail(OCNN_ERR_UNSUPPORTED, "ocnn_octree_conv: unsupported kernel size %dx%dx%d",
+                kernel_size[0], kernel_size[1], kernel_size[2]);
+  OCNN_REQUIRE(cin > 0 && cout > 0, "ocnn_octree_conv: channel counts must be positive");
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "ocnn_octree_conv: unknown dtype %d", dtype);
+  OCNN_REQUIRE(layout == OCNN_CHANNEL_MAJOR || layout == OCNN_NODE_MAJOR,
+               "ocnn_octree_conv: unknown layout %d", layout);
+  OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv: negative height");
+  if (h_out == 0) return OCNN_OK;
+  const bool identity = tl.count == 1 && stride == 1;
+  OCNN_REQUIRE(x && w && y, "ocnn_octree_conv: null data pointer");
+  OCNN_REQUIRE(identity || neigh != nullptr, "ocnn_octree_conv: neighbour table required");
+  if (stride == 2) {
+    OCNN_REQUIRE((long long)h_out * 8 == h_in,
+                 "ocnn_octree_conv: stride 2 needs h_in == 8*h_out (got %d, %d)", h_in, h_out);
+  } else {
+    OCNN_REQUIRE(h_in == h_out, "ocnn_octree_conv: stride 1 needs h_in == h_out (got %d, %d)",
+                 h_in, h_out);
+  }
+  ConvArgs a;
+  a.x = x; a.w = w; a.y = y; a.neigh = neigh;
+  a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout;
+  a.K = tl.count; a.stride = stride; a.identity = identity ? 1 : 0;
+  a.scale = ep ? ep->scale_dev : nullptr;
+  a.bias = ep ? ep->bias_dev : nullptr;
+  a.residual = ep ? ep->residual_dev : nullptr;
+  a.relu = ep ? ep->relu : 0;
+  for (int i = 0; i < 27; ++i) a.tap[i] = i < tl.count ? tl.tap[i] : 0;
+  dim3 grid(ceil_div(h_out, BM), ceil_div(cout, BN));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == OCNN_F32) {
+    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<float, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    else conv_simt_kernel<float, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+  } else {
+    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__nv_bfloat16, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    else conv_simt_kernel<__nv_bfloat16, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+  }
+  OCNN_LAUNCH_OK("conv_simt_kernel");
+  return OCNN_OK;
+}

@@ -1,0 +1,44 @@
+// Small layout-conversion kernels between the octree's stored feature block and the node-major
+// tensors the tensor-core convolution reads.
+#include "common.cuh"
+
+namespace ocnn {
+namespace {
+
+// feature [C, nnum] fp32 channel-major -> out [nnum, c_pad] node-major (zeros in the padding
+// channels).  One thread per output element; reads are coalesced along nodes for each channel.
+template <typename T>
+__global__ void feature_to_nm_kernel(const float* __restrict__ f, T* __restrict__ out, int C,
+                                     int c_pad, long long nnum) {
+  const long long total = nnum * c_pad;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long h = i / c_pad;
+    const int c = (int)(i % c_pad);
+    const float v = c < C ? f[(long long)c * nnum + h] : 0.f;
+    if (sizeof(T) == 2) out[i] = (T)__float2bfloat16(v); else out[i] = (T)v;
+  }
+}
+
+}  // namespace
+}  // namespace ocnn
+
+extern "C" int ocnn_feature_to_node_major(const float* feature, void* out, int channels, int c_pad,
+                                          int nnum, int dtype, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(feature && out, "ocnn_feature_to_node_major: null pointer");
+  OCNN_REQUIRE(channels > 0 && c_pad >= channels && nnum >= 0,
+               "ocnn_feature_to_node_major: bad shape (C=%d, c_pad=%d, nnum=%d)", channels, c_pad, nnum);
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "ocnn_feature_to_node_major: unknown dtype");
+  if (nnum == 0) return OCNN_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long total = (long long)nnum * c_pad;
+  if (dtype == OCNN_BF16)
+    feature_to_nm_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>(
+        feature, static_cast<__nv_bfloat16*>(out), channels, c_pad, nnum);
+  else
+    feature_to_nm_kernel<float><<<grid_for(total, 256), 256, 0, st>>>(
+        feature, static_cast<float*>(out), channels, c_pad, nnum);
+  OCNN_LAUNCH_OK("feature_to_nm_kernel");
+  return OCNN_OK;
+}

@@ -1,0 +1,128 @@
+// Neighbour table: for every sibling group of a level, the 4x4x4 block of node indices around it.
+//
+// Algorithmic traffic of a split level d: read child[d-1] (4 B/node) and neigh[d-1] (32 B/node),
+// write neigh[d] (32 B/node): the kernels below are HBM-bound integer kernels; each warp writes
+// 128 contiguous bytes, every lookup inside a parent's block hits one 256-byte line.
+#include "common.cuh"
+
+namespace ocnn {
+namespace {
+
+__device__ __forceinline__ unsigned spread3(unsigned v) {
+  // bit i of v -> bit 3i (v < 2^10 is enough: full levels never exceed depth 10 in practice)
+  unsigned r = 0;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) r |= ((v >> i) & 1u) << (3 * i);
+  return r;
+}
+
+__device__ __forceinline__ unsigned gather3(unsigned key) {
+  unsigned r = 0;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) r |= ((key >> (3 * i)) & 1u) << i;
+  return r;
+}
+
+// Full level: one thread per output int; out[(n*per + g)*8 + j], j = (X<<4)|(Y<<2)|Z.
+// Restates calc_neigh_cpu(neigh, depth, batch), octree/octree/octree_nn.cpp:382-424.
+__global__ void neigh_full_kernel(int* __restrict__ out, int depth, long long per,
+                                  long long total) {
+  const int side = 1 << depth;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i & 63);
+    const long long blk = i >> 6;                  // sibling group over the whole batch
+    const long long n = (blk << 3) / per;          // batch item
+    const unsigned g = (unsigned)((blk << 3) - n * per);   // first node of the group
+    const int x = (int)gather3(g >> 2) + (j >> 4) - 1;
+    const int y = (int)gather3(g >> 1) + ((j >> 2) & 3) - 1;
+    const int z = (int)gather3(g) + (j & 3) - 1;
+    int v = -1;
+    if (x >= 0 && y >= 0 && z >= 0 && x < side && y < side && z < side)
+      v = (int)((spread3(x) << 2) | (spread3(y) << 1) | spread3(z)) + (int)(n * per);
+    out[i] = v;
+  }
+}
+
+// Split level: 64 threads per parent node i (two warps); threads of empty parents exit.
+// Restates calc_neigh_cpu(neigh_split, neigh, children, node_num), octree_nn.cpp:357-380, with
+// the parent/displacement tables (octree_nn.cpp:53-81) in arithmetic form.
+__global__ void neigh_split_kernel(int* __restrict__ out, const int* __restrict__ neigh,
+                                   const int* __restrict__ child, long long total) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total;
+       t += (long long)gridDim.x * blockDim.x) {
+    const int i = (int)(t >> 6), j = (int)(t & 63);
+    const int l0 = child[i];
+    if (l0 < 0) continue;
+    const int x = (j >> 4) + 1, y = ((j >> 2) & 3) + 1, z = (j & 3) + 1;
+    const int tap = (x >> 1) * 9 + (y >> 1) * 3 + (z >> 1);
+    const int oct = ((x & 1) << 2) | ((y & 1) << 1) | (z & 1);
+    const int k = neigh[((long long)(i >> 3) << 6) + ni333(i & 7, tap)];
+    int v = -1;
+    if (k >= 0) {
+      const int l1 = child[k];
+      if (l1 >= 0) v = (l1 << 3) + oct;
+    }
+    out[((long long)l0 << 6) + j] = v;
+  }
+}
+
+}  // namespace
+}  // namespace ocnn
+
+extern "C" {
+
+int ocnn_calc_neigh_full(int32_t* neigh, int depth, int batch, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(neigh != nullptr, "ocnn_calc_neigh_full: null output");
+  OCNN_REQUIRE(depth >= 1 && depth <= 10 && batch >= 1, "ocnn_calc_neigh_full: depth %d / batch %d "
+               "out of range", depth, batch);
+  const long long per = 1LL << (3 * depth);
+  const long long total = per * batch * 8;
+  OCNN_REQUIRE(per * batch < (1LL << 31), "ocnn_calc_neigh_full: level too large for int32 indices");
+  neigh_full_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      neigh, depth, per, total);
+  OCNN_LAUNCH_OK("neigh_full_kernel");
+  return OCNN_OK;
+}
+
+int ocnn_calc_neigh_split(int32_t* neigh_child, const int32_t* neigh, const int32_t* child,
+                          int nnum_parent, void* stream) {
+  using namespace ocnn;
+  if (nnum_parent == 0) return OCNN_OK;
+  OCNN_REQUIRE(neigh_child && neigh && child, "ocnn_calc_neigh_split: null pointer");
+  OCNN_REQUIRE(nnum_parent > 0 && nnum_parent % 8 == 0,
+               "ocnn_calc_neigh_split: parent level must hold whole sibling groups (got %d nodes)",
+               nnum_parent);
+  const long long total = (long long)nnum_parent * 64;
+  neigh_split_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      neigh_child, neigh, child, total);
+  OCNN_LAUNCH_OK("neigh_split_kernel");
+  return OCNN_OK;
+}
+
+int ocnn_calc_neigh(void* octree_dev, const ocnn_octree_meta* m, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(octree_dev != nullptr && m != nullptr, "ocnn_calc_neigh: null argument");
+  OCNN_REQUIRE(m->channels[OCNN_PROP_NEIGH] == 8 && m->locations[OCNN_PROP_NEIGH] == -1,
+               "ocnn_calc_neigh: the octree has no neighbour block (not a merged batch)");
+  OCNN_REQUIRE(m->channels[OCNN_PROP_CHILD] == 1 && m->locations[OCNN_PROP_CHILD] == -1,
+               "ocnn_calc_neigh: the octree has no child block");
+  uint8_t* base = static_cast<uint8_t*>(octree_dev);
+  for (int d = 1; d <= m->depth; ++d) {
+    int32_t* nd = reinterpret_cast<int32_t*>(base + ocnn_prop_offset(m, OCNN_PROP_NEIGH, d));
+    int s;
+    if (d <= m->full_depth) {
+      s = ocnn_calc_neigh_full(nd, d, m->batch_size, stream);
+    } else {
+      s = ocnn_calc_neigh_split(
+          nd, reinterpret_cast<const int32_t*>(base + ocnn_prop_offset(m, OCNN_PROP_NEIGH, d - 1)),
+          reinterpret_cast<const int32_t*>(base + ocnn_prop_offset(m, OCNN_PROP_CHILD, d - 1)),
+          m->nnum[d - 1], stream);
+    }
+    if (s != OCNN_OK) return s;
+  }
+  return OCNN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,27 @@
+"""octree2col as a function and module (pytorch/ocnn/octree2col.py:7-81 of the reference)."""
+import torch
+from torch import nn as _nn
+
+from . import nn
+
+
+def octree2col(data_in, octree, depth, kernel_size, stride, nempty=False):
+  """[1,C,H,1] float32 -> [C, K, H_out]: the neighbourhood of every node, K taps per channel."""
+  with torch.no_grad():
+    return nn.octree2col(data_in, octree, depth, list(kernel_size), stride, nempty)
+
+
+class Octree2Col(_nn.Module):
+  def __init__(self, depth, kernel_size, stride, nempty=False):
+    super().__init__()
+    self.depth = depth
+    self.kernel_size = kernel_size
+    self.stride = stride
+    self.nempty = nempty
+
+  def forward(self, data_in, octree):
+    return octree2col(data_in, octree, self.depth, self.kernel_size, self.stride, self.nempty)
+
+  def extra_repr(self) -> str:
+    return 'depth={}, kernel_size={}, stride={}, nempty={}'.format(
+        self.depth, self.kernel_size, self.stride, self.nempty)

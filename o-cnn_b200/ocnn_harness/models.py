@@ -1,0 +1,255 @@
+"""Inference forward passes of the networks the benchmark configurations name, assembled from the
+octree operators.  Architectures follow the reference's modules (pytorch/ocnn/modules.py:23-139,
+resnet.py:5-31, lenet.py:5-32) with BatchNorm in inference mode folded into a per-channel
+scale/bias.  Weights are seeded random: no trained checkpoint exists for the PyTorch reference.
+
+Two executors share one parameter set:
+  * `GpuNet`  — the CUDA operators of `ocnn` (fp32 channel-major, or bf16 node-major);
+  * `CpuNet`  — a numpy chain over a CPU implementation of the operators (the oracle, or the
+                compiled reference), used as the checker and as the timed CPU baseline.  It lives
+                here so that tests and the benchmark drive both from the same description; it is
+                handed its operator module by the caller and imports nothing from oracle/ itself.
+"""
+import numpy as np
+
+BN_EPS = 0.001   # pytorch/ocnn/modules.py:5
+
+
+def _bn_fold(rng, c):
+  gamma = rng.uniform(0.5, 1.5, size=c)
+  beta = rng.normal(scale=0.1, size=c)
+  mean = rng.normal(scale=0.1, size=c)
+  var = rng.uniform(0.5, 1.5, size=c)
+  scale = gamma / np.sqrt(var + BN_EPS)
+  return scale.astype(np.float32), (beta - mean * scale).astype(np.float32)
+
+
+def _conv_param(rng, cin, cout, kdim, name, bn=True, relu=True):
+  """Xavier-uniform weights [cout, cin*kdim] (pytorch/ocnn/octree_conv.py:90-91) + folded BN."""
+  bound = np.sqrt(6.0 / (cin * kdim + cout))
+  w = rng.uniform(-bound, bound, size=(cout, cin * kdim)).astype(np.float32)
+  scale, bias = _bn_fold(rng, cout) if bn else (None, None)
+  return {'name': name, 'w': w, 'scale': scale, 'bias': bias, 'relu': relu, 'cin': cin,
+          'cout': cout, 'ks': [3, 3, 3] if kdim == 27 else [1, 1, 1]}
+
+
+def resnet_params(depth=6, channel_in=3, nout=40, resblk_num=2, seed=0, min_depth=2):
+  """ResNet O-CNN: conv3x3x3 at `depth`, then per level `resblk_num` bottleneck blocks
+  (1x1 -> 3x3x3 at Cout/4 -> 1x1, skip, ReLU; modules.py:110-139) and a max-pool, channels
+  2^max(11-d, 2) per level d (resnet.py:9) down to `min_depth`, global average pool, FC."""
+  rng = np.random.default_rng(seed)
+  ch = lambda d: 2 ** max(11 - d, 2)
+  net = {'kind': 'resnet', 'depth': depth, 'min_depth': min_depth, 'channel_in': channel_in,
+         'nout': nout}
+  net['conv1'] = _conv_param(rng, channel_in, ch(depth), 27, 'conv1')
+  levels = []
+  cin = ch(depth)
+  for d in range(depth, min_depth - 1, -1):
+    cout = ch(d)
+    blocks = []
+    for b in range(resblk_num):
+      cb = cout // 4
+      blk = {'a': _conv_param(rng, cin, cb, 1, 'd%d.b%d.1x1a' % (d, b)),
+             'conv': _conv_param(rng, cb, cb, 27, 'd%d.b%d.3x3' % (d, b)),
+             'b': _conv_param(rng, cb, cout, 1, 'd%d.b%d.1x1b' % (d, b), relu=False),
+             'c': _conv_param(rng, cin, cout, 1, 'd%d.b%d.1x1c' % (d, b), relu=False)
+             if cin != cout else None}
+      blocks.append(blk)
+      cin = cout
+    levels.append({'depth': d, 'blocks': blocks, 'pool': d > min_depth})
+  net['levels'] = levels
+  bound = 1.0 / np.sqrt(cin)
+  net['fc_w'] = rng.uniform(-bound, bound, size=(nout, cin)).astype(np.float32)
+  net['fc_b'] = rng.uniform(-bound, bound, size=nout).astype(np.float32)
+  return net
+
+
+def lenet_params(depth=5, channel_in=3, nout=40, seed=0, channels=(32, 64, 128, 256)):
+  """LeNet-style classifier: per level conv3x3x3 + BN + ReLU + max-pool from `depth` down to
+  level 2, then FC on the flattened 8x8x8... full-level voxels' global average (lenet.py:24-32,
+  with the channel plan of the benchmark configuration)."""
+  rng = np.random.default_rng(seed)
+  net = {'kind': 'lenet', 'depth': depth, 'channel_in': channel_in, 'nout': nout}
+  convs = []
+  cin = channel_in
+  for i, d in enumerate(range(depth, depth - len(channels), -1)):
+    convs.append({'depth': d, 'conv': _conv_param(rng, cin, channels[i], 27, 'd%d.conv' % d)})
+    cin = channels[i]
+  net['convs'] = convs
+  net['out_depth'] = depth - len(channels)
+  bound = 1.0 / np.sqrt(cin)
+  net['fc_w'] = rng.uniform(-bound, bound, size=(nout, cin)).astype(np.float32)
+  net['fc_b'] = rng.uniform(-bound, bound, size=nout).astype(np.float32)
+  return net
+
+
+def conv_layers(net):
+  """Every convolution of the network with the level it runs at: (depth, param dict)."""
+  if net['kind'] == 'lenet':
+    return [(c['depth'], c['conv']) for c in net['convs']]
+  out = [(net['depth'], net['conv1'])]
+  for lv in net['levels']:
+    for blk in lv['blocks']:
+      for k in ('a', 'conv', 'b', 'c'):
+        if blk[k] is not None:
+          out.append((lv['depth'], blk[k]))
+  return out
+
+
+# ---- CPU executor ---------------------------------------------------------------------------------
+class CpuNet:
+  """fp32 forward over a CPU operator module exposing octree_conv / max_pool / pad and an
+  OctreeView-like reader (`view`).  `ops` is oracle.oracle or an adapter around the compiled
+  reference; the caller chooses."""
+
+  def __init__(self, net, ops, view):
+    self.net, self.ops, self.view = net, ops, view
+
+  def _conv(self, x, p, octree, d):
+    if p['ks'] == [1, 1, 1]:
+      y = p['w'] @ x                      # torch Conv1d(kernel 1) in the reference, modules.py:71-83
+    else:
+      y = self.ops.octree_conv(x, p['w'], octree, d, p['cout'], p['ks'], 1)
+    if p['scale'] is not None:
+      y = y * p['scale'][:, None] + p['bias'][:, None]
+    return y
+
+  def _pool(self, x, v, d):
+    top, _ = self.ops.max_pool(x)
+    return self.ops.pad(top, v.prop('child', d - 1), 0.0)
+
+  def forward(self, octree):
+    net = self.net
+    v = self.view(octree)
+    x = np.ascontiguousarray(v.prop('feature', net['depth']))
+    if net['kind'] == 'lenet':
+      for c in net['convs']:
+        x = np.maximum(self._conv(x, c['conv'], octree, c['depth']), 0)
+        x = self._pool(x, v, c['depth'])
+      d_out = net['out_depth']
+    else:
+      x = np.maximum(self._conv(x, net['conv1'], octree, net['depth']), 0)
+      for lv in net['levels']:
+        d = lv['depth']
+        for blk in lv['blocks']:
+          y = np.maximum(self._conv(x, blk['a'], octree, d), 0)
+          y = np.maximum(self._conv(y, blk['conv'], octree, d), 0)
+          y = self._conv(y, blk['b'], octree, d)
+          skip = x if blk['c'] is None else self._conv(x, blk['c'], octree, d)
+          x = np.maximum(y + skip, 0)
+        if lv['pool']:
+          x = self._pool(x, v, d)
+      d_out = net['min_depth'] if not net['levels'][-1]['pool'] else net['min_depth'] - 1
+    per = 8 ** d_out
+    pooled = x.reshape(x.shape[0], -1, per).mean(axis=2)        # FullOctreeGlobalPool
+    return pooled.T @ net['fc_w'].T + net['fc_b']
+
+
+# ---- GPU executor ---------------------------------------------------------------------------------
+class GpuNet:
+  """Forward on the CUDA operators.  mode = 'fp32' (reference layout, parity path) or 'bf16'
+  (node-major activations; 3x3x3 and 1x1 convolutions on the tensor-core kernel when
+  `tensor_core` is set and the shape allows, fp32-accumulating CUDA-core kernel otherwise)."""
+
+  def __init__(self, net, mode='bf16', tensor_core=True, device='cuda'):
+    import torch
+    import ocnn
+    self.torch, self.ocnn = torch, ocnn
+    self.net, self.mode = net, mode
+    self.bf16 = mode == 'bf16'
+    self.device = device
+    self.status = torch.zeros(1, dtype=torch.int32, device=device)
+    self.tc = bool(tensor_core) and self.bf16
+    for _, p in conv_layers(net):
+      self._upload(p)
+    self.fc_w = torch.from_numpy(net['fc_w']).to(device)
+    self.fc_b = torch.from_numpy(net['fc_b']).to(device)
+    self.launches = 0
+    # per-layer CUDA-event tracing (benchmark only): trace = {layer name: [(start, end), ...]};
+    # trace_only restricts it to one layer
+    self.trace = None
+    self.trace_only = None
+
+  def _traced(self, name, fn):
+    if self.trace is None or (self.trace_only is not None and self.trace_only != name):
+      return fn()
+    t = self.torch
+    a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+    a.record()
+    out = fn()
+    b.record()
+    self.trace.setdefault(name, []).append((a, b))
+    return out
+
+  def _upload(self, p):
+    t = self.torch
+    cin = p['cin']
+    w = p['w']
+    if self.bf16 and cin % 8 != 0:
+      # node-major bf16 activations are padded to 8 channels (the octree's 3 normal channels):
+      # widen the weight matrix with zero columns to match
+      kd = w.shape[1] // cin
+      cpad = (cin + 7) // 8 * 8
+      wp = np.zeros((w.shape[0], cpad, kd), np.float32)
+      wp[:, :cin, :] = w.reshape(w.shape[0], cin, kd)
+      w, cin = wp.reshape(w.shape[0], cpad * kd), cpad
+    p['_cin'] = cin
+    p['_w'] = t.from_numpy(np.ascontiguousarray(w)).to(self.device)
+    p['_scale'] = None if p['scale'] is None else t.from_numpy(p['scale']).to(self.device)
+    p['_bias'] = None if p['bias'] is None else t.from_numpy(p['bias']).to(self.device)
+    p['_packed'] = None
+    if self.tc and cin % 8 == 0 and p['cout'] % 8 == 0 and p['cout'] <= 256:
+      try:
+        p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, p['cout'], p['ks'])
+      except RuntimeError:
+        p['_packed'] = None
+
+  def _conv(self, x, p, octree, d, relu, residual=None):
+    nn = self.ocnn.nn
+    self.launches += 1
+    if p['_packed'] is not None:
+      return self._traced(p['name'], lambda: nn.octree_conv_tc(
+          x, p['_packed'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual,
+          relu, self.status))
+    return self._traced(p['name'], lambda: nn.octree_conv_fused(
+        x, p['_w'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual, relu))
+
+  def _pool(self, x, octree, d):
+    nn = self.ocnn.nn
+    top, _ = nn.octree_max_pool(x, octree, d)
+    self.launches += 2
+    return nn.octree_pad(top, octree, d - 1, 0.0)
+
+  def forward(self, octree):
+    t, net = self.torch, self.net
+    nn = self.ocnn.nn
+    with t.no_grad():
+      if self.bf16:
+        x = nn.feature_node_major(octree, (net['channel_in'] + 7) // 8 * 8, True)
+        self.launches += 1
+      else:
+        x = self.ocnn.octree_property(octree, 'feature', net['depth'])
+      if net['kind'] == 'lenet':
+        for c in net['convs']:
+          x = self._conv(x, c['conv'], octree, c['depth'], True)
+          x = self._pool(x, octree, c['depth'])
+        d_out = net['out_depth']
+      else:
+        x = self._conv(x, net['conv1'], octree, net['depth'], True)
+        for lv in net['levels']:
+          d = lv['depth']
+          for blk in lv['blocks']:
+            y = self._conv(x, blk['a'], octree, d, True)
+            y = self._conv(y, blk['conv'], octree, d, True)
+            skip = x if blk['c'] is None else self._conv(x, blk['c'], octree, d, False)
+            x = self._conv(y, blk['b'], octree, d, True, residual=skip)
+          if lv['pool']:
+            x = self._pool(x, octree, d)
+        d_out = net['min_depth'] if not net['levels'][-1]['pool'] else net['min_depth'] - 1
+      per = 8 ** d_out
+      C = x.shape[1]
+      if x.is_contiguous():                                     # [C, B*per]
+        pooled = x.view(C, -1, per).float().mean(dim=2).t()
+      else:                                                     # node-major [B*per, C]
+        pooled = x.permute(0, 2, 1, 3).reshape(-1, per, C).float().mean(dim=1)
+      return pooled @ self.fc_w.t() + self.fc_b

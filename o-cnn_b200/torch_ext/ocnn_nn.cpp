@@ -1,0 +1,769 @@
+// `ocnn.nn` — the PyTorch binding of the octree hot path, with the function names, argument
+// order and tensor conventions of the reference's extension (pytorch/cpp/pybind.cpp:3-49,
+// pytorch/cpp/ocnn.h:11-72), implemented on libocnn_b200.so through its C ABI.
+//
+// Differences from the reference binding, all on purpose:
+//  * points2octree / octree_batch run on the GPU and return CUDA tensors (the reference builds on
+//    the CPU and the caller moves the result, pytorch/projects/classification.py:24).  CPU inputs
+//    are uploaded; there is no CPU compute path.
+//  * The 716-byte octree header is copied device->host once per octree tensor and cached, not once
+//    per operator call (octree/octree/octree_parser.cu:4-15).
+//  * Data tensors may be fp32 or bf16, and [1,C,H,1] contiguous (the reference layout) or
+//    channels_last (node-major).  Outputs keep the dtype and layout of the input.
+//  * Errors raise Python exceptions; nothing aborts (pytorch/cpp uses CHECK -> abort()).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
+#include <torch/extension.h>
+
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "ocnn_b200.h"
+
+namespace {
+
+using torch::Tensor;
+using std::string;
+using std::vector;
+
+#define OCNN_CALL(expr)                                                      \
+  do {                                                                       \
+    int status__ = (expr);                                                   \
+    TORCH_CHECK(status__ == OCNN_OK, "ocnn_b200: ", ocnn_last_error());      \
+  } while (0)
+
+int g_key_bits = 64;  // the reference's PyTorch extension is always built with -DKEY64
+
+void* current_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// ---- octree header cache ------------------------------------------------------------------------
+// Keyed by the tensor's StorageImpl; the weak reference keeps that address from being reused for
+// another storage while the entry lives, so a hit is always the same buffer.
+struct CachedHeader {
+  c10::weak_intrusive_ptr<c10::StorageImpl> storage;
+  int64_t offset;
+  uint32_t version;
+  ocnn_octree_meta meta;
+  uint8_t raw[OCNN_HEADER_BYTES];
+};
+std::mutex g_cache_mutex;
+std::unordered_map<const void*, CachedHeader> g_cache;
+
+struct OctreeRef {
+  ocnn_octree_meta meta;
+  uint8_t raw[OCNN_HEADER_BYTES];
+  uint8_t* base;   // device (or host) pointer of byte 0
+  bool cuda;
+};
+
+OctreeRef get_octree(const Tensor& octree) {
+  TORCH_CHECK(octree.scalar_type() == torch::kUInt8 && octree.dim() == 1 && octree.is_contiguous(),
+              "the octree must be a contiguous 1-D uint8 tensor");
+  TORCH_CHECK(octree.numel() >= 716, "the octree tensor is shorter than an octree header");
+  OctreeRef ref;
+  ref.base = octree.data_ptr<uint8_t>();
+  ref.cuda = octree.is_cuda();
+  if (!ref.cuda) {
+    memset(ref.raw, 0, sizeof(ref.raw));
+    memcpy(ref.raw, ref.base, 716);
+    OCNN_CALL(ocnn_parse_header(ref.raw, (size_t)octree.numel(), &ref.meta));
+    return ref;
+  }
+  c10::StorageImpl* impl = octree.storage().unsafeGetStorageImpl();
+  const uint32_t version = octree._version();
+  {
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    auto it = g_cache.find(impl);
+    if (it != g_cache.end()) {
+      CachedHeader& c = it->second;
+      if (!c.storage.expired() && c.offset == octree.storage_offset() && c.version == version) {
+        ref.meta = c.meta;
+        memcpy(ref.raw, c.raw, sizeof(ref.raw));
+        return ref;
+      }
+      g_cache.erase(it);
+    }
+  }
+  memset(ref.raw, 0, sizeof(ref.raw));
+  cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+  TORCH_CHECK(cudaMemcpyAsync(ref.raw, ref.base, 716, cudaMemcpyDeviceToHost, st) == cudaSuccess &&
+                  cudaStreamSynchronize(st) == cudaSuccess,
+              "reading the octree header from the device failed");
+  OCNN_CALL(ocnn_parse_header(ref.raw, (size_t)octree.numel(), &ref.meta));
+  TORCH_CHECK(ref.meta.ptr_dis[OCNN_PROP_COUNT] <= octree.numel(),
+              "the octree tensor is shorter than its header says");
+  std::lock_guard<std::mutex> lock(g_cache_mutex);
+  if (g_cache.size() > 256) {
+    for (auto it = g_cache.begin(); it != g_cache.end();)
+      it = it->second.storage.expired() ? g_cache.erase(it) : std::next(it);
+  }
+  CachedHeader c{c10::weak_intrusive_ptr<c10::StorageImpl>(
+                     c10::intrusive_ptr<c10::StorageImpl>::reclaim_copy(impl)),
+                 octree.storage_offset(), version, ref.meta, {}};
+  memcpy(c.raw, ref.raw, sizeof(c.raw));
+  g_cache.emplace(impl, std::move(c));
+  return ref;
+}
+
+void remember_header(const Tensor& octree, const ocnn_octree_meta& meta, const uint8_t* raw) {
+  c10::StorageImpl* impl = octree.storage().unsafeGetStorageImpl();
+  CachedHeader c{c10::weak_intrusive_ptr<c10::StorageImpl>(
+                     c10::intrusive_ptr<c10::StorageImpl>::reclaim_copy(impl)),
+                 octree.storage_offset(), (uint32_t)octree._version(), meta, {}};
+  memcpy(c.raw, raw, sizeof(c.raw));
+  std::lock_guard<std::mutex> lock(g_cache_mutex);
+  g_cache.erase(impl);
+  g_cache.emplace(impl, std::move(c));
+}
+
+// ---- data tensor conventions ----------------------------------------------------------------------
+struct DataRef {
+  Tensor t;      // a tensor whose memory is exactly [C,H] (channel-major) or [H,C] (node-major)
+  int C, H, dtype, layout;
+};
+
+DataRef get_data(const Tensor& data, const char* what) {
+  TORCH_CHECK(data.is_cuda(), what, ": the data tensor must be a CUDA tensor (there is no CPU path)");
+  TORCH_CHECK(data.dim() == 4 && data.size(0) == 1 && data.size(3) == 1, what,
+              ": data must have shape [1, C, H, 1]");
+  DataRef d;
+  d.C = (int)data.size(1);
+  d.H = (int)data.size(2);
+  if (data.scalar_type() == torch::kFloat32) d.dtype = OCNN_F32;
+  else if (data.scalar_type() == torch::kBFloat16) d.dtype = OCNN_BF16;
+  else TORCH_CHECK(false, what, ": data must be float32 or bfloat16");
+  if (data.is_contiguous()) {
+    d.layout = OCNN_CHANNEL_MAJOR;
+    d.t = data;
+  } else if (data.is_contiguous(at::MemoryFormat::ChannelsLast)) {
+    d.layout = OCNN_NODE_MAJOR;
+    d.t = data;
+  } else {
+    d.layout = OCNN_CHANNEL_MAJOR;
+    d.t = data.contiguous();
+  }
+  return d;
+}
+
+Tensor new_data(int C, int H, const DataRef& like, bool zero = false) {
+  auto opts = like.t.options();
+  if (like.layout == OCNN_NODE_MAJOR) opts = opts.memory_format(at::MemoryFormat::ChannelsLast);
+  return zero ? torch::zeros({1, C, H, 1}, opts) : torch::empty({1, C, H, 1}, opts);
+}
+
+vector<int> kernel3(vector<int> ks) {
+  TORCH_CHECK(!ks.empty() && ks.size() <= 3, "kernel_size must hold 1 to 3 values");
+  while (ks.size() < 3) ks.push_back(ks.back());   // resize_with_last_val, octree_nn.cpp:128-140
+  for (int k : ks) TORCH_CHECK(k > 0 && k < 4, "Invalide kernel size");
+  return ks;
+}
+
+const int32_t* level_ptr(const OctreeRef& o, int prop, int depth, const char* what) {
+  const int64_t off = ocnn_prop_offset(&o.meta, prop, depth);
+  TORCH_CHECK(off >= 0, what, ": the octree lacks the needed property at depth ", depth);
+  return reinterpret_cast<const int32_t*>(o.base + off);
+}
+
+// ---- pad / depad / pool -------------------------------------------------------------------------
+Tensor octree_pad(Tensor data_in, Tensor octree, int depth, float val) {
+  TORCH_CHECK(depth >= 1, "Depth should be larger than 1");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_pad: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth <= o.meta.depth, "octree_pad: depth ", depth, " exceeds the octree depth");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "octree_pad");
+  TORCH_CHECK(o.meta.nnum_nempty[depth] == x.H, "octree_pad: data height ", x.H,
+              " != non-empty node number ", o.meta.nnum_nempty[depth], ", d = ", depth,
+              ", channel = ", x.C);
+  const int top_h = o.meta.nnum[depth];
+  Tensor y = new_data(x.C, top_h, x);
+  OCNN_CALL(ocnn_octree_pad(x.t.data_ptr(), y.data_ptr(),
+                            level_ptr(o, OCNN_PROP_CHILD, depth, "octree_pad"), x.C, x.H, top_h, val,
+                            x.dtype, x.layout, current_stream()));
+  return y;
+}
+
+Tensor octree_depad(Tensor data_in, Tensor octree, int depth) {
+  TORCH_CHECK(depth >= 1, "Depth should be larger than 1");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_depad: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth <= o.meta.depth, "octree_depad: depth ", depth, " exceeds the octree depth");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef y = get_data(data_in, "octree_depad");
+  TORCH_CHECK(o.meta.nnum[depth] == y.H, "octree_depad: data height ", y.H, " != node number ",
+              o.meta.nnum[depth], ", d = ", depth, ", channel = ", y.C);
+  const int btm_h = o.meta.nnum_nempty[depth];
+  Tensor x = new_data(y.C, btm_h, y, /*zero=*/true);
+  OCNN_CALL(ocnn_octree_depad(y.t.data_ptr(), x.data_ptr(),
+                              level_ptr(o, OCNN_PROP_CHILD, depth, "octree_depad"), y.C, btm_h, y.H,
+                              y.dtype, y.layout, current_stream()));
+  return x;
+}
+
+vector<Tensor> octree_max_pool(Tensor data_in, Tensor octree, int depth) {
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(depth > 1, "Depth should be larger than 1");
+  TORCH_CHECK(depth <= o.meta.depth, "octree_max_pool: depth ", depth, " exceeds the octree depth");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef b = get_data(data_in, "octree_max_pool");
+  TORCH_CHECK(o.meta.nnum[depth] == b.H, "octree_max_pool: data height ", b.H, " != node number ",
+              o.meta.nnum[depth]);
+  const int top_h = b.H >> 3;
+  Tensor top = new_data(b.C, top_h, b);
+  auto mopts = b.t.options().dtype(torch::kInt32);
+  if (b.layout == OCNN_NODE_MAJOR) mopts = mopts.memory_format(at::MemoryFormat::ChannelsLast);
+  Tensor mask = torch::empty({1, b.C, top_h, 1}, mopts);
+  OCNN_CALL(ocnn_octree_max_pool(b.t.data_ptr(), top.data_ptr(), mask.data_ptr<int32_t>(), b.C,
+                                 top_h, b.dtype, b.layout, current_stream()));
+  return {top, mask};
+}
+
+// ---- octree2col ----------------------------------------------------------------------------------
+Tensor octree2col(Tensor data_in, Tensor octree, int depth, vector<int> kernel_size, int stride,
+                  bool nempty) {
+  TORCH_CHECK(!nempty, "octree2col on non-empty nodes only (nempty=True) is not implemented");
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(stride == 1 || stride == 2, "Unsupport stride");
+  TORCH_CHECK(depth > 0, "Depth should be larger than 0");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree2col: the octree must be a CUDA tensor");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  TORCH_CHECK(data_in.scalar_type() == torch::kFloat32, "octree2col takes float32 data");
+  DataRef x = get_data(data_in.contiguous(), "octree2col");
+  TORCH_CHECK(o.meta.nnum[depth] == x.H, "octree2col: data height ", x.H, " != node number ",
+              o.meta.nnum[depth]);
+  int top_h = x.H;
+  if (stride == 2) {
+    top_h = x.H / 8;
+    TORCH_CHECK(top_h == o.meta.nnum_nempty[depth - 1], "octree2col: inconsistent octree");
+  }
+  const int kdim = ks[0] * ks[1] * ks[2];
+  Tensor col = torch::empty({x.C, kdim, top_h}, x.t.options());
+  OCNN_CALL(ocnn_octree2col(x.t.data_ptr<float>(), col.data_ptr<float>(),
+                            level_ptr(o, OCNN_PROP_NEIGH, depth, "octree2col"), x.C, top_h,
+                            ks.data(), stride, current_stream()));
+  return col;
+}
+
+// ---- convolution -----------------------------------------------------------------------------------
+struct ConvShape { int h_in, h_out; const int32_t* neigh; };
+
+ConvShape conv_shape(const OctreeRef& o, const DataRef& x, int depth, const vector<int>& ks,
+                     int stride, const char* what) {
+  TORCH_CHECK(depth > 0 && depth <= o.meta.depth, what, ": The depth should be in (0, octree depth]");
+  TORCH_CHECK(stride == 1 || stride == 2, "Unsupport stride");
+  TORCH_CHECK(x.H == o.meta.nnum[depth], what, ": data height ", x.H, " != node number ",
+              o.meta.nnum[depth], ", d: ", depth, ", channel_in: ", x.C);
+  ConvShape s;
+  s.h_in = x.H;
+  s.h_out = stride == 2 ? x.H / 8 : x.H;
+  if (stride == 2)
+    TORCH_CHECK(s.h_out == o.meta.nnum_nempty[depth - 1], what, ": inconsistent octree");
+  const bool identity = ks[0] * ks[1] * ks[2] == 1 && stride == 1;
+  s.neigh = identity ? nullptr : level_ptr(o, OCNN_PROP_NEIGH, depth, what);
+  return s;
+}
+
+ocnn_conv_epilogue make_epilogue(const c10::optional<Tensor>& scale, const c10::optional<Tensor>& bias,
+                                 const c10::optional<Tensor>& residual, bool relu, int cout,
+                                 const Tensor& y) {
+  ocnn_conv_epilogue ep;
+  ep.scale_dev = nullptr; ep.bias_dev = nullptr; ep.residual_dev = nullptr; ep.relu = relu ? 1 : 0;
+  if (scale.has_value() && scale->defined()) {
+    TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == torch::kFloat32 && scale->is_contiguous() &&
+                    scale->numel() == cout, "scale must be a contiguous float32 CUDA tensor of Cout values");
+    ep.scale_dev = scale->data_ptr<float>();
+  }
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kFloat32 && bias->is_contiguous() &&
+                    bias->numel() == cout, "bias must be a contiguous float32 CUDA tensor of Cout values");
+    ep.bias_dev = bias->data_ptr<float>();
+  }
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_cuda() && residual->sizes() == y.sizes() &&
+                    residual->strides() == y.strides() && residual->scalar_type() == y.scalar_type(),
+                "residual must match the output's shape, dtype and memory layout");
+    ep.residual_dev = residual->data_ptr();
+  }
+  return ep;
+}
+
+Tensor octree_conv_fused(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
+                         vector<int> kernel_size, int stride, c10::optional<Tensor> scale,
+                         c10::optional<Tensor> bias, c10::optional<Tensor> residual, bool relu) {
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(num_output > 0, "The num_output should be larger than 0");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_conv: the octree must be a CUDA tensor");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "octree_conv");
+  ConvShape s = conv_shape(o, x, depth, ks, stride, "octree_conv");
+  const int kdim = ks[0] * ks[1] * ks[2];
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 &&
+                  weights.numel() == (int64_t)num_output * x.C * kdim,
+              "weights must be a float32 CUDA tensor of shape [Cout, Cin*K]");
+  Tensor w = weights.contiguous();
+  Tensor y = new_data(num_output, s.h_out, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  OCNN_CALL(ocnn_octree_conv(x.t.data_ptr(), w.data_ptr<float>(), y.data_ptr(), s.neigh, s.h_in,
+                             s.h_out, x.C, num_output, ks.data(), stride, x.dtype, x.layout, &ep,
+                             current_stream()));
+  return y;
+}
+
+Tensor octree_conv(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
+                   vector<int> kernel_size, int stride, bool nempty) {
+  TORCH_CHECK(!nempty, "octree_conv on non-empty nodes only (nempty=True) is not implemented");
+  return octree_conv_fused(data_in, weights, octree, depth, num_output, kernel_size, stride,
+                           c10::nullopt, c10::nullopt, c10::nullopt, false);
+}
+
+Tensor conv_pack_weights(Tensor weights, int cin, int cout, vector<int> kernel_size) {
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32,
+              "weights must be a float32 CUDA tensor");
+  const int kdim = ks[0] * ks[1] * ks[2];
+  TORCH_CHECK(weights.numel() == (int64_t)cout * cin * kdim, "weights must have Cout*Cin*K values");
+  c10::cuda::CUDAGuard guard(weights.device());
+  const size_t bytes = ocnn_conv_packed_weight_bytes(cin, cout, ks.data());
+  TORCH_CHECK(bytes > 0, "this shape is not supported by the tensor-core convolution: ",
+              ocnn_last_error());
+  Tensor packed = torch::empty({(int64_t)bytes}, weights.options().dtype(torch::kUInt8));
+  Tensor w = weights.contiguous();
+  OCNN_CALL(ocnn_conv_pack_weights(w.data_ptr<float>(), packed.data_ptr(), cin, cout, ks.data(),
+                                   current_stream()));
+  return packed;
+}
+
+Tensor octree_conv_tc(Tensor data_in, Tensor packed, Tensor octree, int depth, int num_output,
+                      vector<int> kernel_size, int stride, c10::optional<Tensor> scale,
+                      c10::optional<Tensor> bias, c10::optional<Tensor> residual, bool relu,
+                      Tensor status) {
+  vector<int> ks = kernel3(kernel_size);
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_conv_tc: the octree must be a CUDA tensor");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "octree_conv_tc");
+  TORCH_CHECK(x.dtype == OCNN_BF16 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
+              "octree_conv_tc takes bfloat16 channels_last data");
+  x.layout = OCNN_NODE_MAJOR;
+  ConvShape s = conv_shape(o, x, depth, ks, stride, "octree_conv_tc");
+  TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
+                  (size_t)packed.numel() == ocnn_conv_packed_weight_bytes(x.C, num_output, ks.data()),
+              "packed weights do not match this convolution's shape");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32 && status.numel() >= 1,
+              "status must be an int32 CUDA tensor");
+  Tensor y = new_data(num_output, s.h_out, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  OCNN_CALL(ocnn_octree_conv_tc(x.t.data_ptr(), packed.data_ptr(), y.data_ptr(), s.neigh, s.h_in,
+                                s.h_out, x.C, num_output, ks.data(), stride, &ep,
+                                status.data_ptr<int32_t>(), current_stream()));
+  return y;
+}
+
+// ---- points ------------------------------------------------------------------------------------------
+// Points buffer: 88-byte PointsInfo header (magic[16], pt_num, content_flags, channels[8],
+// ptr_dis[8]) then xyz / normal / feature / label float arrays
+// (octree/octree/points_info.h:8-40, points.cpp:96-150).
+struct PointsHeader {
+  char magic[16];
+  int32_t pt_num, content_flags, channels[8], ptr_dis[8];
+};
+static_assert(sizeof(PointsHeader) == 88, "PointsInfo is 88 bytes");
+
+Tensor points_new(Tensor pts, Tensor normals, Tensor features, Tensor labels) {
+  auto flat = [](const Tensor& t) { return t.to(torch::kCPU, torch::kFloat32).contiguous().view({-1}); };
+  Tensor p = flat(pts);
+  const int64_t n = p.numel() / 3;
+  TORCH_CHECK(n > 0 && p.numel() % 3 == 0, "points_new: pts must hold 3*N values, N > 0");
+  Tensor blocks[4] = {p, flat(normals), flat(features), flat(labels)};
+  PointsHeader h;
+  memset(&h, 0, sizeof(h));
+  strcpy(h.magic, "_POINTS_1.0_");
+  h.pt_num = (int32_t)n;
+  h.content_flags = 1;
+  h.channels[0] = 3;
+  if (blocks[1].numel() > 0) {
+    TORCH_CHECK(blocks[1].numel() == 3 * n, "points_new: the channel of normal has to be 3");
+    h.channels[1] = 3; h.content_flags |= 2;
+  }
+  if (blocks[2].numel() > 0) {
+    TORCH_CHECK(blocks[2].numel() % n == 0, "points_new: features must hold C*N values");
+    h.channels[2] = (int32_t)(blocks[2].numel() / n); h.content_flags |= 4;
+  }
+  if (blocks[3].numel() > 0) {
+    TORCH_CHECK(blocks[3].numel() == n, "points_new: the channel of label has to be 1");
+    h.channels[3] = 1; h.content_flags |= 8;
+  }
+  h.ptr_dis[0] = 88;
+  for (int i = 1; i <= 4; ++i) h.ptr_dis[i] = h.ptr_dis[i - 1] + 4 * (int32_t)n * h.channels[i - 1];
+  Tensor out = torch::empty({(int64_t)h.ptr_dis[4]}, torch::dtype(torch::kUInt8));
+  uint8_t* o = out.data_ptr<uint8_t>();
+  memcpy(o, &h, 88);
+  for (int i = 0; i < 4; ++i)
+    if (h.channels[i] > 0) memcpy(o + h.ptr_dis[i], blocks[i].data_ptr<float>(), 4 * n * h.channels[i]);
+  return out;
+}
+
+struct CloudInfo { int64_t byte_offset; PointsHeader h; };
+
+void check_points_header(const PointsHeader& h, int64_t nbytes) {
+  TORCH_CHECK(strncmp(h.magic, "_POINTS_1.0_", 13) == 0, "The version of points format is not _POINTS_1.0_.");
+  TORCH_CHECK(h.pt_num > 0, "The pt_num_ should be larger than 0.");
+  TORCH_CHECK((h.content_flags & 1) && h.channels[0] == 3, "points need xyz coordinates");
+  TORCH_CHECK(h.ptr_dis[4] <= nbytes, "the points tensor is shorter than its header says");
+}
+
+struct BuildFlags {
+  int depth, full_depth;
+  bool node_dis, node_feature, split_label, adaptive;
+  int adp_depth;
+  float th_normal, th_distance;
+  bool extrapolate, save_pts, key2xyz;
+};
+
+// Build the (merged or single) octree of clouds stored back to back in one CUDA uint8 buffer.
+Tensor build_from_device(const Tensor& packed_dev, const vector<CloudInfo>& clouds,
+                         const BuildFlags& f, bool merged) {
+  TORCH_CHECK(!f.adaptive, "points2octree: adaptive octrees are not implemented");
+  TORCH_CHECK(!f.node_feature, "points2octree: node_feature=True is not implemented");
+  TORCH_CHECK(!f.extrapolate, "points2octree: extrapolate=True is not implemented");
+  TORCH_CHECK(!f.key2xyz, "points2octree: key2xyz=True is not implemented");
+  const int B = (int)clouds.size();
+  const PointsHeader& h0 = clouds[0].h;
+  vector<int32_t> offsets(B + 1, 0);
+  vector<const float*> xyz(B), nrm(B), feat(B), lab(B);
+  const uint8_t* base = packed_dev.data_ptr<uint8_t>();
+  for (int b = 0; b < B; ++b) {
+    const PointsHeader& h = clouds[b].h;
+    TORCH_CHECK(h.content_flags == h0.content_flags && h.channels[1] == h0.channels[1] &&
+                    h.channels[2] == h0.channels[2] && h.channels[3] == h0.channels[3],
+                "all point clouds of a batch must carry the same properties");
+    const uint8_t* p = base + clouds[b].byte_offset;
+    TORCH_CHECK(((uintptr_t)p & 3) == 0, "point buffers must be 4-byte aligned");
+    offsets[b + 1] = offsets[b] + h.pt_num;
+    xyz[b] = reinterpret_cast<const float*>(p + h.ptr_dis[0]);
+    nrm[b] = reinterpret_cast<const float*>(p + h.ptr_dis[1]);
+    feat[b] = reinterpret_cast<const float*>(p + h.ptr_dis[2]);
+    lab[b] = reinterpret_cast<const float*>(p + h.ptr_dis[3]);
+  }
+  ocnn_points_batch pb;
+  pb.batch = B;
+  pb.offsets_host = offsets.data();
+  pb.xyz_dev = xyz.data();
+  pb.normal_dev = (h0.content_flags & 2) ? nrm.data() : nullptr;
+  pb.feature_dev = (h0.content_flags & 4) ? feat.data() : nullptr;
+  pb.feature_channels = (h0.content_flags & 4) ? h0.channels[2] : 0;
+  pb.label_dev = (h0.content_flags & 8) ? lab.data() : nullptr;
+  ocnn_build_params prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.depth = f.depth;
+  prm.full_depth = f.full_depth < 1 ? 1 : f.full_depth;   // OctreeInfo::set_full_layer
+  prm.key_bits = g_key_bits;
+  prm.merged = merged ? 1 : 0;
+  prm.node_dis = f.node_dis; prm.split_label = f.split_label; prm.save_pts = f.save_pts;
+  prm.adp_depth = f.adp_depth; prm.th_normal = f.th_normal; prm.th_distance = f.th_distance;
+  for (int j = 0; j < 3; ++j) { prm.bbmin[j] = -1.f; prm.bbmax[j] = 1.f; }
+
+  const size_t ws_bytes = ocnn_octree_build_workspace_bytes(offsets[B], B, prm.depth, prm.full_depth);
+  TORCH_CHECK(ws_bytes > 0, "points2octree: invalid depth / full_depth");
+  auto opts = packed_dev.options();
+  Tensor ws = torch::empty({(int64_t)ws_bytes}, opts);
+  ocnn_octree_meta meta;
+  OCNN_CALL(ocnn_octree_build_plan(&pb, &prm, ws.data_ptr(), ws_bytes, &meta, current_stream()));
+  Tensor out = torch::empty({(int64_t)meta.ptr_dis[OCNN_PROP_COUNT]}, opts);
+  uint8_t raw[OCNN_HEADER_BYTES];
+  OCNN_CALL(ocnn_octree_build_emit(&pb, &prm, &meta, ws.data_ptr(), ws_bytes, out.data_ptr(),
+                                   (size_t)out.numel(), raw, current_stream()));
+  remember_header(out, meta, raw);   // later operators need no device->host copy of the header
+  return out;
+}
+
+BuildFlags make_flags(int depth, int full_depth, bool node_dis, bool node_feature, bool split_label,
+                      bool adaptive, int adp_depth, float th_normal, float th_distance,
+                      bool extrapolate, bool save_pts, bool key2xyz) {
+  return BuildFlags{depth, full_depth, node_dis, node_feature, split_label, adaptive, adp_depth,
+                    th_normal, th_distance, extrapolate, save_pts, key2xyz};
+}
+
+// Pack CPU point buffers back to back (4-byte sizes keep every cloud aligned) and describe them.
+// meta: int64 [B, 2] = (byte offset, byte size).  pin=True returns pinned memory for async H2D.
+vector<Tensor> points_pack(vector<Tensor> points, bool pin) {
+  TORCH_CHECK(!points.empty(), "points_pack: empty list");
+  int64_t total = 0;
+  for (auto& p : points) {
+    TORCH_CHECK(!p.is_cuda() && p.scalar_type() == torch::kUInt8 && p.dim() == 1 && p.is_contiguous(),
+                "points_pack takes CPU uint8 point buffers");
+    total += (p.numel() + 3) / 4 * 4;
+  }
+  Tensor packed = torch::empty({total}, torch::dtype(torch::kUInt8).pinned_memory(pin));
+  Tensor meta = torch::empty({(int64_t)points.size(), 2}, torch::dtype(torch::kInt64));
+  int64_t at = 0;
+  for (size_t b = 0; b < points.size(); ++b) {
+    memcpy(packed.data_ptr<uint8_t>() + at, points[b].data_ptr<uint8_t>(), points[b].numel());
+    meta.data_ptr<int64_t>()[2 * b] = at;
+    meta.data_ptr<int64_t>()[2 * b + 1] = points[b].numel();
+    at += (points[b].numel() + 3) / 4 * 4;
+  }
+  return {packed, meta};
+}
+
+// packed: all clouds back to back (CPU or CUDA); packed_host: the same bytes on the host when
+// `packed` is a CUDA tensor (only the 88-byte headers are read from it), or undefined.
+Tensor points2octree_packed(Tensor packed, Tensor meta, Tensor headers_host, int depth, int full_depth,
+                            bool node_dis, bool node_feature, bool split_label, bool adaptive,
+                            int adp_depth, float th_normal, float th_distance, bool extrapolate,
+                            bool save_pts, bool key2xyz, bool merged) {
+  TORCH_CHECK(packed.scalar_type() == torch::kUInt8 && packed.dim() == 1 && packed.is_contiguous(),
+              "packed points must be a contiguous 1-D uint8 tensor");
+  TORCH_CHECK(!meta.is_cuda() && meta.scalar_type() == torch::kInt64 && meta.dim() == 2 &&
+                  meta.size(1) == 2 && meta.is_contiguous(), "meta must be a CPU int64 [B,2] tensor");
+  const int B = (int)meta.size(0);
+  TORCH_CHECK(!headers_host.is_cuda() && headers_host.scalar_type() == torch::kUInt8 &&
+                  headers_host.is_contiguous() && headers_host.numel() == 88 * (int64_t)B,
+              "headers_host must be a CPU uint8 tensor of 88*B bytes");
+  vector<CloudInfo> clouds(B);
+  for (int b = 0; b < B; ++b) {
+    clouds[b].byte_offset = meta.data_ptr<int64_t>()[2 * b];
+    memcpy(&clouds[b].h, headers_host.data_ptr<uint8_t>() + 88 * b, 88);
+    check_points_header(clouds[b].h, meta.data_ptr<int64_t>()[2 * b + 1]);
+    TORCH_CHECK(clouds[b].byte_offset >= 0 &&
+                    clouds[b].byte_offset + meta.data_ptr<int64_t>()[2 * b + 1] <= packed.numel(),
+                "meta describes bytes outside the packed tensor");
+  }
+  Tensor dev = packed;
+  if (!packed.is_cuda()) dev = packed.to(torch::kCUDA, /*non_blocking=*/true);
+  c10::cuda::CUDAGuard guard(dev.device());
+  return build_from_device(dev, clouds,
+                           make_flags(depth, full_depth, node_dis, node_feature, split_label, adaptive,
+                                      adp_depth, th_normal, th_distance, extrapolate, save_pts, key2xyz),
+                           merged);
+}
+
+Tensor headers_of(const vector<Tensor>& points) {
+  Tensor headers = torch::empty({88 * (int64_t)points.size()}, torch::dtype(torch::kUInt8));
+  for (size_t b = 0; b < points.size(); ++b) {
+    const Tensor& p = points[b];
+    TORCH_CHECK(p.scalar_type() == torch::kUInt8 && p.dim() == 1 && p.numel() >= 88,
+                "a points tensor must be a 1-D uint8 tensor with an 88-byte header");
+    Tensor head = p.slice(0, 0, 88).to(torch::kCPU).contiguous();   // D2H of 88 bytes for CUDA input
+    memcpy(headers.data_ptr<uint8_t>() + 88 * b, head.data_ptr<uint8_t>(), 88);
+  }
+  return headers;
+}
+
+Tensor points2octree_list(vector<Tensor> points, const BuildFlags& f, bool merged) {
+  TORCH_CHECK(!points.empty(), "points2octree: empty input");
+  bool all_cpu = true;
+  for (auto& p : points) all_cpu = all_cpu && !p.is_cuda();
+  Tensor packed, meta;
+  if (all_cpu) {
+    for (auto& p : points) p = p.contiguous();
+    auto pm = points_pack(points, false);
+    packed = pm[0]; meta = pm[1];
+  } else {
+    // device inputs: concatenate on the device (padded to 4 bytes each)
+    meta = torch::empty({(int64_t)points.size(), 2}, torch::dtype(torch::kInt64));
+    vector<Tensor> parts;
+    int64_t at = 0;
+    for (size_t b = 0; b < points.size(); ++b) {
+      Tensor p = points[b].to(torch::kCUDA).contiguous();
+      const int64_t padded = (p.numel() + 3) / 4 * 4;
+      meta.data_ptr<int64_t>()[2 * b] = at;
+      meta.data_ptr<int64_t>()[2 * b + 1] = p.numel();
+      parts.push_back(p);
+      if (padded != p.numel()) parts.push_back(torch::zeros({padded - p.numel()}, p.options()));
+      at += padded;
+    }
+    packed = parts.size() == 1 ? parts[0] : torch::cat(parts);
+  }
+  Tensor headers = headers_of(points);
+  return points2octree_packed(packed, meta, headers, f.depth, f.full_depth, f.node_dis, f.node_feature,
+                              f.split_label, f.adaptive, f.adp_depth, f.th_normal, f.th_distance,
+                              f.extrapolate, f.save_pts, f.key2xyz, merged);
+}
+
+Tensor points2octree(Tensor points, int depth, int full_depth, bool node_dis, bool node_feature,
+                     bool split_label, bool adaptive, int adp_depth, float th_normal,
+                     float th_distance, bool extrapolate, bool save_pts, bool key2xyz) {
+  return points2octree_list({points},
+                            make_flags(depth, full_depth, node_dis, node_feature, split_label, adaptive,
+                                       adp_depth, th_normal, th_distance, extrapolate, save_pts, key2xyz),
+                            false);
+}
+
+Tensor points2octree_batch(vector<Tensor> points, int depth, int full_depth, bool node_dis,
+                           bool node_feature, bool split_label, bool adaptive, int adp_depth,
+                           float th_normal, float th_distance, bool extrapolate, bool save_pts,
+                           bool key2xyz) {
+  return points2octree_list(points,
+                            make_flags(depth, full_depth, node_dis, node_feature, split_label, adaptive,
+                                       adp_depth, th_normal, th_distance, extrapolate, save_pts, key2xyz),
+                            true);
+}
+
+// ---- octree_batch -------------------------------------------------------------------------------------
+Tensor octree_batch(vector<Tensor> tensors_in) {
+  const int B = (int)tensors_in.size();
+  TORCH_CHECK(B >= 1, "octree_batch: empty input");
+  vector<Tensor> dev(B);
+  vector<ocnn_octree_meta> metas(B);
+  vector<const void*> ptrs(B);
+  uint8_t first[OCNN_HEADER_BYTES];
+  for (int b = 0; b < B; ++b) {
+    OctreeRef o = get_octree(tensors_in[b].contiguous());
+    metas[b] = o.meta;
+    if (b == 0) memcpy(first, o.raw, sizeof(first));
+    dev[b] = tensors_in[b].is_cuda() ? tensors_in[b].contiguous()
+                                     : tensors_in[b].contiguous().to(torch::kCUDA, /*non_blocking=*/false);
+    ptrs[b] = dev[b].data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(dev[0].device());
+  ocnn_octree_meta merged;
+  OCNN_CALL(ocnn_octree_batch_meta(metas.data(), B, &merged));
+  const size_t ws_bytes = ocnn_octree_batch_workspace_bytes(B, merged.depth);
+  Tensor ws = torch::empty({(int64_t)ws_bytes}, dev[0].options());
+  Tensor out = torch::empty({(int64_t)merged.ptr_dis[OCNN_PROP_COUNT]}, dev[0].options());
+  uint8_t raw[OCNN_HEADER_BYTES];
+  OCNN_CALL(ocnn_octree_batch(ptrs.data(), metas.data(), first, B, &merged, ws.data_ptr(), ws_bytes,
+                              out.data_ptr(), raw, current_stream()));
+  remember_header(out, merged, raw);
+  return out;
+}
+
+// ---- octree_property ------------------------------------------------------------------------------------
+Tensor octree_property(Tensor octree, string property, int depth) {
+  OctreeRef o = get_octree(octree);
+  const ocnn_octree_meta& m = o.meta;
+  TORCH_CHECK(depth >= 0 && depth <= m.depth, "octree_property: depth out of range");
+  const int nnum = depth > 0 ? m.nnum[depth] : m.nnum_cum[m.depth + 1];
+  auto block = [&](int prop, int elem_bytes, int channel) {
+    const int64_t off = ocnn_prop_offset(&m, prop, depth);
+    TORCH_CHECK(off >= 0, "The ", property, " do not exist: d = ", depth);
+    return octree.slice(0, off, off + (int64_t)nnum * channel * elem_bytes);
+  };
+  auto small = [&](const int32_t* src, int n) {
+    Tensor t = torch::empty({n}, torch::dtype(torch::kInt32));
+    memcpy(t.data_ptr<int32_t>(), src, sizeof(int32_t) * n);
+    return t.to(octree.device());
+  };
+  if (property == "key" || property == "xyz" || property == "index") {
+    const int kb = m.key_bits / 8;
+    Tensor raw = block(OCNN_PROP_KEY, kb, 1);
+    Tensor key = kb == 8 ? raw.view(torch::kInt64).clone()
+                         : raw.view(torch::kInt32).to(torch::kInt64).bitwise_and(0xffffffffLL);
+    if (property == "index") {
+      Tensor idx = kb == 8 ? key.bitwise_right_shift(48).bitwise_and(0xffff)
+                           : key.bitwise_right_shift(24).bitwise_and(0xff);
+      return idx.to(torch::kInt32);
+    }
+    TORCH_CHECK((property == "key") == (m.key2xyz == 0),
+                "octree_property('", property, "'): converting between Morton keys and packed xyz "
+                "is not implemented");
+    return key;
+  }
+  if (property == "child") return block(OCNN_PROP_CHILD, 4, 1).view(torch::kInt32).clone();
+  if (property == "neigh")
+    return block(OCNN_PROP_NEIGH, 4, 8).view(torch::kInt32).clone().view({nnum, 8});
+  if (property == "feature") {
+    const int ch = m.channels[OCNN_PROP_FEATURE];
+    return block(OCNN_PROP_FEATURE, 4, ch).view(torch::kFloat32).clone().view({1, ch, nnum, 1});
+  }
+  if (property == "label") return block(OCNN_PROP_LABEL, 4, 1).view(torch::kFloat32).clone();
+  if (property == "split") return block(OCNN_PROP_SPLIT, 4, 1).view(torch::kFloat32).clone();
+  if (property == "node_num") return small(m.nnum + depth, depth > 0 ? 1 : m.depth + 1);
+  if (property == "node_num_ne" || property == "node_num_nempty")
+    return small(m.nnum_nempty + depth, depth > 0 ? 1 : m.depth + 1);
+  if (property == "node_num_cum") return small(m.nnum_cum + depth, depth > 0 ? 1 : m.depth + 2);
+  if (property == "batch_size") return small(&m.batch_size, 1);
+  if (property == "depth") return small(&m.depth, 1);
+  if (property == "full_depth") return small(&m.full_depth, 1);
+  TORCH_CHECK(false, "Unsupport octree property: ", property);
+  return Tensor();
+}
+
+// Host-side view of the header: ints only, no device access after the first call on a tensor.
+vector<int64_t> octree_info(Tensor octree) {
+  OctreeRef o = get_octree(octree);
+  const ocnn_octree_meta& m = o.meta;
+  vector<int64_t> out = {m.key_bits, m.batch_size, m.depth, m.full_depth};
+  for (int d = 0; d < OCNN_MAX_DEPTH; ++d) out.push_back(m.nnum[d]);
+  for (int d = 0; d < OCNN_MAX_DEPTH; ++d) out.push_back(m.nnum_nempty[d]);
+  for (int p = 0; p < OCNN_PROP_COUNT; ++p) out.push_back(m.channels[p]);
+  return out;
+}
+
+Tensor feature_node_major(Tensor octree, int c_pad, bool bf16) {
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "feature_node_major: the octree must be a CUDA tensor");
+  const ocnn_octree_meta& m = o.meta;
+  const int d = m.depth, ch = m.channels[OCNN_PROP_FEATURE];
+  const int64_t off = ocnn_prop_offset(&m, OCNN_PROP_FEATURE, d);
+  TORCH_CHECK(off >= 0 && ch > 0, "the octree has no features at its finest level");
+  TORCH_CHECK(c_pad >= ch, "c_pad must be at least the feature channel count ", ch);
+  c10::cuda::CUDAGuard guard(octree.device());
+  auto opts = octree.options().dtype(bf16 ? torch::kBFloat16 : torch::kFloat32)
+                  .memory_format(at::MemoryFormat::ChannelsLast);
+  Tensor out = torch::empty({1, c_pad, m.nnum[d], 1}, opts);
+  OCNN_CALL(ocnn_feature_to_node_major(reinterpret_cast<const float*>(o.base + off), out.data_ptr(),
+                                       ch, c_pad, m.nnum[d], bf16 ? OCNN_BF16 : OCNN_F32,
+                                       current_stream()));
+  return out;
+}
+
+void set_key_bits(int bits) {
+  TORCH_CHECK(bits == 32 || bits == 64, "key bits must be 32 or 64");
+  g_key_bits = bits;
+}
+int get_key_bits() { return g_key_bits; }
+
+template <typename... Args>
+Tensor not_built(const char* name) {
+  TORCH_CHECK(false, "ocnn.nn.", name, " is outside the inference hot path and is not implemented "
+              "in ocnn_b200");
+  return Tensor();
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  namespace py = pybind11;
+  m.doc() = "ocnn.nn on libocnn_b200 (CUDA sm_100a)";
+  // reference names and signatures (pytorch/cpp/pybind.cpp:3-49)
+  m.def("octree_batch", &octree_batch, "merge a batch of octrees");
+  m.def("octree_property", &octree_property, "get the octree property", py::arg("octree"),
+        py::arg("property"), py::arg("depth") = 0);
+  m.def("points2octree", &points2octree, "convert points to octree");
+  m.def("octree2col", &octree2col, "octree2col");
+  m.def("octree_conv", &octree_conv, "octree based convolution");
+  m.def("octree_pad", &octree_pad, "octree pad", py::arg("data_in"), py::arg("octree"),
+        py::arg("depth"), py::arg("val") = 0.0f);
+  m.def("octree_depad", &octree_depad, "octree depad");
+  m.def("octree_max_pool", &octree_max_pool, "octree max pooling");
+  m.def("points_new", &points_new, "create a point cloud");
+  // additions of this implementation
+  m.def("points2octree_batch", &points2octree_batch,
+        "build the merged batch octree of a list of point clouds in one pass");
+  m.def("points_pack", &points_pack, py::arg("points"), py::arg("pin") = false);
+  m.def("points2octree_packed", &points2octree_packed);
+  m.def("octree_conv_fused", &octree_conv_fused, py::arg("data_in"), py::arg("weights"),
+        py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
+        py::arg("stride"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false);
+  m.def("conv_pack_weights", &conv_pack_weights);
+  m.def("octree_conv_tc", &octree_conv_tc, py::arg("data_in"), py::arg("packed"), py::arg("octree"),
+        py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"), py::arg("stride"),
+        py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
+  m.def("octree_info", &octree_info);
+  m.def("feature_node_major", &feature_node_major, py::arg("octree"), py::arg("c_pad"),
+        py::arg("bf16") = true);
+  m.def("set_key_bits", &set_key_bits);
+  m.def("get_key_bits", &get_key_bits);
+  m.def("last_error", []() { return string(ocnn_last_error()); });
+  m.def("launch_count", []() { return (int64_t)ocnn_launch_count(); });
+}

@@ -1,0 +1,126 @@
+"""GPU parity tests of the octree convolution against the CPU oracle.
+Tolerances (max |y - y_ref| / max |y_ref| per tensor): 1e-5 for fp32, 2e-2 for bf16 data."""
+import numpy as np
+import pytest
+import torch
+
+import gpu_util as gu
+from oracle import oracle as oc
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+BF16_TOL = 2e-2
+KERNELS = [[3, 3, 3], [2, 2, 2], [3, 1, 1], [1, 3, 1], [1, 1, 3], [3, 3, 1], [3, 1, 3], [1, 3, 3],
+           [1, 1, 1]]
+
+
+@pytest.fixture(scope='module')
+def ocnn():
+  import ocnn as mod
+  return mod
+
+
+@pytest.fixture(scope='module')
+def batch():
+  clouds = gu.small_clouds(3, 4000, 200)
+  singles, merged, _ = gu.oracle_batch(clouds, 6, 2, 64)
+  return merged, gu.to_cuda_u8(merged), oc.OctreeView(merged)
+
+
+def test_conv_matches_reference_fixture(ocnn, golden):
+  """Every kernel shape and stride against outputs of the reference's own CPU convolution."""
+  merged = golden['k32_b_merged']
+  octree = gu.to_cuda_u8(merged)
+  for ks in KERNELS:
+    name = ''.join(map(str, ks))
+    w = torch.from_numpy(golden['b_w' + name]).cuda()
+    for stride in (1, 2):
+      got = ocnn.octree_conv(gu.data_cuda(golden['b_x']), w, octree, 4, 5, ks, stride)
+      want = golden['b_conv%s_s%d' % (name, stride)]
+      assert gu.rel_err(gu.to_np(got), want) < FP32_TOL, (ks, stride)
+
+
+def test_conv_equals_octree2col_mm(ocnn, golden):
+  # pytorch/test/test_octree_conv.py:10-82 (forward): OctreeConv vs OctreeConvFast on
+  # octree_1 + octree_2, depth 4, 3 -> 5 channels
+  octree = ocnn.octree_batch([torch.from_numpy(golden['k64_octree_1']),
+                              torch.from_numpy(golden['k64_octree_2'])])
+  rng = np.random.default_rng(2)
+  data = gu.data_cuda(rng.uniform(-1, 1, size=(3, 152)).astype(np.float32))
+  for stride in (1, 2):
+    for ks in ([3, 3, 3], [2, 2, 2], [3, 1, 1], [3, 3, 1], [1, 1, 1]):
+      conv1 = ocnn.OctreeConv(4, 3, 5, ks, stride).cuda()
+      conv2 = ocnn.OctreeConvFast(4, 3, 5, ks, stride).cuda()
+      with torch.no_grad():
+        conv2.weights.copy_(conv1.weights)
+      out1, out2 = conv1(data, octree), conv2(data, octree)
+      assert out1.shape == out2.shape == (1, 5, 152 if stride == 1 else 16, 1)
+      assert gu.rel_err(gu.to_np(out1), gu.to_np(out2)) < FP32_TOL, (ks, stride)
+
+
+@pytest.mark.parametrize('ks', KERNELS)
+@pytest.mark.parametrize('stride', [1, 2])
+def test_conv_fp32_channel_major(ocnn, batch, ks, stride):
+  merged, octree, v = batch
+  rng = np.random.default_rng(sum(ks) + 10 * stride)
+  for d, cin, cout in ((6, 3, 32), (5, 16, 24), (3, 70, 65)):
+    H = int(v.nnum[d])
+    x = rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)
+    w = rng.normal(scale=0.1, size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
+    got = ocnn.octree_conv(gu.data_cuda(x), torch.from_numpy(w).cuda(), octree, d, cout, ks, stride)
+    want = oc.octree_conv(x, w, merged, d, cout, ks, stride)
+    assert got.shape == (1, cout, want.shape[1], 1)
+    assert gu.rel_err(gu.to_np(got), want) < FP32_TOL, (d, cin, cout)
+
+
+@pytest.mark.parametrize('bf16', [False, True])
+def test_conv_node_major(ocnn, batch, bf16):
+  merged, octree, v = batch
+  rng = np.random.default_rng(77)
+  for ks, stride in (([3, 3, 3], 1), ([3, 3, 3], 2), ([2, 2, 2], 2), ([1, 1, 1], 1), ([3, 1, 3], 1)):
+    for d, cin, cout in ((6, 8, 16), (5, 32, 64), (4, 3, 7)):
+      H = int(v.nnum[d])
+      x = rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)
+      w = rng.normal(scale=0.1, size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
+      if bf16:
+        x = gu.bf16_round(x)
+      got = ocnn.octree_conv(gu.data_cuda(x, True, bf16), torch.from_numpy(w).cuda(), octree, d,
+                             cout, ks, stride)
+      assert got.is_contiguous(memory_format=torch.channels_last) or cout == 1
+      want = oc.octree_conv(x, w, merged, d, cout, ks, stride)
+      tol = BF16_TOL if bf16 else FP32_TOL
+      assert gu.rel_err(gu.to_np(got), want) < tol, (ks, stride, d)
+
+
+def test_conv_fused_epilogue(ocnn, batch):
+  merged, octree, v = batch
+  rng = np.random.default_rng(5)
+  d, cin, cout, ks = 5, 16, 32, [3, 3, 3]
+  H = int(v.nnum[d])
+  x = rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)
+  w = rng.normal(scale=0.1, size=(cout, cin * 27)).astype(np.float32)
+  scale = rng.uniform(0.5, 1.5, size=cout).astype(np.float32)
+  bias = rng.normal(size=cout).astype(np.float32)
+  res = rng.normal(size=(cout, H)).astype(np.float32)
+  ref = oc.octree_conv(x, w, merged, d, cout, ks, 1)
+  want = np.maximum(ref * scale[:, None] + bias[:, None] + res, 0)
+  for nm in (False, True):
+    got = ocnn.nn.octree_conv_fused(gu.data_cuda(x, nm), torch.from_numpy(w).cuda(), octree, d, cout,
+                                    ks, 1, torch.from_numpy(scale).cuda(),
+                                    torch.from_numpy(bias).cuda(), gu.data_cuda(res, nm), True)
+    assert gu.rel_err(gu.to_np(got), want) < FP32_TOL
+
+
+def test_conv_errors(ocnn, batch):
+  _, octree, v = batch
+  w = torch.zeros(4, 3 * 27, device='cuda')
+  with pytest.raises(RuntimeError, match='data height'):
+    ocnn.octree_conv(torch.zeros(1, 3, 10, 1, device='cuda'), w, octree, 5, 4, [3], 1)
+  with pytest.raises(RuntimeError, match='[Kk]ernel size'):
+    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [4], 1)
+  with pytest.raises(RuntimeError, match='stride'):
+    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [3], 3)
+  with pytest.raises(RuntimeError, match='not implemented'):
+    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[5]), 1, device='cuda'), w, octree, 5, 4,
+                     [3], 1, True)
