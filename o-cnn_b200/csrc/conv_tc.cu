@@ -1,20 +1,443 @@
-// Placeholder translation unit for the tensor-core convolution (filled in by conv_tc.cu proper).
+// Octree convolution on the 5th-generation tensor cores (tcgen05 + TMEM), bf16 in, fp32 accumulate.
+//
+// One CTA computes a tile of 128 output nodes x all output channels as an implicit GEMM
+//     D[128, Cout] = A[128, K] * B[K, Cout],     K = taps * Cin walked tap-major (k = t*Cin + ci),
+// where row r of A is the concatenation, over the taps, of the Cin-channel rows of node r's
+// neighbours (zeros where a neighbour does not exist).  A is never materialised in HBM: each
+// K-block of 64 (128 bytes per row) is gathered straight into the 128B-swizzled K-major shared
+// memory layout the UMMA smem descriptor expects, 16 bytes per cp.async, zero-filled for missing
+// neighbours.  B comes from weights packed once per layer into the same swizzled image, one
+// contiguous chunk per K-block, fetched with one bulk async copy.  Accumulators live in TMEM and
+// are read back by the four epilogue warps with tcgen05.ld.
+//
+// Warp roles (192 threads): warps 0-3 gather A (one tile row per thread) and later run the
+// epilogue (TMEM lane quarter = warp id); warp 4 allocates TMEM and its lane 0 issues the MMAs;
+// lane 0 of warp 5 streams the weight tiles.  A 4-stage ring of {A tile, B tile} buffers is
+// handed between them with mbarriers: full[s] (128 gather arrivals + the weight copy's bytes),
+// empty[s] (tcgen05.commit when the MMAs that read the stage have retired).
+//
+// Every wait is bounded: a wait that runs out sets *status (and a CTA-wide abort flag), the CTA
+// drains its own copies, frees its TMEM and returns — the launch never hangs the GPU.
 #include "common.cuh"
+
+namespace ocnn {
+namespace {
+
+constexpr int kTileM = 128;          // nodes per CTA = TMEM lanes
+constexpr int kBlockK = 64;          // bf16 elements per K-block = one 128-byte swizzle row
+constexpr int kStageA = kTileM * 128;  // bytes of one A stage
+constexpr int kThreads = 192;
+constexpr int kLag = 2;              // gather arrivals trail the issue by this many stages
+constexpr unsigned kSpinLimit = 1u << 22;
+
+enum : int { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccumWait = 3, kErrWeightWait = 4 };
+
+struct TcArgs {
+  const __nv_bfloat16* x;
+  const uint8_t* wpacked;
+  __nv_bfloat16* y;
+  const int* neigh;
+  int h_in, h_out, cin, cout, npad, T, stride, identity, nkb, stages, tmem_cols;
+  const float* scale;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  int relu;
+  int* status;
+  signed char tap[27];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  for (unsigned it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u && *abort_flag != 0) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+// K-major, 128-byte-swizzled shared memory matrix descriptor (sm_100 format): start address >> 4
+// in bits [0,14), leading byte offset (unused for swizzled K-major, 1) in [16,30), stride byte
+// offset = 1024 B between 8-row groups in [32,46), descriptor version 1 in [46,48), layout type
+// SWIZZLE_128B = 2 in [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
+                 "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr));
+}
+
+__global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the swizzle pattern is a function of address bits [4,10)
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stage_b = a.npad * 128;
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + a.stages * kStageA;
+  int* nbr = reinterpret_cast<int*>(sB + a.stages * stage_b);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(nbr + a.T * kTileM);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + a.stages;
+  uint64_t* accum = bars + 2 * a.stages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h0 = blockIdx.x * kTileM;
+
+  if (tid == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(&full[s]), kTileM + 1);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    mbar_init(smem_u32(accum), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)), "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid < kTileM) {
+    const int h = h0 + tid;
+    for (int t = 0; t < a.T; ++t) {
+      int p = -1;
+      if (h < a.h_out) {
+        if (a.identity) {
+          p = h;
+        } else {
+          const int tap = a.tap[t];
+          const long long at = a.stride == 2 ? ((long long)h << 6) + ni333(0, tap)
+                                             : ((long long)(h >> 3) << 6) + ni333(h & 7, tap);
+          p = a.neigh[at];
+        }
+      }
+      nbr[t * kTileM + tid] = p;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp < 4) {
+    // ---------------- A gather: thread = tile row ----------------
+    const int r = tid;
+    const int cpt = a.cin >> 3;                 // 16-byte chunks per tap
+    const uint32_t row_off = (uint32_t)r * 128u;
+    const uint32_t sw = (uint32_t)(r & 7);
+    bool alive = true;
+    for (int kb = 0; kb < a.nkb; ++kb) {
+      const int s = kb % a.stages;
+      if (alive && kb >= a.stages)
+        alive = mbar_wait(smem_u32(&empty[s]), (uint32_t)(((kb / a.stages) - 1) & 1), abort_flag,
+                          a.status, kErrEmptyWait);
+      if (alive) {
+        const uint32_t dst_row = smem_u32(sA + s * kStageA) + row_off;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int q = kb * 8 + c;
+          const int t = q / cpt;
+          const __nv_bfloat16* src = a.x;
+          uint32_t bytes = 0;
+          if (t < a.T) {
+            const int p = nbr[t * kTileM + r];
+            if (p >= 0) {
+              src = a.x + (long long)p * a.cin + ((q - t * cpt) << 3);
+              bytes = 16;
+            }
+          }
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                           dst_row + (((uint32_t)c ^ sw) << 4)), "l"(src), "r"(bytes)
+                       : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (kb >= kLag) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
+        // the gathered bytes were written through the generic proxy; the tensor core reads
+        // shared memory through the async proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(smem_u32(&full[(kb - kLag) % a.stages]));
+      }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int kb = (a.nkb > kLag ? a.nkb - kLag : 0); kb < a.nkb; ++kb)
+      mbar_arrive(smem_u32(&full[kb % a.stages]));
+
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    if (alive) alive = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, kErrAccumWait);
+    alive = __all_sync(0xffffffffu, alive);   // tcgen05.ld is warp-collective: decide per warp
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int h = h0 + r;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    if (alive) {
+      for (int n0 = 0; n0 < a.npad; n0 += 8) {
+        uint32_t v[8];
+        tmem_ld8(lane_base + (uint32_t)n0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (h < a.h_out && n0 < a.cout) {
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            f[j] = __uint_as_float(v[j]);
+            if (a.scale) f[j] *= a.scale[n0 + j];
+            if (a.bias) f[j] += a.bias[n0 + j];
+          }
+          const long long at = (long long)h * a.cout + n0;
+          if (a.residual) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
+            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 rf = __bfloat1622float2(rp[j]);
+              f[2 * j] += rf.x;
+              f[2 * j + 1] += rf.y;
+            }
+          }
+          if (a.relu) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+          }
+          uint4 ov;
+          __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+          *reinterpret_cast<uint4*>(a.y + at) = ov;
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ---------------- MMA issue: one thread ----------------
+    if (lane == 0) {
+      // instruction descriptor: D = F32 (bit 4), A = B = BF16 (bits 7, 10), both K-major,
+      // N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.npad >> 3) << 17) |
+                             ((uint32_t)(kTileM >> 4) << 24);
+      bool alive = true;
+      for (int kb = 0; kb < a.nkb && alive; ++kb) {
+        const int s = kb % a.stages;
+        alive = mbar_wait(smem_u32(&full[s]), (uint32_t)((kb / a.stages) & 1), abort_flag, a.status,
+                          kErrFullWait);
+        if (!alive) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(sA + s * kStageA);
+        const uint32_t b_addr = smem_u32(sB + s * stage_b);
+#pragma unroll
+        for (int k4 = 0; k4 < kBlockK / 16; ++k4) {
+          umma_bf16(tmem_base, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32),
+                    idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&empty[s]));     // stage reusable once these MMAs retire
+      }
+      if (alive) umma_commit(smem_u32(accum));
+    }
+  } else {
+    // ---------------- weight tiles: one thread, one bulk copy per K-block ----------------
+    if (lane == 0) {
+      bool alive = true;
+      for (int kb = 0; kb < a.nkb && alive; ++kb) {
+        const int s = kb % a.stages;
+        if (kb >= a.stages)
+          alive = mbar_wait(smem_u32(&empty[s]), (uint32_t)(((kb / a.stages) - 1) & 1), abort_flag,
+                            a.status, kErrWeightWait);
+        if (!alive) break;
+        const uint32_t bar = smem_u32(&full[s]);
+        mbar_arrive_expect_tx(bar, (uint32_t)stage_b);
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+            ::"r"(smem_u32(sB + s * stage_b)), "l"(a.wpacked + (size_t)kb * stage_b),
+              "r"((uint32_t)stage_b), "r"(bar)
+            : "memory");
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+  }
+}
+
+// ---- weight packing -------------------------------------------------------------------------
+// w: fp32 [cout, cin*T], column ci*T + t (the reference module's layout).  packed: per K-block a
+// [npad x 64] bf16 tile in the swizzled K-major image: element (n, kk) at
+// (n/8)*1024 + (n%8)*128 + (((kk/8) ^ (n%8)) * 16) + (kk%8)*2, k = kb*64 + kk = t*cin + ci.
+__global__ void pack_weights_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ packed,
+                                    int cin, int cout, int T, int npad, int nkb) {
+  const long long total = (long long)nkb * npad * kBlockK;
+  const int KD = cin * T;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int kk = (int)(i % kBlockK);
+    const int n = (int)((i / kBlockK) % npad);
+    const int kb = (int)(i / ((long long)kBlockK * npad));
+    const int k = kb * kBlockK + kk;
+    float v = 0.f;
+    if (n < cout && k < KD) {
+      const int t = k / cin, ci = k % cin;
+      v = w[(long long)n * KD + ci * T + t];
+    }
+    const long long off = (long long)kb * npad * 64 + (n >> 3) * 512 + (n & 7) * 64 +
+                          (((kk >> 3) ^ (n & 7)) << 3) + (kk & 7);
+    packed[off] = __float2bfloat16(v);
+  }
+}
+
+struct TcShape { int T, npad, nkb, tmem_cols, stages; size_t smem; };
+
+int tc_shape(int cin, int cout, const int ks[3], TcShape* s) {
+  const TapList tl = taps_for_kernel(ks);
+  if (tl.count < 0)
+    return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported kernel size %dx%dx%d",
+                ks[0], ks[1], ks[2]);
+  if (cin <= 0 || cin % 8 != 0)
+    return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: Cin (%d) must be a multiple of 8", cin);
+  if (cout <= 0 || cout % 8 != 0 || cout > 256)
+    return fail(OCNN_ERR_UNSUPPORTED,
+                "tensor-core convolution: Cout (%d) must be a multiple of 8, at most 256", cout);
+  s->T = tl.count;
+  s->npad = (cout + 15) / 16 * 16;
+  s->nkb = (cin * tl.count + kBlockK - 1) / kBlockK;
+  s->tmem_cols = 32;
+  while (s->tmem_cols < s->npad) s->tmem_cols *= 2;
+  s->stages = s->npad > 128 ? 3 : 4;
+  if (s->stages > s->nkb) s->stages = s->nkb < 2 ? 2 : s->nkb;
+  s->smem = 1024 + (size_t)s->stages * (kStageA + s->npad * 128) + (size_t)s->T * kTileM * 4 +
+            (2 * s->stages + 1) * 8 + 16;
+  return OCNN_OK;
+}
+
+}  // namespace
+}  // namespace ocnn
 
 extern "C" {
 
 size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3]) {
-  (void)cin; (void)cout; (void)kernel_size;
-  return 0;
+  ocnn::TcShape s;
+  if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, &s) != OCNN_OK) return 0;
+  return (size_t)s.nkb * s.npad * 128;
 }
 
-int ocnn_conv_pack_weights(const float*, void*, int, int, const int*, void*) {
-  return ocnn::fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution not built");
+int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
+                           void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(w && packed && kernel_size, "ocnn_conv_pack_weights: null pointer");
+  TcShape s;
+  if (int st = tc_shape(cin, cout, kernel_size, &s)) return st;
+  const long long total = (long long)s.nkb * s.npad * kBlockK;
+  pack_weights_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      w, static_cast<__nv_bfloat16*>(packed), cin, cout, s.T, s.npad, s.nkb);
+  OCNN_LAUNCH_OK("pack_weights_kernel");
+  return OCNN_OK;
 }
 
-int ocnn_octree_conv_tc(const void*, const void*, void*, const int32_t*, int, int, int, int,
-                        const int*, int, const ocnn_conv_epilogue*, int32_t*, void*) {
-  return ocnn::fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution not built");
+int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_t* neigh, int h_in,
+                        int h_out, int cin, int cout, const int kernel_size[3], int stride,
+                        const ocnn_conv_epilogue* ep, int32_t* status, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_tc: null kernel size");
+  OCNN_REQUIRE(stride == 1 || stride == 2, "ocnn_octree_conv_tc: stride must be 1 or 2 (got %d)", stride);
+  TcShape s;
+  if (int st = tc_shape(cin, cout, kernel_size, &s)) return st;
+  OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv_tc: negative height");
+  if (h_out == 0) return OCNN_OK;
+  const bool identity = s.T == 1 && stride == 1;
+  OCNN_REQUIRE(x && packed && y && status, "ocnn_octree_conv_tc: null pointer");
+  OCNN_REQUIRE(identity || neigh != nullptr, "ocnn_octree_conv_tc: neighbour table required");
+  OCNN_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)packed % 16 == 0),
+               "ocnn_octree_conv_tc: data and weight pointers must be 16-byte aligned");
+  if (stride == 2) {
+    OCNN_REQUIRE((long long)h_out * 8 == h_in,
+                 "ocnn_octree_conv_tc: stride 2 needs h_in == 8*h_out (got %d, %d)", h_in, h_out);
+  } else {
+    OCNN_REQUIRE(h_in == h_out, "ocnn_octree_conv_tc: stride 1 needs h_in == h_out (got %d, %d)",
+                 h_in, h_out);
+  }
+  if (ep && ep->residual_dev)
+    OCNN_REQUIRE((uintptr_t)ep->residual_dev % 16 == 0,
+                 "ocnn_octree_conv_tc: residual must be 16-byte aligned");
+  TcArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.wpacked = static_cast<const uint8_t*>(packed);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.neigh = neigh;
+  a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout; a.npad = s.npad; a.T = s.T;
+  a.stride = stride; a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
+  a.tmem_cols = s.tmem_cols;
+  a.scale = ep ? ep->scale_dev : nullptr;
+  a.bias = ep ? ep->bias_dev : nullptr;
+  a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
+  a.relu = ep ? ep->relu : 0;
+  a.status = status;
+  const TapList tl = taps_for_kernel(kernel_size);
+  for (int i = 0; i < 27; ++i) a.tap[i] = i < tl.count ? tl.tap[i] : 0;
+  // raising the dynamic shared memory limit is per function and per device
+  static bool attr_set[64] = {};
+  int device = 0;
+  OCNN_CUDA_OK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64 || !attr_set[device]) {
+    OCNN_CUDA_OK(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      200 * 1024));
+    if (device >= 0 && device < 64) attr_set[device] = true;
+  }
+  conv_tc_kernel<<<ceil_div(h_out, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
+  OCNN_LAUNCH_OK("conv_tc_kernel");
+  return OCNN_OK;
 }
 
-}
+}  // extern "C"

@@ -109,6 +109,12 @@ int ocnn_calc_neigh(void* octree_dev, const ocnn_octree_meta* m, void* stream) {
   OCNN_REQUIRE(m->channels[OCNN_PROP_CHILD] == 1 && m->locations[OCNN_PROP_CHILD] == -1,
                "ocnn_calc_neigh: the octree has no child block");
   uint8_t* base = static_cast<uint8_t*>(octree_dev);
+  // level 0 has no neighbour table; the reference leaves its slot zero-filled
+  // (merge_octrees.cpp:108-112 resizes a fresh vector, the loop at :184 starts at d = 1)
+  if (m->nnum[0] > 0)
+    OCNN_CUDA_OK(cudaMemsetAsync(base + ocnn_prop_offset(m, OCNN_PROP_NEIGH, 0), 0,
+                                 (size_t)m->nnum[0] * 8 * sizeof(int32_t),
+                                 static_cast<cudaStream_t>(stream)));
   for (int d = 1; d <= m->depth; ++d) {
     int32_t* nd = reinterpret_cast<int32_t*>(base + ocnn_prop_offset(m, OCNN_PROP_NEIGH, d));
     int s;

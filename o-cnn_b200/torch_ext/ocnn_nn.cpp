@@ -149,10 +149,17 @@ DataRef get_data(const Tensor& data, const char* what) {
   return d;
 }
 
+void need_cuda(const Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda(), what, ": the data tensor must be a CUDA tensor (there is no CPU path)");
+}
+
 Tensor new_data(int C, int H, const DataRef& like, bool zero = false) {
   auto opts = like.t.options();
   if (like.layout == OCNN_NODE_MAJOR) opts = opts.memory_format(at::MemoryFormat::ChannelsLast);
-  return zero ? torch::zeros({1, C, H, 1}, opts) : torch::empty({1, C, H, 1}, opts);
+  // torch::zeros drops the memory format of its options, so zero an empty tensor instead
+  Tensor out = torch::empty({1, C, H, 1}, opts);
+  if (zero) out.zero_();
+  return out;
 }
 
 vector<int> kernel3(vector<int> ks) {
@@ -174,6 +181,7 @@ Tensor octree_pad(Tensor data_in, Tensor octree, int depth, float val) {
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "octree_pad: the octree must be a CUDA tensor");
   TORCH_CHECK(depth <= o.meta.depth, "octree_pad: depth ", depth, " exceeds the octree depth");
+  need_cuda(data_in, "octree_pad");
   c10::cuda::CUDAGuard guard(data_in.device());
   DataRef x = get_data(data_in, "octree_pad");
   TORCH_CHECK(o.meta.nnum_nempty[depth] == x.H, "octree_pad: data height ", x.H,
@@ -192,6 +200,7 @@ Tensor octree_depad(Tensor data_in, Tensor octree, int depth) {
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "octree_depad: the octree must be a CUDA tensor");
   TORCH_CHECK(depth <= o.meta.depth, "octree_depad: depth ", depth, " exceeds the octree depth");
+  need_cuda(data_in, "octree_depad");
   c10::cuda::CUDAGuard guard(data_in.device());
   DataRef y = get_data(data_in, "octree_depad");
   TORCH_CHECK(o.meta.nnum[depth] == y.H, "octree_depad: data height ", y.H, " != node number ",
@@ -208,6 +217,7 @@ vector<Tensor> octree_max_pool(Tensor data_in, Tensor octree, int depth) {
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(depth > 1, "Depth should be larger than 1");
   TORCH_CHECK(depth <= o.meta.depth, "octree_max_pool: depth ", depth, " exceeds the octree depth");
+  need_cuda(data_in, "octree_max_pool");
   c10::cuda::CUDAGuard guard(data_in.device());
   DataRef b = get_data(data_in, "octree_max_pool");
   TORCH_CHECK(o.meta.nnum[depth] == b.H, "octree_max_pool: data height ", b.H, " != node number ",
@@ -231,6 +241,7 @@ Tensor octree2col(Tensor data_in, Tensor octree, int depth, vector<int> kernel_s
   TORCH_CHECK(depth > 0, "Depth should be larger than 0");
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "octree2col: the octree must be a CUDA tensor");
+  need_cuda(data_in, "octree2col");
   c10::cuda::CUDAGuard guard(data_in.device());
   TORCH_CHECK(data_in.scalar_type() == torch::kFloat32, "octree2col takes float32 data");
   DataRef x = get_data(data_in.contiguous(), "octree2col");
@@ -299,6 +310,7 @@ Tensor octree_conv_fused(Tensor data_in, Tensor weights, Tensor octree, int dept
   TORCH_CHECK(num_output > 0, "The num_output should be larger than 0");
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "octree_conv: the octree must be a CUDA tensor");
+  need_cuda(data_in, "octree_conv");
   c10::cuda::CUDAGuard guard(data_in.device());
   DataRef x = get_data(data_in, "octree_conv");
   ConvShape s = conv_shape(o, x, depth, ks, stride, "octree_conv");
@@ -346,6 +358,7 @@ Tensor octree_conv_tc(Tensor data_in, Tensor packed, Tensor octree, int depth, i
   vector<int> ks = kernel3(kernel_size);
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "octree_conv_tc: the octree must be a CUDA tensor");
+  need_cuda(data_in, "octree_conv_tc");
   c10::cuda::CUDAGuard guard(data_in.device());
   DataRef x = get_data(data_in, "octree_conv_tc");
   TORCH_CHECK(x.dtype == OCNN_BF16 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),

@@ -55,7 +55,9 @@ def test_conv_equals_octree2col_mm(ocnn, golden):
       with torch.no_grad():
         conv2.weights.copy_(conv1.weights)
       out1, out2 = conv1(data, octree), conv2(data, octree)
-      assert out1.shape == out2.shape == (1, 5, 152 if stride == 1 else 16, 1)
+      # stride 2 is padded to every node of depth 3 by the module (octree_conv.py:111-112)
+      h3 = ocnn.octree_property(octree, 'node_num', 3).item()
+      assert out1.shape == out2.shape == (1, 5, 152 if stride == 1 else h3, 1)
       assert gu.rel_err(gu.to_np(out1), gu.to_np(out2)) < FP32_TOL, (ks, stride)
 
 
@@ -124,3 +126,78 @@ def test_conv_errors(ocnn, batch):
   with pytest.raises(RuntimeError, match='not implemented'):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[5]), 1, device='cuda'), w, octree, 5, 4,
                      [3], 1, True)
+
+
+# ---- tensor-core (tcgen05) path -----------------------------------------------------------------
+TC_CASES = [
+    # (depth, cin, cout, kernel, stride)
+    (6, 8, 8, [3, 3, 3], 1),       # ResNet d6 bottleneck: Cout padded to the UMMA minimum of 16
+    (6, 8, 32, [3, 3, 3], 1),      # conv1 with the 3 normal channels padded to 8
+    (5, 16, 16, [3, 3, 3], 1),
+    (4, 32, 32, [3, 3, 3], 1),
+    (3, 64, 64, [3, 3, 3], 1),
+    (2, 128, 128, [3, 3, 3], 1),
+    (3, 64, 256, [3, 3, 3], 1),
+    (5, 24, 40, [3, 3, 3], 1),     # K = 27*24 is not a multiple of 64; Cout not a multiple of 16
+    (6, 32, 8, [1, 1, 1], 1),      # the 1x1 convolutions of the bottleneck blocks
+    (5, 16, 64, [1, 1, 1], 1),
+    (3, 256, 64, [1, 1, 1], 1),
+    (5, 16, 32, [2, 2, 2], 2),
+    (5, 16, 32, [3, 3, 3], 2),
+    (4, 32, 16, [3, 1, 3], 1),
+]
+
+
+@pytest.mark.parametrize('case', TC_CASES, ids=lambda c: 'd%d_%dto%d_k%s_s%d' % (
+    c[0], c[1], c[2], ''.join(map(str, c[3])), c[4]))
+def test_conv_tensor_core(ocnn, batch, case):
+  merged, octree, v = batch
+  d, cin, cout, ks, stride = case
+  rng = np.random.default_rng(cin * 1000 + cout + stride)
+  H = int(v.nnum[d])
+  x = gu.bf16_round(rng.uniform(-1, 1, size=(cin, H)).astype(np.float32))
+  w = rng.normal(scale=0.1, size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
+  wt = torch.from_numpy(w).cuda()
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights(wt, cin, cout, ks)
+  got = ocnn.nn.octree_conv_tc(gu.data_cuda(x, True, True), packed, octree, d, cout, ks, stride,
+                               None, None, None, False, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0, 'kernel gave up on a wait (code %d)' % int(status.item())
+  want = oc.octree_conv(x, w, merged, d, cout, ks, stride)
+  assert got.shape == (1, cout, want.shape[1], 1)
+  assert gu.rel_err(gu.to_np(got), want) < BF16_TOL
+  # against bf16-rounded weights only the accumulation order and the output rounding differ
+  tight = oc.octree_conv(x, gu.bf16_round(w), merged, d, cout, ks, stride)
+  assert gu.rel_err(gu.to_np(got), tight) < 6e-3
+
+
+def test_conv_tensor_core_epilogue(ocnn, batch):
+  merged, octree, v = batch
+  rng = np.random.default_rng(12)
+  d, cin, cout, ks = 5, 16, 32, [3, 3, 3]
+  H = int(v.nnum[d])
+  x = gu.bf16_round(rng.uniform(-1, 1, size=(cin, H)).astype(np.float32))
+  w = rng.normal(scale=0.1, size=(cout, cin * 27)).astype(np.float32)
+  scale = rng.uniform(0.5, 1.5, size=cout).astype(np.float32)
+  bias = rng.normal(size=cout).astype(np.float32)
+  res = gu.bf16_round(rng.normal(size=(cout, H)).astype(np.float32))
+  ref = oc.octree_conv(x, gu.bf16_round(w), merged, d, cout, ks, 1)
+  want = np.maximum(ref * scale[:, None] + bias[:, None] + res, 0)
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights(torch.from_numpy(w).cuda(), cin, cout, ks)
+  got = ocnn.nn.octree_conv_tc(gu.data_cuda(x, True, True), packed, octree, d, cout, ks, 1,
+                               torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda(),
+                               gu.data_cuda(res, True, True), True, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  assert gu.rel_err(gu.to_np(got), want) < 8e-3
+
+
+def test_conv_tensor_core_rejects_unsupported_shapes(ocnn, batch):
+  _, octree, v = batch
+  w = torch.zeros(16, 3 * 27, device='cuda')
+  with pytest.raises(RuntimeError, match='multiple of 8'):
+    ocnn.nn.conv_pack_weights(w, 3, 16, [3, 3, 3])
+  with pytest.raises(RuntimeError, match='at most 256'):
+    ocnn.nn.conv_pack_weights(torch.zeros(512, 8, device='cuda'), 8, 512, [1, 1, 1])
