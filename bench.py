@@ -398,7 +398,7 @@ def run_ours(args):
                   'ms_per_step': e2e_ms / args.steps},
           'gpu_launches': int(launches), 'clocks': clocks, 'roofline': roofline,
           'tensor_core_layers': sum(1 for _, p in models.conv_layers(net.net) if p.get('_packed') is not None),
-          'layer_ms_top5': dict(sorted(layer_ms.items(), key=lambda kv: -kv[1])[:5]),
+          'layer_ms': {k: round(v, 4) for k, v in layer_ms.items()},
           'finest_nodes': int(nnum[DEPTH])}
 
   if world == 1:

@@ -28,7 +28,7 @@ constexpr int kBlockK = 64;          // bf16 elements per K-block = one 128-byte
 constexpr int kStageA = kTileM * 128;  // bytes of one A stage
 constexpr int kThreads = 192;
 constexpr int kLag = 2;              // gather arrivals trail the issue by this many stages
-constexpr unsigned kSpinLimit = 1u << 22;
+constexpr unsigned kSpinLimit = 1u << 20;
 
 enum : int { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccumWait = 3, kErrWeightWait = 4 };
 
@@ -115,6 +115,63 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                : "r"(taddr));
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+               : "memory");
+}
+
+// Gather one K-block (8 chunks of 16 bytes) of this thread's tile row.  CPT = 16-byte chunks per
+// tap (Cin / 8) when it is one of the specialised values, 0 = any (running counters).  Chunk c of
+// the row lands at position c ^ (row & 7): the 128-byte swizzle.
+template <int CPT>
+__device__ __forceinline__ void gather_block(const TcArgs& a, const int* nbr_col, int kb,
+                                             uint32_t dst_row, uint32_t sw, int& t_run,
+                                             int& cc_run) {
+  const char* xb = reinterpret_cast<const char*>(a.x);
+  const uint32_t row_bytes = (uint32_t)a.cin * 2u;
+  if constexpr (CPT >= 8) {
+    // the whole K-block reads one neighbour row
+    constexpr int kBlocksPerTap = CPT / 8;
+    const int t = kb / kBlocksPerTap;
+    const int p = t < a.T ? nbr_col[t * kTileM] : -1;
+    const char* src = xb;
+    if (p >= 0) src = xb + (size_t)((uint32_t)p * row_bytes) + (kb % kBlocksPerTap) * 128;
+    const uint32_t bytes = p >= 0 ? 16u : 0u;
+    const uint32_t step = p >= 0 ? 16u : 0u;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) cp_async16(dst_row + (((uint32_t)c ^ sw) << 4), src + c * step, bytes);
+  } else if constexpr (CPT > 0) {
+    constexpr int kTapsPerBlock = 8 / CPT;
+#pragma unroll
+    for (int j = 0; j < kTapsPerBlock; ++j) {
+      const int t = kb * kTapsPerBlock + j;
+      const int p = t < a.T ? nbr_col[t * kTileM] : -1;
+      const char* src = xb;
+      if (p >= 0) src = xb + (size_t)((uint32_t)p * row_bytes);
+      const uint32_t bytes = p >= 0 ? 16u : 0u;
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        const int c = j * CPT + cc;
+        cp_async16(dst_row + (((uint32_t)c ^ sw) << 4), p >= 0 ? src + cc * 16 : xb, bytes);
+      }
+    }
+  } else {
+    const int cpt = a.cin >> 3;
+    int p = t_run < a.T ? nbr_col[t_run * kTileM] : -1;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const char* src = p >= 0 ? xb + (size_t)((uint32_t)p * row_bytes) + cc_run * 16 : xb;
+      cp_async16(dst_row + (((uint32_t)c ^ sw) << 4), src, p >= 0 ? 16u : 0u);
+      if (++cc_run == cpt) {
+        cc_run = 0;
+        ++t_run;
+        p = t_run < a.T ? nbr_col[t_run * kTileM] : -1;
+      }
+    }
+  }
+}
+
+template <int CPT>
 __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of address bits [4,10)
@@ -150,15 +207,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   }
   if (tid < kTileM) {
     const int h = h0 + tid;
+    const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
     for (int t = 0; t < a.T; ++t) {
       int p = -1;
       if (h < a.h_out) {
         if (a.identity) {
           p = h;
         } else {
-          const int tap = a.tap[t];
-          const long long at = a.stride == 2 ? ((long long)h << 6) + ni333(0, tap)
-                                             : ((long long)(h >> 3) << 6) + ni333(h & 7, tap);
+          // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
+          // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
+          const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
+                                             : ((long long)(h >> 3) << 6) + a.tap[t] + oct_code;
           p = a.neigh[at];
         }
       }
@@ -173,48 +232,34 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   if (warp < 4) {
     // ---------------- A gather: thread = tile row ----------------
     const int r = tid;
-    const int cpt = a.cin >> 3;                 // 16-byte chunks per tap
     const uint32_t row_off = (uint32_t)r * 128u;
     const uint32_t sw = (uint32_t)(r & 7);
+    const int* nbr_col = nbr + r;
     bool alive = true;
+    int s = 0, s_arr = 0, t_run = 0, cc_run = 0;
+    uint32_t pe = 1;                       // parity of the next empty[] wait, flips per ring turn
     for (int kb = 0; kb < a.nkb; ++kb) {
-      const int s = kb % a.stages;
       if (alive && kb >= a.stages)
-        alive = mbar_wait(smem_u32(&empty[s]), (uint32_t)(((kb / a.stages) - 1) & 1), abort_flag,
-                          a.status, kErrEmptyWait);
-      if (alive) {
-        const uint32_t dst_row = smem_u32(sA + s * kStageA) + row_off;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int q = kb * 8 + c;
-          const int t = q / cpt;
-          const __nv_bfloat16* src = a.x;
-          uint32_t bytes = 0;
-          if (t < a.T) {
-            const int p = nbr[t * kTileM + r];
-            if (p >= 0) {
-              src = a.x + (long long)p * a.cin + ((q - t * cpt) << 3);
-              bytes = 16;
-            }
-          }
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                           dst_row + (((uint32_t)c ^ sw) << 4)), "l"(src), "r"(bytes)
-                       : "memory");
-        }
-      }
+        alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
+      if (alive)
+        gather_block<CPT>(a, nbr_col, kb, smem_u32(sA + s * kStageA) + row_off, sw, t_run, cc_run);
       asm volatile("cp.async.commit_group;" ::: "memory");
       if (kb >= kLag) {
         asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
         // the gathered bytes were written through the generic proxy; the tensor core reads
         // shared memory through the async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(smem_u32(&full[(kb - kLag) % a.stages]));
+        mbar_arrive(smem_u32(&full[s_arr]));
+        if (++s_arr == a.stages) s_arr = 0;
       }
+      if (++s == a.stages) { s = 0; pe ^= 1u; }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int kb = (a.nkb > kLag ? a.nkb - kLag : 0); kb < a.nkb; ++kb)
-      mbar_arrive(smem_u32(&full[kb % a.stages]));
+    for (int kb = (a.nkb > kLag ? a.nkb - kLag : 0); kb < a.nkb; ++kb) {
+      mbar_arrive(smem_u32(&full[s_arr]));
+      if (++s_arr == a.stages) s_arr = 0;
+    }
 
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     if (alive) alive = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, kErrAccumWait);
@@ -266,10 +311,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.npad >> 3) << 17) |
                              ((uint32_t)(kTileM >> 4) << 24);
       bool alive = true;
+      int s = 0;
+      uint32_t pf = 0;
       for (int kb = 0; kb < a.nkb && alive; ++kb) {
-        const int s = kb % a.stages;
-        alive = mbar_wait(smem_u32(&full[s]), (uint32_t)((kb / a.stages) & 1), abort_flag, a.status,
-                          kErrFullWait);
+        alive = mbar_wait(smem_u32(&full[s]), pf, abort_flag, a.status, kErrFullWait);
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(sA + s * kStageA);
@@ -280,6 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
                     idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
         }
         umma_commit(smem_u32(&empty[s]));     // stage reusable once these MMAs retire
+        if (++s == a.stages) { s = 0; pf ^= 1u; }
       }
       if (alive) umma_commit(smem_u32(accum));
     }
@@ -287,11 +333,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     // ---------------- weight tiles: one thread, one bulk copy per K-block ----------------
     if (lane == 0) {
       bool alive = true;
+      int s = 0;
+      uint32_t pe = 1;
       for (int kb = 0; kb < a.nkb && alive; ++kb) {
-        const int s = kb % a.stages;
         if (kb >= a.stages)
-          alive = mbar_wait(smem_u32(&empty[s]), (uint32_t)(((kb / a.stages) - 1) & 1), abort_flag,
-                            a.status, kErrWeightWait);
+          alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrWeightWait);
         if (!alive) break;
         const uint32_t bar = smem_u32(&full[s]);
         mbar_arrive_expect_tx(bar, (uint32_t)stage_b);
@@ -300,6 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
             ::"r"(smem_u32(sB + s * stage_b)), "l"(a.wpacked + (size_t)kb * stage_b),
               "r"((uint32_t)stage_b), "r"(bar)
             : "memory");
+        if (++s == a.stages) { s = 0; pe ^= 1u; }
       }
     }
   }
@@ -425,17 +472,37 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.relu = ep ? ep->relu : 0;
   a.status = status;
   const TapList tl = taps_for_kernel(kernel_size);
-  for (int i = 0; i < 27; ++i) a.tap[i] = i < tl.count ? tl.tap[i] : 0;
+  for (int i = 0; i < 27; ++i) {
+    const int tap = i < tl.count ? tl.tap[i] : 0;
+    a.tap[i] = (signed char)(((tap / 9) << 4) | (((tap / 3) % 3) << 2) | (tap % 3));
+  }
   // raising the dynamic shared memory limit is per function and per device
   static bool attr_set[64] = {};
   int device = 0;
   OCNN_CUDA_OK(cudaGetDevice(&device));
+  void (*kernel)(const TcArgs) = conv_tc_kernel<0>;
+  switch (cin >> 3) {
+    case 1: kernel = conv_tc_kernel<1>; break;
+    case 2: kernel = conv_tc_kernel<2>; break;
+    case 4: kernel = conv_tc_kernel<4>; break;
+    case 8: kernel = conv_tc_kernel<8>; break;
+    case 16: kernel = conv_tc_kernel<16>; break;
+    case 32: kernel = conv_tc_kernel<32>; break;
+    case 64: kernel = conv_tc_kernel<64>; break;
+    default: break;
+  }
   if (device < 0 || device >= 64 || !attr_set[device]) {
-    OCNN_CUDA_OK(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      200 * 1024));
+    void (*all[])(const TcArgs) = {conv_tc_kernel<0>, conv_tc_kernel<1>, conv_tc_kernel<2>,
+                                   conv_tc_kernel<4>, conv_tc_kernel<8>, conv_tc_kernel<16>,
+                                   conv_tc_kernel<32>, conv_tc_kernel<64>};
+    for (auto k : all)
+      OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     if (device >= 0 && device < 64) attr_set[device] = true;
   }
-  conv_tc_kernel<<<ceil_div(h_out, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
+  OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
+               "ocnn_octree_conv_tc: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses",
+               (long long)h_in * cin * 2);
+  kernel<<<ceil_div(h_out, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
   OCNN_LAUNCH_OK("conv_tc_kernel");
   return OCNN_OK;
 }
