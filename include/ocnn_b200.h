@@ -233,6 +233,24 @@ int ocnn_octree_batch(const void* const* octrees_dev, const ocnn_octree_meta* he
                       void* workspace_dev, size_t workspace_bytes, void* out_dev,
                       void* header_host_out /* OCNN_HEADER_BYTES or NULL */, void* stream);
 
+/* octree_batch for callers that cannot provide device scratch (no counterpart in the reference:
+ * its merge runs on the CPU).  Same arguments and result as ocnn_octree_batch, minus the
+ * workspace: the small (octree, level) table the merge kernel reads is kept in a fixed array built
+ * into the library's device image, so the call performs no device (or host heap) allocation.
+ * Use it from code that must not allocate at that point — e.g. while a framework allocator owns
+ * all device memory and a fresh cudaMalloc would fail.
+ *  - Limit: batch * (depth + 1) <= 2048; larger requests fail with OCNN_ERR_CAPACITY.  The array
+ *    (144 KiB) is held on every GPU that loads the library until the process exits.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call before starting any stream capture.
+ *  - All calls share the one array.  Each call rewrites every table entry it uses, so stale
+ *    contents are harmless, but two calls whose kernels overlap on the GPU (different streams)
+ *    race on it: issue them on one stream or order them with events. */
+int ocnn_octree_batch_noalloc(const void* const* octrees_dev, const ocnn_octree_meta* headers_host,
+                              const void* first_header_host, int batch,
+                              const ocnn_octree_meta* merged, void* out_dev,
+                              void* header_host_out /* OCNN_HEADER_BYTES or NULL */, void* stream);
+
 /* Feature block of the finest level (fp32 [C, nnum] channel-major, as stored in the octree) to the
  * bf16 node-major tensor [nnum, c_pad] the tensor-core convolution reads (channels >= C are 0).
  * Replaces the octree_property('feature') copy, pytorch/cpp/octree_property.cpp:89-97. */

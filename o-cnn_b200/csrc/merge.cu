@@ -4,6 +4,7 @@
 // rebased by the running non-empty count, features re-interleaved so each channel row spans the
 // whole batch level.
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "header.h"
@@ -195,3 +196,121 @@ int ocnn_octree_batch(const void* const* octrees_dev, const ocnn_octree_meta* in
 
 
 }  // extern "C"
+
+// ---- octree_batch without any caller-provided or allocated scratch ----------------------------
+// The (octree, level) table that merge_kernel reads lives in a fixed array inside this library's
+// device image instead of in a workspace the caller hands over.  Meant for callers that cannot get
+// device memory at the moment of the call: code running while a stream is being captured into a
+// CUDA graph (cudaMalloc is not allowed there), or a process whose framework allocator has already
+// claimed the whole GPU so that a fresh cudaMalloc fails.
+namespace ocnn {
+namespace {
+
+constexpr int kStaticMergeEntries = 2048;   // (octree, level) pairs: batch * (depth + 1) <= 2048
+static __device__ __align__(256) unsigned char g_merge_scratch[kStaticMergeEntries * sizeof(MergeEntry)];
+
+std::mutex g_static_mutex;
+MergeEntry g_static_stage[kStaticMergeEntries];   // host staging of the table, guarded by the mutex
+void* g_static_dev_ptr[64] = {};                  // device address of g_merge_scratch, per device
+
+}  // namespace
+}  // namespace ocnn
+
+extern "C" int ocnn_octree_batch_noalloc(const void* const* octrees_dev, const ocnn_octree_meta* in,
+                                         const void* first_header_host, int batch,
+                                         const ocnn_octree_meta* merged, void* out,
+                                         void* header_host_out, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(octrees_dev && in && first_header_host && merged && out && batch >= 1,
+               "ocnn_octree_batch_noalloc: null argument");
+  const int depth = merged->depth;
+  const long long pairs = (long long)batch * (depth + 1);
+  if (pairs > kStaticMergeEntries)
+    return fail(OCNN_ERR_CAPACITY,
+                "ocnn_octree_batch_noalloc: batch %d x (depth %d + 1) = %lld (octree, level) pairs "
+                "exceeds the built-in scratch of %d pairs; use ocnn_octree_batch with a workspace",
+                batch, depth, pairs, kStaticMergeEntries);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* o = static_cast<uint8_t*>(out);
+
+  // In host code the name g_merge_scratch is only a handle for the device array; the address a
+  // kernel can use comes from the runtime, once per device, with that device current.
+  int device = -1;
+  OCNN_CUDA_OK(cudaGetDevice(&device));
+  OCNN_REQUIRE(device >= 0 && device < 64, "ocnn_octree_batch_noalloc: device ordinal %d out of range",
+               device);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_dev_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    OCNN_CUDA_OK(cudaGetSymbolAddress(&ptr, g_merge_scratch));
+    OCNN_REQUIRE(ptr != nullptr, "ocnn_octree_batch_noalloc: no device address for the scratch array");
+    g_static_dev_ptr[device] = ptr;
+  }
+  MergeEntry* table_dev = static_cast<MergeEntry*>(g_static_dev_ptr[device]);
+
+  // merged header: the first octree's header with the batch fields replaced
+  // (MergeOctrees::set_batch_info, merge_octrees.cpp:92-106)
+  uint8_t hdr[OCNN_HEADER_BYTES];
+  memset(hdr, 0, sizeof(hdr));
+  memcpy(hdr, first_header_host, 716);
+  auto i32 = [&](int off) { return reinterpret_cast<int32_t*>(hdr + off); };
+  *i32(kOffBatch) = merged->batch_size;
+  int flags = 0;
+  for (int d = 0; d < OCNN_MAX_DEPTH; ++d) {
+    if (d <= depth) { i32(kOffNnum)[d] = merged->nnum[d]; i32(kOffNnumNempty)[d] = merged->nnum_nempty[d]; }
+    if (d <= depth + 2) i32(kOffNnumCum)[d] = merged->nnum_cum[d];
+  }
+  for (int p = 0; p < OCNN_PROP_COUNT; ++p) {
+    i32(kOffChannels)[p] = merged->channels[p];
+    if (merged->channels[p] != 0) { i32(kOffLocations)[p] = merged->locations[p]; flags |= 1 << p; }
+  }
+  for (int p = 0; p <= OCNN_PROP_COUNT; ++p) i32(kOffPtrDis)[p] = (int32_t)merged->ptr_dis[p];
+  *i32(kOffFlags) = flags;
+  if (header_host_out) memcpy(header_host_out, hdr, OCNN_HEADER_BYTES);
+  OCNN_CUDA_OK(cudaMemcpyAsync(o, hdr, OCNN_HEADER_BYTES, cudaMemcpyHostToDevice, st));
+
+  int ne = 0, max_n = 1;
+  for (int d = 0; d <= depth; ++d) {
+    int node0 = 0, ne0 = 0;
+    for (int b = 0; b < batch; ++b) {
+      const ocnn_octree_meta* m = &in[b];
+      MergeEntry e;
+      e.src = static_cast<const uint8_t*>(octrees_dev[b]);
+      e.key = at_level(m, OCNN_PROP_KEY, d) ? ocnn_prop_offset(m, OCNN_PROP_KEY, d) : -1;
+      e.child = at_level(m, OCNN_PROP_CHILD, d) ? ocnn_prop_offset(m, OCNN_PROP_CHILD, d) : -1;
+      e.feat = at_level(m, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(m, OCNN_PROP_FEATURE, d) : -1;
+      e.label = at_level(m, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(m, OCNN_PROP_LABEL, d) : -1;
+      e.split = at_level(m, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(m, OCNN_PROP_SPLIT, d) : -1;
+      e.n = m->nnum[d]; e.node0 = node0; e.ne0 = ne0; e.b = b; e.d = d;
+      if (e.n > 0) g_static_stage[ne++] = e;
+      if (e.n > max_n) max_n = e.n;
+      node0 += m->nnum[d];
+      ne0 += m->nnum_nempty[d];
+    }
+  }
+  MergeDst dst;
+  memset(&dst, 0, sizeof(dst));
+  dst.out = o;
+  dst.key_bytes = merged->key_bits / 8;
+  dst.cfeat = merged->channels[OCNN_PROP_FEATURE];
+  for (int d = 0; d <= depth; ++d) {
+    dst.key[d] = ocnn_prop_offset(merged, OCNN_PROP_KEY, d);
+    dst.child[d] = ocnn_prop_offset(merged, OCNN_PROP_CHILD, d);
+    dst.feat[d] = at_level(merged, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(merged, OCNN_PROP_FEATURE, d) : -1;
+    dst.label[d] = at_level(merged, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(merged, OCNN_PROP_LABEL, d) : -1;
+    dst.split[d] = at_level(merged, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(merged, OCNN_PROP_SPLIT, d) : -1;
+    dst.nnum[d] = merged->nnum[d];
+  }
+  if (ne > 0) {
+    // Only the first `ne` entries are read by the kernel and all of them are rewritten here, so
+    // nothing left over from an earlier call needs clearing.  The staging array is pageable
+    // memory: the runtime has copied it out when cudaMemcpyAsync returns, which is what lets the
+    // mutex be released at the end of this function.
+    OCNN_CUDA_OK(cudaMemcpyAsync(table_dev, g_static_stage, sizeof(MergeEntry) * (size_t)ne,
+                                 cudaMemcpyHostToDevice, st));
+    dim3 grid(ceil_div(max_n, 256) < 64 ? ceil_div(max_n, 256) : 64, ne < 4096 ? ne : 4096);
+    merge_kernel<<<grid, 256, 0, st>>>(table_dev, ne, dst);
+    OCNN_LAUNCH_OK("merge_kernel (built-in scratch)");
+  }
+  return ocnn_calc_neigh(out, merged, stream);
+}
