@@ -157,10 +157,12 @@ int ocnn_octree_conv(const void* x_dev, const float* weights_dev, void* y_dev,
                      const int kernel_size[3], int stride, int dtype, int layout,
                      const ocnn_conv_epilogue* epilogue, void* stream);
 
-/* Tensor-core path: weights packed once per layer into bf16 K-major tiles. */
-size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3]);
+/* Tensor-core path: weights packed once per layer into bf16 K-major tiles.  The packed image
+ * depends on the kernel shape AND the stride the layer will run with (stride-1 neighbourhood
+ * convolutions with few channels use a per-sibling-group formulation with expanded weights). */
+size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride);
 int ocnn_conv_pack_weights(const float* weights_dev, void* packed_dev, int cin, int cout,
-                           const int kernel_size[3], void* stream);
+                           const int kernel_size[3], int stride, void* stream);
 /* x, y: bf16 node-major ([h, C]); cin % 8 == 0, cout % 8 == 0, cout <= 256.
  * status_dev: one int32 in device memory, zero before the call; a kernel that gives up on a
  * bounded wait writes a non-zero code there instead of hanging. */

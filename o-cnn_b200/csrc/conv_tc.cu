@@ -10,6 +10,15 @@
 // contiguous chunk per K-block, fetched with one bulk async copy.  Accumulators live in TMEM and
 // are read back by the four epilogue warps with tcgen05.ld.
 //
+// Sibling-group mode (stride 1, more than one tap, Cin <= 32, Cout <= 32): the eight nodes of a
+// sibling group share one 4x4x4 neighbour block, so gathering per node reads each of its 64 rows
+// 3.4 times (8 x 27 = 216 reads).  Here a tile ROW is a whole group: A row = the group's 64
+// neighbour rows back to back (K = 64*Cin, read once, indices straight from the neighbour block),
+// B = the weights expanded to [64*Cin, 8*Cout] with zeros where a block position is outside an
+// octant's 3x3x3 window, D row = the group's 8 output nodes x Cout, which is exactly the group's
+// contiguous stretch of the node-major output.  2.4x the flops (the tensor core idles anyway at
+// these channel counts) for 3.4x fewer gathers and a tile of 1024 nodes instead of 128.
+//
 // Warp roles (192 threads): warps 0-3 gather A (one tile row per thread) and later run the
 // epilogue (TMEM lane quarter = warp id); warp 4 allocates TMEM and its lane 0 issues the MMAs;
 // lane 0 of warp 5 streams the weight tiles.  A 4-stage ring of {A tile, B tile} buffers is
@@ -38,6 +47,9 @@ struct TcArgs {
   __nv_bfloat16* y;
   const int* neigh;
   int h_in, h_out, cin, cout, npad, T, stride, identity, nkb, stages, tmem_cols;
+  int group;        // 1: tile rows are sibling groups (see the header comment), 0: nodes
+  int rows;         // number of tile rows in total: h_out, or h_out / 8 in group mode
+  int row_elems;    // output elements per tile row: cout, or 8 * cout in group mode
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -206,22 +218,35 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid < kTileM) {
-    const int h = h0 + tid;
-    const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
-    for (int t = 0; t < a.T; ++t) {
-      int p = -1;
-      if (h < a.h_out) {
-        if (a.identity) {
-          p = h;
-        } else {
-          // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
-          // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
-          const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
-                                             : ((long long)(h >> 3) << 6) + a.tap[t] + oct_code;
-          p = a.neigh[at];
-        }
+    const int h = h0 + tid;          // node, or sibling group in group mode
+    if (a.group) {
+      // the group's neighbour block IS the list of rows to gather: 64 contiguous ints
+      if (h < a.rows) {
+        // (a level's neighbour table is only 4-byte aligned inside the octree buffer: the blocks
+        // before it hold B + 8B + ... entries, so no vector loads here)
+        const int* blk = a.neigh + ((long long)h << 6);
+#pragma unroll 8
+        for (int t = 0; t < 64; ++t) nbr[t * kTileM + tid] = blk[t];
+      } else {
+        for (int t = 0; t < 64; ++t) nbr[t * kTileM + tid] = -1;
       }
-      nbr[t * kTileM + tid] = p;
+    } else {
+      const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
+      for (int t = 0; t < a.T; ++t) {
+        int p = -1;
+        if (h < a.rows) {
+          if (a.identity) {
+            p = h;
+          } else {
+            // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
+            // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
+            const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
+                                               : ((long long)(h >> 3) << 6) + a.tap[t] + oct_code;
+            p = a.neigh[at];
+          }
+        }
+        nbr[t * kTileM + tid] = p;
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -272,15 +297,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
         uint32_t v[8];
         tmem_ld8(lane_base + (uint32_t)n0, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (h < a.h_out && n0 < a.cout) {
+        if (h < a.rows && n0 < a.row_elems) {
+          // output channel of column n0: columns are (octant, channel) pairs in group mode
+          const int co0 = a.group ? (n0 & (a.cout - 1)) : n0;
           float f[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             f[j] = __uint_as_float(v[j]);
-            if (a.scale) f[j] *= a.scale[n0 + j];
-            if (a.bias) f[j] += a.bias[n0 + j];
+            if (a.scale) f[j] *= a.scale[co0 + j];
+            if (a.bias) f[j] += a.bias[co0 + j];
           }
-          const long long at = (long long)h * a.cout + n0;
+          const long long at = (long long)h * a.row_elems + n0;
           if (a.residual) {
             const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
             const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
@@ -385,21 +412,59 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, __nv_bfloat16* 
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages; size_t smem; };
+// Group mode: B[k][n], k = j*cin + ci over the 64 block positions j, n = o*cout + co over the
+// 8 octants: W[co, ci*T + t] where tap t of the kernel sits at block position j for octant o
+// (j = ((tx+ox)<<4)|((ty+oy)<<2)|(tz+oz)), zero elsewhere.  Same swizzled tile image as above.
+struct TapsArg { int count; signed char tap[27]; };
 
-int tc_shape(int cin, int cout, const int ks[3], TcShape* s) {
+__global__ void pack_weights_group_kernel(const float* __restrict__ w,
+                                          __nv_bfloat16* __restrict__ packed, int cin, int cout,
+                                          int T, TapsArg taps, int npad, int nkb) {
+  const long long total = (long long)nkb * npad * kBlockK;
+  const int KD = cin * T;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int kk = (int)(i % kBlockK);
+    const int n = (int)((i / kBlockK) % npad);
+    const int kb = (int)(i / ((long long)kBlockK * npad));
+    const int k = kb * kBlockK + kk;
+    const int j = k / cin, ci = k % cin;
+    const int o = n / cout, co = n % cout;
+    float v = 0.f;
+    if (j < 64 && o < 8) {
+      const int tx = (j >> 4) - (o >> 2), ty = ((j >> 2) & 3) - ((o >> 1) & 1), tz = (j & 3) - (o & 1);
+      if (tx >= 0 && tx < 3 && ty >= 0 && ty < 3 && tz >= 0 && tz < 3) {
+        const int tap27 = tx * 9 + ty * 3 + tz;
+        for (int t = 0; t < T; ++t)
+          if (taps.tap[t] == tap27) v = w[(long long)co * KD + ci * T + t];
+      }
+    }
+    const long long off = (long long)kb * npad * 64 + (n >> 3) * 512 + (n & 7) * 64 +
+                          (((kk >> 3) ^ (n & 7)) << 3) + (kk & 7);
+    packed[off] = __float2bfloat16(v);
+  }
+}
+
+struct TcShape { int T, npad, nkb, tmem_cols, stages, group; size_t smem; };
+
+int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
   const TapList tl = taps_for_kernel(ks);
   if (tl.count < 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported kernel size %dx%dx%d",
                 ks[0], ks[1], ks[2]);
+  if (stride != 1 && stride != 2)
+    return fail(OCNN_ERR_INVALID, "tensor-core convolution: stride must be 1 or 2 (got %d)", stride);
   if (cin <= 0 || cin % 8 != 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: Cin (%d) must be a multiple of 8", cin);
   if (cout <= 0 || cout % 8 != 0 || cout > 256)
     return fail(OCNN_ERR_UNSUPPORTED,
                 "tensor-core convolution: Cout (%d) must be a multiple of 8, at most 256", cout);
-  s->T = tl.count;
-  s->npad = (cout + 15) / 16 * 16;
-  s->nkb = (cin * tl.count + kBlockK - 1) / kBlockK;
+  // sibling-group mode: stride 1, a real neighbourhood, few channels (power-of-two Cout so that
+  // column -> channel is a mask)
+  s->group = (stride == 1 && tl.count > 1 && cin <= 32 && cout <= 32 && (cout & (cout - 1)) == 0) ? 1 : 0;
+  s->T = s->group ? 64 : tl.count;
+  s->npad = s->group ? 8 * cout : (cout + 15) / 16 * 16;
+  s->nkb = (cin * s->T + kBlockK - 1) / kBlockK;
   s->tmem_cols = 32;
   while (s->tmem_cols < s->npad) s->tmem_cols *= 2;
   s->stages = s->npad > 128 ? 3 : 4;
@@ -414,19 +479,27 @@ int tc_shape(int cin, int cout, const int ks[3], TcShape* s) {
 
 extern "C" {
 
-size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3]) {
+size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride) {
   ocnn::TcShape s;
-  if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, &s) != OCNN_OK) return 0;
+  if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, stride, &s) != OCNN_OK) return 0;
   return (size_t)s.nkb * s.npad * 128;
 }
 
 int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
-                           void* stream) {
+                           int stride, void* stream) {
   using namespace ocnn;
   OCNN_REQUIRE(w && packed && kernel_size, "ocnn_conv_pack_weights: null pointer");
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, &s)) return st;
+  if (int st = tc_shape(cin, cout, kernel_size, stride, &s)) return st;
   const long long total = (long long)s.nkb * s.npad * kBlockK;
+  if (s.group) {
+    const TapList tl = taps_for_kernel(kernel_size);
+    TapsArg ta;
+    ta.count = tl.count;
+    for (int i = 0; i < 27; ++i) ta.tap[i] = i < tl.count ? tl.tap[i] : -1;
+    pack_weights_group_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        w, static_cast<__nv_bfloat16*>(packed), cin, cout, tl.count, ta, s.npad, s.nkb);
+  } else
   pack_weights_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       w, static_cast<__nv_bfloat16*>(packed), cin, cout, s.T, s.npad, s.nkb);
   OCNN_LAUNCH_OK("pack_weights_kernel");
@@ -440,7 +513,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_tc: null kernel size");
   OCNN_REQUIRE(stride == 1 || stride == 2, "ocnn_octree_conv_tc: stride must be 1 or 2 (got %d)", stride);
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, &s)) return st;
+  if (int st = tc_shape(cin, cout, kernel_size, stride, &s)) return st;
   OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv_tc: negative height");
   if (h_out == 0) return OCNN_OK;
   const bool identity = s.T == 1 && stride == 1;
@@ -466,6 +539,12 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout; a.npad = s.npad; a.T = s.T;
   a.stride = stride; a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
   a.tmem_cols = s.tmem_cols;
+  a.group = s.group;
+  a.rows = s.group ? h_out / 8 : h_out;
+  a.row_elems = s.group ? 8 * cout : cout;
+  if (s.group)
+    OCNN_REQUIRE(h_out % 8 == 0, "ocnn_octree_conv_tc: an octree level holds whole sibling groups "
+                 "(got %d nodes)", h_out);
   a.scale = ep ? ep->scale_dev : nullptr;
   a.bias = ep ? ep->bias_dev : nullptr;
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
@@ -496,13 +575,13 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
                                    conv_tc_kernel<4>, conv_tc_kernel<8>, conv_tc_kernel<16>,
                                    conv_tc_kernel<32>, conv_tc_kernel<64>};
     for (auto k : all)
-      OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     if (device >= 0 && device < 64) attr_set[device] = true;
   }
   OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
                "ocnn_octree_conv_tc: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses",
                (long long)h_in * cin * 2);
-  kernel<<<ceil_div(h_out, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
+  kernel<<<ceil_div(a.rows, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
   OCNN_LAUNCH_OK("conv_tc_kernel");
   return OCNN_OK;
 }

@@ -334,20 +334,20 @@ Tensor octree_conv(Tensor data_in, Tensor weights, Tensor octree, int depth, int
                            c10::nullopt, c10::nullopt, c10::nullopt, false);
 }
 
-Tensor conv_pack_weights(Tensor weights, int cin, int cout, vector<int> kernel_size) {
+Tensor conv_pack_weights(Tensor weights, int cin, int cout, vector<int> kernel_size, int stride) {
   vector<int> ks = kernel3(kernel_size);
   TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32,
               "weights must be a float32 CUDA tensor");
   const int kdim = ks[0] * ks[1] * ks[2];
   TORCH_CHECK(weights.numel() == (int64_t)cout * cin * kdim, "weights must have Cout*Cin*K values");
   c10::cuda::CUDAGuard guard(weights.device());
-  const size_t bytes = ocnn_conv_packed_weight_bytes(cin, cout, ks.data());
+  const size_t bytes = ocnn_conv_packed_weight_bytes(cin, cout, ks.data(), stride);
   TORCH_CHECK(bytes > 0, "this shape is not supported by the tensor-core convolution: ",
               ocnn_last_error());
   Tensor packed = torch::empty({(int64_t)bytes}, weights.options().dtype(torch::kUInt8));
   Tensor w = weights.contiguous();
   OCNN_CALL(ocnn_conv_pack_weights(w.data_ptr<float>(), packed.data_ptr(), cin, cout, ks.data(),
-                                   current_stream()));
+                                   stride, current_stream()));
   return packed;
 }
 
@@ -366,7 +366,8 @@ Tensor octree_conv_tc(Tensor data_in, Tensor packed, Tensor octree, int depth, i
   x.layout = OCNN_NODE_MAJOR;
   ConvShape s = conv_shape(o, x, depth, ks, stride, "octree_conv_tc");
   TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
-                  (size_t)packed.numel() == ocnn_conv_packed_weight_bytes(x.C, num_output, ks.data()),
+                  (size_t)packed.numel() ==
+                      ocnn_conv_packed_weight_bytes(x.C, num_output, ks.data(), stride),
               "packed weights do not match this convolution's shape");
   TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32 && status.numel() >= 1,
               "status must be an int32 CUDA tensor");
@@ -767,7 +768,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
         py::arg("stride"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("relu") = false);
-  m.def("conv_pack_weights", &conv_pack_weights);
+  m.def("conv_pack_weights", &conv_pack_weights, py::arg("weights"), py::arg("cin"), py::arg("cout"),
+        py::arg("kernel_size"), py::arg("stride") = 1);
   m.def("octree_conv_tc", &octree_conv_tc, py::arg("data_in"), py::arg("packed"), py::arg("octree"),
         py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"), py::arg("stride"),
         py::arg("scale") = py::none(), py::arg("bias") = py::none(),

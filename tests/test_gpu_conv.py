@@ -145,6 +145,9 @@ TC_CASES = [
     (5, 16, 32, [2, 2, 2], 2),
     (5, 16, 32, [3, 3, 3], 2),
     (4, 32, 16, [3, 1, 3], 1),
+    (5, 24, 8, [3, 3, 3], 1),      # sibling-group mode with 3 chunks per neighbour row
+    (6, 8, 16, [2, 2, 2], 1),
+    (5, 32, 32, [1, 3, 3], 1),
 ]
 
 
@@ -159,7 +162,7 @@ def test_conv_tensor_core(ocnn, batch, case):
   w = rng.normal(scale=0.1, size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
   wt = torch.from_numpy(w).cuda()
   status = torch.zeros(1, dtype=torch.int32, device='cuda')
-  packed = ocnn.nn.conv_pack_weights(wt, cin, cout, ks)
+  packed = ocnn.nn.conv_pack_weights(wt, cin, cout, ks, stride)
   got = ocnn.nn.octree_conv_tc(gu.data_cuda(x, True, True), packed, octree, d, cout, ks, stride,
                                None, None, None, False, status)
   torch.cuda.synchronize()
