@@ -36,7 +36,6 @@ constexpr int kTileM = 128;          // nodes per CTA = TMEM lanes
 constexpr int kBlockK = 64;          // bf16 elements per K-block = one 128-byte swizzle row
 constexpr int kStageA = kTileM * 128;  // bytes of one A stage
 constexpr int kThreads = 192;
-constexpr int kLag = 2;              // gather arrivals trail the issue by this many stages
 constexpr unsigned kSpinLimit = 1u << 20;
 
 enum : int { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccumWait = 3, kErrWeightWait = 4 };
@@ -47,6 +46,7 @@ struct TcArgs {
   __nv_bfloat16* y;
   const int* neigh;
   int h_in, h_out, cin, cout, npad, T, stride, identity, nkb, stages, tmem_cols;
+  int lag;          // gather arrivals trail the issue by this many K-blocks (1 or 2, < stages)
   int group;        // 1: tile rows are sibling groups (see the header comment), 0: nodes
   int rows;         // number of tile rows in total: h_out, or h_out / 8 in group mode
   int row_elems;    // output elements per tile row: cout, or 8 * cout in group mode
@@ -135,8 +135,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 // Gather one K-block (8 chunks of 16 bytes) of this thread's tile row.  CPT = 16-byte chunks per
 // tap (Cin / 8) when it is one of the specialised values, 0 = any (running counters).  Chunk c of
 // the row lands at position c ^ (row & 7): the 128-byte swizzle.
+// nbr_col[t * nbr_stride] is the row to read for tap t: a column of the shared-memory table in
+// node mode (stride 128), the group's own 64-int neighbour block in global memory in group mode
+// (stride 1).
 template <int CPT>
-__device__ __forceinline__ void gather_block(const TcArgs& a, const int* nbr_col, int kb,
+__device__ __forceinline__ void gather_block(const TcArgs& a, const int* __restrict__ nbr_col,
+                                             const int nbr_stride, const int T, int kb,
                                              uint32_t dst_row, uint32_t sw, int& t_run,
                                              int& cc_run) {
   const char* xb = reinterpret_cast<const char*>(a.x);
@@ -145,7 +149,7 @@ __device__ __forceinline__ void gather_block(const TcArgs& a, const int* nbr_col
     // the whole K-block reads one neighbour row
     constexpr int kBlocksPerTap = CPT / 8;
     const int t = kb / kBlocksPerTap;
-    const int p = t < a.T ? nbr_col[t * kTileM] : -1;
+    const int p = t < T ? nbr_col[t * nbr_stride] : -1;
     const char* src = xb;
     if (p >= 0) src = xb + (size_t)((uint32_t)p * row_bytes) + (kb % kBlocksPerTap) * 128;
     const uint32_t bytes = p >= 0 ? 16u : 0u;
@@ -154,10 +158,15 @@ __device__ __forceinline__ void gather_block(const TcArgs& a, const int* nbr_col
     for (int c = 0; c < 8; ++c) cp_async16(dst_row + (((uint32_t)c ^ sw) << 4), src + c * step, bytes);
   } else if constexpr (CPT > 0) {
     constexpr int kTapsPerBlock = 8 / CPT;
+    int pj[kTapsPerBlock];
+#pragma unroll
+    for (int j = 0; j < kTapsPerBlock; ++j) {       // all index loads first, then the copies
+      const int t = kb * kTapsPerBlock + j;
+      pj[j] = t < T ? nbr_col[t * nbr_stride] : -1;
+    }
 #pragma unroll
     for (int j = 0; j < kTapsPerBlock; ++j) {
-      const int t = kb * kTapsPerBlock + j;
-      const int p = t < a.T ? nbr_col[t * kTileM] : -1;
+      const int p = pj[j];
       const char* src = xb;
       if (p >= 0) src = xb + (size_t)((uint32_t)p * row_bytes);
       const uint32_t bytes = p >= 0 ? 16u : 0u;
@@ -169,7 +178,7 @@ __device__ __forceinline__ void gather_block(const TcArgs& a, const int* nbr_col
     }
   } else {
     const int cpt = a.cin >> 3;
-    int p = t_run < a.T ? nbr_col[t_run * kTileM] : -1;
+    int p = t_run < T ? nbr_col[t_run * nbr_stride] : -1;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const char* src = p >= 0 ? xb + (size_t)((uint32_t)p * row_bytes) + cc_run * 16 : xb;
@@ -177,7 +186,7 @@ __device__ __forceinline__ void gather_block(const TcArgs& a, const int* nbr_col
       if (++cc_run == cpt) {
         cc_run = 0;
         ++t_run;
-        p = t_run < a.T ? nbr_col[t_run * kTileM] : -1;
+        p = t_run < T ? nbr_col[t_run * nbr_stride] : -1;
       }
     }
   }
@@ -192,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   uint8_t* sA = smem;
   uint8_t* sB = sA + a.stages * kStageA;
   int* nbr = reinterpret_cast<int*>(sB + a.stages * stage_b);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(nbr + a.T * kTileM);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(nbr + (a.group ? 0 : a.T * kTileM));
   uint64_t* full = bars;
   uint64_t* empty = bars + a.stages;
   uint64_t* accum = bars + 2 * a.stages;
@@ -220,16 +229,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   if (tid < kTileM) {
     const int h = h0 + tid;          // node, or sibling group in group mode
     if (a.group) {
-      // the group's neighbour block IS the list of rows to gather: 64 contiguous ints
-      if (h < a.rows) {
-        // (a level's neighbour table is only 4-byte aligned inside the octree buffer: the blocks
-        // before it hold B + 8B + ... entries, so no vector loads here)
-        const int* blk = a.neigh + ((long long)h << 6);
-#pragma unroll 8
-        for (int t = 0; t < 64; ++t) nbr[t * kTileM + tid] = blk[t];
-      } else {
-        for (int t = 0; t < 64; ++t) nbr[t * kTileM + tid] = -1;
-      }
+      // nothing to stage: the group's neighbour block IS the list of rows to gather, 64
+      // contiguous ints that the gather reads straight from global memory
     } else {
       const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
       for (int t = 0; t < a.T; ++t) {
@@ -259,7 +260,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     const int r = tid;
     const uint32_t row_off = (uint32_t)r * 128u;
     const uint32_t sw = (uint32_t)(r & 7);
-    const int* nbr_col = nbr + r;
+    // rows past the end of the level gather nothing (T = 0 makes every tap "missing")
+    const bool row_ok = h0 + r < a.rows;
+    const int* nbr_col = a.group ? a.neigh + ((long long)(row_ok ? h0 + r : 0) << 6) : nbr + r;
+    const int nbr_stride = a.group ? 1 : kTileM;
+    const int T = row_ok ? a.T : 0;
     bool alive = true;
     int s = 0, s_arr = 0, t_run = 0, cc_run = 0;
     uint32_t pe = 1;                       // parity of the next empty[] wait, flips per ring turn
@@ -267,10 +272,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       if (alive && kb >= a.stages)
         alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
       if (alive)
-        gather_block<CPT>(a, nbr_col, kb, smem_u32(sA + s * kStageA) + row_off, sw, t_run, cc_run);
+        gather_block<CPT>(a, nbr_col, nbr_stride, T, kb, smem_u32(sA + s * kStageA) + row_off, sw,
+                          t_run, cc_run);
       asm volatile("cp.async.commit_group;" ::: "memory");
-      if (kb >= kLag) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
+      if (kb >= a.lag) {
+        if (a.lag == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 2;" ::: "memory");
         // the gathered bytes were written through the generic proxy; the tensor core reads
         // shared memory through the async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int kb = (a.nkb > kLag ? a.nkb - kLag : 0); kb < a.nkb; ++kb) {
+    for (int kb = (a.nkb > a.lag ? a.nkb - a.lag : 0); kb < a.nkb; ++kb) {
       mbar_arrive(smem_u32(&full[s_arr]));
       if (++s_arr == a.stages) s_arr = 0;
     }
@@ -445,7 +452,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, group; size_t smem; };
+struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group; size_t smem; };
 
 int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
   const TapList tl = taps_for_kernel(ks);
@@ -467,10 +474,19 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
   s->nkb = (cin * s->T + kBlockK - 1) / kBlockK;
   s->tmem_cols = 32;
   while (s->tmem_cols < s->npad) s->tmem_cols *= 2;
-  s->stages = s->npad > 128 ? 3 : 4;
-  if (s->stages > s->nkb) s->stages = s->nkb < 2 ? 2 : s->nkb;
-  s->smem = 1024 + (size_t)s->stages * (kStageA + s->npad * 128) + (size_t)s->T * kTileM * 4 +
-            (2 * s->stages + 1) * 8 + 16;
+  // Ring depth.  Prefer a footprint that lets two CTAs share an SM (their set-up and epilogue
+  // phases then overlap each other's main loop); otherwise take what one CTA can hold.  The gather
+  // arrivals trail the issue by `lag` K-blocks, and the ring must be deeper than the lag.
+  const size_t stage_bytes = (size_t)kStageA + (size_t)s->npad * 128;
+  const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + 256;
+  const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
+  int st = two_cta > fixed ? (int)((two_cta - fixed) / stage_bytes) : 0;
+  if (st < 2 || 2 * s->tmem_cols > 512) st = (int)((one_cta - fixed) / stage_bytes);
+  if (st > 6) st = 6;
+  if (st > s->nkb) st = s->nkb < 2 ? 2 : s->nkb;
+  s->stages = st;
+  s->lag = st >= 3 ? 2 : 1;
+  s->smem = fixed + (size_t)s->stages * stage_bytes;
   return OCNN_OK;
 }
 
@@ -539,6 +555,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout; a.npad = s.npad; a.T = s.T;
   a.stride = stride; a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
   a.tmem_cols = s.tmem_cols;
+  a.lag = s.lag;
   a.group = s.group;
   a.rows = s.group ? h_out / 8 : h_out;
   a.row_elems = s.group ? 8 * cout : cout;
