@@ -297,23 +297,25 @@ def run_ours(args):
 
   sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
 
-  # ---- warm-up; the first warm-up step is instrumented per layer to find the dominant kernel ----
+  # ---- warm-up; one warm-up step is instrumented per layer to find the dominant kernel ----
   layer_ms = {}
   octree, logits = step_resident()
   torch.cuda.synchronize()
   info = ocnn.octree_info(octree)
   nnum = info[4:20]
-  net.trace = {}
+  net.exec.set_trace(-1)
   step_resident()
   torch.cuda.synchronize()
-  for name, evs in net.trace.items():
-    layer_ms[name] = sum(a.elapsed_time(b) for a, b in evs)
-  net.trace = None
-  top_layer = max(layer_ms, key=layer_ms.get)
+  for index, ms in net.exec.trace_ms():
+    layer_ms[net.exec_layers[index]] = ms
+  net.exec.set_trace(-2)
+  conv_names = {p['name'] for _, p in models.conv_layers(net.net)}
+  top_layer = max((k for k in layer_ms if k in conv_names), key=layer_ms.get)
+  top_index = net.exec_layers.index(top_layer)
   for _ in range(max(args.warmup, 3)):
     step_resident()
   torch.cuda.synchronize()
-  assert int(net.status.item()) == 0, 'a kernel reported an error status'
+  assert net.error_status() == 0, 'a kernel reported an error status'
 
   def timed(step_fn, steps):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
@@ -337,21 +339,22 @@ def run_ours(args):
     return total_ms
 
   # ---- timed region: K steps, inputs resident in HBM; only the dominant layer carries events ----
-  net.trace = {}
-  net.trace_only = top_layer
+  net.exec.set_trace(top_index)
   launches0 = ocnn.nn.launch_count()
+  t_host0 = time.perf_counter()
   total_ms = timed(step_resident, args.steps)
+  host_ms = (time.perf_counter() - t_host0) * 1e3
   launches = ocnn.nn.launch_count() - launches0
-  top_evs = net.trace.get(top_layer, [])
-  top_ms = statistics.mean(a.elapsed_time(b) for a, b in top_evs) if top_evs else None
-  net.trace, net.trace_only = None, None
+  top_times = [ms for _, ms in net.exec.trace_ms()]
+  top_ms = statistics.mean(top_times) if top_times else None
+  net.exec.set_trace(-2)
 
   # ---- end to end: pinned host points -> H2D -> build -> forward -> logits D2H ----
   for _ in range(3):
     step_e2e()
   e2e_ms = timed(step_e2e, args.steps)
   clocks = sampler.stop() if sampler else None
-  assert int(net.status.item()) == 0, 'a kernel reported an error status'
+  assert net.error_status() == 0, 'a kernel reported an error status'
 
   if world > 1:
     dist.destroy_process_group()
@@ -399,7 +402,7 @@ def run_ours(args):
           'gpu_launches': int(launches), 'clocks': clocks, 'roofline': roofline,
           'tensor_core_layers': sum(1 for _, p in models.conv_layers(net.net) if p.get('_packed') is not None),
           'layer_ms': {k: round(v, 4) for k, v in layer_ms.items()},
-          'finest_nodes': int(nnum[DEPTH])}
+          'finest_nodes': int(nnum[DEPTH]), 'host_ms_per_step_incl_flush': host_ms / args.steps}
 
   if world == 1:
     sample = max(1, min(args.cpu_sample, BATCH))

@@ -1,0 +1,155 @@
+// 1x1x1 octree convolution (a per-node matrix product) for node-major bf16 data with few
+// channels: the pointwise layers of the reference's bottleneck blocks
+// (pytorch/ocnn/modules.py:71-83, a torch Conv1d there).  With Cin, Cout <= 64 the arithmetic
+// intensity is a few flops per byte, so the kernel is a pure HBM stream: every thread owns ROWS
+// whole node rows (16-byte loads), keeps Cout fp32 accumulators per row in registers, reads the
+// fp32 weights as shared-memory broadcasts, applies the fused epilogue and writes 16-byte pieces.
+// Algorithmic bytes per node: (Cin + Cout [+ Cout residual]) * 2.
+#include "common.cuh"
+
+namespace ocnn {
+namespace {
+
+struct PwArgs {
+  const __nv_bfloat16* x;
+  const float* w;          // [cout, cin], the reference layout
+  __nv_bfloat16* y;
+  int h, cin;
+  const float* scale;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  int relu;
+};
+
+template <int COUT, int ROWS>
+__global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
+  extern __shared__ float ws[];                      // [cin][COUT]
+  for (int i = threadIdx.x; i < a.cin * COUT; i += blockDim.x) {
+    const int co = i / a.cin, ci = i % a.cin;        // coalesced read of w[co][ci], transposed store
+    ws[ci * COUT + co] = a.w[i];
+  }
+  __syncthreads();
+  const int chunks = a.cin >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // thread t of the grid handles rows t, t + stride, ... in packets of ROWS rows spaced by the
+  // grid size, so that a warp always touches 32 consecutive rows
+  for (long long h0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; h0 < a.h; h0 += stride * ROWS) {
+    float acc[ROWS][COUT];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+      for (int co = 0; co < COUT; ++co) acc[r][co] = 0.f;
+    for (int c8 = 0; c8 < chunks; ++c8) {
+      float xv[ROWS][8];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const long long h = h0 + r * stride;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (h < a.h) raw = reinterpret_cast<const uint4*>(a.x + h * a.cin)[c8];
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(p[k]);
+          xv[r][2 * k] = f.x;
+          xv[r][2 * k + 1] = f.y;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float4* wrow = reinterpret_cast<const float4*>(ws + (c8 * 8 + k) * COUT);
+#pragma unroll
+        for (int q = 0; q < COUT / 4; ++q) {
+          const float4 wv = wrow[q];
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            acc[r][4 * q + 0] = fmaf(xv[r][k], wv.x, acc[r][4 * q + 0]);
+            acc[r][4 * q + 1] = fmaf(xv[r][k], wv.y, acc[r][4 * q + 1]);
+            acc[r][4 * q + 2] = fmaf(xv[r][k], wv.z, acc[r][4 * q + 2]);
+            acc[r][4 * q + 3] = fmaf(xv[r][k], wv.w, acc[r][4 * q + 3]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const long long h = h0 + r * stride;
+      if (h >= a.h) continue;
+#pragma unroll
+      for (int q = 0; q < COUT / 8; ++q) {
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          f[j] = acc[r][8 * q + j];
+          if (a.scale) f[j] *= a.scale[8 * q + j];
+          if (a.bias) f[j] += a.bias[8 * q + j];
+        }
+        const long long at = h * COUT + 8 * q;
+        if (a.residual) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 rf = __bfloat1622float2(rp[j]);
+            f[2 * j] += rf.x;
+            f[2 * j + 1] += rf.y;
+          }
+        }
+        if (a.relu) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+        }
+        uint4 ov;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+        *reinterpret_cast<uint4*>(a.y + at) = ov;
+      }
+    }
+  }
+}
+
+template <int COUT, int ROWS>
+int launch_pw(const PwArgs& a, cudaStream_t st) {
+  const size_t smem = (size_t)a.cin * COUT * sizeof(float);
+  static bool attr_set[64] = {};
+  int device = 0;
+  OCNN_CUDA_OK(cudaGetDevice(&device));
+  if (smem > 48 * 1024 && (device < 0 || device >= 64 || !attr_set[device])) {
+    OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<COUT, ROWS>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    if (device >= 0 && device < 64) attr_set[device] = true;
+  }
+  const int grid = grid_for(((long long)a.h + ROWS - 1) / ROWS, 256, 4);
+  conv_pw_kernel<COUT, ROWS><<<grid, 256, smem, st>>>(a);
+  OCNN_LAUNCH_OK("conv_pw_kernel");
+  return OCNN_OK;
+}
+
+}  // namespace
+
+// Used by ocnn_octree_conv for 1x1x1 stride-1 bf16 node-major convolutions.  Returns -1 when the
+// shape is not one this kernel takes (the caller then uses the general kernel).
+int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, int cout,
+                        const ocnn_conv_epilogue* ep, cudaStream_t st) {
+  if (cin % 8 != 0 || cin > 256 || (long long)cin * cout > 16384) return -1;
+  if (((uintptr_t)x % 16) != 0 || ((uintptr_t)y % 16) != 0) return -1;
+  if (ep && ep->residual_dev && ((uintptr_t)ep->residual_dev % 16) != 0) return -1;
+  PwArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.w = w;
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.h = h; a.cin = cin;
+  a.scale = ep ? ep->scale_dev : nullptr;
+  a.bias = ep ? ep->bias_dev : nullptr;
+  a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
+  a.relu = ep ? ep->relu : 0;
+  switch (cout) {
+    case 8: return launch_pw<8, 4>(a, st);
+    case 16: return launch_pw<16, 2>(a, st);
+    case 32: return launch_pw<32, 2>(a, st);
+    case 64: return launch_pw<64, 1>(a, st);
+    default: return -1;
+  }
+}
+
+}  // namespace ocnn

@@ -13,6 +13,10 @@
 #include "common.cuh"
 
 namespace ocnn {
+
+int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, int cout,
+                        const ocnn_conv_epilogue* ep, cudaStream_t st);   // conv_pw.cu
+
 namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, THREADS = 256;
@@ -171,6 +175,11 @@ extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const in
   } else {
     OCNN_REQUIRE(h_in == h_out, "ocnn_octree_conv: stride 1 needs h_in == h_out (got %d, %d)",
                  h_in, h_out);
+  }
+  if (identity && dtype == OCNN_BF16 && layout == OCNN_NODE_MAJOR) {
+    // few-channel pointwise layers: a dedicated streaming kernel (conv_pw.cu)
+    const int s = conv_pointwise_bf16(x, w, y, h_out, cin, cout, ep, static_cast<cudaStream_t>(stream));
+    if (s >= 0) return s;
   }
   ConvArgs a;
   a.x = x; a.w = w; a.y = y; a.neigh = neigh;

@@ -46,7 +46,7 @@ struct TcArgs {
   __nv_bfloat16* y;
   const int* neigh;
   int h_in, h_out, cin, cout, npad, T, stride, identity, nkb, stages, tmem_cols;
-  int lag;          // gather arrivals trail the issue by this many K-blocks (1 or 2, < stages)
+  int lag;          // gather arrivals trail the issue by this many K-blocks (1..4, < stages)
   int group;        // 1: tile rows are sibling groups (see the header comment), 0: nodes
   int rows;         // number of tile rows in total: h_out, or h_out / 8 in group mode
   int row_elems;    // output elements per tile row: cout, or 8 * cout in group mode
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     const int nbr_stride = a.group ? 1 : kTileM;
     const int T = row_ok ? a.T : 0;
     bool alive = true;
-    int s = 0, s_arr = 0, t_run = 0, cc_run = 0;
+    int s = 0, t_run = 0, cc_run = 0;
     uint32_t pe = 1;                       // parity of the next empty[] wait, flips per ring turn
     for (int kb = 0; kb < a.nkb; ++kb) {
       if (alive && kb >= a.stages)
@@ -274,24 +274,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       if (alive)
         gather_block<CPT>(a, nbr_col, nbr_stride, T, kb, smem_u32(sA + s * kStageA) + row_off, sw,
                           t_run, cc_run);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      if (kb >= a.lag) {
-        if (a.lag == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-        else asm volatile("cp.async.wait_group 2;" ::: "memory");
-        // the gathered bytes were written through the generic proxy; the tensor core reads
-        // shared memory through the async proxy
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(smem_u32(&full[s_arr]));
-        if (++s_arr == a.stages) s_arr = 0;
-      }
+      // Arrive on full[s] when this thread's copies of the block have landed; the thread itself
+      // moves on, so up to `stages` blocks of gathers are in flight per thread.
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
+                   : "memory");
       if (++s == a.stages) { s = 0; pe ^= 1u; }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int kb = (a.nkb > a.lag ? a.nkb - a.lag : 0); kb < a.nkb; ++kb) {
-      mbar_arrive(smem_u32(&full[s_arr]));
-      if (++s_arr == a.stages) s_arr = 0;
-    }
+    asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of ours in flight past this point
 
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     if (alive) alive = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, kErrAccumWait);
@@ -350,6 +339,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       for (int kb = 0; kb < a.nkb && alive; ++kb) {
         alive = mbar_wait(smem_u32(&full[s]), pf, abort_flag, a.status, kErrFullWait);
         if (!alive) break;
+        // the gathered bytes were written through the generic proxy (cp.async) and have been
+        // observed through the mbarrier; the tensor core reads shared memory through the async
+        // proxy, so order the two before issuing
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(sA + s * kStageA);
         const uint32_t b_addr = smem_u32(sB + s * stage_b);
@@ -480,12 +473,18 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
   const size_t stage_bytes = (size_t)kStageA + (size_t)s->npad * 128;
   const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
+  // every stage of the ring can be in flight at once, so prefer two CTAs per SM (set-up and
+  // epilogue of one overlap the main loop of the other) whenever each still gets 3 stages
   int st = two_cta > fixed ? (int)((two_cta - fixed) / stage_bytes) : 0;
-  if (st < 2 || 2 * s->tmem_cols > 512) st = (int)((one_cta - fixed) / stage_bytes);
-  if (st > 6) st = 6;
+  if (st < 3 || 2 * s->tmem_cols > 512) {
+    st = (int)((one_cta - fixed) / stage_bytes);
+    if (st > 7) st = 7;
+  } else if (st > 6) {
+    st = 6;
+  }
   if (st > s->nkb) st = s->nkb < 2 ? 2 : s->nkb;
   s->stages = st;
-  s->lag = st >= 3 ? 2 : 1;
+  s->lag = 0;
   s->smem = fixed + (size_t)s->stages * stage_bytes;
   return OCNN_OK;
 }

@@ -151,7 +151,7 @@ class GpuNet:
   (node-major activations; 3x3x3 and 1x1 convolutions on the tensor-core kernel when
   `tensor_core` is set and the shape allows, fp32-accumulating CUDA-core kernel otherwise)."""
 
-  def __init__(self, net, mode='bf16', tensor_core=True, device='cuda'):
+  def __init__(self, net, mode='bf16', tensor_core=True, device='cuda', executor=True):
     import torch
     import ocnn
     self.torch, self.ocnn = torch, ocnn
@@ -165,10 +165,64 @@ class GpuNet:
     self.fc_w = torch.from_numpy(net['fc_w']).to(device)
     self.fc_b = torch.from_numpy(net['fc_b']).to(device)
     self.launches = 0
+    self.exec = self._record() if (self.bf16 and executor) else None
     # per-layer CUDA-event tracing (benchmark only): trace = {layer name: [(start, end), ...]};
     # trace_only restricts it to one layer
     self.trace = None
     self.trace_only = None
+
+  def error_status(self):
+    """Non-zero if a tensor-core kernel gave up on a bounded wait (never expected)."""
+    code = int(self.status.item())
+    if self.exec is not None:
+      code = code or int(self.exec.status())
+    return code
+
+  def _record(self):
+    """The bf16 forward as one recorded op sequence for ocnn.nn.NetExecutor (C++ replay: no Python
+    between the kernel launches).  Activation slots are recycled: 0/1 ping-pong the block
+    input/output, 2-4 hold the bottleneck's intermediates and the projected skip."""
+    net = self.net
+    ex = self.ocnn.nn.NetExecutor()
+    self.exec_layers = []
+
+    def conv(p, d, src, dst, relu, res=-1):
+      # few-channel 1x1 layers stream through the pointwise kernel on big levels (HBM-bound there),
+      # everything else that fits runs on the tensor-core kernel
+      ex.add_conv(p['name'], d, p['_cin'], p['cout'], p['ks'], 1, p['_w'], p['_packed'],
+                  p['_scale'], p['_bias'], relu, src, dst, res,
+                  100000 if p['_pointwise'] else -1)
+      self.exec_layers.append(p['name'])
+
+    cur, other = 0, 1
+    ex.add_feature(net['depth'], (net['channel_in'] + 7) // 8 * 8, cur)
+    self.exec_layers.append('feature')
+    if net['kind'] == 'lenet':
+      for c in net['convs']:
+        conv(c['conv'], c['depth'], cur, other, True)
+        ex.add_pool(c['depth'], c['conv']['cout'], other, cur)
+        self.exec_layers.append('pool%d' % c['depth'])
+      self.exec_out_depth = net['out_depth']
+    else:
+      conv(net['conv1'], net['depth'], cur, other, True)
+      cur, other = other, cur
+      for lv in net['levels']:
+        d = lv['depth']
+        for blk in lv['blocks']:
+          conv(blk['a'], d, cur, 2, True)
+          conv(blk['conv'], d, 2, 3, True)
+          skip = cur
+          if blk['c'] is not None:
+            conv(blk['c'], d, cur, 4, False)
+            skip = 4
+          conv(blk['b'], d, 3, other, True, skip)
+          cur, other = other, cur
+        if lv['pool']:
+          ex.add_pool(d, lv['blocks'][-1]['b']['cout'], cur, other)
+          self.exec_layers.append('pool%d' % d)
+          cur, other = other, cur
+      self.exec_out_depth = net['min_depth'] if not net['levels'][-1]['pool'] else net['min_depth'] - 1
+    return ex
 
   def _traced(self, name, fn):
     if self.trace is None or (self.trace_only is not None and self.trace_only != name):
@@ -198,6 +252,10 @@ class GpuNet:
     p['_scale'] = None if p['scale'] is None else t.from_numpy(p['scale']).to(self.device)
     p['_bias'] = None if p['bias'] is None else t.from_numpy(p['bias']).to(self.device)
     p['_packed'] = None
+    # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
+    # else that fits goes to the tensor-core kernel
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and p['cout'] in (8, 16, 32, 64) and
+                       cin * p['cout'] <= 4096)
     if self.tc and cin % 8 == 0 and p['cout'] % 8 == 0 and p['cout'] <= 256:
       try:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, p['cout'], p['ks'])
@@ -207,7 +265,7 @@ class GpuNet:
   def _conv(self, x, p, octree, d, relu, residual=None):
     nn = self.ocnn.nn
     self.launches += 1
-    if p['_packed'] is not None:
+    if p['_packed'] is not None and not (p['_pointwise'] and x.shape[2] >= 100000):
       return self._traced(p['name'], lambda: nn.octree_conv_tc(
           x, p['_packed'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual,
           relu, self.status))
@@ -223,6 +281,13 @@ class GpuNet:
   def forward(self, octree):
     t, net = self.torch, self.net
     nn = self.ocnn.nn
+    if self.exec is not None:
+      with t.no_grad():
+        x = self.exec.forward(octree)
+        per = 8 ** self.exec_out_depth
+        C = x.shape[1]
+        pooled = x.permute(0, 2, 1, 3).reshape(-1, per, C).float().mean(dim=1)
+        return pooled @ self.fc_w.t() + self.fc_b
     with t.no_grad():
       if self.bf16:
         x = nn.feature_node_major(octree, (net['channel_in'] + 7) // 8 * 8, True)

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 #include <torch/extension.h>
 
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -729,6 +730,189 @@ Tensor feature_node_major(Tensor octree, int c_pad, bool bf16) {
   return out;
 }
 
+
+// ---- network executor ---------------------------------------------------------------------------
+// A recorded sequence of hot-path operators over numbered activation slots, replayed on one octree
+// per call.  It exists because at these problem sizes a Python-level operator call costs more host
+// time than its kernel runs for on a B200: the executor issues the same C-ABI calls back to back
+// from C++, with every activation carved out of one arena that is reused across calls.
+// Activations are bf16 node-major ([H, C]); slot s at depth d holds nnum[d] rows.
+struct ExecOp {
+  enum Kind { kFeature, kConvTc, kConv, kPool } kind;
+  std::string name;
+  int depth = 0, cin = 0, cout = 0, stride = 1, relu = 0;
+  int in = -1, out = -1, res = -1;
+  int64_t pointwise_above = -1;   // >= 0: prefer the streaming pointwise kernel from this many nodes
+  std::vector<int> ks;
+  Tensor weights, packed, scale, bias;     // kept alive here
+};
+
+class NetExecutor {
+ public:
+  NetExecutor() { status_ = Tensor(); }
+
+  int add_feature(int depth, int c_pad, int out) {
+    ExecOp op; op.kind = ExecOp::kFeature; op.name = "feature"; op.depth = depth; op.cout = c_pad;
+    op.out = out;
+    return push(op);
+  }
+  int add_conv(string name, int depth, int cin, int cout, vector<int> ks, int stride, Tensor weights,
+               c10::optional<Tensor> packed, c10::optional<Tensor> scale, c10::optional<Tensor> bias,
+               bool relu, int in, int out, int res, int64_t pointwise_above) {
+    ExecOp op;
+    op.pointwise_above = pointwise_above;
+    op.kind = (packed.has_value() && packed->defined()) ? ExecOp::kConvTc : ExecOp::kConv;
+    op.name = name; op.depth = depth; op.cin = cin; op.cout = cout; op.ks = kernel3(ks);
+    op.stride = stride; op.relu = relu ? 1 : 0; op.in = in; op.out = out; op.res = res;
+    TORCH_CHECK(stride == 1, "the executor records stride-1 convolutions only");
+    TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32, "weights: float32 CUDA");
+    op.weights = weights.contiguous();
+    if (op.kind == ExecOp::kConvTc) op.packed = *packed;
+    if (scale.has_value() && scale->defined()) op.scale = scale->contiguous();
+    if (bias.has_value() && bias->defined()) op.bias = bias->contiguous();
+    return push(op);
+  }
+  int add_pool(int depth, int channels, int in, int out) {
+    ExecOp op; op.kind = ExecOp::kPool; op.name = "pool" + std::to_string(depth); op.depth = depth;
+    op.cin = op.cout = channels; op.in = in; op.out = out;
+    return push(op);
+  }
+  void set_trace(int op_index) { trace_ = op_index; }   // -2 none, -1 every op, >= 0 one op
+
+  // Runs the recorded ops; returns the last op's output as a [1,C,H,1] channels_last tensor
+  // (a view into the arena: valid until the next forward).
+  Tensor forward(Tensor octree) {
+    OctreeRef o = get_octree(octree);
+    TORCH_CHECK(o.cuda, "NetExecutor: the octree must be a CUDA tensor");
+    c10::cuda::CUDAGuard guard(octree.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream().stream();
+    if (!status_.defined())
+      status_ = torch::zeros({1}, octree.options().dtype(torch::kInt32));
+    // slot capacity = the largest tensor any op writes into it (slots are reused along the net)
+    int nslots = 0;
+    for (auto& op : ops_) nslots = std::max(nslots, op.out + 1);
+    vector<int64_t> rows(nslots, 0), chans(nslots, 0), offs(nslots, 0), cap(nslots, 0);
+    for (auto& op : ops_) {
+      const int d = op.kind == ExecOp::kPool ? op.depth - 1 : op.depth;
+      TORCH_CHECK(d >= 1 && d <= o.meta.depth, "NetExecutor: op ", op.name, " outside the octree depth");
+      cap[op.out] = std::max<int64_t>(cap[op.out], (int64_t)o.meta.nnum[d] * op.cout * 2);
+    }
+    int64_t total = 0, pool_tmp = 0;
+    for (int s = 0; s < nslots; ++s) { offs[s] = total; total += (cap[s] + 255) / 256 * 256; }
+    for (auto& op : ops_)
+      if (op.kind == ExecOp::kPool)
+        pool_tmp = std::max<int64_t>(pool_tmp, (int64_t)o.meta.nnum[op.depth] / 8 * op.cin * 6);
+    const int64_t tmp_off = total;
+    total += (pool_tmp + 255) / 256 * 256;
+    if (!arena_.defined() || arena_.numel() < total || arena_.device() != octree.device())
+      arena_ = torch::empty({total + total / 4}, octree.options());
+    uint8_t* base = arena_.data_ptr<uint8_t>();
+    auto slot = [&](int s) { return s < 0 ? nullptr : base + offs[s]; };
+
+    int index = 0;     // (events of earlier forwards stay queued until trace_ms() collects them)
+    for (auto& op : ops_) {
+      const bool traced = trace_ == -1 || trace_ == index;
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      if (traced) {
+        cudaEventCreate(&e0); cudaEventCreate(&e1);
+        cudaEventRecord(e0, st);
+      }
+      const ocnn_octree_meta& m = o.meta;
+      switch (op.kind) {
+        case ExecOp::kFeature: {
+          const int ch = m.channels[OCNN_PROP_FEATURE];
+          const int64_t off = ocnn_prop_offset(&m, OCNN_PROP_FEATURE, op.depth);
+          TORCH_CHECK(off >= 0 && ch > 0 && op.cout >= ch, "NetExecutor: octree features missing");
+          OCNN_CALL(ocnn_feature_to_node_major(reinterpret_cast<const float*>(o.base + off),
+                                               slot(op.out), ch, op.cout, m.nnum[op.depth],
+                                               OCNN_BF16, st));
+          break;
+        }
+        case ExecOp::kConvTc:
+        case ExecOp::kConv: {
+          const int h = m.nnum[op.depth];
+          TORCH_CHECK(op.in >= 0 && op.in != op.out && op.res != op.out && rows[op.in] == h &&
+                          chans[op.in] == op.cin, "NetExecutor: ", op.name, " input slot does not match");
+          TORCH_CHECK(op.res < 0 || (rows[op.res] == h && chans[op.res] == op.cout), "NetExecutor: ",
+                      op.name, " residual slot does not match");
+          ocnn_conv_epilogue ep;
+          ep.scale_dev = op.scale.defined() ? op.scale.data_ptr<float>() : nullptr;
+          ep.bias_dev = op.bias.defined() ? op.bias.data_ptr<float>() : nullptr;
+          ep.residual_dev = slot(op.res);
+          ep.relu = op.relu;
+          const bool identity = op.ks[0] * op.ks[1] * op.ks[2] == 1;
+          const int32_t* neigh = identity ? nullptr : level_ptr(o, OCNN_PROP_NEIGH, op.depth, "conv");
+          const bool stream_pw = identity && op.pointwise_above >= 0 && h >= op.pointwise_above;
+          if (op.kind == ExecOp::kConvTc && !stream_pw) {
+            OCNN_CALL(ocnn_octree_conv_tc(slot(op.in), op.packed.data_ptr(), slot(op.out), neigh, h, h,
+                                          op.cin, op.cout, op.ks.data(), 1, &ep,
+                                          status_.data_ptr<int32_t>(), st));
+          } else {
+            OCNN_CALL(ocnn_octree_conv(slot(op.in), op.weights.data_ptr<float>(), slot(op.out), neigh,
+                                       h, h, op.cin, op.cout, op.ks.data(), 1, OCNN_BF16,
+                                       OCNN_NODE_MAJOR, &ep, st));
+          }
+          break;
+        }
+        case ExecOp::kPool: {
+          // OctreeMaxPool: max over sibling groups, then pad to every node of depth - 1
+          const int h = m.nnum[op.depth], top = h / 8;
+          TORCH_CHECK(rows[op.in] == h && chans[op.in] == op.cin, "NetExecutor: pool input mismatch");
+          uint8_t* tmp = base + tmp_off;
+          int32_t* mask = reinterpret_cast<int32_t*>(tmp + (int64_t)top * op.cin * 2);
+          OCNN_CALL(ocnn_octree_max_pool(slot(op.in), tmp, mask, op.cin, top, OCNN_BF16,
+                                         OCNN_NODE_MAJOR, st));
+          OCNN_CALL(ocnn_octree_pad(tmp, slot(op.out), level_ptr(o, OCNN_PROP_CHILD, op.depth - 1, "pool"),
+                                    op.cin, top, m.nnum[op.depth - 1], 0.f, OCNN_BF16,
+                                    OCNN_NODE_MAJOR, st));
+          break;
+        }
+      }
+      rows[op.out] = m.nnum[op.kind == ExecOp::kPool ? op.depth - 1 : op.depth];
+      chans[op.out] = op.cout;
+      if (traced) {
+        cudaEventRecord(e1, st);
+        events_.push_back({index, e0, e1});
+      }
+      ++index;
+    }
+    const ExecOp& last = ops_.back();
+    auto opts = octree.options().dtype(torch::kBFloat16);
+    return torch::from_blob(slot(last.out), {1, chans[last.out], rows[last.out], 1},
+                            {chans[last.out] * rows[last.out], 1, chans[last.out], chans[last.out]},
+                            opts);
+  }
+
+  // (op index, milliseconds) of the traced ops of the last forward; synchronises on their events.
+  vector<std::pair<int, float>> trace_ms() {
+    vector<std::pair<int, float>> out;
+    for (auto& e : events_) {
+      cudaEventSynchronize(e.e1);
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e.e0, e.e1);
+      out.push_back({e.index, ms});
+      cudaEventDestroy(e.e0);
+      cudaEventDestroy(e.e1);
+    }
+    events_.clear();
+    return out;
+  }
+  vector<string> op_names() const {
+    vector<string> n;
+    for (auto& op : ops_) n.push_back(op.name);
+    return n;
+  }
+  int status() { return status_.defined() ? status_.item<int>() : 0; }
+
+ private:
+  int push(const ExecOp& op) { ops_.push_back(op); return (int)ops_.size() - 1; }
+  struct Ev { int index; cudaEvent_t e0, e1; };
+  vector<ExecOp> ops_;
+  vector<Ev> events_;
+  Tensor arena_, status_;
+  int trace_ = -2;
+};
+
 void set_key_bits(int bits) {
   TORCH_CHECK(bits == 32 || bits == 64, "key bits must be 32 or 64");
   g_key_bits = bits;
@@ -779,6 +963,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bf16") = true);
   m.def("set_key_bits", &set_key_bits);
   m.def("get_key_bits", &get_key_bits);
+  py::class_<NetExecutor>(m, "NetExecutor")
+      .def(py::init<>())
+      .def("add_feature", &NetExecutor::add_feature)
+      .def("add_conv", &NetExecutor::add_conv, py::arg("name"), py::arg("depth"), py::arg("cin"),
+           py::arg("cout"), py::arg("kernel_size"), py::arg("stride"), py::arg("weights"),
+           py::arg("packed") = py::none(), py::arg("scale") = py::none(),
+           py::arg("bias") = py::none(), py::arg("relu") = false, py::arg("input") = 0,
+           py::arg("output") = 0, py::arg("residual") = -1, py::arg("pointwise_above") = -1)
+      .def("add_pool", &NetExecutor::add_pool)
+      .def("set_trace", &NetExecutor::set_trace)
+      .def("forward", &NetExecutor::forward)
+      .def("trace_ms", &NetExecutor::trace_ms)
+      .def("op_names", &NetExecutor::op_names)
+      .def("status", &NetExecutor::status);
   m.def("last_error", []() { return string(ocnn_last_error()); });
   m.def("launch_count", []() { return (int64_t)ocnn_launch_count(); });
 }

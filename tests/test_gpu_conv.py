@@ -204,3 +204,27 @@ def test_conv_tensor_core_rejects_unsupported_shapes(ocnn, batch):
     ocnn.nn.conv_pack_weights(w, 3, 16, [3, 3, 3])
   with pytest.raises(RuntimeError, match='at most 256'):
     ocnn.nn.conv_pack_weights(torch.zeros(512, 8, device='cuda'), 8, 512, [1, 1, 1])
+
+
+# ---- few-channel pointwise (1x1x1) kernel behind octree_conv ---------------------------------------
+@pytest.mark.parametrize('shape', [(6, 32, 8), (6, 8, 32), (5, 64, 16), (5, 16, 64), (4, 24, 16),
+                                   (3, 128, 32), (6, 256, 64)])
+def test_conv_pointwise_bf16(ocnn, batch, shape):
+  merged, octree, v = batch
+  d, cin, cout = shape
+  rng = np.random.default_rng(cin + 7 * cout)
+  H = int(v.nnum[d])
+  x = gu.bf16_round(rng.uniform(-1, 1, size=(cin, H)).astype(np.float32))
+  w = rng.normal(scale=0.2, size=(cout, cin)).astype(np.float32)
+  scale = rng.uniform(0.5, 1.5, size=cout).astype(np.float32)
+  bias = rng.normal(size=cout).astype(np.float32)
+  res = gu.bf16_round(rng.normal(size=(cout, H)).astype(np.float32))
+  got = ocnn.octree_conv(gu.data_cuda(x, True, True), torch.from_numpy(w).cuda(), octree, d, cout,
+                         [1], 1)
+  ref = w @ x
+  assert gu.rel_err(gu.to_np(got), ref) < 6e-3            # only the bf16 rounding of the output
+  got = ocnn.nn.octree_conv_fused(gu.data_cuda(x, True, True), torch.from_numpy(w).cuda(), octree,
+                                  d, cout, [1, 1, 1], 1, torch.from_numpy(scale).cuda(),
+                                  torch.from_numpy(bias).cuda(), gu.data_cuda(res, True, True), True)
+  want = np.maximum(ref * scale[:, None] + bias[:, None] + res, 0)
+  assert gu.rel_err(gu.to_np(got), want) < 6e-3
