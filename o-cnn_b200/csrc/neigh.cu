@@ -44,26 +44,56 @@ __global__ void neigh_full_kernel(int* __restrict__ out, int depth, long long pe
   }
 }
 
-// Split level: 64 threads per parent node i (two warps); threads of empty parents exit.
-// Restates calc_neigh_cpu(neigh_split, neigh, children, node_num), octree_nn.cpp:357-380, with
-// the parent/displacement tables (octree_nn.cpp:53-81) in arithmetic form.
-__global__ void neigh_split_kernel(int* __restrict__ out, const int* __restrict__ neigh,
-                                   const int* __restrict__ child, long long total) {
-  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total;
-       t += (long long)gridDim.x * blockDim.x) {
-    const int i = (int)(t >> 6), j = (int)(t & 63);
-    const int l0 = child[i];
-    if (l0 < 0) continue;
+// Split level, one warp per sibling group of PARENT nodes.  The eight parents of a group share one
+// 4x4x4 neighbour block at their own level, and every entry any of their children's blocks needs
+// is "the child group of one of those 64 cells".  So the warp reads the group's 64 neighbour
+// entries (256 contiguous bytes) and the 64 child pointers behind them ONCE (two gathers per
+// lane), keeps them in shared memory, and then writes the 64-int block of each non-empty parent
+// with two coalesced 128-byte stores: 8 child gathers per parent instead of the 64 of the
+// one-thread-per-output formulation.  Restates calc_neigh_cpu(neigh_split, neigh, children,
+// node_num), octree/octree/octree_nn.cpp:357-380, with the parent/displacement tables
+// (octree_nn.cpp:53-81) in arithmetic form.
+constexpr int kNeighWarps = 8;
+
+__global__ void __launch_bounds__(kNeighWarps * 32) neigh_split_kernel(
+    int* __restrict__ out, const int* __restrict__ neigh, const int* __restrict__ child,
+    long long ngroups) {
+  __shared__ int cblk[kNeighWarps][64];     // child group of each cell of the parents' block
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // child-level block position j = (x,y,z) in 0..3 -> which parent-level cell (tap, as a
+  // (tx<<4)|(ty<<2)|tz code relative to the parent) and which octant inside it; two per lane
+  int tapcode[2], oct[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int j = lane + 32 * k;
     const int x = (j >> 4) + 1, y = ((j >> 2) & 3) + 1, z = (j & 3) + 1;
-    const int tap = (x >> 1) * 9 + (y >> 1) * 3 + (z >> 1);
-    const int oct = ((x & 1) << 2) | ((y & 1) << 1) | (z & 1);
-    const int k = neigh[((long long)(i >> 3) << 6) + ni333(i & 7, tap)];
-    int v = -1;
-    if (k >= 0) {
-      const int l1 = child[k];
-      if (l1 >= 0) v = (l1 << 3) + oct;
+    tapcode[k] = ((x >> 1) << 4) | ((y >> 1) << 2) | (z >> 1);
+    oct[k] = ((x & 1) << 2) | ((y & 1) << 1) | (z & 1);
+  }
+  for (long long g = blockIdx.x * (long long)kNeighWarps + warp; g < ngroups;
+       g += (long long)gridDim.x * kNeighWarps) {
+    const int* blk = neigh + (g << 6);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int cell = blk[lane + 32 * k];
+      cblk[warp][lane + 32 * k] = cell >= 0 ? child[cell] : -1;
     }
-    out[((long long)l0 << 6) + j] = v;
+    // the eight parents themselves: lanes 0..7 read their child pointers
+    const int mine = lane < 8 ? child[(g << 3) + lane] : -1;
+    __syncwarp();
+#pragma unroll
+    for (int o = 0; o < 8; ++o) {
+      const int l0 = __shfl_sync(0xffffffffu, mine, o);
+      if (l0 < 0) continue;                                     // empty parent: no block
+      const int octcode = ((o & 4) << 2) | ((o & 2) << 1) | (o & 1);
+      int* dst = out + ((long long)l0 << 6);
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int c = cblk[warp][tapcode[k] + octcode];
+        dst[lane + 32 * k] = c >= 0 ? (c << 3) + oct[k] : -1;
+      }
+    }
+    __syncwarp();
   }
 }
 
@@ -94,9 +124,9 @@ int ocnn_calc_neigh_split(int32_t* neigh_child, const int32_t* neigh, const int3
   OCNN_REQUIRE(nnum_parent > 0 && nnum_parent % 8 == 0,
                "ocnn_calc_neigh_split: parent level must hold whole sibling groups (got %d nodes)",
                nnum_parent);
-  const long long total = (long long)nnum_parent * 64;
-  neigh_split_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      neigh_child, neigh, child, total);
+  const long long ngroups = nnum_parent / 8;
+  neigh_split_kernel<<<grid_for(ngroups, kNeighWarps, 16), kNeighWarps * 32, 0,
+                       static_cast<cudaStream_t>(stream)>>>(neigh_child, neigh, child, ngroups);
   OCNN_LAUNCH_OK("neigh_split_kernel");
   return OCNN_OK;
 }
