@@ -29,6 +29,8 @@ constexpr int kThreads = 256;
 constexpr int kScanItems = 4;
 constexpr int kScanTile = kThreads * kScanItems;
 constexpr int kMaxScanGrid = kSMs * 4;   // 592 blocks: 4 CTAs of 256 threads per SM
+constexpr int kSortItems = 8;            // keys per thread per sort tile
+constexpr int kSortTile = kThreads * kSortItems;   // 2048 keys
 
 // One entry per cloud (plus a sentinel holding the total point count), uploaded by the plan call.
 struct CloudRef {
@@ -44,8 +46,8 @@ struct Layout {
   int64_t n;            // total points
   int batch, depth, full;
   int key_bytes_sort;   // 4 or 8: width of the sort key
-  int nvb;              // sort: warp-sized virtual blocks
-  int vchunk;           // sort: items per virtual block (multiple of 32)
+  int nvb;              // sort: number of CTAs, each owning one contiguous chunk of the keys
+  int vchunk;           // sort: keys per CTA chunk (multiple of the 2048-key tile)
   int64_t cap[OCNN_MAX_DEPTH + 1];   // capacity of Kd
   size_t off_offsets, off_counts, off_blockcnt, off_hist, off_bintot;
   size_t off_keys[2], off_idx[2];
@@ -66,13 +68,14 @@ Layout make_layout(int64_t n, int batch, int depth, int full) {
   memset(&L, 0, sizeof(L));
   L.n = n; L.batch = batch; L.depth = depth; L.full = full;
   L.key_bytes_sort = (3 * depth + bits_for(batch) <= 32) ? 4 : 8;
-  int64_t nvb = (n + 1023) / 1024;
+  int64_t nvb = (n + 4 * kSortTile - 1) / (4 * kSortTile);
   if (nvb < 1) nvb = 1;
-  if (nvb > kSMs * 8 * 4) nvb = kSMs * 8 * 4;
-  nvb = (nvb + 7) / 8 * 8;                           // whole CTAs of 8 warps
-  L.nvb = (int)nvb;
+  if (nvb > kSMs * 4) nvb = kSMs * 4;
   int64_t vchunk = (n + nvb - 1) / nvb;
-  L.vchunk = (int)((vchunk + 31) / 32 * 32);
+  vchunk = (vchunk + kSortTile - 1) / kSortTile * kSortTile;
+  nvb = (n + vchunk - 1) / vchunk;                   // drop chunks the rounding left empty
+  L.nvb = (int)nvb;
+  L.vchunk = (int)vchunk;
   size_t o = 0;
   auto take = [&](size_t bytes) { size_t at = o; o = align_up(o + bytes); return at; };
   L.off_offsets = take(sizeof(CloudRef) * (size_t)(batch + 1));
@@ -144,36 +147,37 @@ __global__ void encode_kernel(EncodeArgs a, KeyT* __restrict__ keys) {
 }
 
 // ---- stable LSD radix sort, 8 bits per pass -------------------------------------------------------
-// Each warp owns a contiguous run of `vchunk` items (a "virtual block").  Pass = per-warp digit
-// histogram -> exclusive scan over (digit, virtual block) -> stable scatter in which every warp
-// ranks its run 32 items at a time with match_any.
+// Each CTA owns one contiguous chunk of the keys.  A pass is: per-CTA digit histogram -> exclusive
+// scan over (digit, CTA) -> stable scatter.  The scatter works in tiles of 2048 keys: every warp
+// ranks its 256 keys 32 at a time with match_any (stable inside the warp), the per-warp digit counts
+// are prefixed across warps and digits, the tile is written to shared memory in digit order, and
+// only then copied out — consecutive threads then write consecutive global addresses of one digit
+// run, so the 4-byte scatter of the naive formulation becomes coalesced runs.
 template <typename KeyT>
 __global__ void __launch_bounds__(kThreads) sort_hist_kernel(const KeyT* __restrict__ keys,
                                                              long long n, int shift, int vchunk,
                                                              int nvb, int* __restrict__ hist) {
-  __shared__ int sh[kThreads / 32][256];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int vb = blockIdx.x * (kThreads / 32) + warp;
-  for (int b = lane; b < 256; b += 32) sh[warp][b] = 0;
-  __syncwarp();
-  const long long beg = (long long)vb * vchunk;
+  __shared__ int sh[256];
+  const int lane = threadIdx.x & 31;
+  sh[threadIdx.x] = 0;
+  __syncthreads();
+  const long long beg = (long long)blockIdx.x * vchunk;
   long long end = beg + vchunk;
   if (end > n) end = n;
-  for (long long i = beg; i < end; i += 32) {
-    const bool valid = i + lane < end;
+  for (long long i = beg; i < end; i += kThreads) {
+    const bool valid = i + threadIdx.x < end;
     const unsigned mask = __ballot_sync(0xffffffffu, valid);
     if (valid) {
-      const int digit = (int)((keys[i + lane] >> shift) & 255);
+      const int digit = (int)((keys[i + threadIdx.x] >> shift) & 255);
       const unsigned peers = __match_any_sync(mask, digit);
-      if ((peers & ((1u << lane) - 1)) == 0) sh[warp][digit] += __popc(peers);
+      if ((peers & ((1u << lane) - 1)) == 0) atomicAdd(&sh[digit], __popc(peers));
     }
-    __syncwarp();
   }
-  if (vb < nvb)
-    for (int b = lane; b < 256; b += 32) hist[(long long)b * nvb + vb] = sh[warp][b];
+  __syncthreads();
+  hist[(long long)threadIdx.x * nvb + blockIdx.x] = sh[threadIdx.x];
 }
 
-// Exclusive scan of hist[256][nvb] in (digit, virtual block) order: one CTA per digit row.
+// Exclusive scan of hist[256][nvb] in (digit, CTA) order: one CTA per digit row.
 __global__ void __launch_bounds__(kThreads) sort_rowsum_kernel(const int* __restrict__ hist,
                                                                int nvb, int* __restrict__ bintot) {
   __shared__ int red[kThreads / 32];
@@ -244,36 +248,81 @@ __global__ void __launch_bounds__(kThreads) sort_scatter_kernel(
     const KeyT* __restrict__ keys_in, const uint32_t* __restrict__ idx_in,
     KeyT* __restrict__ keys_out, uint32_t* __restrict__ idx_out, long long n, int shift,
     int vchunk, int nvb, const int* __restrict__ hist) {
-  __shared__ int offs[kThreads / 32][256];
+  constexpr int kWarps = kThreads / 32;
+  __shared__ int cnt[kWarps][256];        // per-warp digit counts, then per-warp digit bases
+  __shared__ int tile_start[256];         // first slot of each digit inside the sorted tile
+  __shared__ int gofs[256];               // next global slot of each digit for this CTA
+  __shared__ KeyT skey[kSortTile];
+  __shared__ uint32_t sidx[kSortTile];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int vb = blockIdx.x * (kThreads / 32) + warp;
-  if (vb < nvb)
-    for (int b = lane; b < 256; b += 32) offs[warp][b] = hist[(long long)b * nvb + vb];
-  __syncwarp();
-  const long long beg = (long long)vb * vchunk;
+  gofs[threadIdx.x] = hist[(long long)threadIdx.x * nvb + blockIdx.x];
+  const long long beg = (long long)blockIdx.x * vchunk;
   long long end = beg + vchunk;
   if (end > n) end = n;
-  for (long long i = beg; i < end; i += 32) {
-    const bool valid = i + lane < end;
-    const unsigned mask = __ballot_sync(0xffffffffu, valid);
-    KeyT key = 0;
-    int digit = 0, rank = 0;
-    unsigned peers = 0;
-    int pos = 0;
-    if (valid) {
-      key = keys_in[i + lane];
-      digit = (int)((key >> shift) & 255);
-      peers = __match_any_sync(mask, digit);
-      rank = __popc(peers & ((1u << lane) - 1));
-      pos = offs[warp][digit] + rank;
+  for (long long t0 = beg; t0 < end; t0 += kSortTile) {
+    const int tile_n = (int)((end - t0) < kSortTile ? (end - t0) : kSortTile);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] = 0;
+    __syncthreads();
+    // 1. rank inside the warp's 256 keys (index order = rank order: stable)
+    KeyT key[kSortItems];
+    uint32_t idx[kSortItems];
+    int rank[kSortItems];
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+      const int local = warp * (32 * kSortItems) + r * 32 + lane;
+      const bool valid = local < tile_n;
+      const unsigned mask = __ballot_sync(0xffffffffu, valid);
+      rank[r] = -1;
+      key[r] = 0;
+      idx[r] = 0;
+      if (valid) {
+        key[r] = keys_in[t0 + local];
+        idx[r] = FIRST ? (uint32_t)(t0 + local) : idx_in[t0 + local];
+        const int digit = (int)((key[r] >> shift) & 255);
+        const unsigned peers = __match_any_sync(mask, digit);
+        const int before = __popc(peers & ((1u << lane) - 1));
+        rank[r] = cnt[warp][digit] + before;
+        __syncwarp(mask);
+        if (before == 0) cnt[warp][digit] += __popc(peers);
+      }
+      __syncwarp();
     }
-    __syncwarp();
-    if (valid) {
-      keys_out[pos] = key;
-      idx_out[pos] = FIRST ? (uint32_t)(i + lane) : idx_in[i + lane];
-      if (rank == 0) offs[warp][digit] += __popc(peers);
+    __syncthreads();
+    // 2. thread d: prefix digit d over the warps, then over the digits
+    int total_d = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = cnt[w][threadIdx.x];
+      cnt[w][threadIdx.x] = total_d;
+      total_d += c;
     }
-    __syncwarp();
+    int tile_total;
+    const int start_d = block_exclusive_scan(total_d, &tile_total);
+    tile_start[threadIdx.x] = start_d;
+    __syncthreads();
+    // 3. tile into shared memory in digit order
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+      if (rank[r] >= 0) {
+        const int digit = (int)((key[r] >> shift) & 255);
+        const int pos = tile_start[digit] + cnt[warp][digit] + rank[r];
+        skey[pos] = key[r];
+        sidx[pos] = idx[r];
+      }
+    }
+    __syncthreads();
+    // 4. copy out: slot i of the sorted tile goes to gofs[digit] + (i - tile_start[digit])
+    for (int i = threadIdx.x; i < tile_n; i += kThreads) {
+      const KeyT k = skey[i];
+      const int digit = (int)((k >> shift) & 255);
+      const long long pos = (long long)gofs[digit] + (i - tile_start[digit]);
+      keys_out[pos] = k;
+      idx_out[pos] = sidx[i];
+    }
+    __syncthreads();
+    gofs[threadIdx.x] += total_d;
+    __syncthreads();
   }
 }
 
@@ -563,7 +612,7 @@ int sort_and_unique(const ocnn_points_batch* pts, const ocnn_build_params* prm, 
 
   const int nbits = 3 * prm->depth + bits_for(pts->batch);
   const int passes = (nbits + 7) / 8 < 1 ? 1 : (nbits + 7) / 8;
-  const int sort_grid = L.nvb / (kThreads / 32);
+  const int sort_grid = L.nvb;
   int cur = 0;
   for (int p = 0; p < passes; ++p) {
     const int shift = 8 * p;
