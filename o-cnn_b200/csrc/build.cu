@@ -157,24 +157,22 @@ template <typename KeyT>
 __global__ void __launch_bounds__(kThreads) sort_hist_kernel(const KeyT* __restrict__ keys,
                                                              long long n, int shift, int vchunk,
                                                              int nvb, int* __restrict__ hist) {
-  __shared__ int sh[256];
-  const int lane = threadIdx.x & 31;
-  sh[threadIdx.x] = 0;
+  // one private histogram per warp (shared-memory atomics never cross warps), summed at the end
+  __shared__ int sh[kThreads / 32][256];
+  const int warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) sh[w][threadIdx.x] = 0;
   __syncthreads();
   const long long beg = (long long)blockIdx.x * vchunk;
   long long end = beg + vchunk;
   if (end > n) end = n;
-  for (long long i = beg; i < end; i += kThreads) {
-    const bool valid = i + threadIdx.x < end;
-    const unsigned mask = __ballot_sync(0xffffffffu, valid);
-    if (valid) {
-      const int digit = (int)((keys[i + threadIdx.x] >> shift) & 255);
-      const unsigned peers = __match_any_sync(mask, digit);
-      if ((peers & ((1u << lane) - 1)) == 0) atomicAdd(&sh[digit], __popc(peers));
-    }
-  }
+  for (long long i = beg + threadIdx.x; i < end; i += kThreads)
+    atomicAdd(&sh[warp][(int)((keys[i] >> shift) & 255)], 1);
   __syncthreads();
-  hist[(long long)threadIdx.x * nvb + blockIdx.x] = sh[threadIdx.x];
+  int total = 0;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) total += sh[w][threadIdx.x];
+  hist[(long long)threadIdx.x * nvb + blockIdx.x] = total;
 }
 
 // Exclusive scan of hist[256][nvb] in (digit, CTA) order: one CTA per digit row.
@@ -858,7 +856,7 @@ int ocnn_octree_build_emit(const ocnn_points_batch* pts, const ocnn_build_params
     if (width == 0.0f) width = 1.0e-10f;
     sa.mul = (float)(1 << D) / width;
     for (int j = 0; j < 3; ++j) sa.bbmin[j] = prm->bbmin[j];
-    signal_kernel<<<grid_for(sa.nnum, 128), 128, 0, st>>>(sa);
+    signal_kernel<<<grid_for(sa.nnum, 256, 8), 256, 0, st>>>(sa);
     OCNN_LAUNCH_OK("signal_kernel");
   }
 
