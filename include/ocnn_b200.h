@@ -163,7 +163,8 @@ int ocnn_octree_conv(const void* x_dev, const float* weights_dev, void* y_dev,
 size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride);
 int ocnn_conv_pack_weights(const float* weights_dev, void* packed_dev, int cin, int cout,
                            const int kernel_size[3], int stride, void* stream);
-/* x, y: bf16 node-major ([h, C]); cin % 8 == 0, cout % 8 == 0, cout <= 256.
+/* x, y: bf16 node-major ([h, C]); cin % 8 == 0; cout % 8 == 0 up to 256, or a multiple of 256 up
+ * to 1024 (then produced 256 channels per launch).
  * status_dev: one int32 in device memory, zero before the call; a kernel that gives up on a
  * bounded wait writes a non-zero code there instead of hanging. */
 int ocnn_octree_conv_tc(const void* x_dev, const void* packed_weights_dev, void* y_dev,

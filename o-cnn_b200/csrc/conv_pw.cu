@@ -15,6 +15,8 @@ struct PwArgs {
   const float* w;          // [cout, cin], the reference layout
   __nv_bfloat16* y;
   int h, cin;
+  int y_stride;            // output channels of the whole layer (row stride of y / residual)
+  int co_base;             // first output channel this launch produces
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -26,7 +28,7 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
   extern __shared__ float ws[];                      // [cin][COUT]
   for (int i = threadIdx.x; i < a.cin * COUT; i += blockDim.x) {
     const int co = i / a.cin, ci = i % a.cin;        // coalesced read of w[co][ci], transposed store
-    ws[ci * COUT + co] = a.w[i];
+    ws[ci * COUT + co] = a.w[(long long)a.co_base * a.cin + i];
   }
   __syncthreads();
   const int chunks = a.cin >> 3;
@@ -80,10 +82,10 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           f[j] = acc[r][8 * q + j];
-          if (a.scale) f[j] *= a.scale[8 * q + j];
-          if (a.bias) f[j] += a.bias[8 * q + j];
+          if (a.scale) f[j] *= a.scale[a.co_base + 8 * q + j];
+          if (a.bias) f[j] += a.bias[a.co_base + 8 * q + j];
         }
-        const long long at = h * COUT + 8 * q;
+        const long long at = h * a.y_stride + a.co_base + 8 * q;
         if (a.residual) {
           const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
           const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
@@ -132,6 +134,7 @@ int launch_pw(const PwArgs& a, cudaStream_t st) {
 int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, int cout,
                         const ocnn_conv_epilogue* ep, cudaStream_t st) {
   if (cin % 8 != 0 || cin > 256 || (long long)cin * cout > 16384) return -1;
+  if (cout != 8 && cout != 16 && cout != 32 && cout != 64) return -1;
   if (((uintptr_t)x % 16) != 0 || ((uintptr_t)y % 16) != 0) return -1;
   if (ep && ep->residual_dev && ((uintptr_t)ep->residual_dev % 16) != 0) return -1;
   PwArgs a;
@@ -139,6 +142,7 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.w = w;
   a.y = static_cast<__nv_bfloat16*>(y);
   a.h = h; a.cin = cin;
+  a.y_stride = cout; a.co_base = 0;
   a.scale = ep ? ep->scale_dev : nullptr;
   a.bias = ep ? ep->bias_dev : nullptr;
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
@@ -147,7 +151,13 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
     case 8: return launch_pw<8, 4>(a, st);
     case 16: return launch_pw<16, 2>(a, st);
     case 32: return launch_pw<32, 2>(a, st);
-    case 64: return launch_pw<64, 1>(a, st);
+    case 64: {
+      // 64 accumulators per thread leave too little occupancy: two passes of 32 channels (the
+      // input row is 1/4 of the traffic or less, so reading it twice is cheap)
+      if (int s0 = launch_pw<32, 2>(a, st)) return s0;
+      a.co_base = 32;
+      return launch_pw<32, 2>(a, st);
+    }
     default: return -1;
   }
 }

@@ -50,6 +50,9 @@ struct TcArgs {
   int group;        // 1: tile rows are sibling groups (see the header comment), 0: nodes
   int rows;         // number of tile rows in total: h_out, or h_out / 8 in group mode
   int row_elems;    // output elements per tile row: cout, or 8 * cout in group mode
+  int y_stride;     // elements between consecutive output rows (= row_elems unless the layer's
+                    // output channels are produced in several launches)
+  int co_base;      // first output channel this launch produces
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -125,6 +128,16 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
                  "=r"(v[6]), "=r"(v[7])
                : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
@@ -289,24 +302,41 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     const int h = h0 + r;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
     if (alive) {
-      for (int n0 = 0; n0 < a.npad; n0 += 8) {
-        uint32_t v[8];
-        tmem_ld8(lane_base + (uint32_t)n0, v);
+      // 16 accumulator columns per step; the residual of the NEXT step is requested before this
+      // step's TMEM load is waited for, so its latency hides behind the arithmetic and stores
+      const bool row_ok = h < a.rows;
+      const __nv_bfloat16* res_row =
+          a.residual ? a.residual + (long long)h * a.y_stride + a.co_base : nullptr;
+      __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + a.co_base;
+      uint4 res_next[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      auto load_res = [&](int n0) {
+        if (res_row != nullptr && row_ok) {
+          if (n0 < a.row_elems) res_next[0] = *reinterpret_cast<const uint4*>(res_row + n0);
+          if (n0 + 8 < a.row_elems) res_next[1] = *reinterpret_cast<const uint4*>(res_row + n0 + 8);
+        }
+      };
+      load_res(0);
+      for (int n0 = 0; n0 < a.npad; n0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(lane_base + (uint32_t)n0, v);
+        const uint4 res_cur[2] = {res_next[0], res_next[1]};
+        if (n0 + 16 < a.npad) load_res(n0 + 16);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (h < a.rows && n0 < a.row_elems) {
-          // output channel of column n0: columns are (octant, channel) pairs in group mode
-          const int co0 = a.group ? (n0 & (a.cout - 1)) : n0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int n = n0 + 8 * half;
+          if (!row_ok || n >= a.row_elems) continue;
+          // output channel of column n: columns are (octant, channel) pairs in group mode
+          const int co0 = a.group ? (n & (a.cout - 1)) : a.co_base + n;
           float f[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            f[j] = __uint_as_float(v[j]);
+            f[j] = __uint_as_float(v[8 * half + j]);
             if (a.scale) f[j] *= a.scale[co0 + j];
             if (a.bias) f[j] += a.bias[co0 + j];
           }
-          const long long at = (long long)h * a.row_elems + n0;
-          if (a.residual) {
-            const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
-            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+          if (res_row != nullptr) {
+            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&res_cur[half]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 rf = __bfloat1622float2(rp[j]);
@@ -322,7 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
           __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
           for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-          *reinterpret_cast<uint4*>(a.y + at) = ov;
+          *reinterpret_cast<uint4*>(y_row + n) = ov;
         }
       }
     }
@@ -445,7 +475,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group; size_t smem; };
+struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group, slices; size_t smem; };
 
 int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
   const TapList tl = taps_for_kernel(ks);
@@ -456,9 +486,13 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
     return fail(OCNN_ERR_INVALID, "tensor-core convolution: stride must be 1 or 2 (got %d)", stride);
   if (cin <= 0 || cin % 8 != 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: Cin (%d) must be a multiple of 8", cin);
-  if (cout <= 0 || cout % 8 != 0 || cout > 256)
+  if (cout <= 0 || cout % 8 != 0 || (cout > 256 && cout % 256 != 0) || cout > 1024)
     return fail(OCNN_ERR_UNSUPPORTED,
-                "tensor-core convolution: Cout (%d) must be a multiple of 8, at most 256", cout);
+                "tensor-core convolution: Cout (%d) must be a multiple of 8 up to 256, or a multiple "
+                "of 256 up to 1024", cout);
+  // more than 256 output channels: produced 256 at a time (one TMEM accumulator is 256 columns)
+  s->slices = cout > 256 ? cout / 256 : 1;
+  if (s->slices > 1) cout = 256;
   // sibling-group mode: stride 1, a real neighbourhood, few channels (power-of-two Cout so that
   // column -> channel is a mask)
   s->group = (stride == 1 && tl.count > 1 && cin <= 32 && cout <= 32 && (cout & (cout - 1)) == 0) ? 1 : 0;
@@ -497,7 +531,7 @@ extern "C" {
 size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride) {
   ocnn::TcShape s;
   if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, stride, &s) != OCNN_OK) return 0;
-  return (size_t)s.nkb * s.npad * 128;
+  return (size_t)s.slices * s.nkb * s.npad * 128;
 }
 
 int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
@@ -514,9 +548,16 @@ int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, cons
     for (int i = 0; i < 27; ++i) ta.tap[i] = i < tl.count ? tl.tap[i] : -1;
     pack_weights_group_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         w, static_cast<__nv_bfloat16*>(packed), cin, cout, tl.count, ta, s.npad, s.nkb);
-  } else
-  pack_weights_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      w, static_cast<__nv_bfloat16*>(packed), cin, cout, s.T, s.npad, s.nkb);
+  } else {
+    // one packed image per slice of (at most) 256 output channels: rows of w are contiguous
+    const int cslice = s.slices > 1 ? 256 : cout;
+    for (int sl = 0; sl < s.slices; ++sl) {
+      pack_weights_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+          w + (size_t)sl * cslice * cin * s.T, static_cast<__nv_bfloat16*>(packed) + (size_t)sl * total,
+          cin, cslice, s.T, s.npad, s.nkb);
+      if (sl > 0) note_launches(1);
+    }
+  }
   OCNN_LAUNCH_OK("pack_weights_kernel");
   return OCNN_OK;
 }
@@ -557,7 +598,11 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.lag = s.lag;
   a.group = s.group;
   a.rows = s.group ? h_out / 8 : h_out;
-  a.row_elems = s.group ? 8 * cout : cout;
+  const int cslice = s.slices > 1 ? 256 : cout;
+  a.cout = cslice;
+  a.row_elems = s.group ? 8 * cout : cslice;
+  a.y_stride = s.group ? 8 * cout : cout;
+  a.co_base = 0;
   if (s.group)
     OCNN_REQUIRE(h_out % 8 == 0, "ocnn_octree_conv_tc: an octree level holds whole sibling groups "
                  "(got %d nodes)", h_out);
@@ -597,8 +642,12 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
                "ocnn_octree_conv_tc: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses",
                (long long)h_in * cin * 2);
-  kernel<<<ceil_div(a.rows, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
-  OCNN_LAUNCH_OK("conv_tc_kernel");
+  for (int sl = 0; sl < s.slices; ++sl) {
+    a.co_base = sl * cslice;
+    a.wpacked = static_cast<const uint8_t*>(packed) + (size_t)sl * s.nkb * s.npad * 128;
+    kernel<<<ceil_div(a.rows, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
+    OCNN_LAUNCH_OK("conv_tc_kernel");
+  }
   return OCNN_OK;
 }
 

@@ -191,7 +191,7 @@ class GpuNet:
       # everything else that fits runs on the tensor-core kernel
       ex.add_conv(p['name'], d, p['_cin'], p['cout'], p['ks'], 1, p['_w'], p['_packed'],
                   p['_scale'], p['_bias'], relu, src, dst, res,
-                  100000 if p['_pointwise'] else -1)
+                  500000 if p["_pointwise"] else -1)
       self.exec_layers.append(p['name'])
 
     cur, other = 0, 1
@@ -256,7 +256,7 @@ class GpuNet:
     # else that fits goes to the tensor-core kernel
     p['_pointwise'] = (p['ks'] == [1, 1, 1] and p['cout'] in (8, 16, 32, 64) and
                        cin * p['cout'] <= 4096)
-    if self.tc and cin % 8 == 0 and p['cout'] % 8 == 0 and p['cout'] <= 256:
+    if self.tc and cin % 8 == 0 and p['cout'] % 8 == 0 and (p['cout'] <= 256 or p['cout'] % 256 == 0):
       try:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, p['cout'], p['ks'])
       except RuntimeError:
@@ -265,7 +265,7 @@ class GpuNet:
   def _conv(self, x, p, octree, d, relu, residual=None):
     nn = self.ocnn.nn
     self.launches += 1
-    if p['_packed'] is not None and not (p['_pointwise'] and x.shape[2] >= 100000):
+    if p['_packed'] is not None and not (p['_pointwise'] and x.shape[2] >= 500000):
       return self._traced(p['name'], lambda: nn.octree_conv_tc(
           x, p['_packed'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual,
           relu, self.status))

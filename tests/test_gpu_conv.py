@@ -138,6 +138,8 @@ TC_CASES = [
     (3, 64, 64, [3, 3, 3], 1),
     (2, 128, 128, [3, 3, 3], 1),
     (3, 64, 256, [3, 3, 3], 1),
+    (2, 128, 512, [1, 1, 1], 1),   # 512 output channels: two launches of 256
+    (2, 16, 512, [3, 3, 3], 1),
     (5, 24, 40, [3, 3, 3], 1),     # K = 27*24 is not a multiple of 64; Cout not a multiple of 16
     (6, 32, 8, [1, 1, 1], 1),      # the 1x1 convolutions of the bottleneck blocks
     (5, 16, 64, [1, 1, 1], 1),
@@ -202,8 +204,8 @@ def test_conv_tensor_core_rejects_unsupported_shapes(ocnn, batch):
   w = torch.zeros(16, 3 * 27, device='cuda')
   with pytest.raises(RuntimeError, match='multiple of 8'):
     ocnn.nn.conv_pack_weights(w, 3, 16, [3, 3, 3])
-  with pytest.raises(RuntimeError, match='at most 256'):
-    ocnn.nn.conv_pack_weights(torch.zeros(512, 8, device='cuda'), 8, 512, [1, 1, 1])
+  with pytest.raises(RuntimeError, match='multiple of 256'):
+    ocnn.nn.conv_pack_weights(torch.zeros(264, 8, device='cuda'), 8, 264, [1, 1, 1])
 
 
 # ---- few-channel pointwise (1x1x1) kernel behind octree_conv ---------------------------------------
