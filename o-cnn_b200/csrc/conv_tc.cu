@@ -246,20 +246,27 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       // contiguous ints that the gather reads straight from global memory
     } else {
       const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
-      for (int t = 0; t < a.T; ++t) {
+      if (a.identity) {
+        nbr[tid] = h < a.rows ? h : -1;
+      } else {
+      // all (up to 27) table reads are issued before the first result is used: a load-then-store
+      // loop would expose the L2 latency once per tap
+      int pv[27];
+#pragma unroll
+      for (int t = 0; t < 27; ++t) {
         int p = -1;
-        if (h < a.rows) {
-          if (a.identity) {
-            p = h;
-          } else {
-            // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
-            // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
-            const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
-                                               : ((long long)(h >> 3) << 6) + a.tap[t] + oct_code;
-            p = a.neigh[at];
-          }
+        if (t < a.T && h < a.rows) {
+          // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
+          // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
+          const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
+                                             : ((long long)(h >> 3) << 6) + a.tap[t] + oct_code;
+          p = a.neigh[at];
         }
-        nbr[t * kTileM + tid] = p;
+        pv[t] = p;
+      }
+#pragma unroll
+      for (int t = 0; t < 27; ++t)
+        if (t < a.T) nbr[t * kTileM + tid] = pv[t];
       }
     }
   }
@@ -477,7 +484,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
 
 struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group, slices; size_t smem; };
 
-int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
+int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1) {
   const TapList tl = taps_for_kernel(ks);
   if (tl.count < 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported kernel size %dx%dx%d",
@@ -510,7 +517,11 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s) {
   // every stage of the ring can be in flight at once, so prefer two CTAs per SM (set-up and
   // epilogue of one overlap the main loop of the other) whenever each still gets 3 stages
   int st = two_cta > fixed ? (int)((two_cta - fixed) / stage_bytes) : 0;
-  if (st < 3 || 2 * s->tmem_cols > 512) {
+  // a grid that does not even fill the SMs once gains nothing from co-residency: give the lone CTA
+  // of each SM the deepest ring instead (its K loop is a pure latency chain)
+  const long long rows = rows_hint < 0 ? -1 : (s->group ? rows_hint / 8 : rows_hint);
+  const bool small_grid = rows >= 0 && (rows + kTileM - 1) / kTileM <= kSMs;
+  if (st < 3 || 2 * s->tmem_cols > 512 || small_grid) {
     st = (int)((one_cta - fixed) / stage_bytes);
     if (st > 7) st = 7;
   } else if (st > 6) {
@@ -569,7 +580,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_tc: null kernel size");
   OCNN_REQUIRE(stride == 1 || stride == 2, "ocnn_octree_conv_tc: stride must be 1 or 2 (got %d)", stride);
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, stride, &s)) return st;
+  if (int st = tc_shape(cin, cout, kernel_size, stride, &s, h_out)) return st;
   OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv_tc: negative height");
   if (h_out == 0) return OCNN_OK;
   const bool identity = s.T == 1 && stride == 1;
