@@ -53,6 +53,7 @@ struct TcArgs {
   int y_stride;     // elements between consecutive output rows (= row_elems unless the layer's
                     // output channels are produced in several launches)
   int co_base;      // first output channel this launch produces
+  int rowsplit;     // gather mapping: 1 = four tile rows per warp instruction, 0 = one per thread
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -205,6 +206,23 @@ __device__ __forceinline__ void gather_block(const TcArgs& a, const int* __restr
   }
 }
 
+// Which tap the 16-byte chunk `chunk` of K-block kb belongs to, and the byte offset inside that
+// neighbour's row.  CPT as in gather_block.
+template <int CPT>
+__device__ __forceinline__ void chunk_src(int cpt, int kb, int chunk, int& t, uint32_t& off) {
+  if constexpr (CPT >= 8) {
+    t = kb / (CPT / 8);
+    off = (uint32_t)(kb % (CPT / 8)) * 128u + (uint32_t)chunk * 16u;
+  } else if constexpr (CPT > 0) {
+    t = kb * (8 / CPT) + chunk / CPT;
+    off = (uint32_t)(chunk % CPT) * 16u;
+  } else {
+    const int g = kb * 8 + chunk;
+    t = g / cpt;
+    off = (uint32_t)(g - t * cpt) * 16u;
+  }
+}
+
 template <int CPT>
 __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -276,29 +294,89 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-    // ---------------- A gather: thread = tile row ----------------
+    // ---------------- A gather ----------------
     const int r = tid;
-    const uint32_t row_off = (uint32_t)r * 128u;
-    const uint32_t sw = (uint32_t)(r & 7);
-    // rows past the end of the level gather nothing (T = 0 makes every tap "missing")
-    const bool row_ok = h0 + r < a.rows;
-    const int* nbr_col = a.group ? a.neigh + ((long long)(row_ok ? h0 + r : 0) << 6) : nbr + r;
-    const int nbr_stride = a.group ? 1 : kTileM;
-    const int T = row_ok ? a.T : 0;
     bool alive = true;
-    int s = 0, t_run = 0, cc_run = 0;
-    uint32_t pe = 1;                       // parity of the next empty[] wait, flips per ring turn
-    for (int kb = 0; kb < a.nkb; ++kb) {
-      if (alive && kb >= a.stages)
-        alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
-      if (alive)
-        gather_block<CPT>(a, nbr_col, nbr_stride, T, kb, smem_u32(sA + s * kStageA) + row_off, sw,
-                          t_run, cc_run);
-      // Arrive on full[s] when this thread's copies of the block have landed; the thread itself
-      // moves on, so up to `stages` blocks of gathers are in flight per thread.
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
-                   : "memory");
-      if (++s == a.stages) { s = 0; pe ^= 1u; }
+    if (a.rowsplit) {
+      // Sibling-group mode with 8 or 16 channels: every 16-byte chunk of a tile row comes from a
+      // different node, so "one tile row per thread" makes each warp instruction touch 32
+      // unrelated lines.  Here a warp instruction copies the 8 chunks of a K-block for 4 tile rows
+      // (lane = row within the four, chunk): the chunks of one row are 8 (or 4) consecutive
+      // positions of the group's 4x4x4 block, i.e. whole sibling sets, which are contiguous in
+      // memory.  A thread serves chunk position `chunk` of rows rbase + 4*i, i = 0..7.
+      const int sub = lane >> 3, chunk = lane & 7;
+      const int rbase = warp * 32 + sub;
+      const char* xb = reinterpret_cast<const char*>(a.x);
+      const uint32_t row_bytes = (uint32_t)a.cin * 2u;
+      const int cpt = a.cin >> 3;
+      uint32_t row_mask = 0;        // bit i: tile row rbase + 4*i exists
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
+      auto fetch = [&](int kb, int (&p)[8], uint32_t& off) {
+        int t;
+        chunk_src<CPT>(cpt, kb, chunk, t, off);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          p[i] = -1;
+          if (t < a.T && ((row_mask >> i) & 1u))
+            p[i] = __ldg(a.neigh + (((long long)(h0 + rbase + 4 * i)) << 6) + t);
+        }
+      };
+      int s = 0;
+      uint32_t pe = 1;
+      int p_cur[8];
+      uint32_t off_cur;
+      fetch(0, p_cur, off_cur);
+      for (int kb = 0; kb < a.nkb; ++kb) {
+        // the indices of the next block are requested before this block's copies are issued
+        int p_nxt[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+        uint32_t off_nxt = 0;
+        if (kb + 1 < a.nkb) fetch(kb + 1, p_nxt, off_nxt);
+        if (alive && kb >= a.stages)
+          alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
+        if (alive) {
+          const uint32_t stage_base = smem_u32(sA + s * kStageA);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = rbase + 4 * i;
+            const uint32_t dst = stage_base + (uint32_t)row * 128u +
+                                 (((uint32_t)chunk ^ (uint32_t)(row & 7)) << 4);
+            const int p = p_cur[i];
+            const char* src = p >= 0 ? xb + (size_t)((uint32_t)p * row_bytes) + off_cur : xb;
+            cp_async16(dst, src, p >= 0 ? 16u : 0u);
+          }
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
+                     : "memory");
+        if (++s == a.stages) { s = 0; pe ^= 1u; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) p_cur[i] = p_nxt[i];
+        off_cur = off_nxt;
+      }
+    } else {
+      // one tile row per thread
+      const uint32_t row_off = (uint32_t)r * 128u;
+      const uint32_t sw = (uint32_t)(r & 7);
+      // rows past the end of the level gather nothing (T = 0 makes every tap "missing")
+      const bool row_ok = h0 + r < a.rows;
+      const int* nbr_col = a.group ? a.neigh + ((long long)(row_ok ? h0 + r : 0) << 6) : nbr + r;
+      const int nbr_stride = a.group ? 1 : kTileM;
+      const int T = row_ok ? a.T : 0;
+      int s = 0, t_run = 0, cc_run = 0;
+      uint32_t pe = 1;                       // parity of the next empty[] wait, flips per ring turn
+      for (int kb = 0; kb < a.nkb; ++kb) {
+        if (alive && kb >= a.stages)
+          alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
+        if (alive)
+          gather_block<CPT>(a, nbr_col, nbr_stride, T, kb, smem_u32(sA + s * kStageA) + row_off, sw,
+                            t_run, cc_run);
+        // Arrive on full[s] when this thread's copies of the block have landed; the thread itself
+        // moves on, so up to `stages` blocks of gathers are in flight per thread.
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
+                     : "memory");
+        if (++s == a.stages) { s = 0; pe ^= 1u; }
+      }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of ours in flight past this point
 
@@ -395,6 +473,19 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     }
   } else {
     // ---------------- weight tiles: one thread, one bulk copy per K-block ----------------
+    // Every CTA streams the same nkb tiles in the same order, so on a cold L2 each tile would be a
+    // DRAM miss that all CTAs of the wave wait for, one ring turn after the other.  The CTAs of the
+    // first wave therefore start by asking L2 for the whole weight image, each for its own
+    // share of the tiles.
+    {
+      const int wave = gridDim.x < kSMs ? (int)gridDim.x : kSMs;
+      if ((int)blockIdx.x < wave) {
+        for (int kb = blockIdx.x + lane * wave; kb < a.nkb; kb += 32 * wave)
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.wpacked + (size_t)kb * stage_b),
+                       "r"((uint32_t)stage_b)
+                       : "memory");
+      }
+    }
     if (lane == 0) {
       bool alive = true;
       int s = 0;
@@ -614,6 +705,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.row_elems = s.group ? 8 * cout : cslice;
   a.y_stride = s.group ? 8 * cout : cout;
   a.co_base = 0;
+  a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
   if (s.group)
     OCNN_REQUIRE(h_out % 8 == 0, "ocnn_octree_conv_tc: an octree level holds whole sibling groups "
                  "(got %d nodes)", h_out);
