@@ -232,7 +232,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   uint8_t* sA = smem;
   uint8_t* sB = sA + a.stages * kStageA;
   int* nbr = reinterpret_cast<int*>(sB + a.stages * stage_b);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(nbr + (a.group ? 0 : a.T * kTileM));
+  // per-column scale and bias of the epilogue, staged once per CTA: read from global memory in
+  // the epilogue they were a chain of cold misses (one per 128-byte line of each array) that every
+  // thread of a one-wave launch sat through
+  float* s_scale = reinterpret_cast<float*>(nbr + (a.group ? 0 : a.T * kTileM));
+  float* s_bias = s_scale + a.npad;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + a.npad);
   uint64_t* full = bars;
   uint64_t* empty = bars + a.stages;
   uint64_t* accum = bars + 2 * a.stages;
@@ -250,6 +255,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     mbar_init(smem_u32(accum), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int n = tid; n < a.npad; n += kThreads) {
+    // output channel of column n: columns are (octant, channel) pairs in group mode
+    const int co = a.group ? (n & (a.cout - 1)) : a.co_base + n;
+    const bool live = n < a.row_elems;
+    s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
+    s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
   }
   if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -381,63 +393,79 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of ours in flight past this point
 
     // ---------------- epilogue: TMEM -> registers -> global ----------------
+    // The residual is read one 128-byte line (64 channels) of the row at a time, all eight 16-byte
+    // pieces of a line at once and the next line before the current one is used; the first line
+    // is requested before the wait for the accumulator.
+    const int h = h0 + r;
+    const bool row_ok = h < a.rows;
+    const __nv_bfloat16* res_row =
+        (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + a.co_base : nullptr;
+    uint4 res_nxt[8];
+    auto load_line = [&](int c0) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        res_nxt[q] = make_uint4(0, 0, 0, 0);
+        if (res_row != nullptr && c0 + 8 * q < a.row_elems)
+          res_nxt[q] = *reinterpret_cast<const uint4*>(res_row + c0 + 8 * q);
+      }
+    };
+    load_line(0);
     if (alive) alive = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, kErrAccumWait);
     alive = __all_sync(0xffffffffu, alive);   // tcgen05.ld is warp-collective: decide per warp
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int h = h0 + r;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
     if (alive) {
-      // 16 accumulator columns per step; the residual of the NEXT step is requested before this
-      // step's TMEM load is waited for, so its latency hides behind the arithmetic and stores
-      const bool row_ok = h < a.rows;
-      const __nv_bfloat16* res_row =
-          a.residual ? a.residual + (long long)h * a.y_stride + a.co_base : nullptr;
       __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + a.co_base;
-      uint4 res_next[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-      auto load_res = [&](int n0) {
-        if (res_row != nullptr && row_ok) {
-          if (n0 < a.row_elems) res_next[0] = *reinterpret_cast<const uint4*>(res_row + n0);
-          if (n0 + 8 < a.row_elems) res_next[1] = *reinterpret_cast<const uint4*>(res_row + n0 + 8);
-        }
-      };
-      load_res(0);
-      for (int n0 = 0; n0 < a.npad; n0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(lane_base + (uint32_t)n0, v);
-        const uint4 res_cur[2] = {res_next[0], res_next[1]};
-        if (n0 + 16 < a.npad) load_res(n0 + 16);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const bool has_sb = a.scale != nullptr || a.bias != nullptr;
+      for (int c0 = 0; c0 < a.npad; c0 += 64) {
+        uint4 res_cur[8];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int n = n0 + 8 * half;
-          if (!row_ok || n >= a.row_elems) continue;
-          // output channel of column n: columns are (octant, channel) pairs in group mode
-          const int co0 = a.group ? (n & (a.cout - 1)) : a.co_base + n;
-          float f[8];
+        for (int q = 0; q < 8; ++q) res_cur[q] = res_nxt[q];
+        if (c0 + 64 < a.npad) load_line(c0 + 64);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            f[j] = __uint_as_float(v[8 * half + j]);
-            if (a.scale) f[j] *= a.scale[co0 + j];
-            if (a.bias) f[j] += a.bias[co0 + j];
-          }
-          if (res_row != nullptr) {
-            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&res_cur[half]);
+        for (int step = 0; step < 4; ++step) {
+          const int n0 = c0 + 16 * step;
+          if (n0 >= a.npad) break;
+          uint32_t v[16];
+          tmem_ld16(lane_base + (uint32_t)n0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 rf = __bfloat1622float2(rp[j]);
-              f[2 * j] += rf.x;
-              f[2 * j + 1] += rf.y;
+          for (int half = 0; half < 2; ++half) {
+            const int n = n0 + 8 * half;
+            if (!row_ok || n >= a.row_elems) continue;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[8 * half + j]);
+            if (has_sb) {
+              const float4 sc0 = *reinterpret_cast<const float4*>(s_scale + n);
+              const float4 sc1 = *reinterpret_cast<const float4*>(s_scale + n + 4);
+              const float4 bi0 = *reinterpret_cast<const float4*>(s_bias + n);
+              const float4 bi1 = *reinterpret_cast<const float4*>(s_bias + n + 4);
+              const float sc[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
+              const float bi[8] = {bi0.x, bi0.y, bi0.z, bi0.w, bi1.x, bi1.y, bi1.z, bi1.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], bi[j]);
             }
-          }
-          if (a.relu) {
+            if (res_row != nullptr) {
+              const __nv_bfloat162* rp =
+                  reinterpret_cast<const __nv_bfloat162*>(&res_cur[2 * step + half]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
-          }
-          uint4 ov;
-          __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+              for (int j = 0; j < 4; ++j) {
+                const float2 rf = __bfloat1622float2(rp[j]);
+                f[2 * j] += rf.x;
+                f[2 * j + 1] += rf.y;
+              }
+            }
+            if (a.relu) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-          *reinterpret_cast<uint4*>(y_row + n) = ov;
+              for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+            }
+            uint4 ov;
+            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+            *reinterpret_cast<uint4*>(y_row + n) = ov;
+          }
         }
       }
     }
@@ -603,7 +631,7 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   // phases then overlap each other's main loop); otherwise take what one CTA can hold.  The gather
   // arrivals trail the issue by `lag` K-blocks, and the ring must be deeper than the lag.
   const size_t stage_bytes = (size_t)kStageA + (size_t)s->npad * 128;
-  const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + 256;
+  const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + (size_t)s->npad * 8 + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
   // every stage of the ring can be in flight at once, so prefer two CTAs per SM (set-up and
   // epilogue of one overlap the main loop of the other) whenever each still gets 3 stages
