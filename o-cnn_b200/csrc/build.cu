@@ -68,7 +68,7 @@ Layout make_layout(int64_t n, int batch, int depth, int full) {
   memset(&L, 0, sizeof(L));
   L.n = n; L.batch = batch; L.depth = depth; L.full = full;
   L.key_bytes_sort = (3 * depth + bits_for(batch) <= 32) ? 4 : 8;
-  int64_t nvb = (n + 4 * kSortTile - 1) / (4 * kSortTile);
+  int64_t nvb = (n + kSortTile - 1) / kSortTile;       // one tile per CTA until the grid is 4 waves
   if (nvb < 1) nvb = 1;
   if (nvb > kSMs * 4) nvb = kSMs * 4;
   int64_t vchunk = (n + nvb - 1) / nvb;
@@ -222,14 +222,10 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
 
 __global__ void __launch_bounds__(kThreads) sort_rowscan_kernel(int* __restrict__ hist, int nvb,
                                                                 const int* __restrict__ bintot) {
-  __shared__ int base_s;
-  if (threadIdx.x == 0) {
-    int b = 0;
-    for (int i = 0; i < (int)blockIdx.x; ++i) b += bintot[i];
-    base_s = b;
-  }
-  __syncthreads();
-  int base = base_s;
+  // first slot of this digit = number of keys with a smaller digit (kThreads == 256 digits)
+  int below_total;
+  block_exclusive_scan(threadIdx.x < blockIdx.x ? bintot[threadIdx.x] : 0, &below_total);
+  int base = below_total;
   int* row = hist + (long long)blockIdx.x * nvb;
   for (int i0 = 0; i0 < nvb; i0 += kThreads) {
     const int i = i0 + threadIdx.x;
@@ -267,16 +263,22 @@ __global__ void __launch_bounds__(kThreads) sort_scatter_kernel(
     uint32_t idx[kSortItems];
     int rank[kSortItems];
 #pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {      // all loads of the tile first: one latency, not 8
+      const int local = warp * (32 * kSortItems) + r * 32 + lane;
+      key[r] = 0;
+      idx[r] = 0;
+      if (local < tile_n) {
+        key[r] = keys_in[t0 + local];
+        idx[r] = FIRST ? (uint32_t)(t0 + local) : idx_in[t0 + local];
+      }
+    }
+#pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
       const int local = warp * (32 * kSortItems) + r * 32 + lane;
       const bool valid = local < tile_n;
       const unsigned mask = __ballot_sync(0xffffffffu, valid);
       rank[r] = -1;
-      key[r] = 0;
-      idx[r] = 0;
       if (valid) {
-        key[r] = keys_in[t0 + local];
-        idx[r] = FIRST ? (uint32_t)(t0 + local) : idx_in[t0 + local];
         const int digit = (int)((key[r] >> shift) & 255);
         const unsigned peers = __match_any_sync(mask, digit);
         const int before = __popc(peers & ((1u << lane) - 1));
