@@ -53,6 +53,8 @@ struct TcArgs {
   int y_stride;     // elements between consecutive output rows (= row_elems unless the layer's
                     // output channels are produced in several launches)
   int co_base;      // first output channel this launch produces
+  int tile_rows;    // tile rows a CTA actually computes (128, 64 or 32): small levels are cut into
+                    // more, emptier tiles so that every SM gets one; the MMA is always 128 rows
   int rowsplit;     // gather mapping: 1 = four tile rows per warp instruction, 0 = one per thread
   const float* scale;
   const float* bias;
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h0 = blockIdx.x * kTileM;
+  const int h0 = blockIdx.x * a.tile_rows;
 
   if (tid == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -271,13 +273,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
   }
   if (tid < kTileM) {
     const int h = h0 + tid;          // node, or sibling group in group mode
+    const bool live = tid < a.tile_rows && h < a.rows;
     if (a.group) {
       // nothing to stage: the group's neighbour block IS the list of rows to gather, 64
       // contiguous ints that the gather reads straight from global memory
     } else {
       const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
       if (a.identity) {
-        nbr[tid] = h < a.rows ? h : -1;
+        nbr[tid] = live ? h : -1;
       } else {
       // all (up to 27) table reads are issued before the first result is used: a load-then-store
       // loop would expose the L2 latency once per tap
@@ -285,7 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
 #pragma unroll
       for (int t = 0; t < 27; ++t) {
         int p = -1;
-        if (t < a.T && h < a.rows) {
+        if (t < a.T && live) {
           // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
           // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
           const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
@@ -324,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       uint32_t row_mask = 0;        // bit i: tile row rbase + 4*i exists
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        if (h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
+        if (rbase + 4 * i < a.tile_rows && h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
       auto fetch = [&](int kb, int (&p)[8], uint32_t& off) {
         int t;
         chunk_src<CPT>(cpt, kb, chunk, t, off);
@@ -356,7 +359,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
                                  (((uint32_t)chunk ^ (uint32_t)(row & 7)) << 4);
             const int p = p_cur[i];
             const char* src = p >= 0 ? xb + (size_t)((uint32_t)p * row_bytes) + off_cur : xb;
-            cp_async16(dst, src, p >= 0 ? 16u : 0u);
+            // rows the tile does not have are left as they are: their accumulator lanes are
+            // never read
+            if ((row_mask >> i) & 1u) cp_async16(dst, src, p >= 0 ? 16u : 0u);
           }
         }
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
@@ -370,17 +375,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
       // one tile row per thread
       const uint32_t row_off = (uint32_t)r * 128u;
       const uint32_t sw = (uint32_t)(r & 7);
-      // rows past the end of the level gather nothing (T = 0 makes every tap "missing")
-      const bool row_ok = h0 + r < a.rows;
+      // rows the tile does not have gather nothing: their accumulator lanes are never read
+      const bool row_ok = r < a.tile_rows && h0 + r < a.rows;
       const int* nbr_col = a.group ? a.neigh + ((long long)(row_ok ? h0 + r : 0) << 6) : nbr + r;
       const int nbr_stride = a.group ? 1 : kTileM;
-      const int T = row_ok ? a.T : 0;
+      const int T = a.T;
       int s = 0, t_run = 0, cc_run = 0;
       uint32_t pe = 1;                       // parity of the next empty[] wait, flips per ring turn
       for (int kb = 0; kb < a.nkb; ++kb) {
         if (alive && kb >= a.stages)
           alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
-        if (alive)
+        if (alive && row_ok)
           gather_block<CPT>(a, nbr_col, nbr_stride, T, kb, smem_u32(sA + s * kStageA) + row_off, sw,
                             t_run, cc_run);
         // Arrive on full[s] when this thread's copies of the block have landed; the thread itself
@@ -397,7 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     // pieces of a line at once and the next line before the current one is used; the first line
     // is requested before the wait for the accumulator.
     const int h = h0 + r;
-    const bool row_ok = h < a.rows;
+    const bool row_ok = r < a.tile_rows && h < a.rows;
     const __nv_bfloat16* res_row =
         (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + a.co_base : nullptr;
     uint4 res_nxt[8];
@@ -601,7 +606,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group, slices; size_t smem; };
+struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group, slices, tile_rows; size_t smem; };
 
 int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1) {
   const TapList tl = taps_for_kernel(ks);
@@ -639,7 +644,15 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   // a grid that does not even fill the SMs once gains nothing from co-residency: give the lone CTA
   // of each SM the deepest ring instead (its K loop is a pure latency chain)
   const long long rows = rows_hint < 0 ? -1 : (s->group ? rows_hint / 8 : rows_hint);
-  const bool small_grid = rows >= 0 && (rows + kTileM - 1) / kTileM <= kSMs;
+  // A level too small to give even half of the SMs a 128-row tile is cut into 64- or 32-row
+  // tiles: the gather is then spread over more SMs.  Every CTA still streams the whole weight
+  // image, so halving stops where a K-block's gather (about 8 cycles per row of 16-byte copies)
+  // is no longer above its weight tile (about 3.2 cycles per 128-byte row).
+  s->tile_rows = kTileM;
+  while (rows >= 0 && s->tile_rows > 32 && 2 * ((rows + s->tile_rows - 1) / s->tile_rows) <= kSMs &&
+         8.0 * s->tile_rows > 3.2 * s->npad)
+    s->tile_rows >>= 1;
+  const bool small_grid = rows >= 0 && (rows + s->tile_rows - 1) / s->tile_rows <= kSMs;
   if (st < 3 || 2 * s->tmem_cols > 512 || small_grid) {
     st = (int)((one_cta - fixed) / stage_bytes);
     if (st > 7) st = 7;
@@ -734,6 +747,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.y_stride = s.group ? 8 * cout : cout;
   a.co_base = 0;
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
+  a.tile_rows = s.tile_rows;
   if (s.group)
     OCNN_REQUIRE(h_out % 8 == 0, "ocnn_octree_conv_tc: an octree level holds whole sibling groups "
                  "(got %d nodes)", h_out);
@@ -776,7 +790,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   for (int sl = 0; sl < s.slices; ++sl) {
     a.co_base = sl * cslice;
     a.wpacked = static_cast<const uint8_t*>(packed) + (size_t)sl * s.nkb * s.npad * 128;
-    kernel<<<ceil_div(a.rows, kTileM), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
+    kernel<<<ceil_div(a.rows, a.tile_rows), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
     OCNN_LAUNCH_OK("conv_tc_kernel");
   }
   return OCNN_OK;
