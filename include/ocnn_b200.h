@@ -101,6 +101,16 @@ int ocnn_octree_depad(const void* y_dev, void* x_dev, const int32_t* child_dev, 
 int ocnn_octree_max_pool(const void* btm_dev, void* top_dev, int32_t* mask_dev, int channels,
                          int top_h, int dtype, int layout, void* stream);
 
+/* OctreeMaxPool in one pass: octree_max_pool followed by octree_pad with 0, the pair the
+ * reference's module runs (pytorch/ocnn/octree_pool.py, OctreeMaxPool.forward: octree_max_pool
+ * then octree_pad at depth - 1).  btm: [btm_h, C] rows of level `depth`; top: [top_h, C] rows of
+ * level depth - 1; child_dev: the Child block of level depth - 1 (child[p] = sibling group of
+ * node p, < 0 for a leaf, whose row becomes 0).  bf16 node-major data, C % 8 == 0; no argmax
+ * (inference). */
+int ocnn_octree_max_pool_pad(const void* btm_dev, void* top_dev, const int32_t* child_dev,
+                             int channels, int btm_h, int top_h, int dtype, int layout,
+                             void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Neighbour table.  Replace calc_neigh_gpu (both overloads), octree/octree/octree_nn.cu:331-413,
  * and the CPU loop of merge_octrees that the PyTorch path actually runs

@@ -20,6 +20,23 @@ __global__ void feature_to_nm_kernel(const float* __restrict__ f, T* __restrict_
   }
 }
 
+// c_pad == 8, bf16: one thread per node — up to 8 coalesced plane reads, one 16-byte row store.
+__global__ void __launch_bounds__(256) feature_to_nm_bf16x8_kernel(const float* __restrict__ f,
+                                                                   uint4* __restrict__ out, int C,
+                                                                   long long nnum) {
+  for (long long h = blockIdx.x * (long long)blockDim.x + threadIdx.x; h < nnum;
+       h += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) v[c] = c < C ? f[(long long)c * nnum + h] : 0.f;
+    uint4 row;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&row);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    out[h] = row;
+  }
+}
+
 }  // namespace
 }  // namespace ocnn
 
@@ -33,7 +50,10 @@ extern "C" int ocnn_feature_to_node_major(const float* feature, void* out, int c
   if (nnum == 0) return OCNN_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = (long long)nnum * c_pad;
-  if (dtype == OCNN_BF16)
+  if (dtype == OCNN_BF16 && c_pad == 8 && (uintptr_t)out % 16 == 0)
+    feature_to_nm_bf16x8_kernel<<<grid_for(nnum, 256), 256, 0, st>>>(feature, static_cast<uint4*>(out),
+                                                                    channels, nnum);
+  else if (dtype == OCNN_BF16)
     feature_to_nm_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>(
         feature, static_cast<__nv_bfloat16*>(out), channels, c_pad, nnum);
   else

@@ -167,6 +167,69 @@ __global__ void max_pool_nm_kernel(const T* __restrict__ btm, T* __restrict__ to
   }
 }
 
+// bf16 node-major, C a multiple of 8: one thread per (sibling group, 8-channel chunk).  The eight
+// children's chunks are eight 16-byte loads in flight at once; the result is one 16-byte store
+// (plus two for the argmax rows when the caller wants them).
+// PADDED: the output has one row per node of the parent level; child[p] gives the sibling group
+// of node p (or < 0: the row is zero) — max pool and the pad that follows it in one pass.
+struct Bf16x8 { __nv_bfloat162 v[4]; };
+
+template <bool PADDED>
+__global__ void __launch_bounds__(256) max_pool_nm_bf16x8_kernel(
+    const uint4* __restrict__ btm, uint4* __restrict__ top, int* __restrict__ mask,
+    const int* __restrict__ child, int chunks, long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / chunks;
+    const int q = (int)(i - row * chunks);
+    long long g = row;
+    if (PADDED) {
+      g = child[row];
+      if (g < 0) {
+        top[i] = make_uint4(0, 0, 0, 0);
+        continue;
+      }
+    }
+    const uint4* src = btm + g * 8 * chunks + q;
+    uint4 raw[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) raw[j] = src[(long long)j * chunks];
+    float best[8];
+    int at[8];
+    {
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        best[2 * k] = f.x; best[2 * k + 1] = f.y;
+        at[2 * k] = 0; at[2 * k + 1] = 0;
+      }
+    }
+#pragma unroll
+    for (int j = 1; j < 8; ++j) {
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        if (f.x > best[2 * k]) { best[2 * k] = f.x; at[2 * k] = j; }
+        if (f.y > best[2 * k + 1]) { best[2 * k + 1] = f.y; at[2 * k + 1] = j; }
+      }
+    }
+    // the winner's own bits (the values are exact bf16, so the round trip through fp32 is too)
+    uint4 out;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) op[k] = __floats2bfloat162_rn(best[2 * k], best[2 * k + 1]);
+    top[i] = out;
+    if (mask != nullptr) {
+      const int base = (int)(8 * g);
+      int4* m = reinterpret_cast<int4*>(mask + i * 8);
+      m[0] = make_int4(base + at[0], base + at[1], base + at[2], base + at[3]);
+      m[1] = make_int4(base + at[4], base + at[5], base + at[6], base + at[7]);
+    }
+  }
+}
+
 template <typename T>
 T fill_value(float val);
 template <>
@@ -239,6 +302,11 @@ int pool_impl(const void* btm, void* top, int* mask, int C, int top_h, int layou
       max_pool_cm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)btm, (T*)top, mask,
                                                                   top_h, total);
     }
+  } else if (sizeof(T) == 2 && C % 8 == 0 && (uintptr_t)btm % 16 == 0 && (uintptr_t)top % 16 == 0 &&
+             (uintptr_t)mask % 16 == 0) {
+    const long long vec_total = total / 8;
+    max_pool_nm_bf16x8_kernel<false><<<grid_for(vec_total, 256, 8), 256, 0, st>>>(
+        (const uint4*)btm, (uint4*)top, mask, nullptr, C / 8, vec_total);
   } else {
     max_pool_nm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)btm, (T*)top, mask, C,
                                                                 total);
@@ -271,6 +339,27 @@ int ocnn_octree_pad(const void* x, void* y, const int32_t* child, int C, int hx,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return dtype == OCNN_F32 ? pad_impl<float>(x, y, child, C, hx, hy, val, layout, st)
                            : pad_impl<__nv_bfloat16>(x, y, child, C, hx, hy, val, layout, st);
+}
+
+int ocnn_octree_max_pool_pad(const void* btm, void* top, const int32_t* child, int C, int btm_h,
+                             int top_h, int dtype, int layout, void* stream) {
+  using namespace ocnn;
+  if (top_h == 0) return OCNN_OK;
+  if (int s = check_common("ocnn_octree_max_pool_pad", btm_h > 0 ? btm : top, top, child, C, dtype, layout))
+    return s;
+  OCNN_REQUIRE(btm_h >= 0 && btm_h % 8 == 0 && top_h >= btm_h / 8,
+               "ocnn_octree_max_pool_pad: need btm_h (%d) = 8 * groups and top_h (%d) >= groups",
+               btm_h, top_h);
+  OCNN_REQUIRE(dtype == OCNN_BF16 && layout == OCNN_NODE_MAJOR && C % 8 == 0,
+               "ocnn_octree_max_pool_pad: bf16 node-major data with C %% 8 == 0 only (C = %d); use "
+               "ocnn_octree_max_pool + ocnn_octree_pad otherwise", C);
+  OCNN_REQUIRE((uintptr_t)btm % 16 == 0 && (uintptr_t)top % 16 == 0,
+               "ocnn_octree_max_pool_pad: data pointers must be 16-byte aligned");
+  const long long total = (long long)top_h * (C / 8);
+  max_pool_nm_bf16x8_kernel<true><<<grid_for(total, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint4*)btm, (uint4*)top, nullptr, child, C / 8, total);
+  OCNN_LAUNCH_OK("octree_max_pool_pad");
+  return OCNN_OK;
 }
 
 int ocnn_octree_depad(const void* y, void* x, const int32_t* child, int C, int hx, int hy,

@@ -31,6 +31,10 @@ class OctreeMaxPool(OctreePoolBase):
     self.return_indices = return_indices
 
   def forward(self, data, octree):
+    if (not self.return_indices and data.dtype == torch.bfloat16 and data.shape[1] % 8 == 0 and
+        data.is_contiguous(memory_format=torch.channels_last)):
+      with torch.no_grad():      # both steps in one kernel
+        return nn.octree_max_pool_pad(data, octree, self.depth)
     pool, mask = octree_max_pool(data, octree, self.depth)
     output = octree_pad(pool, octree, self.depth - 1)
     return output if not self.return_indices else (output, mask)

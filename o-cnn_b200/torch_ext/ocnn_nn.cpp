@@ -233,6 +233,25 @@ vector<Tensor> octree_max_pool(Tensor data_in, Tensor octree, int depth) {
   return {top, mask};
 }
 
+// OctreeMaxPool in one pass (bf16 node-major data, C % 8 == 0): pool level `depth`, one row per
+// node of level depth - 1, zeros for leaves.  No argmax.
+Tensor octree_max_pool_pad(Tensor data_in, Tensor octree, int depth) {
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(depth > 1, "Depth should be larger than 1");
+  TORCH_CHECK(depth <= o.meta.depth, "octree_max_pool_pad: depth ", depth, " exceeds the octree depth");
+  need_cuda(data_in, "octree_max_pool_pad");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef b = get_data(data_in, "octree_max_pool_pad");
+  TORCH_CHECK(o.meta.nnum[depth] == b.H, "octree_max_pool_pad: data height ", b.H, " != node number ",
+              o.meta.nnum[depth]);
+  const int top_h = o.meta.nnum[depth - 1];
+  Tensor top = new_data(b.C, top_h, b);
+  OCNN_CALL(ocnn_octree_max_pool_pad(b.t.data_ptr(), top.data_ptr(),
+                                     level_ptr(o, OCNN_PROP_CHILD, depth - 1, "octree_max_pool_pad"),
+                                     b.C, b.H, top_h, b.dtype, b.layout, current_stream()));
+  return top;
+}
+
 // ---- octree2col ----------------------------------------------------------------------------------
 Tensor octree2col(Tensor data_in, Tensor octree, int depth, vector<int> kernel_size, int stride,
                   bool nempty) {
@@ -858,13 +877,20 @@ class NetExecutor {
           // OctreeMaxPool: max over sibling groups, then pad to every node of depth - 1
           const int h = m.nnum[op.depth], top = h / 8;
           TORCH_CHECK(rows[op.in] == h && chans[op.in] == op.cin, "NetExecutor: pool input mismatch");
-          uint8_t* tmp = base + tmp_off;
-          int32_t* mask = reinterpret_cast<int32_t*>(tmp + (int64_t)top * op.cin * 2);
-          OCNN_CALL(ocnn_octree_max_pool(slot(op.in), tmp, mask, op.cin, top, OCNN_BF16,
-                                         OCNN_NODE_MAJOR, st));
-          OCNN_CALL(ocnn_octree_pad(tmp, slot(op.out), level_ptr(o, OCNN_PROP_CHILD, op.depth - 1, "pool"),
-                                    op.cin, top, m.nnum[op.depth - 1], 0.f, OCNN_BF16,
-                                    OCNN_NODE_MAJOR, st));
+          if (op.cin % 8 == 0) {
+            OCNN_CALL(ocnn_octree_max_pool_pad(slot(op.in), slot(op.out),
+                                               level_ptr(o, OCNN_PROP_CHILD, op.depth - 1, "pool"),
+                                               op.cin, h, m.nnum[op.depth - 1], OCNN_BF16,
+                                               OCNN_NODE_MAJOR, st));
+          } else {
+            uint8_t* tmp = base + tmp_off;
+            int32_t* mask = reinterpret_cast<int32_t*>(tmp + (int64_t)top * op.cin * 2);
+            OCNN_CALL(ocnn_octree_max_pool(slot(op.in), tmp, mask, op.cin, top, OCNN_BF16,
+                                           OCNN_NODE_MAJOR, st));
+            OCNN_CALL(ocnn_octree_pad(tmp, slot(op.out), level_ptr(o, OCNN_PROP_CHILD, op.depth - 1, "pool"),
+                                      op.cin, top, m.nnum[op.depth - 1], 0.f, OCNN_BF16,
+                                      OCNN_NODE_MAJOR, st));
+          }
           break;
         }
       }
@@ -942,6 +968,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("depth"), py::arg("val") = 0.0f);
   m.def("octree_depad", &octree_depad, "octree depad");
   m.def("octree_max_pool", &octree_max_pool, "octree max pooling");
+  m.def("octree_max_pool_pad", &octree_max_pool_pad, "octree max pooling + pad to depth - 1 (bf16 node-major)");
   m.def("points_new", &points_new, "create a point cloud");
   // additions of this implementation
   m.def("points2octree_batch", &points2octree_batch,

@@ -123,6 +123,26 @@ def test_pad_depad_pool(ocnn, batch, layout, bf16):
       assert np.array_equal(m, wm)
 
 
+@pytest.mark.parametrize('C', [8, 32, 40])
+def test_max_pool_pad_fused(ocnn, batch, C):
+  """ocnn_octree_max_pool_pad == octree_max_pool followed by octree_pad(0), bit for bit, on every
+  level; also through the OctreeMaxPool module, which takes the fused path for such data."""
+  _, _, _, octree, v = batch
+  rng = np.random.default_rng(11)
+  for d in range(2, v.depth + 1):
+    H = int(v.nnum[d])
+    x = gu.bf16_round(rng.uniform(-1, 1, size=(C, H)).astype(np.float32))
+    x[0, :16] = 0.5
+    data = gu.data_cuda(x, True, True)
+    want = oc.pad(oc.max_pool(x)[0], v.prop('child', d - 1), 0.0)
+    got = ocnn.nn.octree_max_pool_pad(data, octree, d)
+    assert got.shape == (1, C, int(v.nnum[d - 1]), 1)
+    assert np.array_equal(gu.to_np(got), want)
+    assert np.array_equal(gu.to_np(ocnn.OctreeMaxPool(d)(data, octree)), want)
+  with pytest.raises(RuntimeError, match='bf16 node-major'):
+    ocnn.nn.octree_max_pool_pad(torch.zeros(1, 8, int(v.nnum[3]), 1, device='cuda'), octree, 3)
+
+
 def test_pad_shape_errors(ocnn, batch):
   _, _, _, octree, v = batch
   with pytest.raises(RuntimeError, match='data height'):
