@@ -148,15 +148,15 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
   a.relu = ep ? ep->relu : 0;
   switch (cout) {
-    case 8: return launch_pw<8, 4>(a, st);
+    case 8: return launch_pw<8, 2>(a, st);
     case 16: return launch_pw<16, 2>(a, st);
-    case 32: return launch_pw<32, 2>(a, st);
+    case 32: return launch_pw<32, 1>(a, st);
     case 64: {
       // 64 accumulators per thread leave too little occupancy: two passes of 32 channels (the
       // input row is 1/4 of the traffic or less, so reading it twice is cheap)
-      if (int s0 = launch_pw<32, 2>(a, st)) return s0;
+      if (int s0 = launch_pw<32, 1>(a, st)) return s0;
       a.co_base = 32;
-      return launch_pw<32, 2>(a, st);
+      return launch_pw<32, 1>(a, st);
     }
     default: return -1;
   }
