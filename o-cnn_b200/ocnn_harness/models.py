@@ -10,7 +10,13 @@ Two executors share one parameter set:
                 here so that tests and the benchmark drive both from the same description; it is
                 handed its operator module by the caller and imports nothing from oracle/ itself.
 """
+import os
+
 import numpy as np
+
+# 1x1x1 layers with few channels go to the streaming pointwise kernel from this many nodes up
+# (below it the tensor-core kernel is faster)
+PW_MIN_NODES = int(os.environ.get('OCNN_PW_MIN_NODES', '100000'))
 
 BN_EPS = 0.001   # pytorch/ocnn/modules.py:5
 
@@ -191,7 +197,7 @@ class GpuNet:
       # everything else that fits runs on the tensor-core kernel
       ex.add_conv(p['name'], d, p['_cin'], p['cout'], p['ks'], 1, p['_w'], p['_packed'],
                   p['_scale'], p['_bias'], relu, src, dst, res,
-                  500000 if p["_pointwise"] else -1)
+                  PW_MIN_NODES if p["_pointwise"] else -1)
       self.exec_layers.append(p['name'])
 
     cur, other = 0, 1
@@ -254,7 +260,7 @@ class GpuNet:
     p['_packed'] = None
     # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
     # else that fits goes to the tensor-core kernel
-    p['_pointwise'] = (p['ks'] == [1, 1, 1] and p['cout'] in (8, 16, 32, 64) and
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and p['cout'] in (8, 16, 32) and
                        cin * p['cout'] <= 4096)
     if self.tc and cin % 8 == 0 and p['cout'] % 8 == 0 and (p['cout'] <= 256 or p['cout'] % 256 == 0):
       try:
@@ -265,7 +271,7 @@ class GpuNet:
   def _conv(self, x, p, octree, d, relu, residual=None):
     nn = self.ocnn.nn
     self.launches += 1
-    if p['_packed'] is not None and not (p['_pointwise'] and x.shape[2] >= 500000):
+    if p['_packed'] is not None and not (p['_pointwise'] and x.shape[2] >= PW_MIN_NODES):
       return self._traced(p['name'], lambda: nn.octree_conv_tc(
           x, p['_packed'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual,
           relu, self.status))
