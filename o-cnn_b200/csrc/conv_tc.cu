@@ -226,7 +226,7 @@ __device__ __forceinline__ void chunk_src(int cpt, int kb, int chunk, int& t, ui
 }
 
 template <int CPT>
-__global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
+__global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of address bits [4,10)
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -398,17 +398,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of ours in flight past this point
 
     // ---------------- epilogue: TMEM -> registers -> global ----------------
-    // The residual is read one 128-byte line (64 channels) of the row at a time, all eight 16-byte
-    // pieces of a line at once and the next line before the current one is used; the first line
-    // is requested before the wait for the accumulator.
+    // The residual is read 64 bytes (32 channels) of the row at a time, the four 16-byte pieces at
+    // once and the next four before the current ones are used; the first are requested before
+    // the wait for the accumulator.
     const int h = h0 + r;
     const bool row_ok = r < a.tile_rows && h < a.rows;
     const __nv_bfloat16* res_row =
         (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + a.co_base : nullptr;
-    uint4 res_nxt[8];
+    uint4 res_nxt[4];
     auto load_line = [&](int c0) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
+      for (int q = 0; q < 4; ++q) {
         res_nxt[q] = make_uint4(0, 0, 0, 0);
         if (res_row != nullptr && c0 + 8 * q < a.row_elems)
           res_nxt[q] = *reinterpret_cast<const uint4*>(res_row + c0 + 8 * q);
@@ -422,13 +422,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_tc_kernel(const TcArgs a) {
     if (alive) {
       __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + a.co_base;
       const bool has_sb = a.scale != nullptr || a.bias != nullptr;
-      for (int c0 = 0; c0 < a.npad; c0 += 64) {
-        uint4 res_cur[8];
+      for (int c0 = 0; c0 < a.npad; c0 += 32) {
+        uint4 res_cur[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) res_cur[q] = res_nxt[q];
-        if (c0 + 64 < a.npad) load_line(c0 + 64);
+        for (int q = 0; q < 4; ++q) res_cur[q] = res_nxt[q];
+        if (c0 + 32 < a.npad) load_line(c0 + 32);
 #pragma unroll
-        for (int step = 0; step < 4; ++step) {
+        for (int step = 0; step < 2; ++step) {
           const int n0 = c0 + 16 * step;
           if (n0 >= a.npad) break;
           uint32_t v[16];
