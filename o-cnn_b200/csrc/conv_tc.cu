@@ -639,7 +639,7 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + (size_t)s->npad * 8 + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
   // every stage of the ring can be in flight at once, so prefer two CTAs per SM (set-up and
-  // epilogue of one overlap the main loop of the other) whenever each still gets 3 stages
+  // epilogue of one overlap the main loop of the other) whenever each still gets 2 stages
   int st = two_cta > fixed ? (int)((two_cta - fixed) / stage_bytes) : 0;
   // a grid that does not even fill the SMs once gains nothing from co-residency: give the lone CTA
   // of each SM the deepest ring instead (its K loop is a pure latency chain)
@@ -653,7 +653,7 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
          8.0 * s->tile_rows > 3.2 * s->npad)
     s->tile_rows >>= 1;
   const bool small_grid = rows >= 0 && (rows + s->tile_rows - 1) / s->tile_rows <= kSMs;
-  if (st < 3 || 2 * s->tmem_cols > 512 || small_grid) {
+  if (st < 2 || 2 * s->tmem_cols > 512 || small_grid) {
     st = (int)((one_cta - fixed) / stage_bytes);
     if (st > 7) st = 7;
   } else if (st > 6) {
