@@ -412,11 +412,11 @@ def run_ours(args):
       roofline = {'bound': 'hbm', 'achieved': ach, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                   'frac': ach / peaks['hbm_gbs']}
     # DRAM traffic of this kernel per launch: dram__bytes_read + dram__bytes_write from the ncu
-    # capture summarised in profiles/conv_tc_kernel_group_8to32_d6_ncu.md (58.5 B per node at
+    # capture summarised in profiles/conv_tc_kernel_group_8to32_d6_ncu.md (59.7 B per node at
     # 931 k nodes), scaled by the node count of this launch; only known for that kernel shape
     traffic = None
     if top_layer == 'conv1' and pp['cin'] == 8 and p_top['cout'] == 32:
-      traffic = 58.5 * h_top
+      traffic = 59.7 * h_top
     roofline.update({'traffic': traffic, 'kernel': 'octree_conv ' + top_layer,
                      'shape': {'cin': pp['cin'], 'cout': p_top['cout'], 'taps': 27 if p_top['ks'][0] == 3 else 1,
                                'nodes': h_top},
