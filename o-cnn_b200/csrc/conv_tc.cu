@@ -19,11 +19,14 @@
 // contiguous stretch of the node-major output.  2.4x the flops (the tensor core idles anyway at
 // these channel counts) for 3.4x fewer gathers and a tile of 1024 nodes instead of 128.
 //
-// Warp roles (192 threads): warps 0-3 gather A (one tile row per thread) and later run the
-// epilogue (TMEM lane quarter = warp id); warp 4 allocates TMEM and its lane 0 issues the MMAs;
-// lane 0 of warp 5 streams the weight tiles.  A 4-stage ring of {A tile, B tile} buffers is
-// handed between them with mbarriers: full[s] (128 gather arrivals + the weight copy's bytes),
-// empty[s] (tcgen05.commit when the MMAs that read the stage have retired).
+// Warp roles (192 threads): warps 0-3 gather A (one tile row per thread, or four tile rows per
+// warp instruction for the few-channel group layers) and later run the epilogue (TMEM lane
+// quarter = warp id); warp 4 allocates TMEM and its lane 0 issues the MMAs; lane 0 of warp 5
+// streams the weight tiles.  A ring of 2-7 {A tile, B tile} stages is handed between them with
+// mbarriers: full[s] (128 gather arrivals, each fired by cp.async.mbarrier.arrive.noinc when the
+// thread's copies have landed, + the weight copy's bytes), empty[s] (tcgen05.commit when the MMAs
+// that read the stage have retired).  A level too small to fill the SMs runs 64- or 32-row tiles:
+// the MMA is still 128 rows, the rows a tile does not have are neither gathered nor stored.
 //
 // Every wait is bounded: a wait that runs out sets *status (and a CTA-wide abort flag), the CTA
 // drains its own copies, frees its TMEM and returns — the launch never hangs the GPU.
@@ -46,7 +49,6 @@ struct TcArgs {
   __nv_bfloat16* y;
   const int* neigh;
   int h_in, h_out, cin, cout, npad, T, stride, identity, nkb, stages, tmem_cols;
-  int lag;          // gather arrivals trail the issue by this many K-blocks (1..4, < stages)
   int group;        // 1: tile rows are sibling groups (see the header comment), 0: nodes
   int rows;         // number of tile rows in total: h_out, or h_out / 8 in group mode
   int row_elems;    // output elements per tile row: cout, or 8 * cout in group mode
@@ -606,7 +608,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, lag, group, slices, tile_rows; size_t smem; };
+struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows; size_t smem; };
 
 int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1) {
   const TapList tl = taps_for_kernel(ks);
@@ -633,8 +635,7 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   s->tmem_cols = 32;
   while (s->tmem_cols < s->npad) s->tmem_cols *= 2;
   // Ring depth.  Prefer a footprint that lets two CTAs share an SM (their set-up and epilogue
-  // phases then overlap each other's main loop); otherwise take what one CTA can hold.  The gather
-  // arrivals trail the issue by `lag` K-blocks, and the ring must be deeper than the lag.
+  // phases then overlap each other's main loop); otherwise take what one CTA can hold.
   const size_t stage_bytes = (size_t)kStageA + (size_t)s->npad * 128;
   const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + (size_t)s->npad * 8 + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
@@ -661,7 +662,6 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   }
   if (st > s->nkb) st = s->nkb < 2 ? 2 : s->nkb;
   s->stages = st;
-  s->lag = 0;
   s->smem = fixed + (size_t)s->stages * stage_bytes;
   return OCNN_OK;
 }
@@ -738,7 +738,6 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout; a.npad = s.npad; a.T = s.T;
   a.stride = stride; a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
   a.tmem_cols = s.tmem_cols;
-  a.lag = s.lag;
   a.group = s.group;
   a.rows = s.group ? h_out / 8 : h_out;
   const int cslice = s.slices > 1 ? 256 : cout;
