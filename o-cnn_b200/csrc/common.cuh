@@ -57,6 +57,36 @@ inline int grid_for(long long work, int threads, int blocks_per_sm = 8) {
   return (int)(need < cap ? need : cap);
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// The layers of a forward pass are a chain of short dependent kernels.  A kernel launched with
+// launch_chained() may be scheduled while its predecessor in the stream is still running its last
+// wave: its CTAs do their private set-up (barrier init, TMEM allocation) and then block in
+// grid_dependency_wait() until the predecessor has completed and its writes are visible.  Every
+// kernel launched this way must call grid_dependency_wait() before its first access to global
+// memory, and calls grid_dependency_trigger() first thing so that its own successor can queue up.
+__device__ __forceinline__ void grid_dependency_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- neighbour index arithmetic ---------------------------------------------------------------
 // Position, inside the 4x4x4 neighbour block of a sibling group, of the cell at offset
 // (tx-1, ty-1, tz-1) from octant o of that group, tap = tx*9 + ty*3 + tz.  This is the closed

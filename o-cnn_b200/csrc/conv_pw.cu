@@ -26,6 +26,8 @@ struct PwArgs {
 template <int COUT, int ROWS>
 __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
   extern __shared__ float ws[];                      // [cin][COUT]
+  grid_dependency_trigger();
+  grid_dependency_wait();
   for (int i = threadIdx.x; i < a.cin * COUT; i += blockDim.x) {
     const int co = i / a.cin, ci = i % a.cin;        // coalesced read of w[co][ci], transposed store
     ws[ci * COUT + co] = a.w[(long long)a.co_base * a.cin + i];
@@ -122,7 +124,7 @@ int launch_pw(const PwArgs& a, cudaStream_t st) {
     if (device >= 0 && device < 64) attr_set[device] = true;
   }
   const int grid = grid_for(((long long)a.h + ROWS - 1) / ROWS, 256, 4);
-  conv_pw_kernel<COUT, ROWS><<<grid, 256, smem, st>>>(a);
+  OCNN_CUDA_OK(launch_chained(conv_pw_kernel<COUT, ROWS>, dim3(grid), dim3(256), smem, st, a));
   OCNN_LAUNCH_OK("conv_pw_kernel");
   return OCNN_OK;
 }

@@ -250,6 +250,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h0 = blockIdx.x * a.tile_rows;
+  grid_dependency_trigger();     // the next layer's CTAs may queue up behind this grid's last wave
 
   if (tid == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -260,18 +261,21 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)), "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // everything above is private to the CTA; from here on global memory is read, so the previous
+  // kernel of the stream must have completed
+  grid_dependency_wait();
   for (int n = tid; n < a.npad; n += kThreads) {
     // output channel of column n: columns are (octant, channel) pairs in group mode
     const int co = a.group ? (n & (a.cout - 1)) : a.co_base + n;
     const bool live = n < a.row_elems;
     s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
     s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
-  }
-  if (warp == 4) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_holder)), "r"((uint32_t)a.tmem_cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid < kTileM) {
     const int h = h0 + tid;          // node, or sibling group in group mode
@@ -789,7 +793,8 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   for (int sl = 0; sl < s.slices; ++sl) {
     a.co_base = sl * cslice;
     a.wpacked = static_cast<const uint8_t*>(packed) + (size_t)sl * s.nkb * s.npad * 128;
-    kernel<<<ceil_div(a.rows, a.tile_rows), kThreads, s.smem, static_cast<cudaStream_t>(stream)>>>(a);
+    OCNN_CUDA_OK(launch_chained(kernel, dim3(ceil_div(a.rows, a.tile_rows)), dim3(kThreads), s.smem,
+                                static_cast<cudaStream_t>(stream), a));
     OCNN_LAUNCH_OK("conv_tc_kernel");
   }
   return OCNN_OK;

@@ -178,6 +178,8 @@ template <bool PADDED>
 __global__ void __launch_bounds__(256) max_pool_nm_bf16x8_kernel(
     const uint4* __restrict__ btm, uint4* __restrict__ top, int* __restrict__ mask,
     const int* __restrict__ child, int chunks, long long total) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long row = i / chunks;
@@ -305,8 +307,9 @@ int pool_impl(const void* btm, void* top, int* mask, int C, int top_h, int layou
   } else if (sizeof(T) == 2 && C % 8 == 0 && (uintptr_t)btm % 16 == 0 && (uintptr_t)top % 16 == 0 &&
              (uintptr_t)mask % 16 == 0) {
     const long long vec_total = total / 8;
-    max_pool_nm_bf16x8_kernel<false><<<grid_for(vec_total, 256, 8), 256, 0, st>>>(
-        (const uint4*)btm, (uint4*)top, mask, nullptr, C / 8, vec_total);
+    OCNN_CUDA_OK(launch_chained(max_pool_nm_bf16x8_kernel<false>, dim3(grid_for(vec_total, 256, 8)),
+                                dim3(256), 0, st, (const uint4*)btm, (uint4*)top, mask,
+                                (const int*)nullptr, C / 8, vec_total));
   } else {
     max_pool_nm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)btm, (T*)top, mask, C,
                                                                 total);
@@ -356,8 +359,9 @@ int ocnn_octree_max_pool_pad(const void* btm, void* top, const int32_t* child, i
   OCNN_REQUIRE((uintptr_t)btm % 16 == 0 && (uintptr_t)top % 16 == 0,
                "ocnn_octree_max_pool_pad: data pointers must be 16-byte aligned");
   const long long total = (long long)top_h * (C / 8);
-  max_pool_nm_bf16x8_kernel<true><<<grid_for(total, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const uint4*)btm, (uint4*)top, nullptr, child, C / 8, total);
+  OCNN_CUDA_OK(launch_chained(max_pool_nm_bf16x8_kernel<true>, dim3(grid_for(total, 256, 8)), dim3(256),
+                              0, static_cast<cudaStream_t>(stream), (const uint4*)btm, (uint4*)top,
+                              (int*)nullptr, (const int*)child, C / 8, total));
   OCNN_LAUNCH_OK("octree_max_pool_pad");
   return OCNN_OK;
 }
