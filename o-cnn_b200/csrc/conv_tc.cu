@@ -57,6 +57,7 @@ struct TcArgs {
   int co_base;      // first output channel this launch produces
   int tile_rows;    // tile rows a CTA actually computes (128, 64 or 32): small levels are cut into
                     // more, emptier tiles so that every SM gets one; the MMA is always 128 rows
+  int wide;         // output (and residual) rows can be accessed 32 bytes at a time
   int rowsplit;     // gather mapping: 1 = four tile rows per warp instruction, 0 = one per thread
   const float* scale;
   const float* bias;
@@ -143,6 +144,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
         "=r"(v[14]), "=r"(v[15])
       : "r"(taddr));
+}
+
+// 32-byte global accesses (256-bit loads and stores exist from sm_100): half as many requests on
+// the SM's load/store path as 16-byte ones.  The address must be 32-byte aligned.
+__device__ __forceinline__ void ld_global_32B(const void* p, uint4& lo, uint4& hi) {
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
+                 "=r"(hi.w)
+               : "l"(p));
+}
+__device__ __forceinline__ void st_global_32B(void* p, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(lo.x), "r"(lo.y),
+               "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
@@ -414,10 +429,17 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     uint4 res_nxt[4];
     auto load_line = [&](int c0) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        res_nxt[q] = make_uint4(0, 0, 0, 0);
-        if (res_row != nullptr && c0 + 8 * q < a.row_elems)
-          res_nxt[q] = *reinterpret_cast<const uint4*>(res_row + c0 + 8 * q);
+      for (int q = 0; q < 4; ++q) res_nxt[q] = make_uint4(0, 0, 0, 0);
+      if (res_row == nullptr) return;
+      if (a.wide) {
+#pragma unroll
+        for (int q = 0; q < 4; q += 2)
+          if (c0 + 8 * q < a.row_elems) ld_global_32B(res_row + c0 + 8 * q, res_nxt[q], res_nxt[q + 1]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (c0 + 8 * q < a.row_elems)
+            res_nxt[q] = *reinterpret_cast<const uint4*>(res_row + c0 + 8 * q);
       }
     };
     load_line(0);
@@ -440,6 +462,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
           uint32_t v[16];
           tmem_ld16(lane_base + (uint32_t)n0, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          uint4 ov[2];
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             const int n = n0 + 8 * half;
@@ -471,12 +494,12 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
             }
-            uint4 ov;
-            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov[half]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-            *reinterpret_cast<uint4*>(y_row + n) = ov;
+            if (!a.wide) *reinterpret_cast<uint4*>(y_row + n) = ov[half];
           }
+          if (a.wide && row_ok && n0 < a.row_elems) st_global_32B(y_row + n0, ov[0], ov[1]);
         }
       }
     }
@@ -751,6 +774,9 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.co_base = 0;
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
   a.tile_rows = s.tile_rows;
+  // 32-byte epilogue accesses: rows and channel slices on 32-byte boundaries
+  a.wide = (a.row_elems % 16 == 0 && a.y_stride % 16 == 0 && (uintptr_t)y % 32 == 0 &&
+            (!(ep && ep->residual_dev) || (uintptr_t)ep->residual_dev % 32 == 0)) ? 1 : 0;
   if (s.group)
     OCNN_REQUIRE(h_out % 8 == 0, "ocnn_octree_conv_tc: an octree level holds whole sibling groups "
                  "(got %d nodes)", h_out);
