@@ -87,6 +87,21 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// ---- 32-byte global accesses ------------------------------------------------------------------
+// 256-bit loads and stores exist from sm_100: half as many requests on the SM's load/store path as
+// 16-byte ones.  The address must be 32-byte aligned.
+__device__ __forceinline__ void ld_global_32B(const void* p, uint4& lo, uint4& hi) {
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
+                 "=r"(hi.w)
+               : "l"(p));
+}
+__device__ __forceinline__ void st_global_32B(void* p, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(lo.x), "r"(lo.y),
+               "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 // ---- neighbour index arithmetic ---------------------------------------------------------------
 // Position, inside the 4x4x4 neighbour block of a sibling group, of the cell at offset
 // (tx-1, ty-1, tz-1) from octant o of that group, tap = tx*9 + ty*3 + tz.  This is the closed

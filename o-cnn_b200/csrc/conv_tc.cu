@@ -146,20 +146,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr));
 }
 
-// 32-byte global accesses (256-bit loads and stores exist from sm_100): half as many requests on
-// the SM's load/store path as 16-byte ones.  The address must be 32-byte aligned.
-__device__ __forceinline__ void ld_global_32B(const void* p, uint4& lo, uint4& hi) {
-  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
-                 "=r"(hi.w)
-               : "l"(p));
-}
-__device__ __forceinline__ void st_global_32B(void* p, const uint4& lo, const uint4& hi) {
-  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(lo.x), "r"(lo.y),
-               "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
-               : "memory");
-}
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
                : "memory");
