@@ -58,7 +58,8 @@ struct TcArgs {
   int tile_rows;    // tile rows a CTA actually computes (128, 64 or 32): small levels are cut into
                     // more, emptier tiles so that every SM gets one; the MMA is always 128 rows
   int wide;         // output (and residual) rows can be accessed 32 bytes at a time
-  int rowsplit;     // gather mapping: 1 = four tile rows per warp instruction, 0 = one per thread
+  int rowsplit;     // gather mapping: 0 = one tile row per thread; four tile rows per warp
+                    // instruction: 1 = group mode with 8 or 16 channels, 2 = node mode, Cin % 64 == 0
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -287,10 +288,13 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     } else {
       const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
       if (a.identity) {
-        nbr[tid] = live ? h : -1;
+        nbr[a.rowsplit == 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid] = live ? h : -1;
       } else {
       // all (up to 27) table reads are issued before the first result is used: a load-then-store
       // loop would expose the L2 latency once per tap
+      // with the four-rows-per-instruction mapping a thread serves rows sub + 4*i of its warp: their
+      // entries are stored next to each other so that it reads them as two 16-byte words
+      const int slot = a.rowsplit == 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid;
       int pv[27];
 #pragma unroll
       for (int t = 0; t < 27; ++t) {
@@ -306,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
       }
 #pragma unroll
       for (int t = 0; t < 27; ++t)
-        if (t < a.T) nbr[t * kTileM + tid] = pv[t];
+        if (t < a.T) nbr[t * kTileM + slot] = pv[t];
       }
     }
   }
@@ -319,7 +323,56 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     // ---------------- A gather ----------------
     const int r = tid;
     bool alive = true;
-    if (a.rowsplit) {
+    if ((CPT >= 8 || CPT == 0) && a.rowsplit == 2) {
+      // Node mode with Cin a multiple of 64: a K-block of a tile row is one contiguous 128-byte stretch of a
+      // neighbour's row.  A warp instruction copies four whole rows (lane = row within the four,
+      // 16-byte chunk): every fetched sector is used in full, where one row per thread fetches
+      // each 32-byte sector twice.  The thread's eight row indices of a tap are two 16-byte reads
+      // of the shared table, once per tap.
+      if constexpr (CPT >= 8 || CPT == 0) {
+        const int kBlocksPerTap = CPT >= 8 ? CPT / 8 : a.cin >> 6;
+        const int sub = lane >> 3, chunk = lane & 7;
+        const int rbase = warp * 32 + sub;
+        const char* xb = reinterpret_cast<const char*>(a.x);
+        const uint32_t row_bytes = (uint32_t)a.cin * 2u;
+        const int* my_idx = nbr + warp * 32 + sub * 8;
+        uint32_t row_mask = 0;        // bit i: tile row rbase + 4*i exists
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (rbase + 4 * i < a.tile_rows && h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
+        int p[8];
+        int s = 0;
+        uint32_t pe = 1;
+        int t = 0, part = 0;
+        for (int kb = 0; kb < a.nkb; ++kb) {
+          if (part == 0) {
+            const int4 lo = *reinterpret_cast<const int4*>(my_idx + t * kTileM);
+            const int4 hi = *reinterpret_cast<const int4*>(my_idx + t * kTileM + 4);
+            p[0] = lo.x; p[1] = lo.y; p[2] = lo.z; p[3] = lo.w;
+            p[4] = hi.x; p[5] = hi.y; p[6] = hi.z; p[7] = hi.w;
+          }
+          if (alive && kb >= a.stages)
+            alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
+          if (alive) {
+            const uint32_t stage_base = smem_u32(sA + s * kStageA);
+            const uint32_t off = (uint32_t)part * 128u + (uint32_t)chunk * 16u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = rbase + 4 * i;
+              const uint32_t dst = stage_base + (uint32_t)row * 128u +
+                                   (((uint32_t)chunk ^ (uint32_t)(row & 7)) << 4);
+              const int pi = p[i];
+              const char* src = pi >= 0 ? xb + (size_t)((uint32_t)pi * row_bytes) + off : xb;
+              if ((row_mask >> i) & 1u) cp_async16(dst, src, pi >= 0 ? 16u : 0u);
+            }
+          }
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
+                       : "memory");
+          if (++s == a.stages) { s = 0; pe ^= 1u; }
+          if (++part == kBlocksPerTap) { part = 0; ++t; }
+        }
+      }
+    } else if (a.rowsplit) {
       // Sibling-group mode with 8 or 16 channels: every 16-byte chunk of a tile row comes from a
       // different node, so "one tile row per thread" makes each warp instruction touch 32
       // unrelated lines.  Here a warp instruction copies the 8 chunks of a K-block for 4 tile rows
@@ -759,6 +812,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.y_stride = s.group ? 8 * cout : cout;
   a.co_base = 0;
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
+  if (!s.group && cin % 64 == 0) a.rowsplit = 2;
   a.tile_rows = s.tile_rows;
   // 32-byte epilogue accesses: rows and channel slices on 32-byte boundaries
   a.wide = (a.row_elems % 16 == 0 && a.y_stride % 16 == 0 && (uintptr_t)y % 32 == 0 &&

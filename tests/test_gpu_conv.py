@@ -150,6 +150,11 @@ TC_CASES = [
     (5, 24, 8, [3, 3, 3], 1),      # sibling-group mode with 3 chunks per neighbour row
     (6, 8, 16, [2, 2, 2], 1),
     (5, 32, 32, [1, 3, 3], 1),
+    (3, 192, 64, [3, 3, 3], 1),    # Cin a multiple of 64 but not a power of two
+    (4, 64, 32, [3, 3, 3], 2),     # stride 2 with whole-row gathers
+    (4, 64, 48, [2, 2, 2], 2),
+    (3, 128, 128, [1, 1, 1], 1),
+    (4, 320, 16, [1, 1, 1], 1),
 ]
 
 
