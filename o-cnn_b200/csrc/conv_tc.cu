@@ -39,6 +39,8 @@ constexpr int kTileM = 128;          // nodes per CTA = TMEM lanes
 constexpr int kBlockK = 64;          // bf16 elements per K-block = one 128-byte swizzle row
 constexpr int kStageA = kTileM * 128;  // bytes of one A stage
 constexpr int kThreads = 192;
+constexpr int kGroupTableStride = 132;   // ints between positions in the group-mode index table:
+                                         // 4*position + slot spreads a 16-byte read over all banks
 constexpr unsigned kSpinLimit = 1u << 20;
 
 enum : int { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccumWait = 3, kErrWeightWait = 4 };
@@ -59,7 +61,8 @@ struct TcArgs {
                     // more, emptier tiles so that every SM gets one; the MMA is always 128 rows
   int wide;         // output (and residual) rows can be accessed 32 bytes at a time
   int rowsplit;     // gather mapping: 0 = one tile row per thread; four tile rows per warp
-                    // instruction: 1 = group mode with 8 or 16 channels, 2 = node mode, Cin % 64 == 0
+                    // instruction: 1 = group mode with 8 or 16 channels (indices from global memory),
+                    // 2 = node mode, Cin % 64 == 0, 3 = group mode through the shared index table
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -241,7 +244,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   // per-column scale and bias of the epilogue, staged once per CTA: read from global memory in
   // the epilogue they were a chain of cold misses (one per 128-byte line of each array) that every
   // thread of a one-wave launch sat through
-  float* s_scale = reinterpret_cast<float*>(nbr + (a.group ? 0 : a.T * kTileM));
+  float* s_scale = reinterpret_cast<float*>(
+      nbr + (a.group ? (a.rowsplit == 3 ? 64 * kGroupTableStride : 0) : a.T * kTileM));
   float* s_bias = s_scale + a.npad;
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + a.npad);
   uint64_t* full = bars;
@@ -283,8 +287,21 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     const int h = h0 + tid;          // node, or sibling group in group mode
     const bool live = tid < a.tile_rows && h < a.rows;
     if (a.group) {
-      // nothing to stage: the group's neighbour block IS the list of rows to gather, 64
-      // contiguous ints that the gather reads straight from global memory
+      // The group's neighbour block IS the list of rows to gather, 64 contiguous ints.  The
+      // gather either reads them straight from global memory, or (rowsplit == 3) from a shared
+      // table [position][slot] that is filled here, 16 reads in flight at a time.
+      if (a.rowsplit == 3) {
+        const int slot = (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7);
+        const int* blk = a.neigh + ((long long)(live ? h : 0) << 6);
+#pragma unroll
+        for (int t0 = 0; t0 < 64; t0 += 16) {
+          int pv[16];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) pv[t] = live ? __ldg(blk + t0 + t) : -1;
+#pragma unroll
+          for (int t = 0; t < 16; ++t) nbr[(t0 + t) * kGroupTableStride + slot] = pv[t];
+        }
+      }
     } else {
       const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
       if (a.identity) {
@@ -388,9 +405,22 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         if (rbase + 4 * i < a.tile_rows && h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
+      const int* my_idx = nbr + warp * 32 + sub * 8;     // rowsplit == 3: this thread's 8 rows
       auto fetch = [&](int kb, int (&p)[8], uint32_t& off) {
         int t;
         chunk_src<CPT>(cpt, kb, chunk, t, off);
+        if (a.rowsplit == 3) {
+          if (t < a.T) {
+            const int4 lo = *reinterpret_cast<const int4*>(my_idx + t * kGroupTableStride);
+            const int4 hi = *reinterpret_cast<const int4*>(my_idx + t * kGroupTableStride + 4);
+            p[0] = lo.x; p[1] = lo.y; p[2] = lo.z; p[3] = lo.w;
+            p[4] = hi.x; p[5] = hi.y; p[6] = hi.z; p[7] = hi.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) p[i] = -1;
+          }
+          return;
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           p[i] = -1;
@@ -674,7 +704,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows; size_t smem; };
+struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable; size_t smem; };
 
 int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1) {
   const TapList tl = taps_for_kernel(ks);
@@ -703,7 +733,11 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   // Ring depth.  Prefer a footprint that lets two CTAs share an SM (their set-up and epilogue
   // phases then overlap each other's main loop); otherwise take what one CTA can hold.
   const size_t stage_bytes = (size_t)kStageA + (size_t)s->npad * 128;
-  const size_t fixed = 1024 + (s->group ? 0 : (size_t)s->T * kTileM * 4) + (size_t)s->npad * 8 + 256;
+  // group mode with more than 16 channels gathers through a shared index table (fewer index reads
+  // in the loop); with 8 or 16 channels filling the table costs more than it saves
+  s->gtable = (s->group && cin > 16) ? 1 : 0;
+  const size_t fixed = 1024 + (s->group ? (s->gtable ? 64 * kGroupTableStride * 4 : 0) : (size_t)s->T * kTileM * 4) +
+                       (size_t)s->npad * 8 + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
   // every stage of the ring can be in flight at once, so prefer two CTAs per SM (set-up and
   // epilogue of one overlap the main loop of the other) whenever each still gets 2 stages
@@ -812,6 +846,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.y_stride = s.group ? 8 * cout : cout;
   a.co_base = 0;
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
+  if (s.gtable) a.rowsplit = 3;
   if (!s.group && cin % 64 == 0) a.rowsplit = 2;
   a.tile_rows = s.tile_rows;
   // 32-byte epilogue accesses: rows and channel slices on 32-byte boundaries
