@@ -56,7 +56,6 @@ struct TcArgs {
   int row_elems;    // output elements per tile row: cout, or 8 * cout in group mode
   int y_stride;     // elements between consecutive output rows (= row_elems unless the layer's
                     // output channels are produced in several launches)
-  int co_base;      // first output channel this launch produces
   int tile_rows;    // tile rows a CTA actually computes (128, 64 or 32): small levels are cut into
                     // more, emptier tiles so that every SM gets one; the MMA is always 128 rows
   int wide;         // output (and residual) rows can be accessed 32 bytes at a time
@@ -256,6 +255,9 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h0 = blockIdx.x * a.tile_rows;
+  // blockIdx.y = 256-channel slice of the output (layers with more than 256 output channels)
+  const int co_base = blockIdx.y * a.cout;
+  const uint8_t* wpacked = a.wpacked + (size_t)blockIdx.y * a.nkb * (a.npad * 128);
   grid_dependency_trigger();     // the next layer's CTAs may queue up behind this grid's last wave
 
   if (tid == 0) {
@@ -278,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   grid_dependency_wait();
   for (int n = tid; n < a.npad; n += kThreads) {
     // output channel of column n: columns are (octant, channel) pairs in group mode
-    const int co = a.group ? (n & (a.cout - 1)) : a.co_base + n;
+    const int co = a.group ? (n & (a.cout - 1)) : co_base + n;
     const bool live = n < a.row_elems;
     s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
     s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
@@ -494,7 +496,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     const int h = h0 + r;
     const bool row_ok = r < a.tile_rows && h < a.rows;
     const __nv_bfloat16* res_row =
-        (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + a.co_base : nullptr;
+        (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + co_base : nullptr;
     uint4 res_nxt[4];
     auto load_line = [&](int c0) {
 #pragma unroll
@@ -517,7 +519,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
     if (alive) {
-      __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + a.co_base;
+      __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + co_base;
       const bool has_sb = a.scale != nullptr || a.bias != nullptr;
       for (int c0 = 0; c0 < a.npad; c0 += 32) {
         uint4 res_cur[4];
@@ -612,7 +614,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
       const int wave = gridDim.x < kSMs ? (int)gridDim.x : kSMs;
       if ((int)blockIdx.x < wave) {
         for (int kb = blockIdx.x + lane * wave; kb < a.nkb; kb += 32 * wave)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.wpacked + (size_t)kb * stage_b),
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wpacked + (size_t)kb * stage_b),
                        "r"((uint32_t)stage_b)
                        : "memory");
       }
@@ -629,7 +631,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
         mbar_arrive_expect_tx(bar, (uint32_t)stage_b);
         asm volatile(
             "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-            ::"r"(smem_u32(sB + s * stage_b)), "l"(a.wpacked + (size_t)kb * stage_b),
+            ::"r"(smem_u32(sB + s * stage_b)), "l"(wpacked + (size_t)kb * stage_b),
               "r"((uint32_t)stage_b), "r"(bar)
             : "memory");
         if (++s == a.stages) { s = 0; pe ^= 1u; }
@@ -844,7 +846,6 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.cout = cslice;
   a.row_elems = s.group ? 8 * cout : cslice;
   a.y_stride = s.group ? 8 * cout : cout;
-  a.co_base = 0;
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
   if (s.gtable) a.rowsplit = 3;
   if (!s.group && cin % 64 == 0) a.rowsplit = 2;
@@ -891,13 +892,10 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
                "ocnn_octree_conv_tc: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses",
                (long long)h_in * cin * 2);
-  for (int sl = 0; sl < s.slices; ++sl) {
-    a.co_base = sl * cslice;
-    a.wpacked = static_cast<const uint8_t*>(packed) + (size_t)sl * s.nkb * s.npad * 128;
-    OCNN_CUDA_OK(launch_chained(kernel, dim3(ceil_div(a.rows, a.tile_rows)), dim3(kThreads), s.smem,
-                                static_cast<cudaStream_t>(stream), a));
-    OCNN_LAUNCH_OK("conv_tc_kernel");
-  }
+  a.wpacked = static_cast<const uint8_t*>(packed);
+  OCNN_CUDA_OK(launch_chained(kernel, dim3(ceil_div(a.rows, a.tile_rows), s.slices), dim3(kThreads), s.smem,
+                              static_cast<cudaStream_t>(stream), a));
+  OCNN_LAUNCH_OK("conv_tc_kernel");
   return OCNN_OK;
 }
 
