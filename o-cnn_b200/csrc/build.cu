@@ -166,8 +166,33 @@ __global__ void __launch_bounds__(kThreads) sort_hist_kernel(const KeyT* __restr
   const long long beg = (long long)blockIdx.x * vchunk;
   long long end = beg + vchunk;
   if (end > n) end = n;
-  for (long long i = beg + threadIdx.x; i < end; i += kThreads)
-    atomicAdd(&sh[warp][(int)((keys[i] >> shift) & 255)], 1);
+  // Eight keys per thread are requested before the first is counted.  Keys that are close in
+  // memory often share the digit (the input is sorted by the lower digits, and the top digit is
+  // the cloud index): a run of equal digits in consecutive lanes is added once, by its first lane.
+  const int lane = threadIdx.x & 31;
+  for (long long i0 = beg; i0 < end; i0 += 8 * kThreads) {
+    KeyT k[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const long long i = i0 + u * kThreads + threadIdx.x;
+      k[u] = i < end ? keys[i] : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const long long i = i0 + u * kThreads + threadIdx.x;
+      // lanes past the end carry digit 256, which no counted lane has
+      const int digit = i < end ? (int)((k[u] >> shift) & 255) : 256;
+      const int prev = __shfl_up_sync(0xffffffffu, digit, 1);
+      const bool head = lane == 0 || prev != digit;
+      const unsigned heads = __ballot_sync(0xffffffffu, head);
+      if (head && digit < 256) {
+        // the run ends before the next head (or at the end of the warp)
+        const unsigned later = lane == 31 ? 0u : (heads >> (lane + 1));
+        const int run = later ? __ffs(later) : 32 - lane;
+        atomicAdd(&sh[warp][digit], run);
+      }
+    }
+  }
   __syncthreads();
   int total = 0;
 #pragma unroll
@@ -473,10 +498,19 @@ __global__ void emit_level_kernel(EmitLevelArgs a, const uint64_t* __restrict__ 
     const uint64_t pk = Kp[p];
     const int b = (int)(pk >> (3 * (a.d - 1)));
     store_key(a.out, a.off_key, i, ((pk & local_mask) << 3) | (uint64_t)j, b, a.key_bytes);
+    // The group's children are the s1 - s0 <= 8 keys Kc[s0..s1): lane j of the group's 8 lanes
+    // fetches Kc[s0 + j], and each lane then picks, among the group's lanes, the one whose key
+    // ends in its own octant.  (The level's node count is a multiple of 8 and so is the grid's
+    // stride, so the 8 lanes of a group always run together.)
+    const int s0 = start[p], s1 = start[p + 1];
+    const int mine = s0 + j < s1 ? (int)(Kc[s0 + j] & 7) : -1;
+    const unsigned group_mask = 0xffu << (threadIdx.x & 24);
     int ch = -1;
-    const int s1 = start[p + 1];
-    for (int s = start[p]; s < s1; ++s)
-      if ((int)(Kc[s] & 7) == j) ch = s;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int oct = __shfl_sync(group_mask, mine, u, 8);
+      if (oct == j) ch = s0 + u;
+    }
     reinterpret_cast<int*>(a.out + a.off_child)[i] = ch;
     if (a.off_split >= 0) reinterpret_cast<float*>(a.out + a.off_split)[i] = ch < 0 ? 0.f : 1.f;
   }
