@@ -55,27 +55,75 @@ __global__ void depad_cm_kernel(const T* __restrict__ y, T* __restrict__ x,
   }
 }
 
+// fp32 channel-major depad, four consecutive h per thread (16-byte reads of y and child); the
+// grid's y dimension is the channel, so no division per element
+__global__ void depad_cm_f32x4_kernel(const float* __restrict__ y, float* __restrict__ x,
+                                      const int* __restrict__ child, int Hx, int Hy) {
+  const int hv = Hy >> 2;
+  const float* yr = y + (long long)blockIdx.y * Hy;
+  float* xr = x + (long long)blockIdx.y * Hx;
+  for (int h4 = blockIdx.x * blockDim.x + threadIdx.x; h4 < hv; h4 += gridDim.x * blockDim.x) {
+    const int4 l = reinterpret_cast<const int4*>(child)[h4];
+    const float4 v = reinterpret_cast<const float4*>(yr)[h4];
+    if (l.x >= 0) xr[l.x] = v.x;
+    if (l.y >= 0) xr[l.y] = v.y;
+    if (l.z >= 0) xr[l.z] = v.z;
+    if (l.w >= 0) xr[l.w] = v.w;
+  }
+}
+
 // ---- node-major: rows of C elements; one thread per 16-byte chunk of a row ---------------------
 // row_bytes must be a multiple of 16 for the vector kernels.
 __global__ void pad_nm_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y,
                                   const int* __restrict__ child, int Hy, int chunks, uint4 fill) {
+  // four independent child -> row chains per thread and iteration: one chain per iteration makes
+  // the grid-stride loop wait for two dependent reads every time round
   const long long total = (long long)Hy * chunks;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int h = (int)(i / chunks), q = (int)(i % chunks);
-    const int l = child[h];
-    y[i] = l < 0 ? fill : x[(long long)l * chunks + q];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    int l[4], q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      l[u] = -1; q[u] = 0;
+      if (i < total) {
+        const int h = (int)(i / chunks);
+        q[u] = (int)(i - (long long)h * chunks);
+        l[u] = child[h];
+      }
+    }
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = l[u] < 0 ? fill : x[(long long)l[u] * chunks + q[u]];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) y[i] = v[u];
+    }
   }
 }
 
 __global__ void depad_nm_vec_kernel(const uint4* __restrict__ y, uint4* __restrict__ x,
                                     const int* __restrict__ child, int Hy, int chunks) {
   const long long total = (long long)Hy * chunks;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int h = (int)(i / chunks), q = (int)(i % chunks);
-    const int l = child[h];
-    if (l >= 0) x[(long long)l * chunks + q] = y[i];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    int l[4], q[4];
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {                    // all reads of the four items first
+      const long long i = i0 + u * stride;
+      l[u] = -1; q[u] = 0; v[u] = make_uint4(0, 0, 0, 0);
+      if (i < total) {
+        const int h = (int)(i / chunks);
+        q[u] = (int)(i - (long long)h * chunks);
+        l[u] = child[h];
+        v[u] = y[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (l[u] >= 0) x[(long long)l[u] * chunks + q[u]] = v[u];
   }
 }
 
@@ -260,7 +308,7 @@ int pad_impl(const void* x, void* y, const int* child, int C, int Hx, int Hy, fl
       const int chunks = (int)(row / 16);
       union { uint4 v; T e[16 / sizeof(T)]; } f;
       for (size_t k = 0; k < 16 / sizeof(T); ++k) f.e[k] = fv;
-      pad_nm_vec_kernel<<<grid_for((long long)Hy * chunks, 256), 256, 0, st>>>(
+      pad_nm_vec_kernel<<<grid_for(((long long)Hy * chunks + 3) / 4, 256), 256, 0, st>>>(
           (const uint4*)x, (uint4*)y, child, Hy, chunks, f.v);
     } else {
       pad_nm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, (T*)y, child, Hy, C, fv);
@@ -276,12 +324,17 @@ int depad_impl(const void* y, void* x, const int* child, int C, int Hx, int Hy, 
   const long long total = (long long)C * Hy;
   if (total == 0) return OCNN_OK;
   if (layout == OCNN_CHANNEL_MAJOR) {
-    depad_cm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)y, (T*)x, child, C, Hx, Hy);
+    if (sizeof(T) == 4 && Hy % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)child % 16 == 0 && C <= 65535) {
+      const int gx = grid_for(Hy / 4, 256, 8);
+      depad_cm_f32x4_kernel<<<dim3(gx, C), 256, 0, st>>>((const float*)y, (float*)x, child, Hx, Hy);
+    } else {
+      depad_cm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)y, (T*)x, child, C, Hx, Hy);
+    }
   } else {
     const size_t row = (size_t)C * sizeof(T);
     if (row % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
       const int chunks = (int)(row / 16);
-      depad_nm_vec_kernel<<<grid_for((long long)Hy * chunks, 256), 256, 0, st>>>(
+      depad_nm_vec_kernel<<<grid_for(((long long)Hy * chunks + 3) / 4, 256), 256, 0, st>>>(
           (const uint4*)y, (uint4*)x, child, Hy, chunks);
     } else {
       depad_nm_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)y, (T*)x, child, Hy, C);

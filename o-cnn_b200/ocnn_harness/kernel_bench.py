@@ -5,6 +5,7 @@ peaks.  This is also the program the ncu captures under profiles/ are taken from
     python o-cnn_b200/ocnn_harness/kernel_bench.py conv  --depth 6 --shapes 8 --cin 8 --cout 8
     python o-cnn_b200/ocnn_harness/kernel_bench.py conv  --depth 5 --shapes 32 --cin 128 --cout 128
     python o-cnn_b200/ocnn_harness/kernel_bench.py build --config 4 --clouds 64
+    python o-cnn_b200/ocnn_harness/kernel_bench.py merge --config 3
     python o-cnn_b200/ocnn_harness/kernel_bench.py ops   --depth 6 --shapes 32 --channels 32
 
 Algorithmic work per launch (what `achieved` divides by the measured time):
@@ -141,6 +142,26 @@ def run_build(args):
   ocnn.set_key_bits(64)
 
 
+def run_merge(args):
+  """octree_batch over octrees built one by one: the route for octrees that were not built by the
+  fused batch build (the merged result is the same)."""
+  kb = 32 if args.config == 4 else 64
+  depth = {2: 5, 3: 6, 4: 8, 5: 9}[args.config]
+  ocnn.set_key_bits(kb)
+  clouds = synth.config_clouds(args.config, args.clouds)
+  pts = make_points(clouds)
+  singles = [ocnn.nn.points2octree(p, depth, 2, False, False, False, False, 4, 0.1, 2.0, False,
+                                   False, False) for p in pts]
+  fn = lambda: ocnn.nn.octree_batch(singles)
+  merged = fn()
+  byts = sum(int(t.numel()) for t in singles) + int(merged.numel())
+  flush = torch.empty(256 << 20, dtype=torch.uint8, device='cuda') if args.flush else None
+  ms, best = time_op(fn, args.iters, flush=flush)
+  report('octree_batch (merge + neighbour table)', ms, best, byts, 0,
+         {'octrees': len(singles), 'depth': depth, 'key_bits': kb, 'merged_bytes': int(merged.numel())})
+  ocnn.set_key_bits(64)
+
+
 def run_ops(args):
   octree = build_octree(args.shapes, args.points, args.depth)
   info = ocnn.octree_info(octree)
@@ -184,6 +205,11 @@ def main():
   b.add_argument('--clouds', type=int, default=None)
   b.add_argument('--iters', type=int, default=10)
   b.add_argument('--no-flush', dest='flush', action='store_false')
+  g = sub.add_parser('merge')
+  g.add_argument('--config', type=int, default=3, choices=[2, 3, 4, 5])
+  g.add_argument('--clouds', type=int, default=None)
+  g.add_argument('--iters', type=int, default=10)
+  g.add_argument('--no-flush', dest='flush', action='store_false')
   o = sub.add_parser('ops')
   o.add_argument('--depth', type=int, default=6)
   o.add_argument('--shapes', type=int, default=32)
@@ -192,7 +218,7 @@ def main():
   o.add_argument('--iters', type=int, default=20)
   o.add_argument('--no-flush', dest='flush', action='store_false')
   args = ap.parse_args()
-  {'conv': run_conv, 'build': run_build, 'ops': run_ops}[args.cmd](args)
+  {'conv': run_conv, 'build': run_build, 'merge': run_merge, 'ops': run_ops}[args.cmd](args)
 
 
 if __name__ == '__main__':
