@@ -215,7 +215,8 @@ def test_conv_tensor_core_rejects_unsupported_shapes(ocnn, batch):
 
 # ---- few-channel pointwise (1x1x1) kernel behind octree_conv ---------------------------------------
 @pytest.mark.parametrize('shape', [(6, 32, 8), (6, 8, 32), (5, 64, 16), (5, 16, 64), (4, 24, 16),
-                                   (3, 128, 32), (6, 256, 64)])
+                                   (3, 128, 32), (6, 256, 64), (5, 8, 8), (5, 16, 16), (5, 32, 16),
+                                   (5, 64, 8), (4, 8, 64), (3, 16, 8)])
 def test_conv_pointwise_bf16(ocnn, batch, shape):
   merged, octree, v = batch
   d, cin, cout = shape
