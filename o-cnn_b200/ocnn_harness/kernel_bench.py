@@ -6,6 +6,7 @@ peaks.  This is also the program the ncu captures under profiles/ are taken from
     python o-cnn_b200/ocnn_harness/kernel_bench.py conv  --depth 5 --shapes 32 --cin 128 --cout 128
     python o-cnn_b200/ocnn_harness/kernel_bench.py build --config 4 --clouds 64
     python o-cnn_b200/ocnn_harness/kernel_bench.py merge --config 3
+    python o-cnn_b200/ocnn_harness/kernel_bench.py net   --config 5
     python o-cnn_b200/ocnn_harness/kernel_bench.py ops   --depth 6 --shapes 32 --channels 32
 
 Algorithmic work per launch (what `achieved` divides by the measured time):
@@ -162,6 +163,37 @@ def run_merge(args):
   ocnn.set_key_bits(64)
 
 
+def run_net(args):
+  """Whole forward of the other named configurations: LeNet (config 2: 32 shapes x 10k points,
+  depth 5, fp32) and the scene U-Net (config 5: one 200k-point scene, depth 9, bf16), octree build
+  included."""
+  from ocnn_harness import models
+  ocnn.set_key_bits(64)
+  if args.config == 2:
+    clouds = synth.config_clouds(2, args.clouds)
+    depth, net, mode = 5, models.lenet_params(5, 3, 40, seed=0), 'fp32'
+  else:
+    clouds = synth.config_clouds(5, args.clouds or 1)
+    depth, net, mode = 9, models.unet_params(9, 6, 20, seed=0), 'bf16'
+  pts = make_points(clouds)
+  packed, meta = ocnn.points_pack(pts, True)
+  headers = torch.cat([p[:88] for p in pts]).contiguous()
+  dev = packed.cuda()
+  bargs = (depth, 2, False, False, False, False, 4, 0.1, 2.0, False, False, False, True)
+  gnet = models.GpuNet(net, mode)
+  fn = lambda: gnet.forward(ocnn.points2octree_packed(dev, meta, headers, *bargs))
+  out = fn()
+  flush = torch.empty(256 << 20, dtype=torch.uint8, device='cuda') if args.flush else None
+  ms, best = time_op(fn, args.iters, warmup=3, flush=flush)
+  assert gnet.error_status() == 0
+  flops = sum(2.0 * p['cout'] * p.get('_cin', p['cin']) * int(np.prod(p['ks'])) *
+              int(ocnn.octree_info(ocnn.points2octree_packed(dev, meta, headers, *bargs))[4 + d])
+              for d, p in models.conv_layers(net))
+  print(json.dumps({'network': net['kind'], 'config': args.config, 'mode': mode, 'clouds': len(clouds),
+                    'ms_median': ms, 'ms_best': best, 'items_per_s': len(clouds) / (ms * 1e-3),
+                    'conv_TFLOPs': flops / (ms * 1e-3) / 1e12, 'output_shape': list(out.shape)}))
+
+
 def run_ops(args):
   octree = build_octree(args.shapes, args.points, args.depth)
   info = ocnn.octree_info(octree)
@@ -210,6 +242,11 @@ def main():
   g.add_argument('--clouds', type=int, default=None)
   g.add_argument('--iters', type=int, default=10)
   g.add_argument('--no-flush', dest='flush', action='store_false')
+  w = sub.add_parser('net')
+  w.add_argument('--config', type=int, default=5, choices=[2, 5])
+  w.add_argument('--clouds', type=int, default=None)
+  w.add_argument('--iters', type=int, default=10)
+  w.add_argument('--no-flush', dest='flush', action='store_false')
   o = sub.add_parser('ops')
   o.add_argument('--depth', type=int, default=6)
   o.add_argument('--shapes', type=int, default=32)
@@ -218,7 +255,7 @@ def main():
   o.add_argument('--iters', type=int, default=20)
   o.add_argument('--no-flush', dest='flush', action='store_false')
   args = ap.parse_args()
-  {'conv': run_conv, 'build': run_build, 'merge': run_merge, 'ops': run_ops}[args.cmd](args)
+  {'conv': run_conv, 'build': run_build, 'merge': run_merge, 'net': run_net, 'ops': run_ops}[args.cmd](args)
 
 
 if __name__ == '__main__':

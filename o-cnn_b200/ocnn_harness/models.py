@@ -89,10 +89,43 @@ def lenet_params(depth=5, channel_in=3, nout=40, seed=0, channels=(32, 64, 128, 
   return net
 
 
+def unet_params(depth=9, channel_in=6, nout=20, seed=0, channels=(32, 64, 128, 256)):
+  """Segmentation U-Net of the scene configuration: encoder conv3x3x3 + BN + ReLU per level with
+  max-pool between levels (channels 32-64-128-256 over depth .. depth-3), decoder = nearest
+  upsampling to the finer level (octree_depad to the non-empty nodes, each repeated for its eight
+  children), concatenation with the encoder's output of that level, conv3x3x3 + BN + ReLU, and a
+  1x1x1 head to `nout` classes per finest node.  Built from the hot-path operators only (the
+  reference's UNet down/up-samples with stride-2 (de)convolutions on non-empty nodes, unet.py:21-36,
+  which are outside this path)."""
+  rng = np.random.default_rng(seed)
+  n = len(channels)
+  net = {'kind': 'unet', 'depth': depth, 'channel_in': channel_in, 'nout': nout,
+         'channels': list(channels)}
+  net['conv1'] = _conv_param(rng, channel_in, channels[0], 27, 'conv1')
+  net['enc'] = []
+  cin = channels[0]
+  for i in range(n):
+    net['enc'].append(_conv_param(rng, cin, channels[i], 27, 'enc%d' % (depth - i)))
+    cin = channels[i]
+  net['dec'] = []
+  for i in range(n - 2, -1, -1):
+    net['dec'].append(_conv_param(rng, channels[i + 1] + channels[i], channels[i], 27,
+                                  'dec%d' % (depth - i)))
+  net['head'] = _conv_param(rng, channels[0], nout, 1, 'head', bn=False, relu=False)
+  return net
+
+
 def conv_layers(net):
   """Every convolution of the network with the level it runs at: (depth, param dict)."""
   if net['kind'] == 'lenet':
     return [(c['depth'], c['conv']) for c in net['convs']]
+  if net['kind'] == 'unet':
+    d, n = net['depth'], len(net['channels'])
+    out = [(d, net['conv1'])]
+    out += [(d - i, net['enc'][i]) for i in range(n)]
+    out += [(d - (n - 2 - k), net['dec'][k]) for k in range(n - 1)]
+    out.append((d, net['head']))
+    return out
   out = [(net['depth'], net['conv1'])]
   for lv in net['levels']:
     for blk in lv['blocks']:
@@ -124,10 +157,32 @@ class CpuNet:
     top, _ = self.ops.max_pool(x)
     return self.ops.pad(top, v.prop('child', d - 1), 0.0)
 
+  def _unet(self, octree, v, x):
+    net = self.net
+    d0, n = net['depth'], len(net['channels'])
+    x = np.maximum(self._conv(x, net['conv1'], octree, d0), 0)
+    skips = []
+    for i in range(n):
+      d = d0 - i
+      x = np.maximum(self._conv(x, net['enc'][i], octree, d), 0)
+      if i < n - 1:
+        skips.append(x)
+        x = self._pool(x, v, d)
+    for k in range(n - 1):
+      d = d0 - (n - 2 - k)                 # level being reconstructed
+      child = v.prop('child', d - 1)
+      nne = int(v.nnum_nempty[d - 1])
+      up = np.repeat(self.ops.depad(x, child, nne), 8, axis=1)
+      x = np.concatenate([up, skips[n - 2 - k]], axis=0)
+      x = np.maximum(self._conv(x, net['dec'][k], octree, d), 0)
+    return self._conv(x, net['head'], octree, d0).T          # [nnum[depth], nout]
+
   def forward(self, octree):
     net = self.net
     v = self.view(octree)
     x = np.ascontiguousarray(v.prop('feature', net['depth']))
+    if net['kind'] == 'unet':
+      return self._unet(octree, v, x)
     if net['kind'] == 'lenet':
       for c in net['convs']:
         x = np.maximum(self._conv(x, c['conv'], octree, c['depth']), 0)
@@ -168,10 +223,11 @@ class GpuNet:
     self.tc = bool(tensor_core) and self.bf16
     for _, p in conv_layers(net):
       self._upload(p)
-    self.fc_w = torch.from_numpy(net['fc_w']).to(device)
-    self.fc_b = torch.from_numpy(net['fc_b']).to(device)
+    if net['kind'] != 'unet':
+      self.fc_w = torch.from_numpy(net['fc_w']).to(device)
+      self.fc_b = torch.from_numpy(net['fc_b']).to(device)
     self.launches = 0
-    self.exec = self._record() if (self.bf16 and executor) else None
+    self.exec = self._record() if (self.bf16 and executor and net['kind'] != 'unet') else None
     # per-layer CUDA-event tracing (benchmark only): trace = {layer name: [(start, end), ...]};
     # trace_only restricts it to one layer
     self.trace = None
@@ -284,6 +340,26 @@ class GpuNet:
     self.launches += 2
     return nn.octree_pad(top, octree, d - 1, 0.0)
 
+  def _unet(self, octree, x):
+    t, net = self.torch, self.net
+    d0, n = net['depth'], len(net['channels'])
+    fmt = dict(memory_format=t.channels_last) if self.bf16 else {}
+    x = self._conv(x, net['conv1'], octree, d0, True)
+    skips = []
+    for i in range(n):
+      d = d0 - i
+      x = self._conv(x, net['enc'][i], octree, d, True)
+      if i < n - 1:
+        skips.append(x)
+        x = self._pool(x, octree, d)
+    for k in range(n - 1):
+      d = d0 - (n - 2 - k)
+      up = self.ocnn.octree_depad(x, octree, d - 1).repeat_interleave(8, dim=2)
+      x = t.cat([up, skips[n - 2 - k]], dim=1).contiguous(**fmt)
+      x = self._conv(x, net['dec'][k], octree, d, True)
+    y = self._conv(x, net['head'], octree, d0, False)
+    return y[0, :, :, 0].t().float()                          # [nnum[depth], nout]
+
   def forward(self, octree):
     t, net = self.torch, self.net
     nn = self.ocnn.nn
@@ -300,6 +376,8 @@ class GpuNet:
         self.launches += 1
       else:
         x = self.ocnn.octree_property(octree, 'feature', net['depth'])
+      if net['kind'] == 'unet':
+        return self._unet(octree, x)
       if net['kind'] == 'lenet':
         for c in net['convs']:
           x = self._conv(x, c['conv'], octree, c['depth'], True)
