@@ -251,7 +251,7 @@ class GpuNet:
     def conv(p, d, src, dst, relu, res=-1):
       # few-channel 1x1 layers stream through the pointwise kernel on big levels (HBM-bound there),
       # everything else that fits runs on the tensor-core kernel
-      ex.add_conv(p['name'], d, p['_cin'], p['cout'], p['ks'], 1, p['_w'], p['_packed'],
+      ex.add_conv(p['name'], d, p['_cin'], p['_cout'], p['ks'], 1, p['_w'], p['_packed'],
                   p['_scale'], p['_bias'], relu, src, dst, res,
                   PW_MIN_NODES if p["_pointwise"] else -1)
       self.exec_layers.append(p['name'])
@@ -309,18 +309,26 @@ class GpuNet:
       wp = np.zeros((w.shape[0], cpad, kd), np.float32)
       wp[:, :cin, :] = w.reshape(w.shape[0], cin, kd)
       w, cin = wp.reshape(w.shape[0], cpad * kd), cpad
+    if self.bf16 and p['cout'] % 8 != 0 and p['ks'] == [1, 1, 1] and p['scale'] is None:
+      # a head with e.g. 20 classes: widen to the next size the bf16 kernels take (zero rows); the
+      # caller slices the extra channels off
+      cpad = 8 if p['cout'] <= 8 else 16 if p['cout'] <= 16 else (p['cout'] + 31) // 32 * 32
+      wp = np.zeros((cpad, w.shape[1]), np.float32)
+      wp[:p['cout']] = w
+      w = wp
     p['_cin'] = cin
+    p['_cout'] = w.shape[0]
     p['_w'] = t.from_numpy(np.ascontiguousarray(w)).to(self.device)
     p['_scale'] = None if p['scale'] is None else t.from_numpy(p['scale']).to(self.device)
     p['_bias'] = None if p['bias'] is None else t.from_numpy(p['bias']).to(self.device)
     p['_packed'] = None
     # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
     # else that fits goes to the tensor-core kernel
-    p['_pointwise'] = (p['ks'] == [1, 1, 1] and p['cout'] in (8, 16, 32) and
-                       cin * p['cout'] <= 4096)
-    if self.tc and cin % 8 == 0 and p['cout'] % 8 == 0 and (p['cout'] <= 256 or p['cout'] % 256 == 0):
+    cout = p['_cout']
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin * cout <= 4096)
+    if self.tc and cin % 8 == 0 and cout % 8 == 0 and (cout <= 256 or cout % 256 == 0):
       try:
-        p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, p['cout'], p['ks'])
+        p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, cout, p['ks'])
       except RuntimeError:
         p['_packed'] = None
 
@@ -329,13 +337,16 @@ class GpuNet:
     self.launches += 1
     if p['_packed'] is not None and not (p['_pointwise'] and x.shape[2] >= PW_MIN_NODES):
       return self._traced(p['name'], lambda: nn.octree_conv_tc(
-          x, p['_packed'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual,
+          x, p['_packed'], octree, d, p['_cout'], p['ks'], 1, p['_scale'], p['_bias'], residual,
           relu, self.status))
     return self._traced(p['name'], lambda: nn.octree_conv_fused(
-        x, p['_w'], octree, d, p['cout'], p['ks'], 1, p['_scale'], p['_bias'], residual, relu))
+        x, p['_w'], octree, d, p['_cout'], p['ks'], 1, p['_scale'], p['_bias'], residual, relu))
 
   def _pool(self, x, octree, d):
     nn = self.ocnn.nn
+    if self.bf16 and x.shape[1] % 8 == 0:
+      self.launches += 1
+      return nn.octree_max_pool_pad(x, octree, d)          # pool + pad in one kernel
     top, _ = nn.octree_max_pool(x, octree, d)
     self.launches += 2
     return nn.octree_pad(top, octree, d - 1, 0.0)
@@ -358,7 +369,7 @@ class GpuNet:
       x = t.cat([up, skips[n - 2 - k]], dim=1).contiguous(**fmt)
       x = self._conv(x, net['dec'][k], octree, d, True)
     y = self._conv(x, net['head'], octree, d0, False)
-    return y[0, :, :, 0].t().float()                          # [nnum[depth], nout]
+    return y[0, :net['nout'], :, 0].t().float()               # [nnum[depth], nout]
 
   def forward(self, octree):
     t, net = self.torch, self.net
