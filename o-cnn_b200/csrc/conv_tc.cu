@@ -61,7 +61,9 @@ struct TcArgs {
   int wide;         // output (and residual) rows can be accessed 32 bytes at a time
   int rowsplit;     // gather mapping: 0 = one tile row per thread; four tile rows per warp
                     // instruction: 1 = group mode with 8 or 16 channels (indices from global memory),
-                    // 2 = node mode, Cin % 64 == 0, 3 = group mode through the shared index table
+                    // 2 = node mode, Cin % 64 == 0, 3 = group mode through the shared index table,
+                    // 4 = node mode, any other Cin with more than one tap (index table with the
+                    // padded stride, two 16-byte index reads per K-block)
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -244,7 +246,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   // the epilogue they were a chain of cold misses (one per 128-byte line of each array) that every
   // thread of a one-wave launch sat through
   float* s_scale = reinterpret_cast<float*>(
-      nbr + (a.group ? (a.rowsplit == 3 ? 64 * kGroupTableStride : 0) : a.T * kTileM));
+      nbr + (a.group ? (a.rowsplit == 3 ? 64 * kGroupTableStride : 0)
+                     : a.T * (a.rowsplit == 4 ? kGroupTableStride : kTileM)));
   float* s_bias = s_scale + a.npad;
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + a.npad);
   uint64_t* full = bars;
@@ -307,13 +310,14 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     } else {
       const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
       if (a.identity) {
-        nbr[a.rowsplit == 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid] = live ? h : -1;
+        nbr[a.rowsplit >= 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid] = live ? h : -1;
       } else {
       // all (up to 27) table reads are issued before the first result is used: a load-then-store
       // loop would expose the L2 latency once per tap
       // with the four-rows-per-instruction mapping a thread serves rows sub + 4*i of its warp: their
       // entries are stored next to each other so that it reads them as two 16-byte words
-      const int slot = a.rowsplit == 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid;
+      const int slot = a.rowsplit >= 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid;
+      const int tstride = a.rowsplit == 4 ? kGroupTableStride : kTileM;
       int pv[27];
 #pragma unroll
       for (int t = 0; t < 27; ++t) {
@@ -329,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
       }
 #pragma unroll
       for (int t = 0; t < 27; ++t)
-        if (t < a.T) nbr[t * kTileM + slot] = pv[t];
+        if (t < a.T) nbr[t * tstride + slot] = pv[t];
       }
     }
   }
@@ -411,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
       auto fetch = [&](int kb, int (&p)[8], uint32_t& off) {
         int t;
         chunk_src<CPT>(cpt, kb, chunk, t, off);
-        if (a.rowsplit == 3) {
+        if (a.rowsplit >= 3) {
           if (t < a.T) {
             const int4 lo = *reinterpret_cast<const int4*>(my_idx + t * kGroupTableStride);
             const int4 hi = *reinterpret_cast<const int4*>(my_idx + t * kGroupTableStride + 4);
@@ -706,7 +710,7 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable; size_t smem; };
+struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable, ntable_stride; size_t smem; };
 
 int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1) {
   const TapList tl = taps_for_kernel(ks);
@@ -738,7 +742,10 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   // group mode with more than 16 channels gathers through a shared index table (fewer index reads
   // in the loop); with 8 or 16 channels filling the table costs more than it saves
   s->gtable = (s->group && cin > 16) ? 1 : 0;
-  const size_t fixed = 1024 + (s->group ? (s->gtable ? 64 * kGroupTableStride * 4 : 0) : (size_t)s->T * kTileM * 4) +
+  // node mode keeps a [taps][128] index table; Cin not a multiple of 64 reads it per K-block with
+  // lanes on different taps, which wants the padded stride
+  s->ntable_stride = (!s->group && cin % 64 != 0 && s->T > 1) ? kGroupTableStride : kTileM;
+  const size_t fixed = 1024 + (s->group ? (s->gtable ? 64 * kGroupTableStride * 4 : 0) : (size_t)s->T * s->ntable_stride * 4) +
                        (size_t)s->npad * 8 + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
   // every stage of the ring can be in flight at once, so prefer two CTAs per SM (set-up and
@@ -849,6 +856,7 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
   if (s.gtable) a.rowsplit = 3;
   if (!s.group && cin % 64 == 0) a.rowsplit = 2;
+  if (!s.group && s.ntable_stride == kGroupTableStride) a.rowsplit = 4;
   a.tile_rows = s.tile_rows;
   // 32-byte epilogue accesses: rows and channel slices on 32-byte boundaries
   a.wide = (a.row_elems % 16 == 0 && a.y_stride % 16 == 0 && (uintptr_t)y % 32 == 0 &&
