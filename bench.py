@@ -40,7 +40,7 @@ def parse_args():
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
   ap.add_argument('--no-tensor-core', action='store_true',
                   help='run every convolution on the CUDA-core kernel')
-  ap.add_argument('--cpu-sample', type=int, default=8, help='shapes in the CPU baseline sample')
+  ap.add_argument('--cpu-sample', type=int, default=32, help='shapes in the CPU baseline sample')
   return ap.parse_args()
 
 
