@@ -101,6 +101,14 @@ int ocnn_octree_depad(const void* y_dev, void* x_dev, const int32_t* child_dev, 
 int ocnn_octree_max_pool(const void* btm_dev, void* top_dev, int32_t* mask_dev, int channels,
                          int top_h, int dtype, int layout, void* stream);
 
+/* OctreeTile: nearest-neighbour upsampling to the next finer level, the octree_depad followed by
+ * an eightfold repeat that the reference's module runs (pytorch/ocnn/modules.py:193-207).
+ * y: [C, hy] rows of level `depth`; out: [C, hout] rows of level depth + 1 (hout = 8 * number of
+ * non-empty nodes of level `depth`); child_dev: the Child block of level `depth`.
+ * out[., 8*child[h] + j] = y[., h] for child[h] >= 0, j = 0..7. */
+int ocnn_octree_tile(const void* y_dev, void* out_dev, const int32_t* child_dev, int channels,
+                     int hy, int hout, int dtype, int layout, void* stream);
+
 /* OctreeMaxPool in one pass: octree_max_pool followed by octree_pad with 0, the pair the
  * reference's module runs (pytorch/ocnn/octree_pool.py, OctreeMaxPool.forward: octree_max_pool
  * then octree_pad at depth - 1).  btm: [btm_h, C] rows of level `depth`; top: [top_h, C] rows of

@@ -151,6 +151,44 @@ __global__ void depad_nm_kernel(const T* __restrict__ y, T* __restrict__ x,
   }
 }
 
+// ---- tile: nearest-neighbour upsampling, depad followed by "repeat each row for its 8 children" ---
+// out[., 8*child[h] + j] = y[., h] for child[h] >= 0, j = 0..7.  Every row of the finer level is
+// written (each of its nodes has a non-empty parent).
+__global__ void tile_nm_vec_kernel(const uint4* __restrict__ y, uint4* __restrict__ out,
+                                   const int* __restrict__ child, int Hy, int chunks) {
+  const long long total = (long long)Hy * chunks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int h = (int)(i / chunks), q = (int)(i - (long long)h * chunks);
+    const int l = child[h];
+    if (l < 0) continue;
+    const uint4 v = y[i];
+    uint4* dst = out + (long long)l * 8 * chunks + q;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[(long long)j * chunks] = v;
+  }
+}
+
+template <typename T>
+__global__ void tile_kernel(const T* __restrict__ y, T* __restrict__ out,
+                            const int* __restrict__ child, int C, int Hy, long long Hout,
+                            int node_major) {
+  const long long total = (long long)C * Hy;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    int c, h;
+    if (node_major) { h = (int)(i / C); c = (int)(i % C); } else { c = (int)(i / Hy); h = (int)(i % Hy); }
+    const int l = child[h];
+    if (l < 0) continue;
+    const T v = y[i];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long row = (long long)l * 8 + j;
+      out[node_major ? row * C + c : (long long)c * Hout + row] = v;
+    }
+  }
+}
+
 // ---- max pool ------------------------------------------------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -428,6 +466,31 @@ int ocnn_octree_depad(const void* y, void* x, const int32_t* child, int C, int h
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return dtype == OCNN_F32 ? depad_impl<float>(y, x, child, C, hx, hy, layout, st)
                            : depad_impl<__nv_bfloat16>(y, x, child, C, hx, hy, layout, st);
+}
+
+int ocnn_octree_tile(const void* y, void* out, const int32_t* child, int C, int hy, int hout,
+                     int dtype, int layout, void* stream) {
+  using namespace ocnn;
+  if (hy == 0 || hout == 0) return OCNN_OK;
+  if (int s = check_common("ocnn_octree_tile", y, out, child, C, dtype, layout)) return s;
+  OCNN_REQUIRE(hy > 0 && hout > 0 && hout % 8 == 0, "ocnn_octree_tile: need hy (%d) > 0 and hout (%d) "
+               "a multiple of 8", hy, hout);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t esize = dtype == OCNN_F32 ? 4 : 2;
+  const size_t row = (size_t)C * esize;
+  if (layout == OCNN_NODE_MAJOR && row % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    const int chunks = (int)(row / 16);
+    tile_nm_vec_kernel<<<grid_for((long long)hy * chunks, 256), 256, 0, st>>>(
+        (const uint4*)y, (uint4*)out, child, hy, chunks);
+  } else if (dtype == OCNN_F32) {
+    tile_kernel<float><<<grid_for((long long)C * hy, 256), 256, 0, st>>>(
+        (const float*)y, (float*)out, child, C, hy, hout, layout == OCNN_NODE_MAJOR);
+  } else {
+    tile_kernel<__nv_bfloat16><<<grid_for((long long)C * hy, 256), 256, 0, st>>>(
+        (const __nv_bfloat16*)y, (__nv_bfloat16*)out, child, C, hy, hout, layout == OCNN_NODE_MAJOR);
+  }
+  OCNN_LAUNCH_OK("octree_tile");
+  return OCNN_OK;
 }
 
 int ocnn_octree_max_pool(const void* btm, void* top, int32_t* mask, int C, int top_h, int dtype,

@@ -20,7 +20,8 @@ from .nn import (octree_batch, octree_property, points2octree, points2octree_bat
 from .transforms import Points2Octree, collate_octrees
 from .octree2voxel import FullOctree2Voxel
 from .octree2col import octree2col, Octree2Col
-from .octree_pad import octree_pad, OctreePad, octree_depad, OctreeDepad
+from .octree_pad import (octree_pad, OctreePad, octree_depad, OctreeDepad, octree_tile,
+                         OctreeTile)
 from .octree_conv import octree_conv, OctreeConv, OctreeConvFast
 from .octree_pool import octree_max_pool, OctreeMaxPool, OctreeAvgPool, FullOctreeGlobalPool
 

@@ -41,3 +41,24 @@ class OctreeDepad(_nn.Module):
 
   def extra_repr(self) -> str:
     return 'depth={}'.format(self.depth)
+
+
+def octree_tile(data_in, octree, depth):
+  """Nearest-neighbour upsampling from level `depth` to `depth + 1`: octree_depad, then every row
+  repeated for its eight children (one kernel)."""
+  with torch.no_grad():
+    return nn.octree_tile(data_in, octree, depth)
+
+
+class OctreeTile(_nn.Module):
+  """pytorch/ocnn/modules.py:193-207 of the reference."""
+
+  def __init__(self, depth):
+    super().__init__()
+    self.depth = depth
+
+  def forward(self, data_in, octree):
+    return octree_tile(data_in, octree, self.depth)
+
+  def extra_repr(self) -> str:
+    return 'depth={}'.format(self.depth)

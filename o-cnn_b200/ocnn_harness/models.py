@@ -365,7 +365,7 @@ class GpuNet:
         x = self._pool(x, octree, d)
     for k in range(n - 1):
       d = d0 - (n - 2 - k)
-      up = self.ocnn.octree_depad(x, octree, d - 1).repeat_interleave(8, dim=2)
+      up = self.ocnn.octree_tile(x, octree, d - 1)            # OctreeTile: nearest upsampling
       x = t.cat([up, skips[n - 2 - k]], dim=1).contiguous(**fmt)
       x = self._conv(x, net['dec'][k], octree, d, True)
     y = self._conv(x, net['head'], octree, d0, False)

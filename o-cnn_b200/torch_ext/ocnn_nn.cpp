@@ -214,6 +214,28 @@ Tensor octree_depad(Tensor data_in, Tensor octree, int depth) {
   return x;
 }
 
+// OctreeTile (pytorch/ocnn/modules.py:193-207): depad at `depth`, every row repeated for its 8
+// children: [1,C,nnum[depth],1] -> [1,C,nnum[depth+1],1], in one kernel.
+Tensor octree_tile(Tensor data_in, Tensor octree, int depth) {
+  TORCH_CHECK(depth >= 1, "Depth should be larger than 1");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_tile: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth < o.meta.depth, "octree_tile: depth ", depth, " has no finer level in the octree");
+  need_cuda(data_in, "octree_tile");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef y = get_data(data_in, "octree_tile");
+  TORCH_CHECK(o.meta.nnum[depth] == y.H, "octree_tile: data height ", y.H, " != node number ",
+              o.meta.nnum[depth], ", d = ", depth, ", channel = ", y.C);
+  const int hout = o.meta.nnum_nempty[depth] * 8;
+  TORCH_CHECK(hout == o.meta.nnum[depth + 1], "octree_tile: level ", depth + 1, " does not hold the "
+              "children of level ", depth);
+  Tensor out = new_data(y.C, hout, y);
+  OCNN_CALL(ocnn_octree_tile(y.t.data_ptr(), out.data_ptr(),
+                             level_ptr(o, OCNN_PROP_CHILD, depth, "octree_tile"), y.C, y.H, hout,
+                             y.dtype, y.layout, current_stream()));
+  return out;
+}
+
 vector<Tensor> octree_max_pool(Tensor data_in, Tensor octree, int depth) {
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(depth > 1, "Depth should be larger than 1");
@@ -967,6 +989,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("octree_pad", &octree_pad, "octree pad", py::arg("data_in"), py::arg("octree"),
         py::arg("depth"), py::arg("val") = 0.0f);
   m.def("octree_depad", &octree_depad, "octree depad");
+  m.def("octree_tile", &octree_tile, "nearest upsampling: depad + repeat each row for its 8 children");
   m.def("octree_max_pool", &octree_max_pool, "octree max pooling");
   m.def("octree_max_pool_pad", &octree_max_pool_pad, "octree max pooling + pad to depth - 1 (bf16 node-major)");
   m.def("points_new", &points_new, "create a point cloud");

@@ -143,6 +143,26 @@ def test_max_pool_pad_fused(ocnn, batch, C):
     ocnn.nn.octree_max_pool_pad(torch.zeros(1, 8, int(v.nnum[3]), 1, device='cuda'), octree, 3)
 
 
+@pytest.mark.parametrize('nm,bf16,C', [(False, False, 5), (True, False, 6), (True, True, 8), (True, True, 40),
+                                       (True, True, 12)])
+def test_octree_tile(ocnn, batch, nm, bf16, C):
+  """OctreeTile = octree_depad + eightfold repeat, bit for bit, on every level that has a finer one."""
+  _, _, _, octree, v = batch
+  rng = np.random.default_rng(13)
+  for d in range(1, v.depth):
+    H = int(v.nnum[d])
+    x = rng.uniform(-1, 1, size=(C, H)).astype(np.float32)
+    if bf16:
+      x = gu.bf16_round(x)
+    want = np.repeat(oc.depad(x, v.prop('child', d), int(v.nnum_nempty[d])), 8, axis=1)
+    got = ocnn.octree_tile(gu.data_cuda(x, nm, bf16), octree, d)
+    assert got.shape == (1, C, int(v.nnum[d + 1]), 1)
+    assert np.array_equal(gu.to_np(got), want)
+    assert np.array_equal(gu.to_np(ocnn.OctreeTile(d)(gu.data_cuda(x, nm, bf16), octree)), want)
+  with pytest.raises(RuntimeError, match='no finer level'):
+    ocnn.octree_tile(torch.zeros(1, 2, int(v.nnum[v.depth]), 1, device='cuda'), octree, v.depth)
+
+
 def test_pad_shape_errors(ocnn, batch):
   _, _, _, octree, v = batch
   with pytest.raises(RuntimeError, match='data height'):
