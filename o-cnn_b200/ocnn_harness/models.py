@@ -325,7 +325,7 @@ class GpuNet:
     # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
     # else that fits goes to the tensor-core kernel
     cout = p['_cout']
-    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin * cout <= 4096)
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin <= 32)
     if self.tc and cin % 8 == 0 and cout % 8 == 0 and (cout <= 256 or cout % 256 == 0):
       try:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, cout, p['ks'])
