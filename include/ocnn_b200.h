@@ -175,6 +175,20 @@ int ocnn_octree_conv(const void* x_dev, const float* weights_dev, void* y_dev,
                      const int kernel_size[3], int stride, int dtype, int layout,
                      const ocnn_conv_epilogue* epilogue, void* stream);
 
+/* The convolution on the non-empty nodes only: OctreeConv(nempty = True), stride 1.  Replaces
+ * octree2colP_gpu + GEMM (octree/octree/octree_nn.cu:179-253, octree_conv.cpp:48-140 with nempty_,
+ * binding pytorch/cpp/octree_conv.cpp:109-116).  x, y: nne rows (the non-empty nodes of the level
+ * in order); child_dev: the level's Child block (nnum ints); ichild_dev: its inverse (nne ints),
+ * filled by ocnn_octree_ichild.  y[co, i] = sum w[co, ci*K + t] * x[ci, child[nbr(ichild[i], t)]],
+ * neighbours that are missing or empty contribute 0.  fp32 / bf16 data in either layout on the
+ * CUDA-core kernel (the tensor-core kernel does not take this form yet). */
+int ocnn_octree_ichild(const int32_t* child_dev, int nnum, int32_t* ichild_dev, void* stream);
+int ocnn_octree_conv_nempty(const void* x_dev, const float* weights_dev, void* y_dev,
+                            const int32_t* neigh_dev, const int32_t* child_dev,
+                            const int32_t* ichild_dev, int nne, int cin, int cout,
+                            const int kernel_size[3], int dtype, int layout,
+                            const ocnn_conv_epilogue* epilogue, void* stream);
+
 /* Tensor-core path: weights packed once per layer into bf16 K-major tiles.  The packed image
  * depends on the kernel shape AND the stride the layer will run with (stride-1 neighbourhood
  * convolutions with few channels use a per-sibling-group formulation with expanded weights). */

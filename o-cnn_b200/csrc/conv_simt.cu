@@ -26,6 +26,8 @@ struct ConvArgs {
   const float* w;
   void* y;
   const int* neigh;
+  const int* child;    // non-empty-node convolution only: child array of the level, and
+  const int* ichild;   // its inverse (node of the i-th non-empty node); NULL for the dense one
   int h_in, h_out, cin, cout, K, stride, identity;
   const float* scale;
   const float* bias;
@@ -60,9 +62,14 @@ __global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
         p = h;
       } else {
         const int tap = a.tap[t];
-        const long long at = a.stride == 2 ? ((long long)h << 6) + ni333(0, tap)
-                                           : ((long long)(h >> 3) << 6) + ni333(h & 7, tap);
+        // on non-empty nodes only (octree2colP, octree/octree/octree_nn.cu:179-201): row h is the
+        // h-th non-empty node, its neighbours are looked up from the node itself and mapped back
+        // to ranks among the non-empty nodes
+        const int hn = a.ichild ? a.ichild[h] : h;
+        const long long at = a.stride == 2 ? ((long long)hn << 6) + ni333(0, tap)
+                                           : ((long long)(hn >> 3) << 6) + ni333(hn & 7, tap);
         p = a.neigh[at];
+        if (a.ichild && p >= 0) p = a.child[p];
       }
     }
     nbr[t][m] = p;
@@ -149,6 +156,46 @@ __global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
 }  // namespace
 }  // namespace ocnn
 
+namespace ocnn {
+namespace {
+
+__global__ void ichild_kernel(const int* __restrict__ child, int* __restrict__ ichild, int nnum) {
+  for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < nnum; h += gridDim.x * blockDim.x) {
+    const int l = child[h];
+    if (l >= 0) ichild[l] = h;
+  }
+}
+
+int conv_simt_launch(const void* x, const float* w, void* y, const int32_t* neigh,
+                     const int32_t* child, const int32_t* ichild, int h_in, int h_out, int cin,
+                     int cout, const TapList& tl, int stride, int dtype, int layout,
+                     const ocnn_conv_epilogue* ep, void* stream) {
+  const bool identity = tl.count == 1 && stride == 1;
+  ConvArgs a;
+  a.x = x; a.w = w; a.y = y; a.neigh = neigh; a.child = child; a.ichild = ichild;
+  a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout;
+  a.K = tl.count; a.stride = stride; a.identity = identity ? 1 : 0;
+  a.scale = ep ? ep->scale_dev : nullptr;
+  a.bias = ep ? ep->bias_dev : nullptr;
+  a.residual = ep ? ep->residual_dev : nullptr;
+  a.relu = ep ? ep->relu : 0;
+  for (int i = 0; i < 27; ++i) a.tap[i] = i < tl.count ? tl.tap[i] : 0;
+  dim3 grid(ceil_div(h_out, BM), ceil_div(cout, BN));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == OCNN_F32) {
+    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<float, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    else conv_simt_kernel<float, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+  } else {
+    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__nv_bfloat16, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    else conv_simt_kernel<__nv_bfloat16, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+  }
+  OCNN_LAUNCH_OK("conv_simt_kernel");
+  return OCNN_OK;
+}
+
+}  // namespace
+}  // namespace ocnn
+
 extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const int32_t* neigh,
                                 int h_in, int h_out, int cin, int cout, const int kernel_size[3],
                                 int stride, int dtype, int layout, const ocnn_conv_epilogue* ep,
@@ -181,24 +228,39 @@ extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const in
     const int s = conv_pointwise_bf16(x, w, y, h_out, cin, cout, ep, static_cast<cudaStream_t>(stream));
     if (s >= 0) return s;
   }
-  ConvArgs a;
-  a.x = x; a.w = w; a.y = y; a.neigh = neigh;
-  a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout;
-  a.K = tl.count; a.stride = stride; a.identity = identity ? 1 : 0;
-  a.scale = ep ? ep->scale_dev : nullptr;
-  a.bias = ep ? ep->bias_dev : nullptr;
-  a.residual = ep ? ep->residual_dev : nullptr;
-  a.relu = ep ? ep->relu : 0;
-  for (int i = 0; i < 27; ++i) a.tap[i] = i < tl.count ? tl.tap[i] : 0;
-  dim3 grid(ceil_div(h_out, BM), ceil_div(cout, BN));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == OCNN_F32) {
-    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<float, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
-    else conv_simt_kernel<float, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
-  } else {
-    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__nv_bfloat16, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
-    else conv_simt_kernel<__nv_bfloat16, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
-  }
-  OCNN_LAUNCH_OK("conv_simt_kernel");
+  return conv_simt_launch(x, w, y, neigh, nullptr, nullptr, h_in, h_out, cin, cout, tl, stride, dtype,
+                          layout, ep, stream);
+}
+
+extern "C" int ocnn_octree_ichild(const int32_t* child, int nnum, int32_t* ichild, void* stream) {
+  using namespace ocnn;
+  if (nnum == 0) return OCNN_OK;
+  OCNN_REQUIRE(child && ichild && nnum > 0, "ocnn_octree_ichild: null pointer or negative size");
+  ichild_kernel<<<grid_for(nnum, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(child, ichild, nnum);
+  OCNN_LAUNCH_OK("ichild_kernel");
   return OCNN_OK;
+}
+
+extern "C" int ocnn_octree_conv_nempty(const void* x, const float* w, void* y, const int32_t* neigh,
+                                       const int32_t* child, const int32_t* ichild, int nne, int cin,
+                                       int cout, const int kernel_size[3], int dtype, int layout,
+                                       const ocnn_conv_epilogue* ep, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_nempty: null kernel size");
+  const TapList tl = taps_for_kernel(kernel_size);
+  if (tl.count < 0)
+    return fail(OCNN_ERR_UNSUPPORTED, "ocnn_octree_conv_nempty: unsupported kernel size %dx%dx%d",
+                kernel_size[0], kernel_size[1], kernel_size[2]);
+  OCNN_REQUIRE(cin > 0 && cout > 0, "ocnn_octree_conv_nempty: channel counts must be positive");
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "ocnn_octree_conv_nempty: unknown dtype %d", dtype);
+  OCNN_REQUIRE(layout == OCNN_CHANNEL_MAJOR || layout == OCNN_NODE_MAJOR,
+               "ocnn_octree_conv_nempty: unknown layout %d", layout);
+  OCNN_REQUIRE(nne >= 0, "ocnn_octree_conv_nempty: negative height");
+  if (nne == 0) return OCNN_OK;
+  OCNN_REQUIRE(x && w && y, "ocnn_octree_conv_nempty: null data pointer");
+  if (tl.count == 1)      // 1x1x1: no neighbours, the same product as on all nodes
+    return ocnn_octree_conv(x, w, y, nullptr, nne, nne, cin, cout, kernel_size, 1, dtype, layout, ep, stream);
+  OCNN_REQUIRE(neigh && child && ichild, "ocnn_octree_conv_nempty: neighbour table, child and ichild required");
+  return conv_simt_launch(x, w, y, neigh, child, ichild, nne, nne, cin, cout, tl, 1, dtype, layout, ep,
+                          stream);
 }

@@ -369,9 +369,43 @@ Tensor octree_conv_fused(Tensor data_in, Tensor weights, Tensor octree, int dept
   return y;
 }
 
+// OctreeConv(nempty=True), stride 1: data and result live on the non-empty nodes of `depth` only
+// (pytorch/cpp/octree_conv.cpp:61-120 with non_empty_).
+Tensor octree_conv_nempty(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
+                          vector<int> kernel_size) {
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(num_output > 0, "The num_output should be larger than 0");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_conv: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth >= 1 && depth <= o.meta.depth, "octree_conv: depth ", depth, " outside the octree");
+  need_cuda(data_in, "octree_conv");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "octree_conv");
+  const int nne = o.meta.nnum_nempty[depth], nnum = o.meta.nnum[depth];
+  TORCH_CHECK(x.H == nne, "octree_conv (nempty): data height ", x.H, " != non-empty node number ", nne);
+  const int kdim = ks[0] * ks[1] * ks[2];
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 &&
+                  weights.numel() == (int64_t)num_output * x.C * kdim,
+              "weights must be a float32 CUDA tensor of shape [Cout, Cin*K]");
+  Tensor w = weights.contiguous();
+  Tensor y = new_data(num_output, nne, x);
+  const int32_t* child = level_ptr(o, OCNN_PROP_CHILD, depth, "octree_conv");
+  Tensor ichild = torch::empty({std::max(nne, 1)}, x.t.options().dtype(torch::kInt32));
+  OCNN_CALL(ocnn_octree_ichild(child, nnum, ichild.data_ptr<int32_t>(), current_stream()));
+  const int32_t* neigh = kdim > 1 ? level_ptr(o, OCNN_PROP_NEIGH, depth, "octree_conv") : nullptr;
+  OCNN_CALL(ocnn_octree_conv_nempty(x.t.data_ptr(), w.data_ptr<float>(), y.data_ptr(), neigh, child,
+                                    ichild.data_ptr<int32_t>(), nne, x.C, num_output, ks.data(),
+                                    x.dtype, x.layout, nullptr, current_stream()));
+  return y;
+}
+
 Tensor octree_conv(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
                    vector<int> kernel_size, int stride, bool nempty) {
-  TORCH_CHECK(!nempty, "octree_conv on non-empty nodes only (nempty=True) is not implemented");
+  if (nempty) {
+    TORCH_CHECK(stride == 1, "octree_conv on non-empty nodes (nempty=True) is implemented for stride 1 "
+                "only (stride ", stride, " given)");
+    return octree_conv_nempty(data_in, weights, octree, depth, num_output, kernel_size);
+  }
   return octree_conv_fused(data_in, weights, octree, depth, num_output, kernel_size, stride,
                            c10::nullopt, c10::nullopt, c10::nullopt, false);
 }

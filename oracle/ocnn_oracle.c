@@ -552,6 +552,70 @@ long oc_octree_conv(float *top, long cap, const float *bottom, const float *weig
   return count;
 }
 
+/* The same on non-empty nodes only (nempty = true, stride 1): octree2colP_cpu,
+ * octree/octree/octree_nn.cpp:244-271.  data: [channel, octree_h] over the non-empty nodes of the
+ * level, col: [channel*kdim, height] with height = number of non-empty nodes; ichild[i] = node of
+ * the i-th non-empty node, child[node] = its rank among the non-empty nodes or -1. */
+void oc_octree2col_p(float *col, const float *data, int channel, int height, int octree_h, int kdim,
+                     const int32_t *neigh, const int32_t *ni, const int32_t *child,
+                     const int32_t *ichild) {
+  for (int c = 0; c < channel; ++c)
+    for (int k = 0; k < kdim; ++k) {
+      float *row = col + ((long)c * kdim + k) * height;
+      for (long h = 0; h < height; ++h) {
+        const long hp = ichild[h];
+        int p = neigh[((hp >> 3) << 6) + ni[(hp & 7) * kdim + k]];
+        if (p >= 0) p = child[p];
+        row[h] = p < 0 ? 0.0f : data[(long)c * octree_h + p];
+      }
+    }
+}
+
+/* ichild as the PyTorch binding builds it: pad_backward of 0..nnum-1 through the child array
+ * (pytorch/cpp/octree_conv.cpp:109-116). */
+void oc_ichild(int32_t *ichild, const int32_t *child, int nnum) {
+  for (int h = 0; h < nnum; ++h) if (child[h] != -1) ichild[child[h]] = h;
+}
+
+/* OctreeConv with nempty = true, stride 1: Y[Cout, nne] = W x colP (octree_conv.cpp:48-122 with
+ * nempty_, 125-140).  Returns Cout * max(nne, 1). */
+long oc_octree_conv_nempty(float *top, long cap, const float *bottom, const float *weights,
+                           const uint8_t *octree, int depth, int cin, int cout, const int ks[3]) {
+  int taps[27];
+  const int K = kernel_taps(ks, taps);
+  if (K < 0) return -1;
+  const int32_t *nnum = hci(octree, H_NNUM), *nne = hci(octree, H_NNUM_NE);
+  const long h_ne = nne[depth];
+  const long top_h = h_ne == 0 ? 1 : h_ne;
+  const long count = (long)cout * top_h;
+  if (top == NULL || cap < count) return count;
+  const long kd = (long)cin * K;
+  const int one = ks[0] == 1 && ks[1] == 1 && ks[2] == 1;
+  float *col = NULL;
+  const float *src = bottom;
+  if (!one && h_ne > 0) {
+    int ni[216];
+    oc_ni_table(ks, ni);
+    const int32_t *child = (const int32_t *)(octree + prop_offset(octree, P_CHILD, depth));
+    int32_t *ichild = (int32_t *)calloc((size_t)h_ne, sizeof(int32_t));
+    oc_ichild(ichild, child, nnum[depth]);
+    col = (float *)malloc(sizeof(float) * (size_t)(kd * h_ne));
+    oc_octree2col_p(col, bottom, cin, (int)h_ne, (int)h_ne, K,
+                    (const int32_t *)(octree + prop_offset(octree, P_NEIGH, depth)), ni, child, ichild);
+    free(ichild);
+    src = col;
+  }
+  for (int m = 0; m < cout; ++m)
+    for (long h = 0; h < top_h; ++h) {
+      float acc = 0.0f;
+      if (h_ne > 0)
+        for (long k = 0; k < kd; ++k) acc += weights[m * kd + k] * src[k * top_h + h];
+      top[m * top_h + h] = acc;
+    }
+  free(col);
+  return count;
+}
+
 /* ---- pool / pad ------------------------------------------------------------------------- */
 /* octree_max_pool_cpu, octree/octree/octree_nn.cpp:301-322: strict '>' so the first maximum
  * wins; mask holds the absolute bottom row. */

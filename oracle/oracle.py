@@ -47,6 +47,12 @@ def lib():
     L.oc_calc_neigh_full.argtypes = [c_int_p, ctypes.c_int, ctypes.c_int]
     L.oc_calc_neigh_split.argtypes = [c_int_p, c_int_p, c_int_p, ctypes.c_int]
     L.oc_octree2col.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 4 + [c_int_p, c_int_p]
+    L.oc_octree2col_p.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 4 + [c_int_p] * 4
+    L.oc_ichild.argtypes = [c_int_p, c_int_p, ctypes.c_int]
+    L.oc_octree_conv_nempty.restype = ctypes.c_long
+    L.oc_octree_conv_nempty.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p,
+                                        ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                        c_int_p]
     L.oc_octree_conv.restype = ctypes.c_long
     L.oc_octree_conv.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p, ctypes.c_char_p,
                                  ctypes.c_int, ctypes.c_int, ctypes.c_int, c_int_p, ctypes.c_int]
@@ -237,6 +243,36 @@ def octree_conv(data, weights, octree, depth, num_output, ksize, stride):
   top = np.zeros((num_output, n // num_output), np.float32)
   lib().oc_octree_conv(_fp(top), n, _fp(data), _fp(weights), obuf, depth, cin, num_output,
                        _ip(ks), stride)
+  return top
+
+
+def octree2col_p(data, neigh, child, ksize):
+  """octree2colP (nempty, stride 1): data [C, nne] over the non-empty nodes -> [C, K, nne]."""
+  data, neigh, child = _f32(data), _i32(neigh), _i32(child)
+  channel, nne = data.shape
+  ni = ni_table(ksize)
+  kdim = int(np.prod(ksize))
+  ichild = np.zeros(max(nne, 1), np.int32)
+  lib().oc_ichild(_ip(ichild), _ip(child), child.shape[0])
+  col = np.empty((channel, kdim, nne), np.float32)
+  lib().oc_octree2col_p(_fp(col), _fp(data), channel, nne, nne, kdim, _ip(neigh), _ip(ni),
+                        _ip(child), _ip(ichild))
+  return col
+
+
+def octree_conv_nempty(data, weights, octree, depth, num_output, ksize):
+  """OctreeConv(nempty=True), stride 1: data [Cin, nne[depth]] -> [Cout, nne[depth]]."""
+  data, weights = _f32(data), _f32(weights)
+  ks = _i32(ksize)
+  obuf = _bytes(octree)
+  cin = data.shape[0]
+  n = lib().oc_octree_conv_nempty(None, 0, _fp(data), _fp(weights), obuf, depth, cin, num_output,
+                                  _ip(ks))
+  if n < 0:
+    raise ValueError('unsupported convolution')
+  top = np.zeros((num_output, n // num_output), np.float32)
+  lib().oc_octree_conv_nempty(_fp(top), n, _fp(data), _fp(weights), obuf, depth, cin, num_output,
+                              _ip(ks))
   return top
 
 

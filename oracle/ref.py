@@ -169,6 +169,22 @@ class Ref:
                             _ip(ni), height, 0)
     return col
 
+  def octree2col_p(self, data, neigh, child, ksize):
+    """octree2colP_cpu with ichild built as the PyTorch binding does (pad_backward of 0..nnum-1)."""
+    data, neigh, child = _f32(data), _i32(neigh), _i32(child)
+    channel, nne = data.shape
+    ni = self.ni_table(ksize)
+    kdim = int(np.prod(ksize))
+    nnum = child.shape[0]
+    ichild = np.zeros((1, max(nne, 1)), dtype=np.float32)
+    self.lib.ref_pad_backward(_fp(ichild), nne, 1, _fp(np.arange(nnum, dtype=np.float32)), nnum,
+                              _ip(child))
+    ichild = ichild.reshape(-1).astype(np.int32)
+    col = np.empty((channel, kdim, nne), dtype=np.float32)
+    self.lib.ref_octree2colP(_fp(col), _fp(data), channel, nne, nne, kdim, 1, _ip(neigh), _ip(ni),
+                             _ip(child), _ip(ichild), nne, 0)
+    return col
+
   def max_pool(self, btm):
     btm = _f32(btm)
     channel, btm_h = btm.shape

@@ -123,9 +123,9 @@ def test_conv_errors(ocnn, batch):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [4], 1)
   with pytest.raises(RuntimeError, match='stride'):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [3], 3)
-  with pytest.raises(RuntimeError, match='not implemented'):
+  with pytest.raises(RuntimeError, match='stride 1'):       # nempty: stride 1 only
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[5]), 1, device='cuda'), w, octree, 5, 4,
-                     [3], 1, True)
+                     [3], 2, True)
 
 
 # ---- tensor-core (tcgen05) path -----------------------------------------------------------------
@@ -236,3 +236,45 @@ def test_conv_pointwise_bf16(ocnn, batch, shape):
                                   torch.from_numpy(bias).cuda(), gu.data_cuda(res, True, True), True)
   want = np.maximum(ref * scale[:, None] + bias[:, None] + res, 0)
   assert gu.rel_err(gu.to_np(got), want) < 6e-3
+
+
+# ---- convolution on the non-empty nodes only (nempty=True) ----------------------------------------
+@pytest.mark.parametrize('ks', [[3, 3, 3], [3, 1, 1], [2, 2, 2], [1, 1, 1]])
+@pytest.mark.parametrize('nm,bf16', [(False, False), (True, False), (True, True)])
+def test_conv_nempty(ocnn, batch, ks, nm, bf16):
+  """OctreeConv(nempty=True), stride 1, against the oracle's octree2colP-based convolution, and the
+  identity the reference's own test relies on (pytorch/test/test_octree_conv.py): it equals the
+  dense convolution of the zero-padded data read back at the non-empty nodes."""
+  merged, octree, v = batch
+  rng = np.random.default_rng(31)
+  for d in (5, 3):
+    nne = int(v.nnum_nempty[d])
+    cin, cout = 6, 10
+    x = rng.uniform(-1, 1, size=(cin, nne)).astype(np.float32)
+    if bf16:
+      x = gu.bf16_round(x)
+    w = rng.normal(scale=0.2, size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
+    want = oc.octree_conv_nempty(x, w, merged, d, cout, ks)
+    wt = torch.from_numpy(w).cuda()
+    got = ocnn.octree_conv(gu.data_cuda(x, nm, bf16), wt, octree, d, cout, ks, 1, True)
+    assert got.shape == (1, cout, nne, 1)
+    assert gu.rel_err(gu.to_np(got), want) < (BF16_TOL if bf16 else 1e-5)
+    if not bf16:
+      dense = ocnn.octree_conv(ocnn.octree_pad(gu.data_cuda(x, nm, False), octree, d, 0.0), wt,
+                               octree, d, cout, ks, 1, False)
+      assert np.array_equal(gu.to_np(ocnn.octree_depad(dense, octree, d)), gu.to_np(got))
+    mod = ocnn.OctreeConv(d, cin, cout, ks, 1, nempty=True).cuda()
+    with torch.no_grad():
+      mod.weights.copy_(wt.view_as(mod.weights))
+    assert np.array_equal(gu.to_np(mod(gu.data_cuda(x, nm, bf16), octree)), gu.to_np(got))
+
+
+def test_conv_nempty_errors(ocnn, batch):
+  _, octree, v = batch
+  w = torch.zeros(4, 3 * 8, device='cuda')
+  with pytest.raises(RuntimeError, match='stride 1'):
+    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[4]), 1, device='cuda'), w, octree, 4, 4,
+                     [2], 2, True)
+  with pytest.raises(RuntimeError, match='non-empty node number'):
+    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[4]), 1, device='cuda'),
+                     torch.zeros(4, 81, device='cuda'), octree, 4, 4, [3], 1, True)

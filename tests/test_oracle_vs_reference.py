@@ -120,6 +120,26 @@ def test_conv_and_octree2col(batch, ks, stride):
                      oc.octree2col(x, v.prop('neigh', d), ks, stride, hc))
 
 
+@pytest.mark.parametrize('ks', [[3, 3, 3], [3, 1, 1], [2, 2, 2], [1, 1, 1]])
+def test_octree2col_nempty(batch, ks):
+  """octree2colP (the convolution restricted to non-empty nodes): the restatement against the
+  reference's octree2colP_cpu, and the convolution built on it against the identity the
+  reference's own test uses (pytorch/test/test_octree_conv.py: OctreeConv(nempty=True) equals the
+  dense convolution of the zero-padded data, read back at the non-empty nodes)."""
+  kb, R, _, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(21)
+  for d in (6, 4):
+    nne = int(v.nnum_nempty[d])
+    child, neigh = v.prop('child', d), v.prop('neigh', d)
+    x = rng.uniform(-1, 1, size=(3, nne)).astype(np.float32)
+    assert same_bits(R.octree2col_p(x, neigh, child, ks), oc.octree2col_p(x, neigh, child, ks))
+    w = rng.normal(size=(5, 3 * int(np.prod(ks)))).astype(np.float32)
+    got = oc.octree_conv_nempty(x, w, merged_o, d, 5, ks)
+    dense = oc.octree_conv(oc.pad(x, child, 0.0), w, merged_o, d, 5, ks, 1)
+    assert same_bits(got, oc.depad(dense, child, nne))
+
+
 def test_pool_pad_depad(batch):
   kb, R, _, merged_o = batch
   v = oc.OctreeView(merged_o)
