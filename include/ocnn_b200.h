@@ -181,7 +181,9 @@ int ocnn_octree_conv(const void* x_dev, const float* weights_dev, void* y_dev,
  * in order); child_dev: the level's Child block (nnum ints); ichild_dev: its inverse (nne ints),
  * filled by ocnn_octree_ichild.  y[co, i] = sum w[co, ci*K + t] * x[ci, child[nbr(ichild[i], t)]],
  * neighbours that are missing or empty contribute 0.  fp32 / bf16 data in either layout on the
- * CUDA-core kernel (the tensor-core kernel does not take this form yet). */
+ * CUDA-core kernel; bf16 node-major data on the tensor-core kernel through the *_nempty entry
+ * points below (weights packed with ocnn_conv_pack_weights_nempty: a tile row is a single node
+ * here, never a sibling group). */
 int ocnn_octree_ichild(const int32_t* child_dev, int nnum, int32_t* ichild_dev, void* stream);
 int ocnn_octree_conv_nempty(const void* x_dev, const float* weights_dev, void* y_dev,
                             const int32_t* neigh_dev, const int32_t* child_dev,
@@ -192,6 +194,14 @@ int ocnn_octree_conv_nempty(const void* x_dev, const float* weights_dev, void* y
 /* Tensor-core path: weights packed once per layer into bf16 K-major tiles.  The packed image
  * depends on the kernel shape AND the stride the layer will run with (stride-1 neighbourhood
  * convolutions with few channels use a per-sibling-group formulation with expanded weights). */
+size_t ocnn_conv_packed_weight_bytes_nempty(int cin, int cout, const int kernel_size[3]);
+int ocnn_conv_pack_weights_nempty(const float* weights_dev, void* packed_dev, int cin, int cout,
+                                  const int kernel_size[3], void* stream);
+int ocnn_octree_conv_tc_nempty(const void* x_dev, const void* packed_dev, void* y_dev,
+                               const int32_t* neigh_dev, const int32_t* child_dev,
+                               const int32_t* ichild_dev, int nne, int cin, int cout,
+                               const int kernel_size[3], const ocnn_conv_epilogue* epilogue,
+                               int32_t* status_dev, void* stream);
 size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride);
 int ocnn_conv_pack_weights(const float* weights_dev, void* packed_dev, int cin, int cout,
                            const int kernel_size[3], int stride, void* stream);

@@ -50,6 +50,8 @@ struct TcArgs {
   const uint8_t* wpacked;
   __nv_bfloat16* y;
   const int* neigh;
+  const int* child;    // convolution on non-empty nodes only: the level's child array and its
+  const int* ichild;   // inverse (node of the i-th non-empty node); NULL otherwise
   int h_in, h_out, cin, cout, npad, T, stride, identity, nkb, stages, tmem_cols;
   int group;        // 1: tile rows are sibling groups (see the header comment), 0: nodes
   int rows;         // number of tile rows in total: h_out, or h_out / 8 in group mode
@@ -308,7 +310,10 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
         }
       }
     } else {
-      const int oct_code = ((h & 4) << 2) | ((h & 2) << 1) | (h & 1);
+      // on non-empty nodes only (octree2colP): tile row h is the h-th non-empty node; its
+      // neighbours are looked up from the node itself and mapped back to non-empty ranks
+      const int hn = (a.ichild != nullptr && live) ? a.ichild[h] : h;
+      const int oct_code = ((hn & 4) << 2) | ((hn & 2) << 1) | (hn & 1);
       if (a.identity) {
         nbr[a.rowsplit >= 2 ? (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7) : tid] = live ? h : -1;
       } else {
@@ -325,11 +330,16 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
         if (t < a.T && live) {
           // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
           // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
-          const long long at = a.stride == 2 ? ((long long)h << 6) + a.tap[t]
-                                             : ((long long)(h >> 3) << 6) + a.tap[t] + oct_code;
+          const long long at = a.stride == 2 ? ((long long)hn << 6) + a.tap[t]
+                                             : ((long long)(hn >> 3) << 6) + a.tap[t] + oct_code;
           p = a.neigh[at];
         }
         pv[t] = p;
+      }
+      if (a.ichild != nullptr) {
+#pragma unroll
+        for (int t = 0; t < 27; ++t)
+          if (t < a.T && pv[t] >= 0) pv[t] = a.child[pv[t]];
       }
 #pragma unroll
       for (int t = 0; t < 27; ++t)
@@ -712,7 +722,8 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
 
 struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable, ntable_stride; size_t smem; };
 
-int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1) {
+int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1,
+             bool nempty = false) {
   const TapList tl = taps_for_kernel(ks);
   if (tl.count < 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported kernel size %dx%dx%d",
@@ -730,7 +741,8 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   if (s->slices > 1) cout = 256;
   // sibling-group mode: stride 1, a real neighbourhood, few channels (power-of-two Cout so that
   // column -> channel is a mask)
-  s->group = (stride == 1 && tl.count > 1 && cin <= 32 && cout <= 32 && (cout & (cout - 1)) == 0) ? 1 : 0;
+  // (not on non-empty nodes only: their tile rows are single nodes, not sibling groups)
+  s->group = (!nempty && stride == 1 && tl.count > 1 && cin <= 32 && cout <= 32 && (cout & (cout - 1)) == 0) ? 1 : 0;
   s->T = s->group ? 64 : tl.count;
   s->npad = s->group ? 8 * cout : (cout + 15) / 16 * 16;
   s->nkb = (cin * s->T + kBlockK - 1) / kBlockK;
@@ -785,18 +797,27 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
 
 extern "C" {
 
-size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride) {
+static size_t packed_bytes_impl(int cin, int cout, const int kernel_size[3], int stride, bool nempty) {
   ocnn::TcShape s;
-  if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, stride, &s) != OCNN_OK) return 0;
+  if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, stride, &s, -1, nempty) != OCNN_OK)
+    return 0;
   return (size_t)s.slices * s.nkb * s.npad * 128;
 }
 
-int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
-                           int stride, void* stream) {
+size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride) {
+  return packed_bytes_impl(cin, cout, kernel_size, stride, false);
+}
+
+size_t ocnn_conv_packed_weight_bytes_nempty(int cin, int cout, const int kernel_size[3]) {
+  return packed_bytes_impl(cin, cout, kernel_size, 1, true);
+}
+
+static int pack_weights_impl(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
+                             int stride, bool nempty, void* stream) {
   using namespace ocnn;
   OCNN_REQUIRE(w && packed && kernel_size, "ocnn_conv_pack_weights: null pointer");
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, stride, &s)) return st;
+  if (int st = tc_shape(cin, cout, kernel_size, stride, &s, -1, nempty)) return st;
   const long long total = (long long)s.nkb * s.npad * kBlockK;
   if (s.group) {
     const TapList tl = taps_for_kernel(kernel_size);
@@ -819,14 +840,26 @@ int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, cons
   return OCNN_OK;
 }
 
-int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_t* neigh, int h_in,
-                        int h_out, int cin, int cout, const int kernel_size[3], int stride,
+int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
+                           int stride, void* stream) {
+  return pack_weights_impl(w, packed, cin, cout, kernel_size, stride, false, stream);
+}
+
+int ocnn_conv_pack_weights_nempty(const float* w, void* packed, int cin, int cout,
+                                  const int kernel_size[3], void* stream) {
+  return pack_weights_impl(w, packed, cin, cout, kernel_size, 1, true, stream);
+}
+
+static int conv_tc_impl(const void* x, const void* packed, void* y, const int32_t* neigh,
+                        const int32_t* child, const int32_t* ichild, int h_in, int h_out, int cin,
+                        int cout, const int kernel_size[3], int stride,
                         const ocnn_conv_epilogue* ep, int32_t* status, void* stream) {
   using namespace ocnn;
+  const bool nempty = ichild != nullptr;
   OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_tc: null kernel size");
   OCNN_REQUIRE(stride == 1 || stride == 2, "ocnn_octree_conv_tc: stride must be 1 or 2 (got %d)", stride);
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, stride, &s, h_out)) return st;
+  if (int st = tc_shape(cin, cout, kernel_size, stride, &s, h_out, nempty)) return st;
   OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv_tc: negative height");
   if (h_out == 0) return OCNN_OK;
   const bool identity = s.T == 1 && stride == 1;
@@ -849,6 +882,8 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   a.wpacked = static_cast<const uint8_t*>(packed);
   a.y = static_cast<__nv_bfloat16*>(y);
   a.neigh = neigh;
+  a.child = child;
+  a.ichild = ichild;
   a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout; a.npad = s.npad; a.T = s.T;
   a.stride = stride; a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
   a.tmem_cols = s.tmem_cols;
@@ -910,6 +945,24 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
                               static_cast<cudaStream_t>(stream), a));
   OCNN_LAUNCH_OK("conv_tc_kernel");
   return OCNN_OK;
+}
+
+int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_t* neigh, int h_in,
+                        int h_out, int cin, int cout, const int kernel_size[3], int stride,
+                        const ocnn_conv_epilogue* ep, int32_t* status, void* stream) {
+  return conv_tc_impl(x, packed, y, neigh, nullptr, nullptr, h_in, h_out, cin, cout, kernel_size,
+                      stride, ep, status, stream);
+}
+
+int ocnn_octree_conv_tc_nempty(const void* x, const void* packed, void* y, const int32_t* neigh,
+                               const int32_t* child, const int32_t* ichild, int nne, int cin,
+                               int cout, const int kernel_size[3], const ocnn_conv_epilogue* ep,
+                               int32_t* status, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(child != nullptr && ichild != nullptr,
+               "ocnn_octree_conv_tc_nempty: child and ichild required");
+  return conv_tc_impl(x, packed, y, neigh, child, ichild, nne, nne, cin, cout, kernel_size, 1, ep,
+                      status, stream);
 }
 
 }  // extern "C"

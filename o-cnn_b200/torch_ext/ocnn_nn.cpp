@@ -455,6 +455,59 @@ Tensor octree_conv_tc(Tensor data_in, Tensor packed, Tensor octree, int depth, i
   return y;
 }
 
+// Tensor-core convolution on the non-empty nodes only (nempty = True, stride 1).
+Tensor conv_pack_weights_nempty(Tensor weights, int cin, int cout, vector<int> kernel_size) {
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32,
+              "weights must be a float32 CUDA tensor");
+  const int kdim = ks[0] * ks[1] * ks[2];
+  TORCH_CHECK(weights.numel() == (int64_t)cout * cin * kdim, "weights must have Cout*Cin*K values");
+  c10::cuda::CUDAGuard guard(weights.device());
+  const size_t bytes = ocnn_conv_packed_weight_bytes_nempty(cin, cout, ks.data());
+  TORCH_CHECK(bytes > 0, "this shape is not supported by the tensor-core convolution: ",
+              ocnn_last_error());
+  Tensor packed = torch::empty({(int64_t)bytes}, weights.options().dtype(torch::kUInt8));
+  Tensor w = weights.contiguous();
+  OCNN_CALL(ocnn_conv_pack_weights_nempty(w.data_ptr<float>(), packed.data_ptr(), cin, cout,
+                                          ks.data(), current_stream()));
+  return packed;
+}
+
+Tensor octree_conv_tc_nempty(Tensor data_in, Tensor packed, Tensor octree, int depth, int num_output,
+                             vector<int> kernel_size, c10::optional<Tensor> scale,
+                             c10::optional<Tensor> bias, c10::optional<Tensor> residual, bool relu,
+                             Tensor status) {
+  vector<int> ks = kernel3(kernel_size);
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_conv_tc_nempty: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth >= 1 && depth <= o.meta.depth, "octree_conv_tc_nempty: depth ", depth,
+              " outside the octree");
+  need_cuda(data_in, "octree_conv_tc_nempty");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "octree_conv_tc_nempty");
+  TORCH_CHECK(x.dtype == OCNN_BF16 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
+              "octree_conv_tc_nempty takes bfloat16 channels_last data");
+  x.layout = OCNN_NODE_MAJOR;
+  const int nne = o.meta.nnum_nempty[depth], nnum = o.meta.nnum[depth];
+  TORCH_CHECK(x.H == nne, "octree_conv_tc_nempty: data height ", x.H, " != non-empty node number ", nne);
+  TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
+                  (size_t)packed.numel() == ocnn_conv_packed_weight_bytes_nempty(x.C, num_output, ks.data()),
+              "packed weights do not match this convolution's shape");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32 && status.numel() >= 1,
+              "status must be an int32 CUDA tensor");
+  Tensor y = new_data(num_output, nne, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  const int32_t* child = level_ptr(o, OCNN_PROP_CHILD, depth, "octree_conv_tc_nempty");
+  Tensor ichild = torch::empty({std::max(nne, 1)}, x.t.options().dtype(torch::kInt32));
+  OCNN_CALL(ocnn_octree_ichild(child, nnum, ichild.data_ptr<int32_t>(), current_stream()));
+  const int kdim = ks[0] * ks[1] * ks[2];
+  const int32_t* neigh = kdim > 1 ? level_ptr(o, OCNN_PROP_NEIGH, depth, "octree_conv_tc_nempty") : nullptr;
+  OCNN_CALL(ocnn_octree_conv_tc_nempty(x.t.data_ptr(), packed.data_ptr(), y.data_ptr(), neigh, child,
+                                       ichild.data_ptr<int32_t>(), nne, x.C, num_output, ks.data(),
+                                       &ep, status.data_ptr<int32_t>(), current_stream()));
+  return y;
+}
+
 // ---- points ------------------------------------------------------------------------------------------
 // Points buffer: 88-byte PointsInfo header (magic[16], pt_num, content_flags, channels[8],
 // ptr_dis[8]) then xyz / normal / feature / label float arrays
@@ -1040,6 +1093,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("kernel_size"), py::arg("stride") = 1);
   m.def("octree_conv_tc", &octree_conv_tc, py::arg("data_in"), py::arg("packed"), py::arg("octree"),
         py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"), py::arg("stride"),
+        py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
+  m.def("conv_pack_weights_nempty", &conv_pack_weights_nempty, py::arg("weights"), py::arg("cin"),
+        py::arg("cout"), py::arg("kernel_size"));
+  m.def("octree_conv_tc_nempty", &octree_conv_tc_nempty, py::arg("data_in"), py::arg("packed"),
+        py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
         py::arg("scale") = py::none(), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
   m.def("octree_info", &octree_info);

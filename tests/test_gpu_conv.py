@@ -278,3 +278,38 @@ def test_conv_nempty_errors(ocnn, batch):
   with pytest.raises(RuntimeError, match='non-empty node number'):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[4]), 1, device='cuda'),
                      torch.zeros(4, 81, device='cuda'), octree, 4, 4, [3], 1, True)
+
+
+@pytest.mark.parametrize('case', [(5, 16, 16, [3, 3, 3]), (5, 8, 32, [3, 3, 3]), (4, 64, 64, [3, 3, 3]),
+                                  (3, 128, 128, [3, 3, 3]), (4, 24, 40, [3, 3, 3]), (5, 32, 64, [1, 1, 1]),
+                                  (4, 32, 16, [3, 1, 3])],
+                         ids=lambda c: 'd%d_%dto%d_k%s' % (c[0], c[1], c[2], ''.join(map(str, c[3]))))
+def test_conv_tensor_core_nempty(ocnn, batch, case):
+  """The tensor-core kernel on the non-empty nodes only, with the fused epilogue, against the
+  oracle's octree2colP-based convolution."""
+  merged, octree, v = batch
+  d, cin, cout, ks = case
+  rng = np.random.default_rng(41 + cin + cout)
+  nne = int(v.nnum_nempty[d])
+  x = gu.bf16_round(rng.uniform(-1, 1, size=(cin, nne)).astype(np.float32))
+  w = rng.normal(scale=0.1, size=(cout, cin * int(np.prod(ks)))).astype(np.float32)
+  scale = rng.uniform(0.5, 1.5, size=cout).astype(np.float32)
+  bias = rng.normal(size=cout).astype(np.float32)
+  res = gu.bf16_round(rng.normal(size=(cout, nne)).astype(np.float32))
+  wt = torch.from_numpy(w).cuda()
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights_nempty(wt, cin, cout, ks)
+  got = ocnn.nn.octree_conv_tc_nempty(gu.data_cuda(x, True, True), packed, octree, d, cout, ks,
+                                      None, None, None, False, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  want = oc.octree_conv_nempty(x, w, merged, d, cout, ks)
+  assert got.shape == (1, cout, nne, 1)
+  assert gu.rel_err(gu.to_np(got), want) < BF16_TOL
+  got = ocnn.nn.octree_conv_tc_nempty(gu.data_cuda(x, True, True), packed, octree, d, cout, ks,
+                                      torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda(),
+                                      gu.data_cuda(res, True, True), True, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  full = np.maximum(want * scale[:, None] + bias[:, None] + res, 0)
+  assert gu.rel_err(gu.to_np(got), full) < BF16_TOL
