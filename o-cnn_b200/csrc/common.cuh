@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/ocnn_b200.h"
 
@@ -44,7 +45,16 @@ void note_launches(int n);
   } while (0)
 
 // ---- launch geometry --------------------------------------------------------------------------
-constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs
+constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs (compile-time sizing of fixed scan grids)
+// Streaming multiprocessors of the current device, queried once per device (kSMs if the query
+// fails); grid-size decisions taken at launch time use this.
+int sm_count();
+
+// "Done once per device" flags for per-function attributes (cudaFuncSetAttribute is per device).
+struct PerDeviceOnce {
+  std::mutex mutex;
+  bool done[64] = {};
+};
 
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
@@ -52,7 +62,7 @@ inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 // waves over the 148 SMs.
 inline int grid_for(long long work, int threads, int blocks_per_sm = 8) {
   long long need = (work + threads - 1) / threads;
-  long long cap = (long long)kSMs * blocks_per_sm;
+  long long cap = (long long)sm_count() * blocks_per_sm;
   if (need < 1) need = 1;
   return (int)(need < cap ? need : cap);
 }

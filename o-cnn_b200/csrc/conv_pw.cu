@@ -115,13 +115,17 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
 template <int COUT, int ROWS>
 int launch_pw(const PwArgs& a, cudaStream_t st) {
   const size_t smem = (size_t)a.cin * COUT * sizeof(float);
-  static bool attr_set[64] = {};
+  static PerDeviceOnce attr_once;      // one per template instance
   int device = 0;
   OCNN_CUDA_OK(cudaGetDevice(&device));
-  if (smem > 48 * 1024 && (device < 0 || device >= 64 || !attr_set[device])) {
-    OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<COUT, ROWS>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-    if (device >= 0 && device < 64) attr_set[device] = true;
+  if (smem > 48 * 1024) {
+    std::lock_guard<std::mutex> lock(attr_once.mutex);
+    const bool known = device >= 0 && device < 64;
+    if (!known || !attr_once.done[device]) {
+      OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<COUT, ROWS>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      if (known) attr_once.done[device] = true;
+    }
   }
   const int grid = grid_for(((long long)a.h + ROWS - 1) / ROWS, 256, 4);
   OCNN_CUDA_OK(launch_chained(conv_pw_kernel<COUT, ROWS>, dim3(grid), dim3(256), smem, st, a));

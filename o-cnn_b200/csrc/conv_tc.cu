@@ -771,10 +771,11 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   // image, so halving stops where a K-block's gather (about 8 cycles per row of 16-byte copies)
   // is no longer above its weight tile (about 3.2 cycles per 128-byte row).
   s->tile_rows = kTileM;
-  while (rows >= 0 && s->tile_rows > 32 && 2 * ((rows + s->tile_rows - 1) / s->tile_rows) <= kSMs &&
+  const int sms = rows >= 0 ? sm_count() : kSMs;
+  while (rows >= 0 && s->tile_rows > 32 && 2 * ((rows + s->tile_rows - 1) / s->tile_rows) <= sms &&
          8.0 * s->tile_rows > 3.2 * s->npad)
     s->tile_rows >>= 1;
-  const bool small_grid = rows >= 0 && (rows + s->tile_rows - 1) / s->tile_rows <= kSMs;
+  const bool small_grid = rows >= 0 && (rows + s->tile_rows - 1) / s->tile_rows <= sms;
   if (st < 2 || 2 * s->tmem_cols > 512 || small_grid) {
     st = (int)((one_cta - fixed) / stage_bytes);
     if (st > 7) st = 7;
@@ -915,7 +916,7 @@ static int conv_tc_impl(const void* x, const void* packed, void* y, const int32_
     a.tap[i] = (signed char)(((tap / 9) << 4) | (((tap / 3) % 3) << 2) | (tap % 3));
   }
   // raising the dynamic shared memory limit is per function and per device
-  static bool attr_set[64] = {};
+  static PerDeviceOnce attr_once;
   int device = 0;
   OCNN_CUDA_OK(cudaGetDevice(&device));
   void (*kernel)(const TcArgs) = conv_tc_kernel<0>;
@@ -929,13 +930,17 @@ static int conv_tc_impl(const void* x, const void* packed, void* y, const int32_
     case 64: kernel = conv_tc_kernel<64>; break;
     default: break;
   }
-  if (device < 0 || device >= 64 || !attr_set[device]) {
+  {
+    std::lock_guard<std::mutex> lock(attr_once.mutex);
+    const bool known = device >= 0 && device < 64;
+    if (!known || !attr_once.done[device]) {
     void (*all[])(const TcArgs) = {conv_tc_kernel<0>, conv_tc_kernel<1>, conv_tc_kernel<2>,
                                    conv_tc_kernel<4>, conv_tc_kernel<8>, conv_tc_kernel<16>,
                                    conv_tc_kernel<32>, conv_tc_kernel<64>};
     for (auto k : all)
       OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    if (device >= 0 && device < 64) attr_set[device] = true;
+    if (known) attr_once.done[device] = true;
+    }
   }
   OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
                "ocnn_octree_conv_tc: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses",

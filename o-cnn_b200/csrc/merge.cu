@@ -67,6 +67,81 @@ bool at_level(const ocnn_octree_meta* m, int prop, int d) {
   return m->channels[prop] != 0 && (m->locations[prop] == -1 || m->locations[prop] == d);
 }
 
+// The merged header: the first octree's header with batch size, neighbour property, node counts
+// and block offsets replaced (MergeOctrees::set_batch_info, merge_octrees.cpp:92-106).
+void merged_header(const void* first_header_host, const ocnn_octree_meta* merged,
+                   uint8_t (&hdr)[OCNN_HEADER_BYTES]) {
+  const int depth = merged->depth;
+  memset(hdr, 0, sizeof(hdr));
+  memcpy(hdr, first_header_host, 716);
+  auto i32 = [&](int off) { return reinterpret_cast<int32_t*>(hdr + off); };
+  *i32(kOffBatch) = merged->batch_size;
+  int flags = 0;
+  for (int d = 0; d < OCNN_MAX_DEPTH; ++d) {
+    if (d <= depth) { i32(kOffNnum)[d] = merged->nnum[d]; i32(kOffNnumNempty)[d] = merged->nnum_nempty[d]; }
+    if (d <= depth + 2) i32(kOffNnumCum)[d] = merged->nnum_cum[d];
+  }
+  for (int p = 0; p < OCNN_PROP_COUNT; ++p) {
+    i32(kOffChannels)[p] = merged->channels[p];
+    if (merged->channels[p] != 0) { i32(kOffLocations)[p] = merged->locations[p]; flags |= 1 << p; }
+  }
+  for (int p = 0; p <= OCNN_PROP_COUNT; ++p) i32(kOffPtrDis)[p] = (int32_t)merged->ptr_dis[p];
+  *i32(kOffFlags) = flags;
+}
+
+// The (octree, level) table merge_kernel walks, written to `entries` (room for batch*(depth+1));
+// returns the number of entries; *max_n = the largest node count of any entry.
+int merge_table(const void* const* octrees_dev, const ocnn_octree_meta* in, int batch, int depth,
+                MergeEntry* entries, int* max_n) {
+  int ne = 0;
+  *max_n = 1;
+  for (int d = 0; d <= depth; ++d) {
+    int node0 = 0, ne0 = 0;
+    for (int b = 0; b < batch; ++b) {
+      const ocnn_octree_meta* m = &in[b];
+      MergeEntry e;
+      e.src = static_cast<const uint8_t*>(octrees_dev[b]);
+      e.key = at_level(m, OCNN_PROP_KEY, d) ? ocnn_prop_offset(m, OCNN_PROP_KEY, d) : -1;
+      e.child = at_level(m, OCNN_PROP_CHILD, d) ? ocnn_prop_offset(m, OCNN_PROP_CHILD, d) : -1;
+      e.feat = at_level(m, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(m, OCNN_PROP_FEATURE, d) : -1;
+      e.label = at_level(m, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(m, OCNN_PROP_LABEL, d) : -1;
+      e.split = at_level(m, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(m, OCNN_PROP_SPLIT, d) : -1;
+      e.n = m->nnum[d]; e.node0 = node0; e.ne0 = ne0; e.b = b; e.d = d;
+      if (e.n > 0) entries[ne++] = e;
+      if (e.n > *max_n) *max_n = e.n;
+      node0 += m->nnum[d];
+      ne0 += m->nnum_nempty[d];
+    }
+  }
+  return ne;
+}
+
+MergeDst merge_destination(const ocnn_octree_meta* merged, uint8_t* out) {
+  MergeDst dst;
+  memset(&dst, 0, sizeof(dst));
+  dst.out = out;
+  dst.key_bytes = merged->key_bits / 8;
+  dst.cfeat = merged->channels[OCNN_PROP_FEATURE];
+  for (int d = 0; d <= merged->depth; ++d) {
+    dst.key[d] = ocnn_prop_offset(merged, OCNN_PROP_KEY, d);
+    dst.child[d] = ocnn_prop_offset(merged, OCNN_PROP_CHILD, d);
+    dst.feat[d] = at_level(merged, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(merged, OCNN_PROP_FEATURE, d) : -1;
+    dst.label[d] = at_level(merged, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(merged, OCNN_PROP_LABEL, d) : -1;
+    dst.split[d] = at_level(merged, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(merged, OCNN_PROP_SPLIT, d) : -1;
+    dst.nnum[d] = merged->nnum[d];
+  }
+  return dst;
+}
+
+// Enqueue the merge of `ne` table entries already resident at table_dev.
+int launch_merge(const MergeEntry* table_dev, int ne, int max_n, const MergeDst& dst,
+                 cudaStream_t st, const char* what) {
+  dim3 grid(ceil_div(max_n, 256) < 64 ? ceil_div(max_n, 256) : 64, ne < 4096 ? ne : 4096);
+  merge_kernel<<<grid, 256, 0, st>>>(table_dev, ne, dst);
+  OCNN_LAUNCH_OK(what);
+  return OCNN_OK;
+}
+
 }  // namespace
 }  // namespace ocnn
 
@@ -127,69 +202,21 @@ int ocnn_octree_batch(const void* const* octrees_dev, const ocnn_octree_meta* in
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* o = static_cast<uint8_t*>(out);
 
-  // header: the first octree's header with batch size, neighbour property, node counts and
-  // block offsets replaced (MergeOctrees::set_batch_info, merge_octrees.cpp:92-106)
   uint8_t hdr[OCNN_HEADER_BYTES];
-  memset(hdr, 0, sizeof(hdr));
-  memcpy(hdr, first_header_host, 716);
-  auto i32 = [&](int off) { return reinterpret_cast<int32_t*>(hdr + off); };
-  *i32(kOffBatch) = merged->batch_size;
-  int flags = 0;
-  for (int d = 0; d < OCNN_MAX_DEPTH; ++d) {
-    if (d <= depth) { i32(kOffNnum)[d] = merged->nnum[d]; i32(kOffNnumNempty)[d] = merged->nnum_nempty[d]; }
-    if (d <= depth + 2) i32(kOffNnumCum)[d] = merged->nnum_cum[d];
-  }
-  for (int p = 0; p < OCNN_PROP_COUNT; ++p) {
-    i32(kOffChannels)[p] = merged->channels[p];
-    if (merged->channels[p] != 0) { i32(kOffLocations)[p] = merged->locations[p]; flags |= 1 << p; }
-  }
-  for (int p = 0; p <= OCNN_PROP_COUNT; ++p) i32(kOffPtrDis)[p] = (int32_t)merged->ptr_dis[p];
-  *i32(kOffFlags) = flags;
+  merged_header(first_header_host, merged, hdr);
   if (header_host_out) memcpy(header_host_out, hdr, OCNN_HEADER_BYTES);
   OCNN_CUDA_OK(cudaMemcpyAsync(o, hdr, OCNN_HEADER_BYTES, cudaMemcpyHostToDevice, st));
 
-  std::vector<MergeEntry> entries;
-  entries.reserve((size_t)batch * (depth + 1));
+  std::vector<MergeEntry> entries((size_t)batch * (depth + 1));
   int max_n = 1;
-  for (int d = 0; d <= depth; ++d) {
-    int node0 = 0, ne0 = 0;
-    for (int b = 0; b < batch; ++b) {
-      const ocnn_octree_meta* m = &in[b];
-      MergeEntry e;
-      e.src = static_cast<const uint8_t*>(octrees_dev[b]);
-      e.key = at_level(m, OCNN_PROP_KEY, d) ? ocnn_prop_offset(m, OCNN_PROP_KEY, d) : -1;
-      e.child = at_level(m, OCNN_PROP_CHILD, d) ? ocnn_prop_offset(m, OCNN_PROP_CHILD, d) : -1;
-      e.feat = at_level(m, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(m, OCNN_PROP_FEATURE, d) : -1;
-      e.label = at_level(m, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(m, OCNN_PROP_LABEL, d) : -1;
-      e.split = at_level(m, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(m, OCNN_PROP_SPLIT, d) : -1;
-      e.n = m->nnum[d]; e.node0 = node0; e.ne0 = ne0; e.b = b; e.d = d;
-      if (e.n > 0) entries.push_back(e);
-      if (e.n > max_n) max_n = e.n;
-      node0 += m->nnum[d];
-      ne0 += m->nnum_nempty[d];
-    }
-  }
-  MergeDst dst;
-  memset(&dst, 0, sizeof(dst));
-  dst.out = o;
-  dst.key_bytes = merged->key_bits / 8;
-  dst.cfeat = merged->channels[OCNN_PROP_FEATURE];
-  for (int d = 0; d <= depth; ++d) {
-    dst.key[d] = ocnn_prop_offset(merged, OCNN_PROP_KEY, d);
-    dst.child[d] = ocnn_prop_offset(merged, OCNN_PROP_CHILD, d);
-    dst.feat[d] = at_level(merged, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(merged, OCNN_PROP_FEATURE, d) : -1;
-    dst.label[d] = at_level(merged, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(merged, OCNN_PROP_LABEL, d) : -1;
-    dst.split[d] = at_level(merged, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(merged, OCNN_PROP_SPLIT, d) : -1;
-    dst.nnum[d] = merged->nnum[d];
-  }
-  if (!entries.empty()) {
-    OCNN_CUDA_OK(cudaMemcpyAsync(workspace, entries.data(), sizeof(MergeEntry) * entries.size(),
-                                 cudaMemcpyHostToDevice, st));
+  const int ne = merge_table(octrees_dev, in, batch, depth, entries.data(), &max_n);
+  if (ne > 0) {
     // the staging vector is pageable memory: the runtime has copied it out before returning
-    const int ne = (int)entries.size();
-    dim3 grid(ceil_div(max_n, 256) < 64 ? ceil_div(max_n, 256) : 64, ne < 4096 ? ne : 4096);
-    merge_kernel<<<grid, 256, 0, st>>>(static_cast<const MergeEntry*>(workspace), ne, dst);
-    OCNN_LAUNCH_OK("merge_kernel");
+    OCNN_CUDA_OK(cudaMemcpyAsync(workspace, entries.data(), sizeof(MergeEntry) * (size_t)ne,
+                                 cudaMemcpyHostToDevice, st));
+    if (int rc = launch_merge(static_cast<const MergeEntry*>(workspace), ne, max_n,
+                              merge_destination(merged, o), st, "merge_kernel"))
+      return rc;
   }
   return ocnn_calc_neigh(out, merged, stream);
 }
@@ -200,8 +227,7 @@ int ocnn_octree_batch(const void* const* octrees_dev, const ocnn_octree_meta* in
 // ---- octree_batch without any caller-provided or allocated scratch ----------------------------
 // The (octree, level) table that merge_kernel reads lives in a fixed array inside this library's
 // device image instead of in a workspace the caller hands over.  Meant for callers that cannot get
-// device memory at the moment of the call: code running while a stream is being captured into a
-// CUDA graph (cudaMalloc is not allowed there), or a process whose framework allocator has already
+// device memory at the moment of the call, e.g. a process whose framework allocator has already
 // claimed the whole GPU so that a fresh cudaMalloc fails.
 namespace ocnn {
 namespace {
@@ -248,59 +274,13 @@ extern "C" int ocnn_octree_batch_noalloc(const void* const* octrees_dev, const o
   }
   MergeEntry* table_dev = static_cast<MergeEntry*>(g_static_dev_ptr[device]);
 
-  // merged header: the first octree's header with the batch fields replaced
-  // (MergeOctrees::set_batch_info, merge_octrees.cpp:92-106)
   uint8_t hdr[OCNN_HEADER_BYTES];
-  memset(hdr, 0, sizeof(hdr));
-  memcpy(hdr, first_header_host, 716);
-  auto i32 = [&](int off) { return reinterpret_cast<int32_t*>(hdr + off); };
-  *i32(kOffBatch) = merged->batch_size;
-  int flags = 0;
-  for (int d = 0; d < OCNN_MAX_DEPTH; ++d) {
-    if (d <= depth) { i32(kOffNnum)[d] = merged->nnum[d]; i32(kOffNnumNempty)[d] = merged->nnum_nempty[d]; }
-    if (d <= depth + 2) i32(kOffNnumCum)[d] = merged->nnum_cum[d];
-  }
-  for (int p = 0; p < OCNN_PROP_COUNT; ++p) {
-    i32(kOffChannels)[p] = merged->channels[p];
-    if (merged->channels[p] != 0) { i32(kOffLocations)[p] = merged->locations[p]; flags |= 1 << p; }
-  }
-  for (int p = 0; p <= OCNN_PROP_COUNT; ++p) i32(kOffPtrDis)[p] = (int32_t)merged->ptr_dis[p];
-  *i32(kOffFlags) = flags;
+  merged_header(first_header_host, merged, hdr);
   if (header_host_out) memcpy(header_host_out, hdr, OCNN_HEADER_BYTES);
   OCNN_CUDA_OK(cudaMemcpyAsync(o, hdr, OCNN_HEADER_BYTES, cudaMemcpyHostToDevice, st));
 
-  int ne = 0, max_n = 1;
-  for (int d = 0; d <= depth; ++d) {
-    int node0 = 0, ne0 = 0;
-    for (int b = 0; b < batch; ++b) {
-      const ocnn_octree_meta* m = &in[b];
-      MergeEntry e;
-      e.src = static_cast<const uint8_t*>(octrees_dev[b]);
-      e.key = at_level(m, OCNN_PROP_KEY, d) ? ocnn_prop_offset(m, OCNN_PROP_KEY, d) : -1;
-      e.child = at_level(m, OCNN_PROP_CHILD, d) ? ocnn_prop_offset(m, OCNN_PROP_CHILD, d) : -1;
-      e.feat = at_level(m, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(m, OCNN_PROP_FEATURE, d) : -1;
-      e.label = at_level(m, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(m, OCNN_PROP_LABEL, d) : -1;
-      e.split = at_level(m, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(m, OCNN_PROP_SPLIT, d) : -1;
-      e.n = m->nnum[d]; e.node0 = node0; e.ne0 = ne0; e.b = b; e.d = d;
-      if (e.n > 0) g_static_stage[ne++] = e;
-      if (e.n > max_n) max_n = e.n;
-      node0 += m->nnum[d];
-      ne0 += m->nnum_nempty[d];
-    }
-  }
-  MergeDst dst;
-  memset(&dst, 0, sizeof(dst));
-  dst.out = o;
-  dst.key_bytes = merged->key_bits / 8;
-  dst.cfeat = merged->channels[OCNN_PROP_FEATURE];
-  for (int d = 0; d <= depth; ++d) {
-    dst.key[d] = ocnn_prop_offset(merged, OCNN_PROP_KEY, d);
-    dst.child[d] = ocnn_prop_offset(merged, OCNN_PROP_CHILD, d);
-    dst.feat[d] = at_level(merged, OCNN_PROP_FEATURE, d) ? ocnn_prop_offset(merged, OCNN_PROP_FEATURE, d) : -1;
-    dst.label[d] = at_level(merged, OCNN_PROP_LABEL, d) ? ocnn_prop_offset(merged, OCNN_PROP_LABEL, d) : -1;
-    dst.split[d] = at_level(merged, OCNN_PROP_SPLIT, d) ? ocnn_prop_offset(merged, OCNN_PROP_SPLIT, d) : -1;
-    dst.nnum[d] = merged->nnum[d];
-  }
+  int max_n = 1;
+  const int ne = merge_table(octrees_dev, in, batch, depth, g_static_stage, &max_n);
   if (ne > 0) {
     // Only the first `ne` entries are read by the kernel and all of them are rewritten here, so
     // nothing left over from an earlier call needs clearing.  The staging array is pageable
@@ -308,9 +288,9 @@ extern "C" int ocnn_octree_batch_noalloc(const void* const* octrees_dev, const o
     // mutex be released at the end of this function.
     OCNN_CUDA_OK(cudaMemcpyAsync(table_dev, g_static_stage, sizeof(MergeEntry) * (size_t)ne,
                                  cudaMemcpyHostToDevice, st));
-    dim3 grid(ceil_div(max_n, 256) < 64 ? ceil_div(max_n, 256) : 64, ne < 4096 ? ne : 4096);
-    merge_kernel<<<grid, 256, 0, st>>>(table_dev, ne, dst);
-    OCNN_LAUNCH_OK("merge_kernel (built-in scratch)");
+    if (int rc = launch_merge(table_dev, ne, max_n, merge_destination(merged, o), st,
+                              "merge_kernel (built-in scratch)"))
+      return rc;
   }
   return ocnn_calc_neigh(out, merged, stream);
 }

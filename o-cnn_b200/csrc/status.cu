@@ -8,6 +8,21 @@ namespace ocnn {
 static thread_local char g_error[512] = "";
 static std::atomic<long long> g_launches{0};
 
+int sm_count() {
+  static std::mutex mutex;
+  static int cached[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return kSMs;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0)
+      n = kSMs;
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
 void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {

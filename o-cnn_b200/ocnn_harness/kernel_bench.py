@@ -1,6 +1,6 @@
 """Per-kernel measurements of the hot path on one GPU: CUDA-event timings of single operators on
 seeded synthetic octrees, reported as achieved algorithmic GB/s or TFLOP/s against the measured
-peaks.  This is also the program the ncu captures under profiles/ are taken from.
+peaks.  Profiler captures of single kernels are taken from this program as well.
 
     python o-cnn_b200/ocnn_harness/kernel_bench.py conv  --depth 6 --shapes 8 --cin 8 --cout 8
     python o-cnn_b200/ocnn_harness/kernel_bench.py conv  --depth 5 --shapes 32 --cin 128 --cout 128

@@ -616,6 +616,143 @@ long oc_octree_conv_nempty(float *top, long cap, const float *bottom, const floa
   return count;
 }
 
+/* ---- general convolution / deconvolution (all strides, dense or non-empty) ------------------ */
+/* col2octree_cpu, octree/octree/octree_nn.cpp:216-241 (single chunk): the transpose of octree2col,
+ * data[c*octree_h + p] += col[(c*K + k)*H + h], visited in (c, k, h) order. */
+void oc_col2octree(const float *col, float *data, int channel, int height, int kdim, int stride,
+                   const int32_t *neigh, const int32_t *ni) {
+  const long octree_h = (long)height << (3 * (stride - 1));
+  memset(data, 0, sizeof(float) * (size_t)(channel * octree_h));
+  for (int c = 0; c < channel; ++c)
+    for (int k = 0; k < kdim; ++k) {
+      const float *row = col + ((long)c * kdim + k) * height;
+      for (long h = 0; h < height; ++h) {
+        long at = stride == 2 ? (h << 6) + ni[k] : ((h >> 3) << 6) + ni[(h & 7) * kdim + k];
+        int p = neigh[at];
+        if (p != -1) data[c * octree_h + p] += row[h];
+      }
+    }
+}
+
+/* octree2colP_cpu with either stride, octree/octree/octree_nn.cpp:244-271: at stride 2 the column
+ * rows are the sibling groups themselves (no ichild), the gathered node still goes through child. */
+void oc_octree2col_p2(float *col, const float *data, int channel, int height, int octree_h, int kdim,
+                      int stride, const int32_t *neigh, const int32_t *ni, const int32_t *child,
+                      const int32_t *ichild) {
+  for (int c = 0; c < channel; ++c)
+    for (int k = 0; k < kdim; ++k) {
+      float *row = col + ((long)c * kdim + k) * height;
+      for (long h = 0; h < height; ++h) {
+        const long hp = ichild[h];
+        const long at = stride == 2 ? (h << 6) + ni[k] : ((hp >> 3) << 6) + ni[(hp & 7) * kdim + k];
+        int p = neigh[at];
+        if (p >= 0) p = child[p];
+        row[h] = p < 0 ? 0.0f : data[(long)c * octree_h + p];
+      }
+    }
+}
+
+/* col2octreeP_cpu, octree/octree/octree_nn.cpp:273-298 */
+void oc_col2octree_p(const float *col, float *data, int channel, int height, int octree_h, int kdim,
+                     int stride, const int32_t *neigh, const int32_t *ni, const int32_t *child,
+                     const int32_t *ichild) {
+  memset(data, 0, sizeof(float) * (size_t)((long)channel * octree_h));
+  for (int c = 0; c < channel; ++c)
+    for (int k = 0; k < kdim; ++k) {
+      const float *row = col + ((long)c * kdim + k) * height;
+      for (long h = 0; h < height; ++h) {
+        const long hp = ichild[h];
+        const long at = stride == 2 ? (h << 6) + ni[k] : ((hp >> 3) << 6) + ni[(hp & 7) * kdim + k];
+        int p = neigh[at];
+        if (p >= 0) p = child[p];
+        if (p >= 0) data[(long)c * octree_h + p] += row[h];
+      }
+    }
+}
+
+/* OctreeConv / OctreeDeconv forward for every combination of stride (1, 2), nempty and
+ * transposition: OctreeBaseConv::setup / reshape (octree/octree/octree_conv.cpp:10-122) followed
+ * by forward_cpu_gemm (:158-180) for the convolution or backward_cpu_gemm (:182-206) for the
+ * deconvolution (pytorch/cpp/octree_conv.cpp:191-217 runs the deconvolution's forward through
+ * backward_gpu_gemm).  channel_in = channels of `bottom`, num_output = channels of `top`;
+ * weights: [conv_out, conv_in*K] with (conv_in, conv_out) = (channel_in, num_output) for the
+ * convolution and swapped for the deconvolution.  Bottom height: nnum[depth], or nnum_nempty[depth]
+ * when nempty or for a stride-2 deconvolution.  Returns num_output * top_h; call with top == NULL
+ * to size the output. */
+long oc_octree_conv_general(float *top, long cap, const float *bottom, const float *weights,
+                            const uint8_t *octree, int depth, int channel_in, int num_output,
+                            const int ks[3], int stride, int nempty, int deconv) {
+  int taps[27];
+  const int K = kernel_taps(ks, taps);
+  if (K < 0 || stride < 1 || stride > 2) return -1;
+  const int32_t *nnum = hci(octree, H_NNUM), *nne = hci(octree, H_NNUM_NE);
+  const int odepth = *hci(octree, H_DEPTH);
+  int top_depth = depth, work_depth = depth;
+  if (stride == 2) {
+    if (deconv) top_depth = work_depth = depth + 1; else top_depth = depth - 1;
+    if (top_depth < 0 || top_depth > odepth) return -1;
+  }
+  const int conv_in = deconv ? num_output : channel_in, conv_out = deconv ? channel_in : num_output;
+  const long kd = (long)K * conv_in;
+  long top_h = nempty ? nne[top_depth] : nnum[top_depth];
+  if (!nempty && stride == 2 && !deconv) top_h = nne[top_depth];
+  if (top_h == 0) top_h = 1;
+  long work_h = top_h;
+  if (stride == 2) work_h = deconv ? nnum[top_depth] / 8 : nnum[depth] / 8;
+  const long count = (long)num_output * top_h;
+  if (top == NULL || cap < count) return count;
+  const int one = ks[0] == 1 && ks[1] == 1 && ks[2] == 1 && stride == 1;
+  int ni[216];
+  oc_ni_table(ks, ni);
+  const int32_t *neigh = one ? NULL : (const int32_t *)(octree + prop_offset(octree, P_NEIGH, work_depth));
+  const int32_t *child = NULL;
+  int32_t *ichild = NULL;
+  long octree_h = 0;
+  if (nempty) {
+    child = (const int32_t *)(octree + prop_offset(octree, P_CHILD, work_depth));
+    const long ich = nne[work_depth] > 0 ? nne[work_depth] : 1;
+    /* at stride 2 the column rows outnumber nothing: ichild is read for h < work_h only at
+     * stride 1, but the reference indexes it unconditionally, so size it for both */
+    ichild = (int32_t *)calloc((size_t)(ich > work_h ? ich : work_h), sizeof(int32_t));
+    oc_ichild(ichild, child, nnum[work_depth]);
+    octree_h = (stride == 2 && deconv) ? nne[top_depth] : nne[depth];
+  }
+  float *col = one ? NULL : (float *)calloc((size_t)(kd * (work_h > 0 ? work_h : 1)), sizeof(float));
+  if (!deconv) {
+    const float *src = bottom;
+    if (!one) {
+      if (nempty)
+        oc_octree2col_p2(col, bottom, conv_in, (int)work_h, (int)octree_h, K, stride, neigh, ni, child, ichild);
+      else
+        oc_octree2col(col, bottom, conv_in, (int)work_h, K, stride, neigh, ni);
+      src = col;
+    }
+    for (int m = 0; m < conv_out; ++m)
+      for (long h = 0; h < work_h; ++h) {
+        float acc = 0.0f;
+        for (long k = 0; k < kd; ++k) acc += weights[m * kd + k] * src[k * work_h + h];
+        top[m * work_h + h] = acc;
+      }
+  } else {
+    float *dst = one ? top : col;
+    for (long m = 0; m < kd; ++m)
+      for (long h = 0; h < work_h; ++h) {
+        float acc = 0.0f;
+        for (int k = 0; k < conv_out; ++k) acc += weights[k * kd + m] * bottom[k * work_h + h];
+        dst[m * work_h + h] = acc;
+      }
+    if (!one) {
+      if (nempty)
+        oc_col2octree_p(col, top, conv_in, (int)work_h, (int)octree_h, K, stride, neigh, ni, child, ichild);
+      else
+        oc_col2octree(col, top, conv_in, (int)work_h, K, stride, neigh, ni);
+    }
+  }
+  free(col);
+  free(ichild);
+  return count;
+}
+
 /* ---- pool / pad ------------------------------------------------------------------------- */
 /* octree_max_pool_cpu, octree/octree/octree_nn.cpp:301-322: strict '>' so the first maximum
  * wins; mask holds the absolute bottom row. */

@@ -56,6 +56,13 @@ def lib():
     L.oc_octree_conv.restype = ctypes.c_long
     L.oc_octree_conv.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p, ctypes.c_char_p,
                                  ctypes.c_int, ctypes.c_int, ctypes.c_int, c_int_p, ctypes.c_int]
+    L.oc_octree_conv_general.restype = ctypes.c_long
+    L.oc_octree_conv_general.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p,
+                                         ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                         c_int_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    L.oc_col2octree.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 4 + [c_int_p, c_int_p]
+    L.oc_octree2col_p2.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 5 + [c_int_p] * 4
+    L.oc_col2octree_p.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 5 + [c_int_p] * 4
     L.oc_max_pool.argtypes = [c_float_p, ctypes.c_int, c_int_p, c_float_p, ctypes.c_int,
                               ctypes.c_int]
     L.oc_pad.argtypes = [c_float_p, ctypes.c_int, ctypes.c_int, c_float_p, ctypes.c_int, c_int_p,
@@ -274,6 +281,64 @@ def octree_conv_nempty(data, weights, octree, depth, num_output, ksize):
   lib().oc_octree_conv_nempty(_fp(top), n, _fp(data), _fp(weights), obuf, depth, cin, num_output,
                               _ip(ks))
   return top
+
+
+def octree_conv_general(data, weights, octree, depth, num_output, ksize, stride=1, nempty=False,
+                        deconv=False):
+  """OctreeConv / OctreeDeconv forward for any stride / nempty combination.  data: [Cin, H] with
+  H = nnum[depth], or nnum_nempty[depth] when nempty or for a stride-2 deconvolution."""
+  data, weights = _f32(data), _f32(weights)
+  ks = _i32(ksize)
+  obuf = _bytes(octree)
+  cin = data.shape[0]
+  args = (_fp(data), _fp(weights), obuf, depth, cin, num_output, _ip(ks), stride, int(nempty),
+          int(deconv))
+  n = lib().oc_octree_conv_general(None, 0, *args)
+  if n < 0:
+    raise ValueError('unsupported convolution')
+  top = np.zeros((num_output, n // num_output), np.float32)
+  lib().oc_octree_conv_general(_fp(top), n, *args)
+  return top
+
+
+def ichild_of(child, nne):
+  child = _i32(child)
+  ichild = np.zeros(max(nne, 1), np.int32)
+  lib().oc_ichild(_ip(ichild), _ip(child), child.shape[0])
+  return ichild
+
+
+def octree2col_general(data, neigh, ksize, stride, height, child=None):
+  """octree2col (child is None) or octree2colP (child given: data holds the non-empty nodes
+  only).  height = rows of the column matrix (nodes at stride 1, sibling groups at stride 2)."""
+  if child is None:
+    return octree2col(data, neigh, ksize, stride, height)
+  data, neigh, child = _f32(data), _i32(neigh), _i32(child)
+  channel, octree_h = data.shape
+  ni = ni_table(ksize)
+  kdim = int(np.prod(ksize))
+  ichild = ichild_of(child, max(octree_h, height))
+  col = np.empty((channel, kdim, height), np.float32)
+  lib().oc_octree2col_p2(_fp(col), _fp(data), channel, height, octree_h, kdim, stride, _ip(neigh),
+                         _ip(ni), _ip(child), _ip(ichild))
+  return col
+
+
+def col2octree_general(col, neigh, ksize, stride, octree_h, child=None):
+  """col2octree / col2octreeP: col [C, K, height] scattered back to data [C, octree_h]."""
+  col, neigh = _f32(col), _i32(neigh)
+  channel, kdim, height = col.shape
+  ni = ni_table(ksize)
+  data = np.zeros((channel, octree_h), np.float32)
+  if child is None:
+    assert octree_h == height << (3 * (stride - 1))
+    lib().oc_col2octree(_fp(col), _fp(data), channel, height, kdim, stride, _ip(neigh), _ip(ni))
+  else:
+    child = _i32(child)
+    ichild = ichild_of(child, max(octree_h, height))
+    lib().oc_col2octree_p(_fp(col), _fp(data), channel, height, octree_h, kdim, stride,
+                          _ip(neigh), _ip(ni), _ip(child), _ip(ichild))
+  return data
 
 
 def max_pool(btm):

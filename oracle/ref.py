@@ -51,7 +51,7 @@ class Ref:
     assert L.ref_key_bits() == key_bits
     self.key_bits = key_bits
     for name in ('ref_points_new', 'ref_points2octree', 'ref_octree_batch', 'ref_octree_sample',
-                 'ref_octree_conv'):
+                 'ref_octree_conv', 'ref_octree_conv_general'):
       getattr(L, name).restype = ctypes.c_long
     L.ref_points_new.argtypes = [c_float_p, c_float_p, c_float_p, c_float_p, ctypes.c_int,
                                  ctypes.c_int, ctypes.c_char_p, ctypes.c_long]
@@ -80,6 +80,13 @@ class Ref:
     L.ref_octree_conv.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p,
                                   ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                   c_int_p, ctypes.c_int]
+    L.ref_octree_conv_general.argtypes = [c_float_p, ctypes.c_long, c_float_p, c_float_p,
+                                          ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                          c_int_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    L.ref_col2octree.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 4 + [
+        c_int_p, c_int_p, ctypes.c_int, ctypes.c_int]
+    L.ref_col2octreeP.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 5 + [
+        c_int_p, c_int_p, c_int_p, c_int_p, ctypes.c_int, ctypes.c_int]
     L.ref_set_gemm.argtypes = [ctypes.c_void_p]
     self._gemm_cb = None
 
@@ -224,6 +231,63 @@ class Ref:
     self.lib.ref_octree_conv(_fp(top), n, _fp(data), _fp(weights), obuf, depth, cin,
                              num_output, _ip(ks), stride)
     return top
+
+
+def _general_methods():
+  def octree_conv_general(self, data, weights, octree, depth, num_output, ksize, stride=1,
+                          nempty=False, deconv=False):
+    data, weights = _f32(data), _f32(weights)
+    ks = _i32(ksize)
+    obuf = np.ascontiguousarray(octree, dtype=np.uint8).tobytes()
+    cin = data.shape[0]
+    args = (_fp(data), _fp(weights), obuf, depth, cin, num_output, _ip(ks), stride, int(nempty),
+            int(deconv))
+    n = self.lib.ref_octree_conv_general(None, 0, *args)
+    top = np.zeros((num_output, n // num_output), np.float32)
+    self.lib.ref_octree_conv_general(_fp(top), n, *args)
+    return top
+
+  def _ichild(self, child, n):
+    ichild = np.zeros(max(n, 1), np.int32)
+    pos = child >= 0
+    ichild[child[pos]] = np.nonzero(pos)[0].astype(np.int32)
+    return ichild
+
+  def octree2col_general(self, data, neigh, ksize, stride, height, child=None):
+    if child is None:
+      return self.octree2col(data, neigh, ksize, stride, height)
+    data, neigh, child = _f32(data), _i32(neigh), _i32(child)
+    channel, octree_h = data.shape
+    ni = self.ni_table(ksize)
+    kdim = int(np.prod(ksize))
+    ichild = self._ichild(child, max(octree_h, height))
+    col = np.empty((channel, kdim, height), dtype=np.float32)
+    self.lib.ref_octree2colP(_fp(col), _fp(data), channel, height, octree_h, kdim, stride,
+                             _ip(neigh), _ip(ni), _ip(child), _ip(ichild), height, 0)
+    return col
+
+  def col2octree_general(self, col, neigh, ksize, stride, octree_h, child=None):
+    col, neigh = _f32(col), _i32(neigh)
+    channel, kdim, height = col.shape
+    ni = self.ni_table(ksize)
+    data = np.full((channel, octree_h), 7.0, np.float32)     # the call must clear it (n == 0)
+    if child is None:
+      self.lib.ref_col2octree(_fp(col), _fp(data), channel, height, kdim, stride, _ip(neigh),
+                              _ip(ni), height, 0)
+    else:
+      child = _i32(child)
+      ichild = self._ichild(child, max(octree_h, height))
+      self.lib.ref_col2octreeP(_fp(col), _fp(data), channel, height, octree_h, kdim, stride,
+                               _ip(neigh), _ip(ni), _ip(child), _ip(ichild), height, 0)
+    return data
+
+  Ref.octree_conv_general = octree_conv_general
+  Ref._ichild = _ichild
+  Ref.octree2col_general = octree2col_general
+  Ref.col2octree_general = col2octree_general
+
+
+_general_methods()
 
 
 def get(key_bits=32):

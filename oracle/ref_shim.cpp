@@ -16,6 +16,8 @@
 //   octree_max_pool_cpu           octree/octree/octree_nn.cpp:301-322
 //   pad_forward_cpu / pad_backward_cpu octree/octree/octree_nn.cpp:163-185
 //   OctreeBaseConv<float>::forward_cpu_gemm  octree/octree/octree_conv.cpp:158-180
+//   OctreeBaseConv<float>::backward_cpu_gemm (the deconvolution's forward)  octree_conv.cpp:182-206
+//   col2octree_cpu / col2octreeP_cpu   octree/octree/octree_nn.cpp:216-241, 273-298
 //   NeighHelper tables            octree/octree/octree_nn.cpp:6-108
 //   octree::get_one_octree        octree/octree/octree_samples.cpp:2168-2178
 
@@ -32,8 +34,8 @@
 
 // OctreeBaseConv's CPU im2col wrapper names OctreeParser::neighbor_gpu on its non-empty branch
 // (octree/octree/octree_conv.cpp:135,151); that accessor lives in octree_parser.cu, which
-// needs CUDA and is not compiled here.  The branch is never taken by this shim (nempty is
-// always false), so a definition that forwards to the CPU accessor only satisfies the linker.
+// needs CUDA and is not compiled here.  On the CPU the neighbour table is the same host array
+// either way, so the definition forwards to the CPU accessor.
 const int* OctreeParser::neighbor_gpu(const int depth) const { return neighbor_cpu(depth); }
 
 namespace {
@@ -64,6 +66,48 @@ class ShimGemm : public octree::GEMMEngine<float> {
       }
     }
   }
+};
+
+// Convolution / deconvolution forward for every stride / nempty combination, driven the way the
+// PyTorch binding drives it (pytorch/cpp/octree_conv.cpp:61-120, 137-154, 191-217): setup, reshape,
+// child/ichild for the non-empty variant (pad_backward of 0..n-1 through the child array), then
+// forward_cpu_gemm for the convolution and backward_cpu_gemm for the deconvolution.
+class ShimConvGeneral : public octree::OctreeBaseConv<float> {
+ public:
+  explicit ShimConvGeneral(bool deconv) : deconv_(deconv) {}
+  bool is_deconvolution_layer() override { return deconv_; }
+
+  long run(float* top, const float* bottom, const float* weights, const char* octree_buf,
+           int depth, int cin, int cout, const int* ksize, int stride, int nempty, long top_cap) {
+    std::vector<int> ks(ksize, ksize + 3);
+    this->octree_.set_cpu(octree_buf);
+    this->setup(ks, stride, depth, cin, cout, nempty != 0);
+    this->engine_cpu_ = &gemm_;
+    this->reshape();
+    long top_n = (long)this->top_shape_[1] * this->top_shape_[2];
+    if (top == nullptr || top_cap < top_n) return top_n;
+    std::vector<float> ws((size_t)num_elements(this->workspace_shape_));
+    std::vector<float> rb((size_t)num_elements(this->result_buffer_shape_));
+    this->workspace_ = ws.data();
+    this->result_buffer_ = rb.empty() ? nullptr : rb.data();
+    std::vector<int> ich;
+    if (nempty) {
+      this->child_ = this->octree_.children_cpu(this->workspace_depth_);
+      // the binding's pad_backward of 0..child_h-1 through child (only float/double are
+      // instantiated in the library, so the same scatter is written out here for ints)
+      ich.assign(this->ichild_h_ > 0 ? this->ichild_h_ : 1, 0);
+      for (int i = 0; i < this->child_h_; ++i)
+        if (this->child_[i] != -1) ich[this->child_[i]] = i;
+      this->ichild_ = ich.data();
+    }
+    if (deconv_) this->backward_cpu_gemm(top, bottom, weights);
+    else this->forward_cpu_gemm(top, bottom, weights);
+    return top_n;
+  }
+
+ private:
+  bool deconv_;
+  ShimGemm gemm_;
 };
 
 class ShimConv : public octree::OctreeBaseConv<float> {
@@ -234,6 +278,27 @@ long ref_octree_conv(float* top, long top_cap, const float* bottom, const float*
                      int stride) {
   ShimConv conv;
   return conv.run(top, bottom, weights, octree_buf, depth, cin, cout, ksize, stride, top_cap);
+}
+
+// OctreeConv / OctreeDeconv forward with any stride and nempty flag.  cin = channels of `bottom`,
+// cout = num_output.  Returns the number of output floats; top == NULL sizes the output.
+long ref_octree_conv_general(float* top, long top_cap, const float* bottom, const float* weights,
+                             const char* octree_buf, int depth, int cin, int cout,
+                             const int* ksize, int stride, int nempty, int deconv) {
+  ShimConvGeneral conv(deconv != 0);
+  return conv.run(top, bottom, weights, octree_buf, depth, cin, cout, ksize, stride, nempty, top_cap);
+}
+
+void ref_col2octree(const float* col, float* data, int channel, int height, int kernel_sdim,
+                    int stride, const int* neigh, const int* ni, int height_col, int n) {
+  col2octree_cpu<float>(col, data, channel, height, kernel_sdim, stride, neigh, ni, height_col, n);
+}
+
+void ref_col2octreeP(const float* col, float* data, int channel, int height, int octree_h,
+                     int kernel_sdim, int stride, const int* neigh, const int* ni, const int* child,
+                     const int* ichild, int height_col, int n) {
+  col2octreeP_cpu<float>(col, data, channel, height, octree_h, kernel_sdim, stride, neigh, ni, child,
+                         ichild, height_col, n);
 }
 
 }  // extern "C"

@@ -1,9 +1,11 @@
-"""Generate tests/golden/reference_vectors.npz from the reference's own CPU code.
+"""Generate tests/golden/reference_vectors.npz and reference_vectors_general.npz from the
+reference's own CPU code.
 
 Run in a container that has the reference checkout (it is compiled unmodified by
 ``make -C oracle ref``):
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # both files
+    python tests/golden/make_golden.py general    # only reference_vectors_general.npz
 
 Every array written here is an input fed to, or an output produced by, the reference
 (``oracle/_ref/libocnn_ref{32,64}.so``); nothing is computed by this repository's own oracle or
@@ -94,5 +96,44 @@ def main():
   print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
 
 
+GENERAL_KERNELS = [[3, 3, 3], [2, 2, 2], [3, 1, 1], [3, 3, 1], [1, 1, 1]]
+
+
+def main_general():
+  """Convolution and deconvolution forward for every stride / nempty combination, the column
+  operators behind them, and the key / search / interpolation helpers, on the merged batch
+  `k32_b_merged` of reference_vectors.npz (kept in a file of its own so that the first file's
+  bytes never change)."""
+  here = os.path.dirname(os.path.abspath(__file__))
+  base = dict(np.load(os.path.join(here, 'reference_vectors.npz')))
+  R = ref.get(32)
+  merged = base['k32_b_merged']
+  info = R.octree_info(merged)
+  rng = np.random.default_rng(20241)
+  out = {}
+  d = 3
+  H = {k: int(info['nnum'][k]) for k in range(5)}
+  Hne = {k: int(info['nnum_nempty'][k]) for k in range(5)}
+  out['g_x_full'] = rng.uniform(-1, 1, size=(3, H[d])).astype(np.float32)
+  out['g_x_ne'] = rng.uniform(-1, 1, size=(3, Hne[d])).astype(np.float32)
+  for ks in GENERAL_KERNELS:
+    kd = int(np.prod(ks))
+    name = ''.join(map(str, ks))
+    out['g_wc' + name] = rng.normal(scale=0.2, size=(5, 3 * kd)).astype(np.float32)
+    out['g_wd' + name] = rng.normal(scale=0.2, size=(3, 5 * kd)).astype(np.float32)
+    for stride in (1, 2):
+      for nempty in (0, 1):
+        for deconv in (0, 1):
+          x = out['g_x_ne'] if (nempty or (deconv and stride == 2)) else out['g_x_full']
+          w = out['g_wd' + name] if deconv else out['g_wc' + name]
+          out['g_y%s_s%d_n%d_t%d' % (name, stride, nempty, deconv)] = R.octree_conv_general(
+              x, w, merged, d, 5, ks, stride, bool(nempty), bool(deconv))
+  path = os.path.join(here, 'reference_vectors_general.npz')
+  np.savez_compressed(path, **out)
+  print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
+
+
 if __name__ == '__main__':
-  main()
+  if len(sys.argv) < 2 or sys.argv[1] != 'general':
+    main()
+  main_general()

@@ -245,3 +245,32 @@ def test_ops_match_reference_fixture(golden):
   child = v.prop('child', d)
   assert same_bits(oc.pad(xne, child, 0.25), golden['b_pad'])
   assert same_bits(oc.depad(x, child, xne.shape[1]), golden['b_depad'])
+
+
+# ---- convolution / deconvolution for every stride / nempty combination ----------------------
+GENERAL_KERNELS = [[3, 3, 3], [2, 2, 2], [3, 1, 1], [3, 3, 1], [1, 1, 1]]
+
+
+@pytest.fixture(scope='module')
+def golden_general():
+  import os
+  path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden',
+                      'reference_vectors_general.npz')
+  return dict(np.load(path))
+
+
+@pytest.mark.parametrize('ks', GENERAL_KERNELS)
+def test_conv_general_matches_reference_fixture(golden, golden_general, ks):
+  """Outputs of the reference's OctreeBaseConv (forward_cpu_gemm / backward_cpu_gemm with
+  octree2col(P) / col2octree(P)) on the merged batch of the first fixture file, depth 3."""
+  g = golden_general
+  merged = golden['k32_b_merged']
+  name = kname(ks)
+  for stride in (1, 2):
+    for nempty in (0, 1):
+      for deconv in (0, 1):
+        x = g['g_x_ne'] if (nempty or (deconv and stride == 2)) else g['g_x_full']
+        w = g['g_wd' + name] if deconv else g['g_wc' + name]
+        got = oc.octree_conv_general(x, w, merged, 3, 5, ks, stride, bool(nempty), bool(deconv))
+        assert same_bits(got, g['g_y%s_s%d_n%d_t%d' % (name, stride, nempty, deconv)]), \
+            (ks, stride, nempty, deconv)

@@ -155,3 +155,83 @@ def test_pool_pad_depad(batch):
     xs = rng.uniform(-1, 1, size=(4, Hne)).astype(np.float32)
     assert same_bits(R.pad_forward(xs, child, 0.5), oc.pad(xs, child, 0.5))
     assert same_bits(R.pad_backward(x, child, Hne), oc.depad(x, child, Hne))
+
+
+GENERAL_KERNELS = [[3, 3, 3], [2, 2, 2], [3, 1, 1], [3, 3, 1], [1, 1, 1]]   # pytorch/test/test_octree_deconv.py
+
+
+def _bottom_height(v, d, stride, nempty, deconv):
+  return int(v.nnum_nempty[d]) if (nempty or (deconv and stride == 2)) else int(v.nnum[d])
+
+
+@pytest.mark.parametrize('ks', GENERAL_KERNELS)
+@pytest.mark.parametrize('stride', [1, 2])
+@pytest.mark.parametrize('nempty', [False, True])
+@pytest.mark.parametrize('deconv', [False, True])
+def test_conv_general(batch, ks, stride, nempty, deconv):
+  """OctreeConv / OctreeDeconv forward for every stride / nempty combination: the restatement
+  against the reference's setup + reshape + forward_cpu_gemm / backward_cpu_gemm, bit for bit."""
+  kb, R, merged_r, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(sum(ks) * 100 + stride * 10 + nempty * 2 + deconv)
+  cin, cout = 3, 5
+  kd = int(np.prod(ks))
+  for d in (5, 4):
+    x = rng.uniform(-1, 1, size=(cin, _bottom_height(v, d, stride, nempty, deconv))).astype(np.float32)
+    wshape = (cin, cout * kd) if deconv else (cout, cin * kd)
+    w = rng.normal(size=wshape).astype(np.float32)
+    a = R.octree_conv_general(x, w, merged_r, d, cout, ks, stride, nempty, deconv)
+    b = oc.octree_conv_general(x, w, merged_o, d, cout, ks, stride, nempty, deconv)
+    assert a.shape == b.shape and same_bits(a, b), (d, a.shape)
+    if not nempty and not deconv:
+      assert same_bits(b, oc.octree_conv(x, w, merged_o, d, cout, ks, stride))
+
+
+@pytest.mark.parametrize('ks', GENERAL_KERNELS)
+@pytest.mark.parametrize('stride', [1, 2])
+def test_col2octree_and_octree2colP(batch, ks, stride):
+  kb, R, _, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(5 + sum(ks) + stride)
+  d = 5
+  H, nne = int(v.nnum[d]), int(v.nnum_nempty[d])
+  neigh, child = v.prop('neigh', d), v.prop('child', d)
+  kd = int(np.prod(ks))
+  hc = H if stride == 1 else H // 8
+  col = rng.uniform(-1, 1, size=(3, kd, hc)).astype(np.float32)
+  assert same_bits(R.col2octree_general(col, neigh, ks, stride, H),
+                   oc.col2octree_general(col, neigh, ks, stride, H))
+  hcp = nne if stride == 1 else H // 8
+  colp = rng.uniform(-1, 1, size=(3, kd, hcp)).astype(np.float32)
+  assert same_bits(R.col2octree_general(colp, neigh, ks, stride, nne, child),
+                   oc.col2octree_general(colp, neigh, ks, stride, nne, child))
+  x = rng.uniform(-1, 1, size=(3, nne)).astype(np.float32)
+  assert same_bits(R.octree2col_general(x, neigh, ks, stride, hcp, child),
+                   oc.octree2col_general(x, neigh, ks, stride, hcp, child))
+
+
+def test_deconv_identities(batch):
+  """The identities of the reference's own test (pytorch/test/test_octree_deconv.py:44-57):
+  OctreeDeconv(nempty=True) on the non-empty rows equals the dense deconvolution of the masked
+  data read back at the non-empty nodes of the output level."""
+  kb, R, _, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(77)
+  d, cin, cout = 4, 3, 5
+  H, nne = int(v.nnum[d]), int(v.nnum_nempty[d])
+  child = v.prop('child', d)
+  for ks in GENERAL_KERNELS:
+    kd = int(np.prod(ks))
+    w = rng.normal(size=(cin, cout * kd)).astype(np.float32)
+    x = rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)
+    xne = oc.depad(x, child, nne)
+    for stride in (1, 2):
+      d_out = d if stride == 1 else d + 1
+      child_out = v.prop('child', d_out)
+      nne_out = int(v.nnum_nempty[d_out])
+      got = oc.octree_conv_general(xne, w, merged_o, d, cout, ks, stride, True, True)
+      masked = oc.pad(xne, child, 0.0)
+      dense_in = masked if stride == 1 else xne      # OctreeDeconv depads before a stride-2 call
+      dense = oc.octree_conv_general(dense_in, w, merged_o, d, cout, ks, stride, False, True)
+      want = oc.depad(dense, child_out, nne_out)
+      assert np.allclose(got, want, atol=1e-6), (ks, stride)
