@@ -41,6 +41,8 @@ def parse_args():
   ap.add_argument('--no-tensor-core', action='store_true',
                   help='run every convolution on the CUDA-core kernel')
   ap.add_argument('--cpu-sample', type=int, default=32, help='shapes in the CPU baseline sample')
+  ap.add_argument('--conv-iters', type=int, default=50,
+                  help='timed launches per shape of the OctreeConv TFLOP/s measurement')
   return ap.parse_args()
 
 
@@ -51,7 +53,14 @@ def workload_config(n_gpus):
           'shapes_per_gpu': BATCH, 'points_per_shape': NPT, 'depth': DEPTH,
           'global_batch': BATCH * n_gpus, 'parallelism': 'shard-by-shape x%d, no collective' % n_gpus,
           'key_bits': 64,
-          'l2': 'flushed between timed steps by a 256 MiB write (outside the timed events)'}
+          'l2': 'every timed step reads its points from the next of several device copies, together '
+                'larger than the 126 MB L2, and builds a fresh octree; nothing is flushed inside the '
+                'timed region',
+          'pipeline': 'octree build of step k+1 on a second CUDA stream while step k runs through '
+                      'the network; K builds and K forwards inside one event pair',
+          'deviation_from_reference_resnet': 'the named configuration puts blocks on depths 6..2 '
+              '(512 channels at depth 2); the reference class pytorch/ocnn/resnet.py stops at depth 3 '
+              '(256 channels)'}
 
 
 def make_clouds(rank, count=BATCH):
@@ -118,12 +127,14 @@ def _worker_init(seed_base, shape_ids):
   _WORKER['pts'] = {i: ops.points_new(*synth.primitive_union(NPT, seed_base + i)) for i in shape_ids}
 
 
-def _worker_step(shape_ids):
+def _worker_step(shape_ids, keep=False):
   ops, net = _WORKER['ops'], _WORKER['net']
   if not shape_ids:
     return 0
   octree = ops.build([_WORKER['pts'][i] for i in shape_ids])
   logits = net.forward(octree)
+  if keep:
+    _WORKER['last'] = (logits, octree)
   return int(logits.shape[0])
 
 
@@ -132,8 +143,10 @@ def cpu_forward_time(sample):
   _worker_init(3000, list(range(sample)))
   _worker_step(list(range(min(2, sample))))          # touch code and data once
   t0 = time.perf_counter()
-  _worker_step(list(range(sample)))
-  return time.perf_counter() - t0, _WORKER['ops'].kind
+  _worker_step(list(range(sample)), keep=True)
+  secs = time.perf_counter() - t0
+  logits, octree = _WORKER['last']
+  return secs, _WORKER['ops'].kind, logits, octree
 
 
 def run_reference(args):
@@ -256,15 +269,55 @@ def load_peaks():
     with open(path) as f:
       pk = json.load(f)
     return {'hbm_gbs': pk['hbm_gbs'], 'bf16_tflops': pk.get('bf16_tflops_sustained', pk['bf16_tflops']),
-            'source': 'measured'}
-  return {'hbm_gbs': 6650.0, 'bf16_tflops': 1400.0, 'source': 'fallback'}
+            'bf16_burst': pk['bf16_tflops'], 'source': 'measured'}
+  return {'hbm_gbs': 6650.0, 'bf16_tflops': 1400.0, 'bf16_burst': 1590.0, 'source': 'fallback'}
+
+
+def conv_throughput(ocnn, octree, nodes, depth, peaks, flush, iters):
+  """3x3x3 OctreeConv on the finest level of the benchmark batch at the channel counts where the
+  contraction is tensor-bound: CUDA-event time per launch (L2 flushed before each), TFLOP/s by the
+  reference's dense count 2*Cout*Cin*27*H, and the fraction of the measured bf16 peaks."""
+  import statistics as st
+  import torch
+  out = []
+  status = torch.zeros(1, dtype=torch.int32, device=octree.device)
+  g = torch.Generator(device=octree.device).manual_seed(1)
+  for cin, cout in ((64, 64), (128, 128), (256, 256)):
+    x = (torch.rand(1, cin, nodes, 1, device=octree.device, generator=g) - 0.5).to(torch.bfloat16)
+    x = x.contiguous(memory_format=torch.channels_last)
+    w = torch.randn(cout, cin * 27, device=octree.device, generator=g) * 0.05
+    packed = ocnn.nn.conv_pack_weights(w, cin, cout, [3, 3, 3])
+    fn = lambda: ocnn.nn.octree_conv_tc(x, packed, octree, depth, cout, [3, 3, 3], 1, None, None, None,
+                                        False, status)
+    for _ in range(5):
+      fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+      flush.zero_()
+      e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      e0.record()
+      fn()
+      e1.record()
+      e1.synchronize()
+      times.append(e0.elapsed_time(e1))
+    assert int(status.item()) == 0
+    flops = 2.0 * cout * cin * 27 * nodes
+    ms = st.mean(times)
+    tf = flops / (ms * 1e-3) / 1e12
+    out.append({'cin': cin, 'cout': cout, 'kernel': '3x3x3', 'nodes': nodes, 'iters': iters,
+                'ms': ms, 'ms_median': st.median(times), 'tflops': tf,
+                'frac_of_bf16_burst': tf / peaks['bf16_burst'],
+                'frac_of_bf16_sustained': tf / peaks['bf16_tflops']})
+    del x, w, packed
+  return out
 
 
 def run_ours(args):
   import numpy as np
   import torch
   import ocnn
-  from ocnn_harness import models
+  from ocnn_harness import models, shard, synth
 
   rank = int(os.environ.get('RANK', '0'))
   world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -275,62 +328,39 @@ def run_ours(args):
     dist.init_process_group('nccl', device_id=torch.device('cuda', local))
   dev = torch.device('cuda', local)
   ocnn.set_key_bits(64)
+  peaks = load_peaks()
+
+  def pack(clouds):
+    pts = [ocnn.points_new(torch.from_numpy(p), torch.from_numpy(q), torch.zeros(0), torch.zeros(0))
+           for p, q in clouds]
+    packed_host, meta = ocnn.points_pack(pts, True)
+    headers = torch.cat([p[:88] for p in pts]).contiguous()
+    return packed_host, meta, headers
 
   clouds = make_clouds(rank)
-  pts = [ocnn.points_new(torch.from_numpy(p), torch.from_numpy(q), torch.zeros(0), torch.zeros(0))
-         for p, q in clouds]
-  packed_host, meta = ocnn.points_pack(pts, True)
-  headers = torch.cat([p[:88] for p in pts]).contiguous()
+  packed_host, meta, headers = pack(clouds)
   packed_dev = packed_host.to(dev)
-  net = models.GpuNet(models.resnet_params(DEPTH, 3, 40, 2, seed=0), 'bf16',
-                      tensor_core=not args.no_tensor_core, device=dev)
+  params = models.resnet_params(DEPTH, 3, 40, 2, seed=0)
+  net = models.GpuNet(params, 'bf16', tensor_core=not args.no_tensor_core, device=dev)
   flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-  def step_resident():
-    octree = ocnn.points2octree_packed(packed_dev, meta, headers, *BUILD_ARGS, True)
+  def build(src):
+    return ocnn.points2octree_packed(src, meta, headers, *BUILD_ARGS, True)
+
+  def step_serial():
+    octree = build(packed_dev)
     return octree, net.forward(octree)
-
-  # End-to-end step: the points come from pinned host memory and the logits go back to pinned host
-  # memory, every step.  The copies are double-buffered the way a data loader feeds a GPU: while
-  # step k builds and runs on the compute stream, the copy stream already moves the points of step
-  # k+1 into the other device buffer, so each timed step contains exactly one H2D of a full batch
-  # (the next one's) and one D2H (its own logits).
-  copy_stream = torch.cuda.Stream(device=dev)
-  dev_bufs = [torch.empty_like(packed_dev) for _ in range(2)]
-  copied = [torch.cuda.Event() for _ in range(2)]
-  consumed = [torch.cuda.Event() for _ in range(2)]
-  logits_host = [torch.empty((BATCH, 40), dtype=torch.float32).pin_memory() for _ in range(2)]
-  e2e_state = {'k': 0}
-  for ev in consumed:
-    ev.record()
-
-  def prefetch(slot):
-    with torch.cuda.stream(copy_stream):
-      copy_stream.wait_event(consumed[slot])          # the build of two steps ago has read it
-      dev_bufs[slot].copy_(packed_host, non_blocking=True)
-      copied[slot].record(copy_stream)
-
-  def step_e2e():
-    slot = e2e_state['k'] & 1
-    if e2e_state['k'] == 0:
-      prefetch(slot)
-    prefetch(slot ^ 1)
-    torch.cuda.current_stream().wait_event(copied[slot])
-    octree = ocnn.points2octree_packed(dev_bufs[slot], meta, headers, *BUILD_ARGS, True)
-    consumed[slot].record()
-    logits_host[slot].copy_(net.forward(octree).float().reshape(BATCH, 40), non_blocking=True)
-    e2e_state['k'] += 1
 
   sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
 
   # ---- warm-up; one warm-up step is instrumented per layer to find the dominant kernel ----
   layer_ms = {}
-  octree, logits = step_resident()
+  octree, logits = step_serial()
   torch.cuda.synchronize()
   info = ocnn.octree_info(octree)
   nnum = info[4:20]
   net.exec.set_trace(-1)
-  step_resident()
+  step_serial()
   torch.cuda.synchronize()
   for index, ms in net.exec.trace_ms():
     layer_ms[net.exec_layers[index]] = ms
@@ -339,49 +369,200 @@ def run_ours(args):
   top_layer = max((k for k in layer_ms if k in conv_names), key=layer_ms.get)
   top_index = net.exec_layers.index(top_layer)
   for _ in range(max(args.warmup, 3)):
-    step_resident()
+    step_serial()
   torch.cuda.synchronize()
   assert net.error_status() == 0, 'a kernel reported an error status'
 
-  def timed(step_fn, steps):
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+  def barrier():
     if world > 1:
       dist.barrier()
     torch.cuda.synchronize()
+
+  def max_over_ranks(ms):
+    if world > 1:
+      t = torch.tensor([ms], dtype=torch.float64, device=dev)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      return float(t.item())
+    return ms
+
+  # ---- serial figure: one stream, L2 flushed between steps, one event pair per step ----
+  def timed_serial(step_fn, steps):
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    barrier()
     for k in range(steps):
       flush.zero_()
       starts[k].record()
       step_fn()
       ends[k].record()
-    torch.cuda.synchronize()
-    if world > 1:
-      dist.barrier()
-    total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-    if world > 1:
-      t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-      dist.all_reduce(t, op=dist.ReduceOp.MAX)
-      total_ms = float(t.item())
-    return total_ms
+    barrier()
+    return max_over_ranks(sum(s.elapsed_time(e) for s, e in zip(starts, ends)))
 
-  # ---- timed region: K steps, inputs resident in HBM; only the dominant layer carries events ----
   net.exec.set_trace(top_index)
-  launches0 = ocnn.nn.launch_count()
-  t_host0 = time.perf_counter()
-  total_ms = timed(step_resident, args.steps)
-  host_ms = (time.perf_counter() - t_host0) * 1e3
-  launches = ocnn.nn.launch_count() - launches0
+  serial_ms = timed_serial(step_serial, args.steps)
   top_times = [ms for _, ms in net.exec.trace_ms()]
   top_ms = statistics.mean(top_times) if top_times else None
   net.exec.set_trace(-2)
 
-  # ---- end to end: pinned host points -> H2D -> build -> forward -> logits D2H ----
-  for _ in range(3):
-    step_e2e()
-  e2e_ms = timed(step_e2e, args.steps)
+  # ---- headline: the same K steps as a two-stream pipeline ----
+  # The octree of batch k+1 is built on a second stream while batch k runs through the network:
+  # the builder's short dependent kernels fill the SMs that the network's coarse levels leave idle,
+  # and its one blocking read-back (the node counts) stalls only that stream's host thread.  Every
+  # step reads its points from the next of NBUF device copies, together larger than L2, so no step
+  # finds its input cached; nothing is flushed inside the region.
+  l2_bytes = 126 << 20
+  nbuf = max(2, -(-int(1.25 * l2_bytes) // int(packed_dev.numel())))
+  inputs = [packed_dev] + [packed_dev.clone() for _ in range(nbuf - 1)]
+  build_stream = torch.cuda.Stream(device=dev)
+  main_stream = torch.cuda.current_stream(dev)
+
+  def pipelined(steps, src_of, on_result=None):
+    """K builds on build_stream, K forwards on the current stream; returns the device time from the
+    first build's start to the last forward's end."""
+    built = [torch.cuda.Event() for _ in range(steps)]
+    keep = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(main_stream)
+    build_stream.wait_event(e0)
+
+    def enqueue_build(k):
+      with torch.cuda.stream(build_stream):
+        oct_k = build(src_of(k))
+        built[k].record(build_stream)
+      oct_k.record_stream(main_stream)
+      return oct_k
+
+    nxt = enqueue_build(0)
+    for k in range(steps):
+      cur = nxt
+      if k + 1 < steps:
+        nxt = enqueue_build(k + 1)
+      main_stream.wait_event(built[k])
+      out = net.forward(cur)
+      if on_result is not None:
+        on_result(k, out)
+      keep.append(cur)
+      if len(keep) > 3:
+        keep.pop(0)
+    e1.record(main_stream)
+    barrier()
+    return max_over_ranks(e0.elapsed_time(e1))
+
+  pipelined(max(args.warmup, 3), lambda k: inputs[k % nbuf])
+  launches0 = ocnn.nn.launch_count()
+  t_host0 = time.perf_counter()
+  total_ms = pipelined(args.steps, lambda k: inputs[k % nbuf])
+  host_ms = (time.perf_counter() - t_host0) * 1e3
+  launches = ocnn.nn.launch_count() - launches0
+  assert net.error_status() == 0, 'a kernel reported an error status'
+
+  # ---- end to end: pinned host points -> H2D -> build -> forward -> logits D2H, every step ----
+  copy_stream = torch.cuda.Stream(device=dev)
+  stage = [torch.empty_like(packed_dev) for _ in range(3)]
+  copied = [torch.cuda.Event() for _ in range(3)]
+  logits_host = [torch.empty((BATCH, 40), dtype=torch.float32).pin_memory() for _ in range(2)]
+
+  def e2e_src(k):
+    # the H2D copy of batch k runs on the copy stream; the build waits for it.  A staging buffer is
+    # reused three steps later, when the build that read it has long finished (the builds are
+    # ordered on one stream and the host waits for each build's read-back).
+    slot = k % 3
+    with torch.cuda.stream(copy_stream):
+      stage[slot].copy_(packed_host, non_blocking=True)
+      copied[slot].record(copy_stream)
+    build_stream.wait_event(copied[slot])
+    return stage[slot]
+
+  def e2e_result(k, out):
+    logits_host[k & 1].copy_(out.float().reshape(BATCH, 40), non_blocking=True)
+
+  pipelined(3, e2e_src, e2e_result)
+  e2e_ms = pipelined(args.steps, e2e_src, e2e_result)
+  torch.cuda.synchronize()
   assert all(bool(torch.isfinite(t).all()) for t in logits_host), 'end-to-end logits are not finite'
+
+  # ---- sustained: the pipelined step back to back for about two seconds (clocks sampled over it) ----
+  sustained_steps = int(max(200, min(4000, 2000.0 / max(total_ms / args.steps, 0.05))))
+  sustained_ms = pipelined(sustained_steps, lambda k: inputs[k % nbuf])
+
+  extras = {}
+  if rank == 0:
+    # ---- the convolution where it is tensor-bound, on this batch's finest level ----
+    extras['octree_conv'] = conv_throughput(ocnn, octree, int(nnum[DEPTH]), DEPTH, peaks, flush,
+                                            args.conv_iters)
+
+  # ---- the module route: the same network assembled from ocnn.OctreeConv* / OctreeMaxPool modules ----
+  mod_net = models.module_resnet_build(params, True, dev)
+  with torch.no_grad():
+    def step_module(fused=True):
+      ocnn.modules.FUSE_EVAL_BN = fused
+      o = build(packed_dev)
+      return mod_net(o, ocnn.nn.feature_node_major(o, 8, True))
+    mod_logits = step_module()
+    for _ in range(3):
+      step_module()
+    module_ms = timed_serial(step_module, args.steps)
+    for _ in range(2):
+      step_module(False)
+    module_torch_bn_ms = timed_serial(lambda: step_module(False), args.steps)
+    ocnn.modules.FUSE_EVAL_BN = True
+  torch.cuda.synchronize()
+  module_vs_exec = float((mod_logits.float() - logits.float()).abs().max() / logits.float().abs().max())
+
+  # ---- LeNet fp32 (the fp32 configuration: 32 shapes x 10k points, depth 5) ----
+  lenet_ms = None
+  if rank == 0:
+    lp, lm, lh = pack([synth.primitive_union(10000, 2000 + i) for i in range(BATCH)])
+    ldev = lp.to(dev)
+    lenet = models.GpuNet(models.lenet_params(5, 3, 40, seed=0), 'fp32', device=dev)
+    largs = (5, FULL_DEPTH) + BUILD_ARGS[2:]
+    lstep = lambda: lenet.forward(ocnn.points2octree_packed(ldev, lm, lh, *largs, True))
+    for _ in range(3):
+      lstep()
+    torch.cuda.synchronize()
+    ls = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps)]
+    for k in range(args.steps):
+      flush.zero_()
+      ls[2 * k].record()
+      lstep()
+      ls[2 * k + 1].record()
+    torch.cuda.synchronize()
+    lenet_ms = sum(ls[2 * k].elapsed_time(ls[2 * k + 1]) for k in range(args.steps)) / args.steps
+
+  # ---- strong scaling: ONE global batch of 32 shapes of unequal size, sharded over the ranks ----
+  sizes = [10000 + 1000 * ((7 * i) % 31) for i in range(BATCH)]            # 10k .. 40k points
+  plan = shard.plan_shards(sizes, world)
+  mine = plan[rank]
+  sclouds = [synth.primitive_union(sizes[i], 6000 + i) for i in range(BATCH)]
+
+  def strong_step_fn(ids):
+    sp, sm, sh = pack([sclouds[i] for i in ids])
+    sdev = sp.to(dev)
+    return lambda: net.forward(ocnn.points2octree_packed(sdev, sm, sh, *BUILD_ARGS, True))
+
+  strong = None
+  if mine:
+    whole = strong_step_fn(list(range(BATCH)))
+    part = strong_step_fn(mine)
+    for _ in range(3):
+      whole()
+      part()
+    n1_ms = timed_serial(whole, args.steps)
+    part_ms = timed_serial(part, args.steps)
+  else:
+    n1_ms = timed_serial(lambda: None, args.steps)
+    part_ms = timed_serial(lambda: None, args.steps)
+  strong = {'global_batch': BATCH, 'points_per_shape': '10000..40000 (unequal)',
+            'shapes_per_gpu': [len(s) for s in plan], 'planner': 'ocnn_harness.shard.plan_shards (LPT)',
+            'value': BATCH * args.steps / (part_ms * 1e-3), 'unit': UNIT,
+            'ms_per_step': part_ms / args.steps, 'n1_ms_per_step': n1_ms / args.steps,
+            'efficiency_vs_n1': (n1_ms / part_ms) / world}
+
   clocks = sampler.stop() if sampler else None
   assert net.error_status() == 0, 'a kernel reported an error status'
+  gpu_octree = octree.cpu().numpy() if rank == 0 and world == 1 else None
+  gpu_logits = logits.float().cpu().numpy() if rank == 0 and world == 1 else None
 
   if world > 1:
     dist.destroy_process_group()
@@ -389,7 +570,6 @@ def run_ours(args):
     return
 
   shapes = BATCH * world * args.steps
-  peaks = load_peaks()
   # roofline of the dominant kernel (the layer with the largest device time in a step)
   layer = {p['name']: (d, p) for d, p in models.conv_layers(net.net)}
   d_top, p_top = layer[top_layer]
@@ -397,7 +577,7 @@ def run_ours(args):
   pp = dict(p_top)
   pp['cin'] = p_top.get('_cin', p_top['cin'])
   flops, byts = conv_work(pp, h_top)
-  if p_top is not None and top_layer.endswith('1x1b'):
+  if top_layer.endswith('1x1b'):
     byts += p_top['cout'] * h_top * 2            # fused residual read
   roofline = None
   if top_ms:
@@ -411,42 +591,69 @@ def run_ours(args):
       ach = byts / (top_ms * 1e-3) / 1e9
       roofline = {'bound': 'hbm', 'achieved': ach, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                   'frac': ach / peaks['hbm_gbs']}
-    # DRAM traffic of this kernel per launch: dram__bytes_read + dram__bytes_write from the ncu
-    # capture summarised in profiles/conv_tc_kernel_group_8to32_d6_ncu.md (59.7 B per node at
-    # 931 k nodes), scaled by the node count of this launch; only known for that kernel shape
-    traffic = None
-    if top_layer == 'conv1' and pp['cin'] == 8 and p_top['cout'] == 32:
-      traffic = 59.7 * h_top
-    roofline.update({'traffic': traffic, 'kernel': 'octree_conv ' + top_layer,
+    roofline.update({'traffic': None, 'kernel': 'octree_conv ' + top_layer,
                      'shape': {'cin': pp['cin'], 'cout': p_top['cout'], 'taps': 27 if p_top['ks'][0] == 3 else 1,
                                'nodes': h_top},
                      'ms_per_launch': top_ms, 'algorithmic_bytes': byts, 'flops': flops,
-                     'peak_source': peaks['source'],
-                     'share_of_step': top_ms / (total_ms / args.steps)})
+                     'peak_source': peaks['source'], 'timed_in': 'the serial steps',
+                     'share_of_serial_step': top_ms / (serial_ms / args.steps)})
 
+  cfg = workload_config(world)
   line = {'metric': METRIC, 'value': shapes / (total_ms * 1e-3), 'unit': UNIT, 'n_gpus': world,
-          'steps': args.steps, 'warmup': max(args.warmup, 3) + 2, 'ms_per_step': total_ms / args.steps,
+          'steps': args.steps, 'warmup': args.warmup, 'warmup_run': max(args.warmup, 3) + 2,
+          'ms_per_step': total_ms / args.steps,
           'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16',
-          'data': 'synthetic', 'config': workload_config(world),
+          'data': 'synthetic', 'config': cfg,
           'e2e': {'value': shapes / (e2e_ms * 1e-3), 'unit': UNIT,
                   'h2d_bytes_per_step': int(packed_host.numel()) * world,
                   'd2h_bytes_per_step': BATCH * 40 * 4 * world,
                   'ms_per_step': e2e_ms / args.steps,
-                  'pipeline': 'pinned host buffers; H2D of the next batch on a copy stream while '
-                              'this one runs; logits copied back to pinned memory every step'},
+                  'pipeline': 'pinned host buffers; the H2D copy of every batch on a copy stream, its '
+                              'build on the build stream, the network on the main stream; logits '
+                              'copied back to pinned memory every step'},
+          'serial': {'ms_per_step': serial_ms / args.steps,
+                     'value': shapes / (serial_ms * 1e-3),
+                     'how': 'one stream, L2 flushed by a 256 MiB write between steps (outside the '
+                            'events), one event pair per step: the latency of a single batch'},
+          'sustained': {'steps': sustained_steps, 'ms_per_step': sustained_ms / sustained_steps,
+                        'value': BATCH * world * sustained_steps / (sustained_ms * 1e-3)},
+          'module_route': {'ms_per_step': module_ms / args.steps,
+                           'ms_per_step_torch_bn_relu': module_torch_bn_ms / args.steps,
+                           'how': 'the network assembled from ocnn.OctreeConvBnRelu / OctreeResBlock / '
+                                  'OctreeMaxPool modules (bf16 channels_last), serial steps incl. the '
+                                  'build; first figure with BatchNorm + ReLU folded into the kernels '
+                                  '(eval mode default), second with the torch modules between them',
+                           'rel_diff_vs_executor_logits': module_vs_exec},
+          'lenet_fp32': None if lenet_ms is None else {
+              'ms_per_step': lenet_ms, 'value': BATCH / (lenet_ms * 1e-3), 'unit': UNIT,
+              'workload': 'LeNet-style forward incl. build, fp32, 32 shapes x 10k points, depth 5'},
+          'strong': strong,
           'gpu_launches': int(launches), 'clocks': clocks, 'roofline': roofline,
           'tensor_core_layers': sum(1 for _, p in models.conv_layers(net.net) if p.get('_packed') is not None),
           'layer_ms': {k: round(v, 4) for k, v in layer_ms.items()},
-          'finest_nodes': int(nnum[DEPTH]), 'host_ms_per_step_incl_flush': host_ms / args.steps}
+          'finest_nodes': int(nnum[DEPTH]), 'host_ms_per_step': host_ms / args.steps,
+          'input_rotation': {'device_copies': nbuf, 'bytes_each': int(packed_dev.numel()),
+                             'l2_bytes': l2_bytes}}
+  line.update(extras)
 
   if world == 1:
     sample = max(1, min(args.cpu_sample, BATCH))
-    secs, kind = cpu_forward_time(sample)
+    secs, kind, cpu_logits, cpu_octree = cpu_forward_time(sample)
     line['cpu_baseline'] = {'value': sample / secs, 'unit': UNIT, 'cores': 1, 'kind': kind,
                             'sample': 'build + merge + fp32 forward of the first %d shapes of the '
                                       'batch on one core (%.1f s)' % (sample, secs)}
-  else:
-    line['cpu_baseline'] = None
+    # parity of what was timed: the GPU's logits for those shapes against the CPU forward, and the
+    # GPU-built octree against the CPU-built one (whole batch only)
+    rel = float(np.abs(gpu_logits[:sample] - cpu_logits).max() / np.abs(cpu_logits).max())
+    same = bool(sample == BATCH and np.array_equal(gpu_octree, cpu_octree))
+    line['parity'] = {'rel_err_logits': rel, 'octree_bytes_equal': same if sample == BATCH else None,
+                      'shapes': sample, 'tolerance': 6e-2,
+                      'against': 'fp32 CPU forward (%s) of the same shapes' % kind}
+    print(json.dumps(line))
+    assert rel < 6e-2, 'GPU logits differ from the CPU forward (rel %g)' % rel
+    assert sample != BATCH or same, 'the GPU-built octree differs from the CPU-built one'
+    return
+  line['cpu_baseline'] = None
   print(json.dumps(line))
 
 

@@ -35,7 +35,8 @@ typedef enum ocnn_status {
   OCNN_ERR_DEVICE = 5        /* a kernel reported an internal error through its status word */
 } ocnn_status;
 
-typedef enum ocnn_dtype { OCNN_F32 = 0, OCNN_BF16 = 1 } ocnn_dtype;
+/* Element type of a data tensor.  The 16-bit types are accumulated in fp32 by every kernel. */
+typedef enum ocnn_dtype { OCNN_F32 = 0, OCNN_BF16 = 1, OCNN_F16 = 2 } ocnn_dtype;
 
 /* Memory layout of a data tensor of C channels over H octree nodes.
  * OCNN_CHANNEL_MAJOR is the reference's [1,C,H,1] contiguous tensor (data[c*H + h],
@@ -143,6 +144,20 @@ int ocnn_calc_neigh(void* octree_dev, const ocnn_octree_meta* meta, void* stream
 int ocnn_octree2col(const float* data_dev, float* col_dev, const int32_t* neigh_dev,
                     int channels, int h_out, const int kernel_size[3], int stride, void* stream);
 
+/* octree2col on all nodes (child_dev == NULL) or on the non-empty nodes only, and its transpose.
+ * Replace octree2colP_gpu and col2octree_gpu / col2octreeP_gpu, octree/octree/octree_nn.cu:130-253
+ * (bindings pytorch/cpp/octree2col.cpp:47-226).  data: [C, octree_h] fp32 channel-major; col:
+ * [C, K, h_col] with h_col = nodes (stride 1; the non-empty ones when child is given) or sibling
+ * groups (stride 2).  ocnn_col2octree clears `data` and then adds every column entry to the node
+ * it was gathered from (atomic additions: the summation order is not fixed). */
+int ocnn_octree2col_general(const float* data_dev, float* col_dev, const int32_t* neigh_dev,
+                            const int32_t* child_dev, const int32_t* ichild_dev, int channels,
+                            int h_col, int octree_h, const int kernel_size[3], int stride,
+                            void* stream);
+int ocnn_col2octree(const float* col_dev, float* data_dev, const int32_t* neigh_dev,
+                    const int32_t* child_dev, const int32_t* ichild_dev, int channels, int h_col,
+                    int octree_h, const int kernel_size[3], int stride, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Octree convolution, forward.  Replaces OctreeBaseConv::forward_gpu_gemm
  * (octree/octree/octree_conv.cpp:276-298: octree2col_gpu + cublasSgemm through
@@ -191,6 +206,39 @@ int ocnn_octree_conv_nempty(const void* x_dev, const float* weights_dev, void* y
                             const int kernel_size[3], int dtype, int layout,
                             const ocnn_conv_epilogue* epilogue, void* stream);
 
+/* Every OctreeConv / OctreeDeconv forward the reference offers, in one entry point: stride 1 or 2,
+ * on all nodes or on the non-empty nodes only, convolution or deconvolution.  Replaces
+ * OctreeBaseConv::forward_gpu_gemm / backward_gpu_gemm with octree2col(P)_gpu / col2octree(P)_gpu
+ * (octree/octree/octree_conv.cpp:48-122, 276-330; octree_nn.cu:110-253; bindings
+ * pytorch/cpp/octree_conv.cpp:137-154 octree_conv, :191-217 octree_deconv).  The deconvolution is
+ * computed in gather form (each output node sums over the nodes that would scatter into it), so
+ * there is no column buffer and no atomic addition.
+ *
+ * Rows of x / y, with d = the layer's depth (nnum, nne = node / non-empty node counts):
+ *   convolution    stride 1: x nnum[d]          -> y nnum[d]        (nempty: nne[d] -> nne[d])
+ *                  stride 2: x nnum[d]          -> y nnum[d]/8      (nempty: nne[d] -> nnum[d]/8)
+ *   deconvolution  stride 1: x nnum[d]          -> y nnum[d]        (nempty: nne[d] -> nne[d])
+ *                  stride 2: x nne[d]           -> y nnum[d+1]      (nempty: nne[d] -> nne[d+1])
+ * neigh_dev / child_dev / ichild_dev belong to the level the reference's column matrix lives at:
+ * d, except d + 1 for the stride-2 deconvolution.  child / ichild are read only when nempty is set
+ * (ichild not by the stride-2 convolution).  Weights: fp32 [Cout, Cin*K] for the convolution,
+ * [Cin, Cout*K] for the deconvolution, as the reference modules hold them
+ * (pytorch/ocnn/octree_conv.py:51-58). */
+typedef struct ocnn_conv_geometry {
+  int32_t transposed;          /* 0: OctreeConv, 1: OctreeDeconv                              */
+  int32_t stride;              /* 1 or 2                                                      */
+  int32_t nempty;              /* data lives on the non-empty nodes only                      */
+  int32_t h_in, h_out;         /* rows of x and of y                                          */
+  const int32_t* neigh_dev;    /* NULL allowed for 1x1x1 stride 1                             */
+  const int32_t* child_dev;
+  const int32_t* ichild_dev;
+} ocnn_conv_geometry;
+
+int ocnn_octree_conv_general(const void* x_dev, const float* weights_dev, void* y_dev,
+                             const ocnn_conv_geometry* geometry, int cin, int cout,
+                             const int kernel_size[3], int dtype, int layout,
+                             const ocnn_conv_epilogue* epilogue, void* stream);
+
 /* Tensor-core path: weights packed once per layer into bf16 K-major tiles.  The packed image
  * depends on the kernel shape AND the stride the layer will run with (stride-1 neighbourhood
  * convolutions with few channels use a per-sibling-group formulation with expanded weights). */
@@ -206,13 +254,31 @@ size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3]
 int ocnn_conv_pack_weights(const float* weights_dev, void* packed_dev, int cin, int cout,
                            const int kernel_size[3], int stride, void* stream);
 /* x, y: bf16 node-major ([h, C]); cin % 8 == 0; cout % 8 == 0 up to 256, or a multiple of 256 up
- * to 1024 (then produced 256 channels per launch).
+ * to 4096 (then produced in 256-channel slices of one launch).
  * status_dev: one int32 in device memory, zero before the call; a kernel that gives up on a
  * bounded wait writes a non-zero code there instead of hanging. */
 int ocnn_octree_conv_tc(const void* x_dev, const void* packed_weights_dev, void* y_dev,
                         const int32_t* neigh_dev, int h_in, int h_out, int cin, int cout,
                         const int kernel_size[3], int stride,
                         const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
+
+/* The tensor-core kernel for every layer kind ocnn_octree_conv_general takes, on bf16 or fp16
+ * node-major data (dtype = OCNN_BF16 / OCNN_F16; fp32 accumulation in TMEM either way).  The packed
+ * image depends on (cin, cout, kernel, stride, transposed, nempty, dtype): pack with the same
+ * values the layer runs with.  Kernel 2 with stride 2 — the down- and up-sampling layers of the
+ * reference's U-Net (pytorch/ocnn/unet.py:19-36) — runs as a dense product: the convolution on all
+ * nodes reads a sibling group's eight children as one row of 8*Cin channels, the deconvolution
+ * writes a parent's eight children as one row of 8*Cout channels (through child on non-empty
+ * nodes); neither gathers.  status_dev as for ocnn_octree_conv_tc. */
+size_t ocnn_conv_packed_weight_bytes_general(int cin, int cout, const int kernel_size[3], int stride,
+                                             int transposed, int nempty);
+int ocnn_conv_pack_weights_general(const float* weights_dev, void* packed_dev, int cin, int cout,
+                                   const int kernel_size[3], int stride, int transposed, int nempty,
+                                   int dtype, void* stream);
+int ocnn_octree_conv_tc_general(const void* x_dev, const void* packed_dev, void* y_dev,
+                                const ocnn_conv_geometry* geometry, int cin, int cout,
+                                const int kernel_size[3], int dtype,
+                                const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * points -> octree, batched, on the device.  Replaces Octree::build
@@ -295,6 +361,45 @@ int ocnn_octree_batch_noalloc(const void* const* octrees_dev, const ocnn_octree_
                               const void* first_header_host, int batch,
                               const ocnn_octree_meta* merged, void* out_dev,
                               void* header_host_out /* OCNN_HEADER_BYTES or NULL */, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Keys: conversion, search, and the operators built on the search.  A key packs four lanes
+ * (x, y, z, batch id): bytes for 32-bit keys, 16-bit words for 64-bit keys
+ * (octree/octree/types.h:16-24).
+ * ------------------------------------------------------------------------------------------ */
+/* xyz lanes -> Morton key (to_key != 0) or back.  Replaces xyz2key_gpu / key2xyz_gpu,
+ * octree/octree/octree_nn.cu:594-660 (bindings pytorch/cpp/octree_key.cpp:47-77). */
+int ocnn_convert_key(const void* in_dev, void* out_dev, int64_t num, int depth, int key_bits,
+                     int to_key, void* stream);
+/* idx[i] = position of query[i] among the n_key ascending keys, or -1.  query_is_xyz != 0: the
+ * queries are xyz lanes and are converted with `depth` first.  Replaces search_key_gpu,
+ * octree/octree/octree_nn.cu:575-590 (binding pytorch/cpp/octree_key.cpp:79-126). */
+int ocnn_search_key(const void* keys_dev, int n_key, const void* query_dev, int64_t n_query,
+                    int32_t* idx_dev, int query_is_xyz, int depth, int key_bits, void* stream);
+/* out[child[h]] = key[h] for child[h] >= 0: the keys of a level's non-empty nodes, in order (the
+ * pad_backward_gpu call on the key array at pytorch/cpp/octree_key.cpp:100-108). */
+int ocnn_key_depad(const void* key_dev, const int32_t* child_dev, int nnum, void* out_dev,
+                   int key_bits, void* stream);
+/* Node data sampled at points, in one kernel.  Replaces the reference's octree_nearest_pts /
+ * octree_trilinear_pts (pytorch/ocnn/modules.py:209-275: key arithmetic, octree_search_key, a
+ * sparse matrix and two sparse products).  data: [C, h] rows of the nodes whose ascending keys are
+ * keys_dev[0..n_key) (a level's Key block, or ocnn_key_depad of it); pts_dev: [n_pts, 4] float32 =
+ * (x, y, z) scaled to [0, 2^depth] and the batch id; out: [C, n_pts] in the data's dtype / layout.
+ * linear == 0: the row of the cell holding the point (0 if absent); linear != 0: trilinear weights
+ * over the 8 cells around the point, renormalised over those that exist. */
+int ocnn_octree_interp(const void* data_dev, void* out_dev, const float* pts_dev, const void* keys_dev,
+                       int n_key, int channels, int h, int64_t n_pts, int depth, int key_bits,
+                       int linear, int dtype, int layout, void* stream);
+/* dst[., idx[h]] = src[., h] for idx[h] >= 0, every other row of dst 0.  Replaces
+ * align_forward_gpu, octree/octree/octree_nn.cu:711-732 (binding pytorch/cpp/octree_align.cpp:9-60;
+ * idx comes from ocnn_search_key of the source keys among the destination keys). */
+int ocnn_octree_align(const void* src_dev, void* dst_dev, const int32_t* idx_dev, int channels,
+                      int src_h, int dst_h, int dtype, int layout, void* stream);
+/* Its transpose: src_grad[., h] = idx[h] < 0 ? 0 : dst_grad[., idx[h]].  Replaces
+ * align_backward_gpu, octree/octree/octree_nn.cu:734-752 (binding octree_align.cpp:62-82). */
+int ocnn_octree_align_backward(const void* dst_grad_dev, void* src_grad_dev, const int32_t* idx_dev,
+                               int channels, int src_h, int dst_h, int dtype, int layout,
+                               void* stream);
 
 /* Feature block of the finest level (fp32 [C, nnum] channel-major, as stored in the octree) to the
  * bf16 node-major tensor [nnum, c_pad] the tensor-core convolution reads (channels >= C are 0).

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -112,6 +113,20 @@ __device__ __forceinline__ void st_global_32B(void* p, const uint4& lo, const ui
                : "memory");
 }
 
+// ---- two 16-bit floats in one 32-bit word ------------------------------------------------------
+// `half` selects fp16 (true) or bf16 (false); kernels that serve both take it as a launch-uniform
+// flag, so the branch never diverges.
+__device__ __forceinline__ float2 unpack2(uint32_t w, bool half) {
+  if (half) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, bool half) {
+  uint32_t w;
+  if (half) *reinterpret_cast<__half2*>(&w) = __floats2half2_rn(a, b);
+  else *reinterpret_cast<__nv_bfloat162*>(&w) = __floats2bfloat162_rn(a, b);
+  return w;
+}
+
 // ---- neighbour index arithmetic ---------------------------------------------------------------
 // Position, inside the 4x4x4 neighbour block of a sibling group, of the cell at offset
 // (tx-1, ty-1, tz-1) from octant o of that group, tap = tx*9 + ty*3 + tz.  This is the closed
@@ -123,6 +138,28 @@ __host__ __device__ __forceinline__ int ni333(int octant, int tap) {
   return ((tx + ox) << 4) | ((ty + oy) << 2) | (tz + oz);
 }
 
+// Stride-2 deconvolution in gather form.  The reference scatters: sibling group h of the finer
+// level adds its product to the node at offset (tx-1, ty-1, tz-1) from the group's first cell
+// (col2octree_cpu with stride 2, octree/octree/octree_nn.cpp:216-241).  Read from the receiving
+// node `node` (group g = node >> 3, octant o): along an axis where the octant bit is 0 only the
+// offset 0 of its own group reaches it; where the bit is 1, offset +1 of its own group and offset
+// -1 of the group two cells further.  Returns the sending group (= rank of its parent among the
+// non-empty nodes of the coarser level) for tap = tx*9 + ty*3 + tz, or -1 when that tap does not
+// reach this octant or the group does not exist.  neigh = the finer level's neighbour table.
+__device__ __forceinline__ int up_source_group(const int* __restrict__ neigh, int node, int tap) {
+  const int o = node & 7;
+  const int off[3] = {tap / 9 - 1, (tap / 3) % 3 - 1, tap % 3 - 1};
+  int pos = 0;
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+    const int bit = (o >> (2 - a)) & 1;
+    if (bit == 0 ? off[a] != 0 : off[a] == 0) return -1;
+    pos = (pos << 2) | ((bit == 1 && off[a] == -1) ? 3 : 1);
+  }
+  const int q = neigh[((long long)(node >> 3) << 6) + pos];
+  return q >= 0 ? (q >> 3) : -1;
+}
+
 // The taps of the 3x3x3 neighbourhood that each supported kernel shape uses
 // (octree/octree/octree_nn.cpp:7-19).  Returns the tap count or -1.
 struct TapList {
@@ -130,5 +167,9 @@ struct TapList {
   signed char tap[27];
 };
 TapList taps_for_kernel(const int kernel_size[3]);
+
+// Row-count and pointer rules of ocnn_conv_geometry, shared by the CUDA-core and the tensor-core
+// route (defined in conv_simt.cu).
+int check_conv_geometry(const ocnn_conv_geometry* g, const TapList& tl, const char* who);
 
 }  // namespace ocnn

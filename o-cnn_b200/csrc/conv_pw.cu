@@ -21,6 +21,7 @@ struct PwArgs {
   const float* bias;
   const __nv_bfloat16* residual;
   int relu;
+  int f16;                 // the 16-bit elements are fp16 instead of bf16
 };
 
 template <int COUT, int ROWS>
@@ -50,10 +51,10 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
         const long long h = h0 + r * stride;
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (h < a.h) raw = reinterpret_cast<const uint4*>(a.x + h * a.cin)[c8];
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 f = __bfloat1622float2(p[k]);
+          const float2 f = unpack2(p[k], a.f16 != 0);
           xv[r][2 * k] = f.x;
           xv[r][2 * k + 1] = f.y;
         }
@@ -90,10 +91,10 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
         const long long at = h * a.y_stride + a.co_base + 8 * q;
         if (a.residual) {
           const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
-          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+          const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rv);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float2 rf = __bfloat1622float2(rp[j]);
+            const float2 rf = unpack2(rp[j], a.f16 != 0);
             f[2 * j] += rf.x;
             f[2 * j + 1] += rf.y;
           }
@@ -103,9 +104,9 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
           for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
         }
         uint4 ov;
-        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+        uint32_t* op = reinterpret_cast<uint32_t*>(&ov);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+        for (int j = 0; j < 4; ++j) op[j] = pack2(f[2 * j], f[2 * j + 1], a.f16 != 0);
         *reinterpret_cast<uint4*>(a.y + at) = ov;
       }
     }
@@ -138,7 +139,7 @@ int launch_pw(const PwArgs& a, cudaStream_t st) {
 // Used by ocnn_octree_conv for 1x1x1 stride-1 bf16 node-major convolutions.  Returns -1 when the
 // shape is not one this kernel takes (the caller then uses the general kernel).
 int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, int cout,
-                        const ocnn_conv_epilogue* ep, cudaStream_t st) {
+                        const ocnn_conv_epilogue* ep, cudaStream_t st, bool f16) {
   if (cin % 8 != 0 || cin > 256 || (long long)cin * cout > 16384) return -1;
   if (cout != 8 && cout != 16 && cout != 32 && cout != 64) return -1;
   if (((uintptr_t)x % 16) != 0 || ((uintptr_t)y % 16) != 0) return -1;
@@ -153,6 +154,7 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.bias = ep ? ep->bias_dev : nullptr;
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
   a.relu = ep ? ep->relu : 0;
+  a.f16 = f16 ? 1 : 0;
   switch (cout) {
     case 8: return launch_pw<8, 2>(a, st);
     case 16: return launch_pw<16, 2>(a, st);

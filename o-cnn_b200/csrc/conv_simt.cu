@@ -15,7 +15,7 @@
 namespace ocnn {
 
 int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, int cout,
-                        const ocnn_conv_epilogue* ep, cudaStream_t st);   // conv_pw.cu
+                        const ocnn_conv_epilogue* ep, cudaStream_t st, bool f16);   // conv_pw.cu
 
 namespace {
 
@@ -29,6 +29,9 @@ struct ConvArgs {
   const int* child;    // non-empty-node convolution only: child array of the level, and
   const int* ichild;   // its inverse (node of the i-th non-empty node); NULL for the dense one
   int h_in, h_out, cin, cout, K, stride, identity;
+  int transposed;      // deconvolution: weights are [Cin, Cout*K], element (ci, co*K + t)
+  int up;              // stride-2 deconvolution: rows are nodes of the finer level, x rows are
+                       // their parents' ranks among the non-empty nodes (= sibling-group indices)
   const float* scale;
   const float* bias;
   const void* residual;
@@ -38,6 +41,8 @@ struct ConvArgs {
 
 __device__ __forceinline__ float ld(const float* p, long long i) { return p[i]; }
 __device__ __forceinline__ float ld(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ float ld(const __half* p, long long i) { return __half2float(p[i]); }
+__device__ __forceinline__ void st(__half* p, long long i, float v) { p[i] = __float2half(v); }
 __device__ __forceinline__ void st(float* p, long long i, float v) { p[i] = v; }
 __device__ __forceinline__ void st(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
 
@@ -65,11 +70,15 @@ __global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
         // on non-empty nodes only (octree2colP, octree/octree/octree_nn.cu:179-201): row h is the
         // h-th non-empty node, its neighbours are looked up from the node itself and mapped back
         // to ranks among the non-empty nodes
-        const int hn = a.ichild ? a.ichild[h] : h;
-        const long long at = a.stride == 2 ? ((long long)hn << 6) + ni333(0, tap)
-                                           : ((long long)(hn >> 3) << 6) + ni333(hn & 7, tap);
-        p = a.neigh[at];
-        if (a.ichild && p >= 0) p = a.child[p];
+        const int hn = (a.ichild && (a.stride == 1 || a.up)) ? a.ichild[h] : h;
+        if (a.up) {
+          p = up_source_group(a.neigh, hn, tap);
+        } else {
+          const long long at = a.stride == 2 ? ((long long)hn << 6) + ni333(0, tap)
+                                             : ((long long)(hn >> 3) << 6) + ni333(hn & 7, tap);
+          p = a.neigh[at];
+          if (a.child && p >= 0) p = a.child[p];
+        }
       }
     }
     nbr[t][m] = p;
@@ -109,9 +118,10 @@ __global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
       const int kk = k0 + kl, co = n0 + n;
       float v = 0.f;
       if (kk < KD && co < a.cout) {
-        int col = kk;
-        if (LAYOUT != OCNN_CHANNEL_MAJOR) col = (kk % a.cin) * a.K + kk / a.cin;
-        v = a.w[(long long)co * KD + col];
+        int ci, t;
+        if (LAYOUT == OCNN_CHANNEL_MAJOR) { ci = kk / a.K; t = kk % a.K; } else { t = kk / a.cin; ci = kk % a.cin; }
+        v = a.transposed ? a.w[((long long)ci * a.cout + co) * a.K + t]
+                         : a.w[(long long)co * KD + ci * a.K + t];
       }
       Bs[kl][n] = v;
     }
@@ -169,22 +179,30 @@ __global__ void ichild_kernel(const int* __restrict__ child, int* __restrict__ i
 int conv_simt_launch(const void* x, const float* w, void* y, const int32_t* neigh,
                      const int32_t* child, const int32_t* ichild, int h_in, int h_out, int cin,
                      int cout, const TapList& tl, int stride, int dtype, int layout,
-                     const ocnn_conv_epilogue* ep, void* stream) {
+                     const ocnn_conv_epilogue* ep, void* stream, bool transposed = false) {
   const bool identity = tl.count == 1 && stride == 1;
   ConvArgs a;
   a.x = x; a.w = w; a.y = y; a.neigh = neigh; a.child = child; a.ichild = ichild;
   a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout;
   a.K = tl.count; a.stride = stride; a.identity = identity ? 1 : 0;
+  a.transposed = transposed ? 1 : 0;
+  a.up = (transposed && stride == 2) ? 1 : 0;
   a.scale = ep ? ep->scale_dev : nullptr;
   a.bias = ep ? ep->bias_dev : nullptr;
   a.residual = ep ? ep->residual_dev : nullptr;
   a.relu = ep ? ep->relu : 0;
-  for (int i = 0; i < 27; ++i) a.tap[i] = i < tl.count ? tl.tap[i] : 0;
+  // a stride-1 deconvolution gathers from the mirrored offsets: node p receives from the node h
+  // with p = h + offset(t), i.e. h = p - offset(t)
+  for (int i = 0; i < 27; ++i)
+    a.tap[i] = i < tl.count ? (signed char)((transposed && stride == 1) ? 26 - tl.tap[i] : tl.tap[i]) : 0;
   dim3 grid(ceil_div(h_out, BM), ceil_div(cout, BN));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == OCNN_F32) {
     if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<float, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
     else conv_simt_kernel<float, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+  } else if (dtype == OCNN_F16) {
+    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__half, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    else conv_simt_kernel<__half, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
   } else {
     if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__nv_bfloat16, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
     else conv_simt_kernel<__nv_bfloat16, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
@@ -208,7 +226,8 @@ extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const in
     return fail(OCNN_ERR_UNSUPPORTED, "ocnn_octree_conv: unsupported kernel size %dx%dx%d",
                 kernel_size[0], kernel_size[1], kernel_size[2]);
   OCNN_REQUIRE(cin > 0 && cout > 0, "ocnn_octree_conv: channel counts must be positive");
-  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "ocnn_octree_conv: unknown dtype %d", dtype);
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16 || dtype == OCNN_F16,
+               "ocnn_octree_conv: unknown dtype %d", dtype);
   OCNN_REQUIRE(layout == OCNN_CHANNEL_MAJOR || layout == OCNN_NODE_MAJOR,
                "ocnn_octree_conv: unknown layout %d", layout);
   OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv: negative height");
@@ -223,9 +242,10 @@ extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const in
     OCNN_REQUIRE(h_in == h_out, "ocnn_octree_conv: stride 1 needs h_in == h_out (got %d, %d)",
                  h_in, h_out);
   }
-  if (identity && dtype == OCNN_BF16 && layout == OCNN_NODE_MAJOR) {
+  if (identity && dtype != OCNN_F32 && layout == OCNN_NODE_MAJOR) {
     // few-channel pointwise layers: a dedicated streaming kernel (conv_pw.cu)
-    const int s = conv_pointwise_bf16(x, w, y, h_out, cin, cout, ep, static_cast<cudaStream_t>(stream));
+    const int s = conv_pointwise_bf16(x, w, y, h_out, cin, cout, ep, static_cast<cudaStream_t>(stream),
+                                      dtype == OCNN_F16);
     if (s >= 0) return s;
   }
   return conv_simt_launch(x, w, y, neigh, nullptr, nullptr, h_in, h_out, cin, cout, tl, stride, dtype,
@@ -252,7 +272,8 @@ extern "C" int ocnn_octree_conv_nempty(const void* x, const float* w, void* y, c
     return fail(OCNN_ERR_UNSUPPORTED, "ocnn_octree_conv_nempty: unsupported kernel size %dx%dx%d",
                 kernel_size[0], kernel_size[1], kernel_size[2]);
   OCNN_REQUIRE(cin > 0 && cout > 0, "ocnn_octree_conv_nempty: channel counts must be positive");
-  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "ocnn_octree_conv_nempty: unknown dtype %d", dtype);
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16 || dtype == OCNN_F16,
+               "ocnn_octree_conv_nempty: unknown dtype %d", dtype);
   OCNN_REQUIRE(layout == OCNN_CHANNEL_MAJOR || layout == OCNN_NODE_MAJOR,
                "ocnn_octree_conv_nempty: unknown layout %d", layout);
   OCNN_REQUIRE(nne >= 0, "ocnn_octree_conv_nempty: negative height");
@@ -263,4 +284,64 @@ extern "C" int ocnn_octree_conv_nempty(const void* x, const float* w, void* y, c
   OCNN_REQUIRE(neigh && child && ichild, "ocnn_octree_conv_nempty: neighbour table, child and ichild required");
   return conv_simt_launch(x, w, y, neigh, child, ichild, nne, nne, cin, cout, tl, 1, dtype, layout, ep,
                           stream);
+}
+
+// Height rules shared by the CUDA-core and the tensor-core route of the general entry points.
+namespace ocnn {
+int check_conv_geometry(const ocnn_conv_geometry* g, const TapList& tl, const char* who) {
+  OCNN_REQUIRE(g != nullptr, "%s: null geometry", who);
+  OCNN_REQUIRE(g->stride == 1 || g->stride == 2, "%s: stride must be 1 or 2 (got %d)", who, g->stride);
+  OCNN_REQUIRE(g->h_in >= 0 && g->h_out >= 0, "%s: negative height", who);
+  const bool identity = tl.count == 1 && g->stride == 1;
+  OCNN_REQUIRE(identity || g->neigh_dev != nullptr, "%s: neighbour table required", who);
+  if (g->nempty && !identity) {
+    const bool need_child = !(g->transposed && g->stride == 2);
+    const bool need_ichild = !(g->stride == 2 && !g->transposed);
+    OCNN_REQUIRE(!need_child || g->child_dev != nullptr, "%s: child array required (nempty)", who);
+    OCNN_REQUIRE(!need_ichild || g->ichild_dev != nullptr, "%s: ichild array required (nempty)", who);
+  }
+  if (g->stride == 1) {
+    OCNN_REQUIRE(g->h_in == g->h_out, "%s: stride 1 needs h_in == h_out (got %d, %d)", who, g->h_in,
+                 g->h_out);
+  } else if (!g->transposed) {
+    if (!g->nempty)
+      OCNN_REQUIRE((long long)g->h_out * 8 == g->h_in, "%s: stride 2 needs h_in == 8*h_out (got %d, %d)",
+                   who, g->h_in, g->h_out);
+  } else {
+    if (!g->nempty)
+      OCNN_REQUIRE((long long)g->h_in * 8 == g->h_out,
+                   "%s: a stride-2 deconvolution needs h_out == 8*h_in (got %d, %d)", who, g->h_in,
+                   g->h_out);
+    else
+      OCNN_REQUIRE((long long)g->h_in * 8 >= g->h_out,
+                   "%s: a stride-2 deconvolution on non-empty nodes needs h_out <= 8*h_in (got %d, %d)",
+                   who, g->h_in, g->h_out);
+  }
+  return OCNN_OK;
+}
+}  // namespace ocnn
+
+extern "C" int ocnn_octree_conv_general(const void* x, const float* w, void* y,
+                                        const ocnn_conv_geometry* g, int cin, int cout,
+                                        const int kernel_size[3], int dtype, int layout,
+                                        const ocnn_conv_epilogue* ep, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_general: null kernel size");
+  const TapList tl = taps_for_kernel(kernel_size);
+  if (tl.count < 0)
+    return fail(OCNN_ERR_UNSUPPORTED, "ocnn_octree_conv_general: unsupported kernel size %dx%dx%d",
+                kernel_size[0], kernel_size[1], kernel_size[2]);
+  OCNN_REQUIRE(cin > 0 && cout > 0, "ocnn_octree_conv_general: channel counts must be positive");
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16 || dtype == OCNN_F16,
+               "ocnn_octree_conv_general: unknown dtype %d", dtype);
+  OCNN_REQUIRE(layout == OCNN_CHANNEL_MAJOR || layout == OCNN_NODE_MAJOR,
+               "ocnn_octree_conv_general: unknown layout %d", layout);
+  if (int rc = check_conv_geometry(g, tl, "ocnn_octree_conv_general")) return rc;
+  if (g->h_out == 0) return OCNN_OK;
+  OCNN_REQUIRE(x && w && y, "ocnn_octree_conv_general: null data pointer");
+  const bool identity = tl.count == 1 && g->stride == 1;
+  const int32_t* child = (g->nempty && !identity && !(g->transposed && g->stride == 2)) ? g->child_dev : nullptr;
+  const int32_t* ichild = (g->nempty && !identity && !(g->stride == 2 && !g->transposed)) ? g->ichild_dev : nullptr;
+  return conv_simt_launch(x, w, y, identity ? nullptr : g->neigh_dev, child, ichild, g->h_in, g->h_out,
+                          cin, cout, tl, g->stride, dtype, layout, ep, stream, g->transposed != 0);
 }

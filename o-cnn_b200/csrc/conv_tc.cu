@@ -66,6 +66,13 @@ struct TcArgs {
                     // 2 = node mode, Cin % 64 == 0, 3 = group mode through the shared index table,
                     // 4 = node mode, any other Cin with more than one tap (index table with the
                     // padded stride, two 16-byte index reads per K-block)
+  int up;           // stride-2 deconvolution in gather form: tile rows are nodes of the finer level,
+                    // the gathered rows are their source sibling groups (common.cuh: up_source_group)
+  int f16;          // the 16-bit elements are fp16 instead of bf16
+  int expand_cout;  // > 0: the kernel-2 stride-2 deconvolution as a dense product: tile row = a
+                    // parent, its row_elems = 8 * expand_cout columns are (octant, channel) pairs
+  const int* scatter_child;   // with expand_cout: Child block of the finer level; octant o of tile
+                              // row h is written to row scatter_child[8h + o] (skipped when < 0)
   const float* scale;
   const float* bias;
   const __nv_bfloat16* residual;
@@ -285,7 +292,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   grid_dependency_wait();
   for (int n = tid; n < a.npad; n += kThreads) {
     // output channel of column n: columns are (octant, channel) pairs in group mode
-    const int co = a.group ? (n & (a.cout - 1)) : co_base + n;
+    const int co = a.group ? (n & (a.cout - 1))
+                           : (a.expand_cout ? (co_base + n) % a.expand_cout : co_base + n);
     const bool live = n < a.row_elems;
     s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
     s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
@@ -330,13 +338,18 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
         if (t < a.T && live) {
           // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
           // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
-          const long long at = a.stride == 2 ? ((long long)hn << 6) + a.tap[t]
-                                             : ((long long)(hn >> 3) << 6) + a.tap[t] + oct_code;
-          p = a.neigh[at];
+          if (a.up) {
+            const int code = a.tap[t];
+            p = up_source_group(a.neigh, hn, (code >> 4) * 9 + ((code >> 2) & 3) * 3 + (code & 3));
+          } else {
+            const long long at = a.stride == 2 ? ((long long)hn << 6) + a.tap[t]
+                                               : ((long long)(hn >> 3) << 6) + a.tap[t] + oct_code;
+            p = a.neigh[at];
+          }
         }
         pv[t] = p;
       }
-      if (a.ichild != nullptr) {
+      if (a.child != nullptr) {
 #pragma unroll
         for (int t = 0; t < 27; ++t)
           if (t < a.T && pv[t] >= 0) pv[t] = a.child[pv[t]];
@@ -509,6 +522,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     // the wait for the accumulator.
     const int h = h0 + r;
     const bool row_ok = r < a.tile_rows && h < a.rows;
+    const bool f16 = a.f16 != 0;
     const __nv_bfloat16* res_row =
         (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + co_base : nullptr;
     uint4 res_nxt[4];
@@ -535,6 +549,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     if (alive) {
       __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + co_base;
       const bool has_sb = a.scale != nullptr || a.bias != nullptr;
+      const bool scatter = a.scatter_child != nullptr;
       for (int c0 = 0; c0 < a.npad; c0 += 32) {
         uint4 res_cur[4];
 #pragma unroll
@@ -566,11 +581,10 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
               for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], bi[j]);
             }
             if (res_row != nullptr) {
-              const __nv_bfloat162* rp =
-                  reinterpret_cast<const __nv_bfloat162*>(&res_cur[2 * step + half]);
+              const uint32_t* rp = reinterpret_cast<const uint32_t*>(&res_cur[2 * step + half]);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const float2 rf = __bfloat1622float2(rp[j]);
+                const float2 rf = unpack2(rp[j], f16);
                 f[2 * j] += rf.x;
                 f[2 * j + 1] += rf.y;
               }
@@ -579,12 +593,23 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
             }
-            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov[half]);
+            uint32_t* op = reinterpret_cast<uint32_t*>(&ov[half]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-            if (!a.wide) *reinterpret_cast<uint4*>(y_row + n) = ov[half];
+            for (int j = 0; j < 4; ++j) op[j] = pack2(f[2 * j], f[2 * j + 1], f16);
+            if (scatter) {
+              // column (co_base + n) = octant * Cout + channel of this parent's children; the child
+              // of octant o lives in row scatter_child[8h + o] of the output (if it is non-empty)
+              const int ng = co_base + n;
+              const int o = ng / a.expand_cout;
+              const int dst = a.scatter_child[((long long)h << 3) + o];
+              if (dst >= 0)
+                *reinterpret_cast<uint4*>(a.y + (long long)dst * a.expand_cout + (ng - o * a.expand_cout)) =
+                    ov[half];
+            } else if (!a.wide) {
+              *reinterpret_cast<uint4*>(y_row + n) = ov[half];
+            }
           }
-          if (a.wide && row_ok && n0 < a.row_elems) st_global_32B(y_row + n0, ov[0], ov[1]);
+          if (a.wide && !scatter && row_ok && n0 < a.row_elems) st_global_32B(y_row + n0, ov[0], ov[1]);
         }
       }
     }
@@ -593,7 +618,9 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     if (lane == 0) {
       // instruction descriptor: D = F32 (bit 4), A = B = BF16 (bits 7, 10), both K-major,
       // N >> 3 at bit 17, M >> 4 at bit 24
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.npad >> 3) << 17) |
+      // (A/B format field: 0 = F16, 1 = BF16)
+      const uint32_t ab = a.f16 ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (ab << 7) | (ab << 10) | ((uint32_t)(a.npad >> 3) << 17) |
                              ((uint32_t)(kTileM >> 4) << 24);
       bool alive = true;
       int s = 0;
@@ -663,27 +690,63 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 }
 
 // ---- weight packing -------------------------------------------------------------------------
-// w: fp32 [cout, cin*T], column ci*T + t (the reference module's layout).  packed: per K-block a
-// [npad x 64] bf16 tile in the swizzled K-major image: element (n, kk) at
-// (n/8)*1024 + (n%8)*128 + (((kk/8) ^ (n%8)) * 16) + (kk%8)*2, k = kb*64 + kk = t*cin + ci.
-__global__ void pack_weights_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ packed,
-                                    int cin, int cout, int T, int npad, int nkb) {
+// packed: per K-block a [npad x 64] tile of 16-bit floats in the swizzled K-major image: element
+// (n, kk) at (n/8)*1024 + (n%8)*128 + (((kk/8) ^ (n%8)) * 16) + (kk%8)*2, k = kb*64 + kk.
+// WeightView says where the value of (output column n, input channel ci, tap t) sits in the
+// reference's fp32 weight tensor:
+//   convolution    w[co, ci*T + t]             (pytorch/ocnn/octree_conv.py:51-58, [Cout, Cin*K])
+//   deconvolution  w[ci, co*T + t]             ([Cin, Cout*K])
+// and how the kernel-2 stride-2 layers are folded into dense products:
+//   fold_in   (convolution):   K index k = o*Cin + ci over the 8 children of a sibling group, tap = o
+//   expand_out (deconvolution): column n = o*Cout + co over the 8 children of a parent, tap = o
+struct WeightView {
+  int cin, cout, T;      // of the layer as the reference sees it
+  int transposed;
+  int fold_in, expand_out;
+  int co_base;           // first output column of this 256-column slice
+};
+
+__device__ __forceinline__ float weight_at(const float* __restrict__ w, const WeightView& v, int n,
+                                           int ci, int t) {
+  return v.transposed ? w[((long long)ci * v.cout + n) * v.T + t]
+                      : w[((long long)n * v.cin + ci) * v.T + t];
+}
+
+__device__ __forceinline__ void store_packed(uint16_t* __restrict__ packed, long long off, float v,
+                                             bool half) {
+  if (half) {
+    const __half h = __float2half(v);
+    packed[off] = *reinterpret_cast<const uint16_t*>(&h);
+  } else {
+    const __nv_bfloat16 b = __float2bfloat16(v);
+    packed[off] = *reinterpret_cast<const uint16_t*>(&b);
+  }
+}
+
+__global__ void pack_weights_kernel(const float* __restrict__ w, uint16_t* __restrict__ packed,
+                                    WeightView v, int ncols, int kdim, int npad, int nkb, bool half) {
+  // ncols = output columns of this slice, kdim = K extent (taps * Cin, or 8*Cin when folded)
   const long long total = (long long)nkb * npad * kBlockK;
-  const int KD = cin * T;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int kk = (int)(i % kBlockK);
     const int n = (int)((i / kBlockK) % npad);
     const int kb = (int)(i / ((long long)kBlockK * npad));
     const int k = kb * kBlockK + kk;
-    float v = 0.f;
-    if (n < cout && k < KD) {
-      const int t = k / cin, ci = k % cin;
-      v = w[(long long)n * KD + ci * T + t];
+    float val = 0.f;
+    if (n < ncols && k < kdim) {
+      const int col = v.co_base + n;
+      if (v.expand_out) {
+        // column = octant * Cout + channel; the only tap that reaches octant o is tap o
+        val = weight_at(w, v, col % v.cout, k, col / v.cout);
+      } else {
+        // K walks tap-major: k = t*Cin + ci (folded: the "tap" is the child's octant)
+        val = weight_at(w, v, col, k % v.cin, k / v.cin);
+      }
     }
     const long long off = (long long)kb * npad * 64 + (n >> 3) * 512 + (n & 7) * 64 +
                           (((kk >> 3) ^ (n & 7)) << 3) + (kk & 7);
-    packed[off] = __float2bfloat16(v);
+    store_packed(packed, off, val, half);
   }
 }
 
@@ -692,9 +755,9 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, __nv_bfloat16* 
 // (j = ((tx+ox)<<4)|((ty+oy)<<2)|(tz+oz)), zero elsewhere.  Same swizzled tile image as above.
 struct TapsArg { int count; signed char tap[27]; };
 
-__global__ void pack_weights_group_kernel(const float* __restrict__ w,
-                                          __nv_bfloat16* __restrict__ packed, int cin, int cout,
-                                          int T, TapsArg taps, int npad, int nkb) {
+__global__ void pack_weights_group_kernel(const float* __restrict__ w, uint16_t* __restrict__ packed,
+                                          int cin, int cout, int T, TapsArg taps, int npad, int nkb,
+                                          bool half) {
   const long long total = (long long)nkb * npad * kBlockK;
   const int KD = cin * T;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -716,15 +779,27 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w,
     }
     const long long off = (long long)kb * npad * 64 + (n >> 3) * 512 + (n & 7) * 64 +
                           (((kk >> 3) ^ (n & 7)) << 3) + (kk & 7);
-    packed[off] = __float2bfloat16(v);
+    store_packed(packed, off, v, half);
   }
 }
 
-struct TcShape { int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable, ntable_stride; size_t smem; };
+// What kind of layer a launch serves (the reference's OctreeConv / OctreeDeconv flags).
+struct LayerKind {
+  int stride;
+  bool transposed, nempty;
+};
 
-int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long long rows_hint = -1,
-             bool nempty = false) {
+struct TcShape {
+  int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable, ntable_stride;
+  int fold_in, expand_out;   // kernel 2, stride 2 as a dense product (see WeightView)
+  int cin_eff, cout_eff;     // channel counts the kernel sees: 8*Cin when folded, 8*Cout when expanded
+  size_t smem;
+};
+
+int tc_shape(int cin, int cout, const int ks[3], const LayerKind& kind, TcShape* s,
+             long long rows_hint = -1) {
   const TapList tl = taps_for_kernel(ks);
+  const int stride = kind.stride;
   if (tl.count < 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported kernel size %dx%dx%d",
                 ks[0], ks[1], ks[2]);
@@ -732,20 +807,31 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
     return fail(OCNN_ERR_INVALID, "tensor-core convolution: stride must be 1 or 2 (got %d)", stride);
   if (cin <= 0 || cin % 8 != 0)
     return fail(OCNN_ERR_UNSUPPORTED, "tensor-core convolution: Cin (%d) must be a multiple of 8", cin);
-  if (cout <= 0 || cout % 8 != 0 || (cout > 256 && cout % 256 != 0) || cout > 1024)
+  const bool k222s2 = ks[0] == 2 && ks[1] == 2 && ks[2] == 2 && stride == 2;
+  // kernel 2, stride 2: a sibling group's eight children are the whole neighbourhood.  On all nodes
+  // the convolution reads them as one contiguous row of 8*Cin channels; the deconvolution writes a
+  // parent's eight children as one row of 8*Cout channels (scattered through child on non-empty
+  // nodes).  Both are then plain dense products with no gather.
+  s->fold_in = (k222s2 && !kind.transposed && !kind.nempty) ? 1 : 0;
+  s->expand_out = (k222s2 && kind.transposed && (cout * 8 <= 256 || cout % 32 == 0) && cout * 8 <= 4096) ? 1 : 0;
+  s->cin_eff = s->fold_in ? 8 * cin : cin;
+  s->cout_eff = s->expand_out ? 8 * cout : cout;
+  cout = s->cout_eff;
+  if (cout <= 0 || cout % 8 != 0 || (cout > 256 && cout % 256 != 0) || cout > 4096)
     return fail(OCNN_ERR_UNSUPPORTED,
                 "tensor-core convolution: Cout (%d) must be a multiple of 8 up to 256, or a multiple "
-                "of 256 up to 1024", cout);
+                "of 256 up to 4096", cout);
   // more than 256 output channels: produced 256 at a time (one TMEM accumulator is 256 columns)
   s->slices = cout > 256 ? cout / 256 : 1;
   if (s->slices > 1) cout = 256;
   // sibling-group mode: stride 1, a real neighbourhood, few channels (power-of-two Cout so that
   // column -> channel is a mask)
-  // (not on non-empty nodes only: their tile rows are single nodes, not sibling groups)
-  s->group = (!nempty && stride == 1 && tl.count > 1 && cin <= 32 && cout <= 32 && (cout & (cout - 1)) == 0) ? 1 : 0;
-  s->T = s->group ? 64 : tl.count;
+  // (not on non-empty nodes only, nor for the deconvolution: their tile rows are single nodes)
+  const bool node_only = kind.nempty || kind.transposed;
+  s->group = (!node_only && stride == 1 && tl.count > 1 && cin <= 32 && cout <= 32 && (cout & (cout - 1)) == 0) ? 1 : 0;
+  s->T = s->group ? 64 : ((s->fold_in || s->expand_out) ? 1 : tl.count);
   s->npad = s->group ? 8 * cout : (cout + 15) / 16 * 16;
-  s->nkb = (cin * s->T + kBlockK - 1) / kBlockK;
+  s->nkb = (s->cin_eff * s->T + kBlockK - 1) / kBlockK;
   s->tmem_cols = 32;
   while (s->tmem_cols < s->npad) s->tmem_cols *= 2;
   // Ring depth.  Prefer a footprint that lets two CTAs share an SM (their set-up and epilogue
@@ -756,7 +842,7 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   s->gtable = (s->group && cin > 16) ? 1 : 0;
   // node mode keeps a [taps][128] index table; Cin not a multiple of 64 reads it per K-block with
   // lanes on different taps, which wants the padded stride
-  s->ntable_stride = (!s->group && cin % 64 != 0 && s->T > 1) ? kGroupTableStride : kTileM;
+  s->ntable_stride = (!s->group && s->cin_eff % 64 != 0 && s->T > 1) ? kGroupTableStride : kTileM;
   const size_t fixed = 1024 + (s->group ? (s->gtable ? 64 * kGroupTableStride * 4 : 0) : (size_t)s->T * s->ntable_stride * 4) +
                        (size_t)s->npad * 8 + 256;
   const size_t two_cta = 112 * 1024, one_cta = 200 * 1024;
@@ -793,47 +879,40 @@ int tc_shape(int cin, int cout, const int ks[3], int stride, TcShape* s, long lo
   return OCNN_OK;
 }
 
-}  // namespace
-}  // namespace ocnn
-
-extern "C" {
-
-static size_t packed_bytes_impl(int cin, int cout, const int kernel_size[3], int stride, bool nempty) {
-  ocnn::TcShape s;
-  if (kernel_size == nullptr || ocnn::tc_shape(cin, cout, kernel_size, stride, &s, -1, nempty) != OCNN_OK)
-    return 0;
+size_t packed_bytes_impl(int cin, int cout, const int kernel_size[3], const LayerKind& kind) {
+  TcShape s;
+  if (kernel_size == nullptr || tc_shape(cin, cout, kernel_size, kind, &s, -1) != OCNN_OK) return 0;
   return (size_t)s.slices * s.nkb * s.npad * 128;
 }
 
-size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride) {
-  return packed_bytes_impl(cin, cout, kernel_size, stride, false);
-}
-
-size_t ocnn_conv_packed_weight_bytes_nempty(int cin, int cout, const int kernel_size[3]) {
-  return packed_bytes_impl(cin, cout, kernel_size, 1, true);
-}
-
-static int pack_weights_impl(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
-                             int stride, bool nempty, void* stream) {
-  using namespace ocnn;
+int pack_weights_impl(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
+                      const LayerKind& kind, int dtype, void* stream) {
   OCNN_REQUIRE(w && packed && kernel_size, "ocnn_conv_pack_weights: null pointer");
+  OCNN_REQUIRE(dtype == OCNN_BF16 || dtype == OCNN_F16,
+               "ocnn_conv_pack_weights: the tensor-core kernel takes bf16 or fp16 (dtype %d given)", dtype);
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, stride, &s, -1, nempty)) return st;
+  if (int st = tc_shape(cin, cout, kernel_size, kind, &s, -1)) return st;
   const long long total = (long long)s.nkb * s.npad * kBlockK;
+  const bool half = dtype == OCNN_F16;
+  const TapList tl = taps_for_kernel(kernel_size);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (s.group) {
-    const TapList tl = taps_for_kernel(kernel_size);
     TapsArg ta;
     ta.count = tl.count;
     for (int i = 0; i < 27; ++i) ta.tap[i] = i < tl.count ? tl.tap[i] : -1;
-    pack_weights_group_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        w, static_cast<__nv_bfloat16*>(packed), cin, cout, tl.count, ta, s.npad, s.nkb);
+    pack_weights_group_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+        w, static_cast<uint16_t*>(packed), cin, cout, tl.count, ta, s.npad, s.nkb, half);
   } else {
-    // one packed image per slice of (at most) 256 output channels: rows of w are contiguous
-    const int cslice = s.slices > 1 ? 256 : cout;
+    // one packed image per slice of (at most) 256 output columns
+    WeightView v;
+    v.cin = cin; v.cout = cout; v.T = tl.count; v.transposed = kind.transposed ? 1 : 0;
+    v.fold_in = s.fold_in; v.expand_out = s.expand_out;
+    const int cslice = s.slices > 1 ? 256 : s.cout_eff;
+    const int kdim = s.cin_eff * s.T;
     for (int sl = 0; sl < s.slices; ++sl) {
-      pack_weights_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-          w + (size_t)sl * cslice * cin * s.T, static_cast<__nv_bfloat16*>(packed) + (size_t)sl * total,
-          cin, cslice, s.T, s.npad, s.nkb);
+      v.co_base = sl * cslice;
+      pack_weights_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+          w, static_cast<uint16_t*>(packed) + (size_t)sl * total, v, cslice, kdim, s.npad, s.nkb, half);
       if (sl > 0) note_launches(1);
     }
   }
@@ -841,78 +920,79 @@ static int pack_weights_impl(const float* w, void* packed, int cin, int cout, co
   return OCNN_OK;
 }
 
-int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
-                           int stride, void* stream) {
-  return pack_weights_impl(w, packed, cin, cout, kernel_size, stride, false, stream);
-}
-
-int ocnn_conv_pack_weights_nempty(const float* w, void* packed, int cin, int cout,
-                                  const int kernel_size[3], void* stream) {
-  return pack_weights_impl(w, packed, cin, cout, kernel_size, 1, true, stream);
-}
-
-static int conv_tc_impl(const void* x, const void* packed, void* y, const int32_t* neigh,
-                        const int32_t* child, const int32_t* ichild, int h_in, int h_out, int cin,
-                        int cout, const int kernel_size[3], int stride,
-                        const ocnn_conv_epilogue* ep, int32_t* status, void* stream) {
-  using namespace ocnn;
-  const bool nempty = ichild != nullptr;
-  OCNN_REQUIRE(kernel_size != nullptr, "ocnn_octree_conv_tc: null kernel size");
-  OCNN_REQUIRE(stride == 1 || stride == 2, "ocnn_octree_conv_tc: stride must be 1 or 2 (got %d)", stride);
+int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geometry* g, int cin,
+                 int cout, const int kernel_size[3], int dtype, const ocnn_conv_epilogue* ep,
+                 int32_t* status, void* stream, const char* who) {
+  OCNN_REQUIRE(kernel_size != nullptr, "%s: null kernel size", who);
+  OCNN_REQUIRE(dtype == OCNN_BF16 || dtype == OCNN_F16, "%s: bf16 or fp16 data only (dtype %d)", who, dtype);
+  const TapList tl = taps_for_kernel(kernel_size);
+  if (tl.count < 0)
+    return fail(OCNN_ERR_UNSUPPORTED, "%s: unsupported kernel size %dx%dx%d", who, kernel_size[0],
+                kernel_size[1], kernel_size[2]);
+  if (int rc = check_conv_geometry(g, tl, who)) return rc;
+  const int stride = g->stride;
+  const LayerKind kind{stride, g->transposed != 0, g->nempty != 0};
+  const int h_in = g->h_in, h_out = g->h_out;
   TcShape s;
-  if (int st = tc_shape(cin, cout, kernel_size, stride, &s, h_out, nempty)) return st;
-  OCNN_REQUIRE(h_in >= 0 && h_out >= 0, "ocnn_octree_conv_tc: negative height");
-  if (h_out == 0) return OCNN_OK;
-  const bool identity = s.T == 1 && stride == 1;
-  OCNN_REQUIRE(x && packed && y && status, "ocnn_octree_conv_tc: null pointer");
-  OCNN_REQUIRE(identity || neigh != nullptr, "ocnn_octree_conv_tc: neighbour table required");
-  OCNN_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)packed % 16 == 0),
-               "ocnn_octree_conv_tc: data and weight pointers must be 16-byte aligned");
-  if (stride == 2) {
-    OCNN_REQUIRE((long long)h_out * 8 == h_in,
-                 "ocnn_octree_conv_tc: stride 2 needs h_in == 8*h_out (got %d, %d)", h_in, h_out);
-  } else {
-    OCNN_REQUIRE(h_in == h_out, "ocnn_octree_conv_tc: stride 1 needs h_in == h_out (got %d, %d)",
-                 h_in, h_out);
+  // tile rows: output rows, except parents for the expanded kernel-2 deconvolution
+  {
+    TcShape probe;
+    if (int st = tc_shape(cin, cout, kernel_size, kind, &probe, -1)) return st;
+    if (int st = tc_shape(cin, cout, kernel_size, kind, &s, probe.expand_out ? h_in : h_out)) return st;
   }
+  if (h_out == 0 || (s.expand_out && h_in == 0)) return OCNN_OK;
+  const bool identity = s.T == 1 && (stride == 1 || s.fold_in || s.expand_out);
+  OCNN_REQUIRE(x && packed && y && status, "%s: null pointer", who);
+  OCNN_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)packed % 16 == 0),
+               "%s: data and weight pointers must be 16-byte aligned", who);
   if (ep && ep->residual_dev)
-    OCNN_REQUIRE((uintptr_t)ep->residual_dev % 16 == 0,
-                 "ocnn_octree_conv_tc: residual must be 16-byte aligned");
+    OCNN_REQUIRE((uintptr_t)ep->residual_dev % 16 == 0, "%s: residual must be 16-byte aligned", who);
+  const bool scatter = s.expand_out && g->nempty;
+  if (scatter) {
+    OCNN_REQUIRE(g->child_dev != nullptr, "%s: child array of the finer level required", who);
+    OCNN_REQUIRE(!(ep && ep->residual_dev), "%s: no residual on a scattered deconvolution", who);
+  }
   TcArgs a;
   a.x = static_cast<const __nv_bfloat16*>(x);
   a.wpacked = static_cast<const uint8_t*>(packed);
   a.y = static_cast<__nv_bfloat16*>(y);
-  a.neigh = neigh;
-  a.child = child;
-  a.ichild = ichild;
-  a.h_in = h_in; a.h_out = h_out; a.cin = cin; a.cout = cout; a.npad = s.npad; a.T = s.T;
-  a.stride = stride; a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
+  a.neigh = identity ? nullptr : g->neigh_dev;
+  const bool plain_gather = !identity && !s.fold_in && !s.expand_out;
+  a.child = (plain_gather && g->nempty && !(kind.transposed && stride == 2)) ? g->child_dev : nullptr;
+  a.ichild = (plain_gather && g->nempty && !(stride == 2 && !kind.transposed)) ? g->ichild_dev : nullptr;
+  a.up = (plain_gather && kind.transposed && stride == 2) ? 1 : 0;
+  a.f16 = dtype == OCNN_F16 ? 1 : 0;
+  a.expand_cout = s.expand_out ? cout : 0;
+  a.scatter_child = scatter ? g->child_dev : nullptr;
+  a.h_in = h_in; a.h_out = h_out; a.cin = s.cin_eff; a.npad = s.npad; a.T = s.T;
+  a.stride = (s.fold_in || s.expand_out) ? 1 : stride;
+  a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
   a.tmem_cols = s.tmem_cols;
   a.group = s.group;
-  a.rows = s.group ? h_out / 8 : h_out;
-  const int cslice = s.slices > 1 ? 256 : cout;
+  a.rows = s.group ? h_out / 8 : (s.expand_out ? h_in : h_out);
+  const int cslice = s.slices > 1 ? 256 : s.cout_eff;
   a.cout = cslice;
   a.row_elems = s.group ? 8 * cout : cslice;
-  a.y_stride = s.group ? 8 * cout : cout;
+  a.y_stride = s.group ? 8 * cout : s.cout_eff;
   a.rowsplit = (s.group && cin <= 16) ? 1 : 0;
   if (s.gtable) a.rowsplit = 3;
-  if (!s.group && cin % 64 == 0) a.rowsplit = 2;
+  if (!s.group && s.cin_eff % 64 == 0) a.rowsplit = 2;
   if (!s.group && s.ntable_stride == kGroupTableStride) a.rowsplit = 4;
   a.tile_rows = s.tile_rows;
   // 32-byte epilogue accesses: rows and channel slices on 32-byte boundaries
   a.wide = (a.row_elems % 16 == 0 && a.y_stride % 16 == 0 && (uintptr_t)y % 32 == 0 &&
             (!(ep && ep->residual_dev) || (uintptr_t)ep->residual_dev % 32 == 0)) ? 1 : 0;
   if (s.group)
-    OCNN_REQUIRE(h_out % 8 == 0, "ocnn_octree_conv_tc: an octree level holds whole sibling groups "
-                 "(got %d nodes)", h_out);
+    OCNN_REQUIRE(h_out % 8 == 0, "%s: an octree level holds whole sibling groups (got %d nodes)", who, h_out);
   a.scale = ep ? ep->scale_dev : nullptr;
   a.bias = ep ? ep->bias_dev : nullptr;
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
   a.relu = ep ? ep->relu : 0;
   a.status = status;
-  const TapList tl = taps_for_kernel(kernel_size);
   for (int i = 0; i < 27; ++i) {
-    const int tap = i < tl.count ? tl.tap[i] : 0;
+    int tap = i < tl.count ? tl.tap[i] : 0;
+    // a stride-1 deconvolution gathers from the mirrored offsets
+    if (kind.transposed && stride == 1) tap = 26 - tap;
     a.tap[i] = (signed char)(((tap / 9) << 4) | (((tap / 3) % 3) << 2) | (tap % 3));
   }
   // raising the dynamic shared memory limit is per function and per device
@@ -920,7 +1000,7 @@ static int conv_tc_impl(const void* x, const void* packed, void* y, const int32_
   int device = 0;
   OCNN_CUDA_OK(cudaGetDevice(&device));
   void (*kernel)(const TcArgs) = conv_tc_kernel<0>;
-  switch (cin >> 3) {
+  switch (a.cin >> 3) {
     case 1: kernel = conv_tc_kernel<1>; break;
     case 2: kernel = conv_tc_kernel<2>; break;
     case 4: kernel = conv_tc_kernel<4>; break;
@@ -934,29 +1014,68 @@ static int conv_tc_impl(const void* x, const void* packed, void* y, const int32_
     std::lock_guard<std::mutex> lock(attr_once.mutex);
     const bool known = device >= 0 && device < 64;
     if (!known || !attr_once.done[device]) {
-    void (*all[])(const TcArgs) = {conv_tc_kernel<0>, conv_tc_kernel<1>, conv_tc_kernel<2>,
-                                   conv_tc_kernel<4>, conv_tc_kernel<8>, conv_tc_kernel<16>,
-                                   conv_tc_kernel<32>, conv_tc_kernel<64>};
-    for (auto k : all)
-      OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    if (known) attr_once.done[device] = true;
+      void (*all[])(const TcArgs) = {conv_tc_kernel<0>, conv_tc_kernel<1>, conv_tc_kernel<2>,
+                                     conv_tc_kernel<4>, conv_tc_kernel<8>, conv_tc_kernel<16>,
+                                     conv_tc_kernel<32>, conv_tc_kernel<64>};
+      for (auto k : all)
+        OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+      if (known) attr_once.done[device] = true;
     }
   }
   OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
-               "ocnn_octree_conv_tc: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses",
+               "%s: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses", who,
                (long long)h_in * cin * 2);
-  a.wpacked = static_cast<const uint8_t*>(packed);
   OCNN_CUDA_OK(launch_chained(kernel, dim3(ceil_div(a.rows, a.tile_rows), s.slices), dim3(kThreads), s.smem,
                               static_cast<cudaStream_t>(stream), a));
   OCNN_LAUNCH_OK("conv_tc_kernel");
   return OCNN_OK;
 }
 
+}  // namespace
+}  // namespace ocnn
+
+extern "C" {
+
+size_t ocnn_conv_packed_weight_bytes(int cin, int cout, const int kernel_size[3], int stride) {
+  return ocnn::packed_bytes_impl(cin, cout, kernel_size, ocnn::LayerKind{stride, false, false});
+}
+
+size_t ocnn_conv_packed_weight_bytes_nempty(int cin, int cout, const int kernel_size[3]) {
+  return ocnn::packed_bytes_impl(cin, cout, kernel_size, ocnn::LayerKind{1, false, true});
+}
+
+size_t ocnn_conv_packed_weight_bytes_general(int cin, int cout, const int kernel_size[3], int stride,
+                                             int transposed, int nempty) {
+  return ocnn::packed_bytes_impl(cin, cout, kernel_size,
+                                 ocnn::LayerKind{stride, transposed != 0, nempty != 0});
+}
+
+int ocnn_conv_pack_weights(const float* w, void* packed, int cin, int cout, const int kernel_size[3],
+                           int stride, void* stream) {
+  return ocnn::pack_weights_impl(w, packed, cin, cout, kernel_size, ocnn::LayerKind{stride, false, false},
+                                 OCNN_BF16, stream);
+}
+
+int ocnn_conv_pack_weights_nempty(const float* w, void* packed, int cin, int cout,
+                                  const int kernel_size[3], void* stream) {
+  return ocnn::pack_weights_impl(w, packed, cin, cout, kernel_size, ocnn::LayerKind{1, false, true},
+                                 OCNN_BF16, stream);
+}
+
+int ocnn_conv_pack_weights_general(const float* w, void* packed, int cin, int cout,
+                                   const int kernel_size[3], int stride, int transposed, int nempty,
+                                   int dtype, void* stream) {
+  return ocnn::pack_weights_impl(w, packed, cin, cout, kernel_size,
+                                 ocnn::LayerKind{stride, transposed != 0, nempty != 0}, dtype, stream);
+}
+
 int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_t* neigh, int h_in,
                         int h_out, int cin, int cout, const int kernel_size[3], int stride,
                         const ocnn_conv_epilogue* ep, int32_t* status, void* stream) {
-  return conv_tc_impl(x, packed, y, neigh, nullptr, nullptr, h_in, h_out, cin, cout, kernel_size,
-                      stride, ep, status, stream);
+  ocnn_conv_geometry g = {};
+  g.stride = stride; g.h_in = h_in; g.h_out = h_out; g.neigh_dev = neigh;
+  return ocnn::conv_tc_impl(x, packed, y, &g, cin, cout, kernel_size, OCNN_BF16, ep, status, stream,
+                            "ocnn_octree_conv_tc");
 }
 
 int ocnn_octree_conv_tc_nempty(const void* x, const void* packed, void* y, const int32_t* neigh,
@@ -966,8 +1085,19 @@ int ocnn_octree_conv_tc_nempty(const void* x, const void* packed, void* y, const
   using namespace ocnn;
   OCNN_REQUIRE(child != nullptr && ichild != nullptr,
                "ocnn_octree_conv_tc_nempty: child and ichild required");
-  return conv_tc_impl(x, packed, y, neigh, child, ichild, nne, nne, cin, cout, kernel_size, 1, ep,
-                      status, stream);
+  ocnn_conv_geometry g = {};
+  g.stride = 1; g.nempty = 1; g.h_in = nne; g.h_out = nne;
+  g.neigh_dev = neigh; g.child_dev = child; g.ichild_dev = ichild;
+  return conv_tc_impl(x, packed, y, &g, cin, cout, kernel_size, OCNN_BF16, ep, status, stream,
+                      "ocnn_octree_conv_tc_nempty");
+}
+
+int ocnn_octree_conv_tc_general(const void* x, const void* packed, void* y,
+                                const ocnn_conv_geometry* geometry, int cin, int cout,
+                                const int kernel_size[3], int dtype, const ocnn_conv_epilogue* ep,
+                                int32_t* status, void* stream) {
+  return ocnn::conv_tc_impl(x, packed, y, geometry, cin, cout, kernel_size, dtype, ep, status, stream,
+                            "ocnn_octree_conv_tc_general");
 }
 
 }  // extern "C"

@@ -16,23 +16,24 @@ __global__ void feature_to_nm_kernel(const float* __restrict__ f, T* __restrict_
     const long long h = i / c_pad;
     const int c = (int)(i % c_pad);
     const float v = c < C ? f[(long long)c * nnum + h] : 0.f;
-    if (sizeof(T) == 2) out[i] = (T)__float2bfloat16(v); else out[i] = (T)v;
+    out[i] = (T)v;
   }
 }
 
-// c_pad == 8, bf16: one thread per node — up to 8 coalesced plane reads, one 16-byte row store.
+// c_pad == 8, bf16 or fp16: one thread per node — up to 8 coalesced plane reads, one 16-byte row
+// store.
 __global__ void __launch_bounds__(256) feature_to_nm_bf16x8_kernel(const float* __restrict__ f,
                                                                    uint4* __restrict__ out, int C,
-                                                                   long long nnum) {
+                                                                   long long nnum, bool half) {
   for (long long h = blockIdx.x * (long long)blockDim.x + threadIdx.x; h < nnum;
        h += (long long)gridDim.x * blockDim.x) {
     float v[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) v[c] = c < C ? f[(long long)c * nnum + h] : 0.f;
     uint4 row;
-    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&row);
+    uint32_t* p = reinterpret_cast<uint32_t*>(&row);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    for (int k = 0; k < 4; ++k) p[k] = pack2(v[2 * k], v[2 * k + 1], half);
     out[h] = row;
   }
 }
@@ -46,13 +47,17 @@ extern "C" int ocnn_feature_to_node_major(const float* feature, void* out, int c
   OCNN_REQUIRE(feature && out, "ocnn_feature_to_node_major: null pointer");
   OCNN_REQUIRE(channels > 0 && c_pad >= channels && nnum >= 0,
                "ocnn_feature_to_node_major: bad shape (C=%d, c_pad=%d, nnum=%d)", channels, c_pad, nnum);
-  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "ocnn_feature_to_node_major: unknown dtype");
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16 || dtype == OCNN_F16,
+               "ocnn_feature_to_node_major: unknown dtype");
   if (nnum == 0) return OCNN_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = (long long)nnum * c_pad;
-  if (dtype == OCNN_BF16 && c_pad == 8 && (uintptr_t)out % 16 == 0)
+  if (dtype != OCNN_F32 && c_pad == 8 && (uintptr_t)out % 16 == 0)
     feature_to_nm_bf16x8_kernel<<<grid_for(nnum, 256), 256, 0, st>>>(feature, static_cast<uint4*>(out),
-                                                                    channels, nnum);
+                                                                    channels, nnum, dtype == OCNN_F16);
+  else if (dtype == OCNN_F16)
+    feature_to_nm_kernel<__half><<<grid_for(total, 256), 256, 0, st>>>(
+        feature, static_cast<__half*>(out), channels, c_pad, nnum);
   else if (dtype == OCNN_BF16)
     feature_to_nm_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>(
         feature, static_cast<__nv_bfloat16*>(out), channels, c_pad, nnum);

@@ -4,6 +4,8 @@
 // ([H,C], fp32 or bf16) is what the tensor-core convolution consumes.  Both layouts are served by
 // the same entry points.  All kernels are grid-stride over 16-byte vectors where the shapes allow,
 // with grids sized in whole waves over the SMs.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ocnn {
@@ -192,6 +194,7 @@ __global__ void tile_kernel(const T* __restrict__ y, T* __restrict__ out,
 // ---- max pool ------------------------------------------------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 
 // channel-major: one thread per (channel, group): 8 consecutive values = two 16-byte loads (fp32).
 __global__ void max_pool_cm_f32_kernel(const float* __restrict__ btm, float* __restrict__ top,
@@ -258,9 +261,8 @@ __global__ void max_pool_nm_kernel(const T* __restrict__ btm, T* __restrict__ to
 // (plus two for the argmax rows when the caller wants them).
 // PADDED: the output has one row per node of the parent level; child[p] gives the sibling group
 // of node p (or < 0: the row is zero) — max pool and the pad that follows it in one pass.
-struct Bf16x8 { __nv_bfloat162 v[4]; };
-
-template <bool PADDED>
+// HALF: the 16-bit elements are fp16 instead of bf16.
+template <bool PADDED, bool HALF>
 __global__ void __launch_bounds__(256) max_pool_nm_bf16x8_kernel(
     const uint4* __restrict__ btm, uint4* __restrict__ top, int* __restrict__ mask,
     const int* __restrict__ child, int chunks, long long total) {
@@ -285,29 +287,29 @@ __global__ void __launch_bounds__(256) max_pool_nm_bf16x8_kernel(
     float best[8];
     int at[8];
     {
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&raw[0]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
+        const float2 f = unpack2(p[k], HALF);
         best[2 * k] = f.x; best[2 * k + 1] = f.y;
         at[2 * k] = 0; at[2 * k + 1] = 0;
       }
     }
 #pragma unroll
     for (int j = 1; j < 8; ++j) {
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&raw[j]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
+        const float2 f = unpack2(p[k], HALF);
         if (f.x > best[2 * k]) { best[2 * k] = f.x; at[2 * k] = j; }
         if (f.y > best[2 * k + 1]) { best[2 * k + 1] = f.y; at[2 * k + 1] = j; }
       }
     }
-    // the winner's own bits (the values are exact bf16, so the round trip through fp32 is too)
+    // the winner's own bits (the values are exact 16-bit floats, so the round trip through fp32 is too)
     uint4 out;
-    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&out);
+    uint32_t* op = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) op[k] = __floats2bfloat162_rn(best[2 * k], best[2 * k + 1]);
+    for (int k = 0; k < 4; ++k) op[k] = pack2(best[2 * k], best[2 * k + 1], HALF);
     top[i] = out;
     if (mask != nullptr) {
       const int base = (int)(8 * g);
@@ -324,6 +326,8 @@ template <>
 float fill_value<float>(float val) { return val; }
 template <>
 __nv_bfloat16 fill_value<__nv_bfloat16>(float val) { return __float2bfloat16(val); }
+template <>
+__half fill_value<__half>(float val) { return __float2half(val); }
 
 template <typename T>
 int pad_impl(const void* x, void* y, const int* child, int C, int Hx, int Hy, float val,
@@ -398,7 +402,8 @@ int pool_impl(const void* btm, void* top, int* mask, int C, int top_h, int layou
   } else if (sizeof(T) == 2 && C % 8 == 0 && (uintptr_t)btm % 16 == 0 && (uintptr_t)top % 16 == 0 &&
              (uintptr_t)mask % 16 == 0) {
     const long long vec_total = total / 8;
-    OCNN_CUDA_OK(launch_chained(max_pool_nm_bf16x8_kernel<false>, dim3(grid_for(vec_total, 256, 8)),
+    constexpr bool kHalf = std::is_same<T, __half>::value;
+    OCNN_CUDA_OK(launch_chained(max_pool_nm_bf16x8_kernel<false, kHalf>, dim3(grid_for(vec_total, 256, 8)),
                                 dim3(256), 0, st, (const uint4*)btm, (uint4*)top, mask,
                                 (const int*)nullptr, C / 8, vec_total));
   } else {
@@ -413,7 +418,8 @@ int check_common(const char* op, const void* a, const void* b, const void* c, in
                  int layout) {
   OCNN_REQUIRE(a != nullptr && b != nullptr && c != nullptr, "%s: null pointer", op);
   OCNN_REQUIRE(C > 0, "%s: channels must be positive (got %d)", op, C);
-  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16, "%s: unknown dtype %d", op, dtype);
+  OCNN_REQUIRE(dtype == OCNN_F32 || dtype == OCNN_BF16 || dtype == OCNN_F16, "%s: unknown dtype %d", op,
+               dtype);
   OCNN_REQUIRE(layout == OCNN_CHANNEL_MAJOR || layout == OCNN_NODE_MAJOR, "%s: unknown layout %d",
                op, layout);
   return OCNN_OK;
@@ -431,8 +437,9 @@ int ocnn_octree_pad(const void* x, void* y, const int32_t* child, int C, int hx,
   if (int s = check_common("ocnn_octree_pad", hx > 0 ? x : y, y, child, C, dtype, layout)) return s;
   OCNN_REQUIRE(hx >= 0 && hy > 0 && hx <= hy, "ocnn_octree_pad: need 0 <= hx (%d) <= hy (%d)", hx, hy);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == OCNN_F32 ? pad_impl<float>(x, y, child, C, hx, hy, val, layout, st)
-                           : pad_impl<__nv_bfloat16>(x, y, child, C, hx, hy, val, layout, st);
+  if (dtype == OCNN_F32) return pad_impl<float>(x, y, child, C, hx, hy, val, layout, st);
+  if (dtype == OCNN_F16) return pad_impl<__half>(x, y, child, C, hx, hy, val, layout, st);
+  return pad_impl<__nv_bfloat16>(x, y, child, C, hx, hy, val, layout, st);
 }
 
 int ocnn_octree_max_pool_pad(const void* btm, void* top, const int32_t* child, int C, int btm_h,
@@ -444,13 +451,15 @@ int ocnn_octree_max_pool_pad(const void* btm, void* top, const int32_t* child, i
   OCNN_REQUIRE(btm_h >= 0 && btm_h % 8 == 0 && top_h >= btm_h / 8,
                "ocnn_octree_max_pool_pad: need btm_h (%d) = 8 * groups and top_h (%d) >= groups",
                btm_h, top_h);
-  OCNN_REQUIRE(dtype == OCNN_BF16 && layout == OCNN_NODE_MAJOR && C % 8 == 0,
-               "ocnn_octree_max_pool_pad: bf16 node-major data with C %% 8 == 0 only (C = %d); use "
-               "ocnn_octree_max_pool + ocnn_octree_pad otherwise", C);
+  OCNN_REQUIRE(dtype != OCNN_F32 && layout == OCNN_NODE_MAJOR && C % 8 == 0,
+               "ocnn_octree_max_pool_pad: bf16 / fp16 node-major data with C %% 8 == 0 only (C = %d); "
+               "use ocnn_octree_max_pool + ocnn_octree_pad otherwise", C);
   OCNN_REQUIRE((uintptr_t)btm % 16 == 0 && (uintptr_t)top % 16 == 0,
                "ocnn_octree_max_pool_pad: data pointers must be 16-byte aligned");
   const long long total = (long long)top_h * (C / 8);
-  OCNN_CUDA_OK(launch_chained(max_pool_nm_bf16x8_kernel<true>, dim3(grid_for(total, 256, 8)), dim3(256),
+  auto kernel = dtype == OCNN_F16 ? max_pool_nm_bf16x8_kernel<true, true>
+                                  : max_pool_nm_bf16x8_kernel<true, false>;
+  OCNN_CUDA_OK(launch_chained(kernel, dim3(grid_for(total, 256, 8)), dim3(256),
                               0, static_cast<cudaStream_t>(stream), (const uint4*)btm, (uint4*)top,
                               (int*)nullptr, (const int*)child, C / 8, total));
   OCNN_LAUNCH_OK("octree_max_pool_pad");
@@ -464,6 +473,7 @@ int ocnn_octree_depad(const void* y, void* x, const int32_t* child, int C, int h
   if (int s = check_common("ocnn_octree_depad", y, x, child, C, dtype, layout)) return s;
   OCNN_REQUIRE(hx > 0 && hx <= hy, "ocnn_octree_depad: need 0 < hx (%d) <= hy (%d)", hx, hy);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // a depad only moves elements: both 16-bit types take the same kernels
   return dtype == OCNN_F32 ? depad_impl<float>(y, x, child, C, hx, hy, layout, st)
                            : depad_impl<__nv_bfloat16>(y, x, child, C, hx, hy, layout, st);
 }
@@ -500,8 +510,9 @@ int ocnn_octree_max_pool(const void* btm, void* top, int32_t* mask, int C, int t
   if (int s = check_common("ocnn_octree_max_pool", btm, top, mask, C, dtype, layout)) return s;
   OCNN_REQUIRE(top_h > 0, "ocnn_octree_max_pool: negative height");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == OCNN_F32 ? pool_impl<float>(btm, top, mask, C, top_h, layout, st)
-                           : pool_impl<__nv_bfloat16>(btm, top, mask, C, top_h, layout, st);
+  if (dtype == OCNN_F32) return pool_impl<float>(btm, top, mask, C, top_h, layout, st);
+  if (dtype == OCNN_F16) return pool_impl<__half>(btm, top, mask, C, top_h, layout, st);
+  return pool_impl<__nv_bfloat16>(btm, top, mask, C, top_h, layout, st);
 }
 
 }  // extern "C"

@@ -1,4 +1,5 @@
-"""octree2col as a function and module (pytorch/ocnn/octree2col.py:7-81 of the reference)."""
+"""octree2col / col2octree as functions and modules (pytorch/ocnn/octree2col.py:7-81 of the
+reference)."""
 import torch
 from torch import nn as _nn
 
@@ -9,6 +10,13 @@ def octree2col(data_in, octree, depth, kernel_size, stride, nempty=False):
   """[1,C,H,1] float32 -> [C, K, H_out]: the neighbourhood of every node, K taps per channel."""
   with torch.no_grad():
     return nn.octree2col(data_in, octree, depth, list(kernel_size), stride, nempty)
+
+
+def col2octree(data_in, octree, depth, kernel_size, stride, nempty=False):
+  """The transpose of octree2col: [C, K, H_col] float32 -> [1,C,H,1], every column entry added to
+  the node it would have been gathered from."""
+  with torch.no_grad():
+    return nn.col2octree(data_in, octree, depth, list(kernel_size), stride, nempty)
 
 
 class Octree2Col(_nn.Module):
@@ -25,3 +33,8 @@ class Octree2Col(_nn.Module):
   def extra_repr(self) -> str:
     return 'depth={}, kernel_size={}, stride={}, nempty={}'.format(
         self.depth, self.kernel_size, self.stride, self.nempty)
+
+
+class Col2Octree(Octree2Col):
+  def forward(self, data_in, octree):
+    return col2octree(data_in, octree, self.depth, self.kernel_size, self.stride, self.nempty)

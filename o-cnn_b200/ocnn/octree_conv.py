@@ -1,15 +1,31 @@
-"""OctreeConv (pytorch/ocnn/octree_conv.py:8-127 of the reference), forward only.
+"""OctreeConv / OctreeDeconv (pytorch/ocnn/octree_conv.py:8-158 of the reference), forward only.
 
-`OctreeConv` holds its weights exactly as the reference module does — float32
-[channel_out, channel_in * K] with column index cin*K + tap — so a reference state_dict loads
-unchanged.  The convolution itself is one implicit-GEMM CUDA kernel; no column buffer is built.
+The modules hold their weights exactly as the reference's do — float32 [channel_out,
+channel_in * K] for the convolution, [channel_in, channel_out * K] for the deconvolution, column
+index c * K + tap — so a reference state_dict loads unchanged.  Every variant (stride 1 or 2, all
+nodes or non-empty nodes only) is one implicit-GEMM CUDA kernel; no column buffer is built.
+
+Data in bfloat16 / float16 with torch's channels_last memory format runs on the tensor-core
+kernel (weights are packed once per module and dtype and cached); float32 data, or the
+reference's contiguous [1,C,H,1] layout, runs on the CUDA-core kernel.
 """
 import torch
 from torch import nn as _nn
 
 from . import nn
-from .octree_pad import octree_pad
-from .octree2col import octree2col
+from .octree_pad import octree_pad, octree_depad
+from .octree2col import octree2col, col2octree
+
+_STATUS = {}
+
+
+def tc_status(device):
+  """The int32 status word the tensor-core kernels write on a bounded wait that ran out (one per
+  device; 0 = no kernel ever gave up)."""
+  key = torch.device(device)
+  if key not in _STATUS:
+    _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=key)
+  return _STATUS[key]
 
 
 def resize_with_last_val(list_in, num=3):
@@ -20,10 +36,22 @@ def resize_with_last_val(list_in, num=3):
   return out
 
 
+def _tensor_core_ready(data):
+  return (data.is_cuda and data.dtype in (torch.bfloat16, torch.float16) and data.dim() == 4 and
+          data.shape[1] % 8 == 0 and data.is_contiguous(memory_format=torch.channels_last))
+
+
 def octree_conv(data_in, weights, octree, depth, channel_out, kernel_size, stride=1, nempty=False):
   with torch.no_grad():
     return nn.octree_conv(data_in, weights, octree, depth, channel_out,
                           resize_with_last_val(list(kernel_size)), stride, nempty)
+
+
+def octree_deconv(data_in, weights, octree, depth, channel_out, kernel_size, stride=1,
+                  nempty=False):
+  with torch.no_grad():
+    return nn.octree_deconv(data_in, weights, octree, depth, channel_out,
+                            resize_with_last_val(list(kernel_size)), stride, nempty)
 
 
 class OctreeConvBase(_nn.Module):
@@ -36,9 +64,40 @@ class OctreeConvBase(_nn.Module):
     self.stride = stride
     self.nempty = nempty
     self.kdim = self.kernel_size[0] * self.kernel_size[1] * self.kernel_size[2]
-    self.cdim = channel_in * self.kdim
-    self.weights = _nn.Parameter(torch.Tensor(channel_out, self.cdim))
+    self.conv_in = channel_in if self.is_conv_layer() else channel_out
+    self.conv_out = channel_out if self.is_conv_layer() else channel_in
+    self.cdim = self.conv_in * self.kdim
+    self.weights = _nn.Parameter(torch.Tensor(self.conv_out, self.cdim))
     _nn.init.xavier_uniform_(self.weights)
+    self._packed = {}
+
+  def is_conv_layer(self):
+    raise NotImplementedError
+
+  def _run(self, data, octree, fused=None):
+    """One kernel for the layer; `fused` = (scale, bias, residual, relu) applied in its epilogue."""
+    scale, bias, residual, relu = fused if fused is not None else (None, None, None, False)
+    transposed = not self.is_conv_layer()
+    w = self.weights.detach()
+    with torch.no_grad():
+      if _tensor_core_ready(data) and self.channel_out % 8 == 0:
+        half = data.dtype == torch.float16
+        key = (w.data_ptr(), w._version, half)
+        if key not in self._packed:
+          self._packed.clear()
+          try:
+            self._packed[key] = nn.conv_pack_weights_general(
+                w, self.channel_in, self.channel_out, self.kernel_size, self.stride, transposed,
+                self.nempty, half)
+          except RuntimeError:
+            self._packed[key] = None          # a shape the tensor-core kernel does not take
+        packed = self._packed[key]
+        if packed is not None:
+          return nn.octree_conv_tc_general(
+              data, packed, octree, self.depth, self.channel_out, self.kernel_size, self.stride,
+              self.nempty, transposed, scale, bias, residual, relu, tc_status(data.device))
+      return nn.octree_conv_general(data, w, octree, self.depth, self.channel_out, self.kernel_size,
+                                    self.stride, self.nempty, transposed, scale, bias, residual, relu)
 
   def extra_repr(self) -> str:
     return ('depth={}, channel_in={}, channel_out={}, kernel_size={}, stride={}, '
@@ -47,18 +106,34 @@ class OctreeConvBase(_nn.Module):
 
 
 class OctreeConv(OctreeConvBase):
+  def is_conv_layer(self):
+    return True
+
   def forward(self, data, octree):
     assert data.size(1) == self.channel_in
-    conv = octree_conv(data, self.weights, octree, self.depth, self.channel_out,
-                       self.kernel_size, self.stride, self.nempty)
+    conv = self._run(data, octree)
     if self.stride == 2 and not self.nempty:
       conv = octree_pad(conv, octree, self.depth - 1)
     return conv
 
 
+class OctreeDeconv(OctreeConvBase):
+  def is_conv_layer(self):
+    return False
+
+  def forward(self, data, octree):
+    assert data.size(1) == self.channel_in
+    if self.stride == 2 and not self.nempty:
+      data = octree_depad(data, octree, self.depth)
+    return self._run(data, octree)
+
+
 class OctreeConvFast(OctreeConvBase):
   """octree2col followed by a dense matrix product — the reference's memory-hungry variant, kept
   because the reference's own test compares OctreeConv against it."""
+
+  def is_conv_layer(self):
+    return True
 
   def forward(self, data, octree):
     col = octree2col(data, octree, self.depth, self.kernel_size, self.stride, False)
@@ -68,3 +143,19 @@ class OctreeConvFast(OctreeConvBase):
     if self.stride == 2:
       conv = octree_pad(conv, octree, self.depth - 1)
     return conv
+
+
+class OctreeDeconvFast(OctreeConvBase):
+  """Dense product followed by col2octree (the scatter-add transpose of octree2col)."""
+
+  def is_conv_layer(self):
+    return False
+
+  def forward(self, data, octree):
+    if self.stride == 2:
+      data = octree_depad(data, octree, self.depth)
+    data = data.contiguous().view(self.channel_in, -1)
+    col = torch.mm(self.weights.detach().t(), data)
+    col = col.view(self.channel_out, self.kdim, -1)
+    depth = self.depth + 1 if self.stride == 2 else self.depth
+    return col2octree(col, octree, depth, self.kernel_size, self.stride, False)

@@ -42,7 +42,13 @@ def _conv_param(rng, cin, cout, kdim, name, bn=True, relu=True):
 def resnet_params(depth=6, channel_in=3, nout=40, resblk_num=2, seed=0, min_depth=2):
   """ResNet O-CNN: conv3x3x3 at `depth`, then per level `resblk_num` bottleneck blocks
   (1x1 -> 3x3x3 at Cout/4 -> 1x1, skip, ReLU; modules.py:110-139) and a max-pool, channels
-  2^max(11-d, 2) per level d (resnet.py:9) down to `min_depth`, global average pool, FC."""
+  2^max(11-d, 2) per level d (resnet.py:9) down to `min_depth`, global average pool, FC.
+
+  With the default min_depth = 2 this is the network the benchmark configuration names (blocks
+  on depths 6..2, channels 32-64-128-256-512, the average taken over the 64 nodes of depth 2).  It
+  is one level deeper than the reference's own ResNet class, which stops its blocks at depth 3
+  (256 channels), max-pools once more and averages depth 2 (resnet.py:12-20); that network is
+  `ocnn.ResNet`, checked in the module-route tests."""
   rng = np.random.default_rng(seed)
   ch = lambda d: 2 ** max(11 - d, 2)
   net = {'kind': 'resnet', 'depth': depth, 'min_depth': min_depth, 'channel_in': channel_in,
@@ -141,10 +147,22 @@ class CpuNet:
   OctreeView-like reader (`view`).  `ops` is oracle.oracle or an adapter around the compiled
   reference; the caller chooses."""
 
-  def __init__(self, net, ops, view):
+  def __init__(self, net, ops, view, round_fn=None):
+    """round_fn (e.g. rounding to bf16) is applied to every convolution's input; with `trace` set
+    to a list, every convolution appends (name, depth, input as used, output before the skip)."""
     self.net, self.ops, self.view = net, ops, view
+    self.round = round_fn
+    self.trace = None
 
   def _conv(self, x, p, octree, d):
+    if self.round is not None:
+      x = self.round(x)
+    y = self._conv_raw(x, p, octree, d)
+    if self.trace is not None:
+      self.trace.append((p['name'], d, x, y))
+    return y
+
+  def _conv_raw(self, x, p, octree, d):
     if p['ks'] == [1, 1, 1]:
       y = p['w'] @ x                      # torch Conv1d(kernel 1) in the reference, modules.py:71-83
     else:
@@ -413,3 +431,79 @@ class GpuNet:
       else:                                                     # node-major [B*per, C]
         pooled = x.permute(0, 2, 1, 3).reshape(-1, per, C).float().mean(dim=1)
       return pooled @ self.fc_w.t() + self.fc_b
+
+
+# ---- the same networks assembled from the `ocnn` modules (the route a reference user takes) ---------
+def module_resnet(net, device='cuda'):
+  """A torch.nn.Module built from ocnn.OctreeConvBnRelu / OctreeResBlock / OctreeMaxPool that computes
+  the ResNet described by `net` (resnet_params), with the weights and BatchNorm statistics of that
+  description loaded: forward(octree, data) -> logits.  Input channels are padded to a multiple of 8
+  when `data` is 16-bit channels_last."""
+  import torch
+  import ocnn
+
+  def load_bn(bn, p):
+    # scale / bias of the description are a folded BatchNorm: store them as weight / bias of a
+    # BatchNorm with zero mean and unit variance (eps compensated)
+    with torch.no_grad():
+      bn.weight.copy_(torch.from_numpy(p['scale'] * np.sqrt(1.0 + bn.eps).astype(np.float32)))
+      bn.bias.copy_(torch.from_numpy(p['bias']))
+      bn.running_mean.zero_()
+      bn.running_var.fill_(1.0)
+
+  class Net(torch.nn.Module):
+    def __init__(self, cin_pad):
+      super().__init__()
+      c1 = net['conv1']
+      self.cin_pad = cin_pad
+      self.conv1 = ocnn.OctreeConvBnRelu(net['depth'], cin_pad, c1['cout'])
+      w = np.zeros((c1['cout'], cin_pad, 27), np.float32)
+      w[:, :c1['cin']] = c1['w'].reshape(c1['cout'], c1['cin'], 27)
+      with torch.no_grad():
+        self.conv1.conv.weights.copy_(torch.from_numpy(w.reshape(c1['cout'], -1)))
+      load_bn(self.conv1.bn, c1)
+      self.levels = torch.nn.ModuleList()
+      self.pools = torch.nn.ModuleDict()
+      for lv in net['levels']:
+        blocks = torch.nn.ModuleList()
+        for blk in lv['blocks']:
+          m = ocnn.OctreeResBlock(lv['depth'], blk['a']['cin'], blk['b']['cout'])
+          with torch.no_grad():
+            m.conv1x1a.conv1x1.conv1x1.weight.copy_(torch.from_numpy(blk['a']['w'])[:, :, None])
+            m.conv3x3.conv.weights.copy_(torch.from_numpy(blk['conv']['w']))
+            m.conv1x1b.conv1x1.conv1x1.weight.copy_(torch.from_numpy(blk['b']['w'])[:, :, None])
+            if blk['c'] is not None:
+              m.conv1x1c.conv1x1.conv1x1.weight.copy_(torch.from_numpy(blk['c']['w'])[:, :, None])
+          load_bn(m.conv1x1a.bn, blk['a'])
+          load_bn(m.conv3x3.bn, blk['conv'])
+          load_bn(m.conv1x1b.bn, blk['b'])
+          if blk['c'] is not None:
+            load_bn(m.conv1x1c.bn, blk['c'])
+          blocks.append(m)
+        self.levels.append(blocks)
+        if lv['pool']:
+          self.pools[str(lv['depth'])] = ocnn.OctreeMaxPool(lv['depth'])
+      self.out_depth = net['min_depth'] if not net['levels'][-1]['pool'] else net['min_depth'] - 1
+      self.fc = torch.nn.Linear(net['fc_w'].shape[1], net['fc_w'].shape[0])
+      with torch.no_grad():
+        self.fc.weight.copy_(torch.from_numpy(net['fc_w']))
+        self.fc.bias.copy_(torch.from_numpy(net['fc_b']))
+
+    def forward(self, octree, data):
+      x = self.conv1(data, octree)
+      for lv, blocks in zip(net['levels'], self.levels):
+        for m in blocks:
+          x = m(x, octree)
+        if lv['pool']:
+          x = self.pools[str(lv['depth'])](x, octree)
+      per = 8 ** self.out_depth
+      pooled = x.float().permute(0, 2, 1, 3).reshape(-1, per, x.shape[1]).mean(dim=1)
+      return self.fc(pooled)
+
+  return Net
+
+
+def module_resnet_build(net, sixteen_bit=True, device='cuda'):
+  cin = net['channel_in']
+  cin_pad = (cin + 7) // 8 * 8 if sixteen_bit else cin
+  return module_resnet(net, device)(cin_pad).to(device).eval()

@@ -136,7 +136,8 @@ DataRef get_data(const Tensor& data, const char* what) {
   d.H = (int)data.size(2);
   if (data.scalar_type() == torch::kFloat32) d.dtype = OCNN_F32;
   else if (data.scalar_type() == torch::kBFloat16) d.dtype = OCNN_BF16;
-  else TORCH_CHECK(false, what, ": data must be float32 or bfloat16");
+  else if (data.scalar_type() == torch::kFloat16) d.dtype = OCNN_F16;
+  else TORCH_CHECK(false, what, ": data must be float32, bfloat16 or float16");
   if (data.is_contiguous()) {
     d.layout = OCNN_CHANNEL_MAJOR;
     d.t = data;
@@ -274,32 +275,89 @@ Tensor octree_max_pool_pad(Tensor data_in, Tensor octree, int depth) {
   return top;
 }
 
-// ---- octree2col ----------------------------------------------------------------------------------
+// ---- octree2col / col2octree ---------------------------------------------------------------------
+// ichild of a level (node of the i-th non-empty node), as pytorch/cpp/octree2col.cpp:8-18 builds it.
+Tensor make_ichild(const OctreeRef& o, int depth, const torch::TensorOptions& like, const char* what) {
+  const int nne = o.meta.nnum_nempty[depth], nnum = o.meta.nnum[depth];
+  Tensor ichild = torch::zeros({std::max(nne, 1)}, like.dtype(torch::kInt32));
+  OCNN_CALL(ocnn_octree_ichild(level_ptr(o, OCNN_PROP_CHILD, depth, what), nnum,
+                               ichild.data_ptr<int32_t>(), current_stream()));
+  return ichild;
+}
+
 Tensor octree2col(Tensor data_in, Tensor octree, int depth, vector<int> kernel_size, int stride,
                   bool nempty) {
-  TORCH_CHECK(!nempty, "octree2col on non-empty nodes only (nempty=True) is not implemented");
   vector<int> ks = kernel3(kernel_size);
   TORCH_CHECK(stride == 1 || stride == 2, "Unsupport stride");
   TORCH_CHECK(depth > 0, "Depth should be larger than 0");
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "octree2col: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth <= o.meta.depth, "octree2col: depth ", depth, " exceeds the octree depth");
   need_cuda(data_in, "octree2col");
   c10::cuda::CUDAGuard guard(data_in.device());
   TORCH_CHECK(data_in.scalar_type() == torch::kFloat32, "octree2col takes float32 data");
   DataRef x = get_data(data_in.contiguous(), "octree2col");
-  TORCH_CHECK(o.meta.nnum[depth] == x.H, "octree2col: data height ", x.H, " != node number ",
-              o.meta.nnum[depth]);
+  const int nnum = o.meta.nnum[depth], nne = o.meta.nnum_nempty[depth];
+  TORCH_CHECK((nempty ? nne : nnum) == x.H, "octree2col: data height ", x.H, " != ",
+              nempty ? "non-empty " : "", "node number ", nempty ? nne : nnum);
   int top_h = x.H;
   if (stride == 2) {
-    top_h = x.H / 8;
+    top_h = nnum / 8;
     TORCH_CHECK(top_h == o.meta.nnum_nempty[depth - 1], "octree2col: inconsistent octree");
   }
   const int kdim = ks[0] * ks[1] * ks[2];
   Tensor col = torch::empty({x.C, kdim, top_h}, x.t.options());
-  OCNN_CALL(ocnn_octree2col(x.t.data_ptr<float>(), col.data_ptr<float>(),
-                            level_ptr(o, OCNN_PROP_NEIGH, depth, "octree2col"), x.C, top_h,
-                            ks.data(), stride, current_stream()));
+  const int32_t* neigh = level_ptr(o, OCNN_PROP_NEIGH, depth, "octree2col");
+  if (!nempty) {
+    OCNN_CALL(ocnn_octree2col(x.t.data_ptr<float>(), col.data_ptr<float>(), neigh, x.C, top_h,
+                              ks.data(), stride, current_stream()));
+  } else {
+    Tensor ichild = make_ichild(o, depth, x.t.options(), "octree2col");
+    OCNN_CALL(ocnn_octree2col_general(x.t.data_ptr<float>(), col.data_ptr<float>(), neigh,
+                                      level_ptr(o, OCNN_PROP_CHILD, depth, "octree2col"),
+                                      ichild.data_ptr<int32_t>(), x.C, top_h, x.H, ks.data(), stride,
+                                      current_stream()));
+  }
   return col;
+}
+
+// The transpose of octree2col (pytorch/cpp/octree2col.cpp:85-122, 170-216): [C, K, h] -> [1,C,H,1].
+Tensor col2octree(Tensor grad_in, Tensor octree, int depth, vector<int> kernel_size, int stride,
+                  bool nempty) {
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(stride == 1 || stride == 2, "Unsupport stride");
+  TORCH_CHECK(depth > 0, "Depth should be larger than 0");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "col2octree: the octree must be a CUDA tensor");
+  TORCH_CHECK(depth <= o.meta.depth, "col2octree: depth ", depth, " exceeds the octree depth");
+  TORCH_CHECK(grad_in.is_cuda() && grad_in.scalar_type() == torch::kFloat32 && grad_in.dim() == 3,
+              "col2octree takes a float32 CUDA tensor of shape [C, K, H]");
+  c10::cuda::CUDAGuard guard(grad_in.device());
+  Tensor col = grad_in.contiguous();
+  const int kdim = ks[0] * ks[1] * ks[2];
+  const int channel = (int)col.size(0), top_h = (int)col.size(2);
+  TORCH_CHECK(col.size(1) == kdim, "col2octree: the column tensor has ", col.size(1),
+              " kernel entries, the kernel size has ", kdim);
+  const int nnum = o.meta.nnum[depth], nne = o.meta.nnum_nempty[depth];
+  if (stride == 2) {
+    TORCH_CHECK(top_h == o.meta.nnum_nempty[depth - 1], "col2octree: height mismatch");
+  } else {
+    TORCH_CHECK(top_h == (nempty ? nne : nnum), "col2octree: height mismatch");
+  }
+  const int btm_h = nempty ? nne : nnum;
+  Tensor out = torch::empty({1, channel, btm_h, 1}, col.options());
+  const int32_t* neigh = level_ptr(o, OCNN_PROP_NEIGH, depth, "col2octree");
+  Tensor ichild;
+  const int32_t* child = nullptr;
+  const int32_t* ich = nullptr;
+  if (nempty) {
+    ichild = make_ichild(o, depth, col.options(), "col2octree");
+    child = level_ptr(o, OCNN_PROP_CHILD, depth, "col2octree");
+    ich = ichild.data_ptr<int32_t>();
+  }
+  OCNN_CALL(ocnn_col2octree(col.data_ptr<float>(), out.data_ptr<float>(), neigh, child, ich, channel,
+                            top_h, btm_h, ks.data(), stride, current_stream()));
+  return out;
 }
 
 // ---- convolution -----------------------------------------------------------------------------------
@@ -399,13 +457,18 @@ Tensor octree_conv_nempty(Tensor data_in, Tensor weights, Tensor octree, int dep
   return y;
 }
 
+Tensor octree_conv_general(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
+                           vector<int> kernel_size, int stride, bool nempty, bool transposed,
+                           c10::optional<Tensor> scale, c10::optional<Tensor> bias,
+                           c10::optional<Tensor> residual, bool relu);
+
 Tensor octree_conv(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
                    vector<int> kernel_size, int stride, bool nempty) {
-  if (nempty) {
-    TORCH_CHECK(stride == 1, "octree_conv on non-empty nodes (nempty=True) is implemented for stride 1 "
-                "only (stride ", stride, " given)");
+  if (nempty && stride == 1)
     return octree_conv_nempty(data_in, weights, octree, depth, num_output, kernel_size);
-  }
+  if (nempty)
+    return octree_conv_general(data_in, weights, octree, depth, num_output, kernel_size, stride, true,
+                               false, c10::nullopt, c10::nullopt, c10::nullopt, false);
   return octree_conv_fused(data_in, weights, octree, depth, num_output, kernel_size, stride,
                            c10::nullopt, c10::nullopt, c10::nullopt, false);
 }
@@ -438,7 +501,7 @@ Tensor octree_conv_tc(Tensor data_in, Tensor packed, Tensor octree, int depth, i
   c10::cuda::CUDAGuard guard(data_in.device());
   DataRef x = get_data(data_in, "octree_conv_tc");
   TORCH_CHECK(x.dtype == OCNN_BF16 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
-              "octree_conv_tc takes bfloat16 channels_last data");
+              "octree_conv_tc takes bfloat16 channels_last data (float16: octree_conv_tc_general)");
   x.layout = OCNN_NODE_MAJOR;
   ConvShape s = conv_shape(o, x, depth, ks, stride, "octree_conv_tc");
   TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
@@ -506,6 +569,323 @@ Tensor octree_conv_tc_nempty(Tensor data_in, Tensor packed, Tensor octree, int d
                                        ichild.data_ptr<int32_t>(), nne, x.C, num_output, ks.data(),
                                        &ep, status.data_ptr<int32_t>(), current_stream()));
   return y;
+}
+
+// ---- every OctreeConv / OctreeDeconv forward (stride 1 or 2, nempty or not) -----------------------
+// Row counts and level pointers as OctreeConvTH::setup_op / OctreeBaseConv::reshape derive them
+// (pytorch/cpp/octree_conv.cpp:61-120, octree/octree/octree_conv.cpp:48-122).
+struct Geometry {
+  ocnn_conv_geometry g;
+  Tensor ichild;      // keeps the inverse child table alive for the launch
+};
+
+Geometry make_geometry(const OctreeRef& o, const DataRef& x, int depth, const vector<int>& ks,
+                       int stride, bool nempty, bool transposed, const char* what) {
+  TORCH_CHECK(depth > 0 && depth <= o.meta.depth, what, ": The depth should be in (0, octree depth]");
+  TORCH_CHECK(stride == 1 || stride == 2, "Unsupport stride");
+  const ocnn_octree_meta& m = o.meta;
+  const bool on_nempty = nempty || (transposed && stride == 2);
+  TORCH_CHECK(x.H == (on_nempty ? m.nnum_nempty[depth] : m.nnum[depth]), what, ": data height ", x.H,
+              " != ", on_nempty ? "non-empty " : "", "node number ",
+              on_nempty ? m.nnum_nempty[depth] : m.nnum[depth], ", d: ", depth, ", channel_in: ", x.C);
+  int work_depth = depth, top_depth = depth;
+  if (stride == 2) {
+    if (transposed) work_depth = top_depth = depth + 1; else top_depth = depth - 1;
+    TORCH_CHECK(top_depth >= 0 && top_depth <= m.depth, what, ": the output level ", top_depth,
+                " is outside the octree");
+  }
+  Geometry out;
+  memset(&out.g, 0, sizeof(out.g));
+  out.g.transposed = transposed ? 1 : 0;
+  out.g.stride = stride;
+  out.g.nempty = nempty ? 1 : 0;
+  out.g.h_in = x.H;
+  if (stride == 2 && !transposed) out.g.h_out = m.nnum[depth] / 8;
+  else out.g.h_out = nempty ? m.nnum_nempty[top_depth] : m.nnum[top_depth];
+  if (stride == 2 && !transposed)
+    TORCH_CHECK(out.g.h_out == m.nnum_nempty[depth - 1], what, ": inconsistent octree");
+  const bool identity = ks[0] * ks[1] * ks[2] == 1 && stride == 1;
+  if (!identity) {
+    out.g.neigh_dev = level_ptr(o, OCNN_PROP_NEIGH, work_depth, what);
+    if (nempty) {
+      out.g.child_dev = level_ptr(o, OCNN_PROP_CHILD, work_depth, what);
+      out.ichild = make_ichild(o, work_depth, x.t.options(), what);
+      out.g.ichild_dev = out.ichild.data_ptr<int32_t>();
+    }
+  }
+  return out;
+}
+
+void check_weights(const Tensor& weights, int cin, int cout, int kdim) {
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 &&
+                  weights.numel() == (int64_t)cout * cin * kdim,
+              "weights must be a float32 CUDA tensor of Cout*Cin*K values");
+}
+
+Tensor octree_conv_general(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
+                           vector<int> kernel_size, int stride, bool nempty, bool transposed,
+                           c10::optional<Tensor> scale, c10::optional<Tensor> bias,
+                           c10::optional<Tensor> residual, bool relu) {
+  const char* what = transposed ? "octree_deconv" : "octree_conv";
+  vector<int> ks = kernel3(kernel_size);
+  TORCH_CHECK(num_output > 0, "The num_output should be larger than 0");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, what, ": the octree must be a CUDA tensor");
+  need_cuda(data_in, what);
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, what);
+  Geometry geo = make_geometry(o, x, depth, ks, stride, nempty, transposed, what);
+  check_weights(weights, x.C, num_output, ks[0] * ks[1] * ks[2]);
+  Tensor w = weights.contiguous();
+  Tensor y = new_data(num_output, geo.g.h_out, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  OCNN_CALL(ocnn_octree_conv_general(x.t.data_ptr(), w.data_ptr<float>(), y.data_ptr(), &geo.g, x.C,
+                                     num_output, ks.data(), x.dtype, x.layout, &ep, current_stream()));
+  return y;
+}
+
+Tensor octree_deconv(Tensor data_in, Tensor weights, Tensor octree, int depth, int num_output,
+                     vector<int> kernel_size, int stride, bool nempty) {
+  return octree_conv_general(data_in, weights, octree, depth, num_output, kernel_size, stride, nempty,
+                             true, c10::nullopt, c10::nullopt, c10::nullopt, false);
+}
+
+Tensor conv_pack_weights_general(Tensor weights, int cin, int cout, vector<int> kernel_size,
+                                 int stride, bool transposed, bool nempty, bool half) {
+  vector<int> ks = kernel3(kernel_size);
+  check_weights(weights, cin, cout, ks[0] * ks[1] * ks[2]);
+  c10::cuda::CUDAGuard guard(weights.device());
+  const size_t bytes = ocnn_conv_packed_weight_bytes_general(cin, cout, ks.data(), stride, transposed,
+                                                             nempty);
+  TORCH_CHECK(bytes > 0, "this shape is not supported by the tensor-core convolution: ",
+              ocnn_last_error());
+  Tensor packed = torch::empty({(int64_t)bytes}, weights.options().dtype(torch::kUInt8));
+  Tensor w = weights.contiguous();
+  OCNN_CALL(ocnn_conv_pack_weights_general(w.data_ptr<float>(), packed.data_ptr(), cin, cout, ks.data(),
+                                           stride, transposed, nempty, half ? OCNN_F16 : OCNN_BF16,
+                                           current_stream()));
+  return packed;
+}
+
+Tensor octree_conv_tc_general(Tensor data_in, Tensor packed, Tensor octree, int depth, int num_output,
+                              vector<int> kernel_size, int stride, bool nempty, bool transposed,
+                              c10::optional<Tensor> scale, c10::optional<Tensor> bias,
+                              c10::optional<Tensor> residual, bool relu, Tensor status) {
+  const char* what = transposed ? "octree_deconv_tc" : "octree_conv_tc";
+  vector<int> ks = kernel3(kernel_size);
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, what, ": the octree must be a CUDA tensor");
+  need_cuda(data_in, what);
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, what);
+  TORCH_CHECK(x.dtype != OCNN_F32 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1), what,
+              " takes bfloat16 or float16 channels_last data");
+  x.layout = OCNN_NODE_MAJOR;
+  Geometry geo = make_geometry(o, x, depth, ks, stride, nempty, transposed, what);
+  TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
+                  (size_t)packed.numel() == ocnn_conv_packed_weight_bytes_general(
+                                                x.C, num_output, ks.data(), stride, transposed, nempty),
+              "packed weights do not match this convolution's shape");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32 && status.numel() >= 1,
+              "status must be an int32 CUDA tensor");
+  Tensor y = new_data(num_output, geo.g.h_out, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  OCNN_CALL(ocnn_octree_conv_tc_general(x.t.data_ptr(), packed.data_ptr(), y.data_ptr(), &geo.g, x.C,
+                                        num_output, ks.data(), x.dtype, &ep,
+                                        status.data_ptr<int32_t>(), current_stream()));
+  return y;
+}
+
+// ---- 1x1x1 convolution without an octree -------------------------------------------------------------
+// The reference's OctreeConv1x1 is a torch Conv1d over [1,C,H] (pytorch/ocnn/modules.py:71-83): a
+// per-node matrix product that needs no octree.  weights: float32 [Cout, Cin].
+Tensor pointwise_conv(Tensor data_in, Tensor weights, c10::optional<Tensor> scale,
+                      c10::optional<Tensor> bias, c10::optional<Tensor> residual, bool relu) {
+  need_cuda(data_in, "pointwise_conv");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "pointwise_conv");
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 && weights.numel() > 0 &&
+                  weights.numel() % x.C == 0, "weights must be a float32 CUDA tensor [Cout, Cin]");
+  const int cout = (int)(weights.numel() / x.C);
+  Tensor w = weights.contiguous();
+  Tensor y = new_data(cout, x.H, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, cout, y);
+  const int ks[3] = {1, 1, 1};
+  OCNN_CALL(ocnn_octree_conv(x.t.data_ptr(), w.data_ptr<float>(), y.data_ptr(), nullptr, x.H, x.H, x.C,
+                             cout, ks, 1, x.dtype, x.layout, &ep, current_stream()));
+  return y;
+}
+
+Tensor pointwise_conv_tc(Tensor data_in, Tensor packed, int num_output, c10::optional<Tensor> scale,
+                         c10::optional<Tensor> bias, c10::optional<Tensor> residual, bool relu,
+                         Tensor status) {
+  need_cuda(data_in, "pointwise_conv_tc");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "pointwise_conv_tc");
+  TORCH_CHECK(x.dtype != OCNN_F32 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
+              "pointwise_conv_tc takes bfloat16 or float16 channels_last data");
+  x.layout = OCNN_NODE_MAJOR;
+  const int ks[3] = {1, 1, 1};
+  TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
+                  (size_t)packed.numel() == ocnn_conv_packed_weight_bytes(x.C, num_output, ks, 1),
+              "packed weights do not match this convolution's shape");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32 && status.numel() >= 1,
+              "status must be an int32 CUDA tensor");
+  Tensor y = new_data(num_output, x.H, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  ocnn_conv_geometry g;
+  memset(&g, 0, sizeof(g));
+  g.stride = 1; g.h_in = x.H; g.h_out = x.H;
+  OCNN_CALL(ocnn_octree_conv_tc_general(x.t.data_ptr(), packed.data_ptr(), y.data_ptr(), &g, x.C,
+                                        num_output, ks, x.dtype, &ep, status.data_ptr<int32_t>(),
+                                        current_stream()));
+  return y;
+}
+
+// ---- keys, search, interpolation, alignment (pytorch/cpp/octree_key.cpp, octree_align.cpp) ------------
+// The reference's binding is compiled with 64-bit keys only (pytorch/cpp/octree_key.cpp:1-3), so
+// key tensors are int64; a 32-bit-key octree is rejected here with a message.
+void need_key64(const OctreeRef& o, const char* what) {
+  TORCH_CHECK(o.meta.key_bits == 64, what, ": int64 key tensors need an octree with 64-bit keys "
+              "(this one has 32-bit keys)");
+}
+
+Tensor octree_encode_key(Tensor xyz) {
+  TORCH_CHECK(xyz.dim() == 2, "The dim of input tensor must be 2.");
+  TORCH_CHECK(xyz.size(1) == 4, "The channel of input tensor must be 4.");
+  TORCH_CHECK(xyz.scalar_type() == torch::kInt16, "octree_encode_key takes an int16 tensor");
+  return xyz.contiguous().view(torch::kInt64).reshape({xyz.size(0)}).clone();
+}
+
+Tensor octree_decode_key(Tensor key) {
+  TORCH_CHECK(key.dim() == 1, "The dim of input tensor must be 1.");
+  TORCH_CHECK(key.scalar_type() == torch::kInt64, "octree_decode_key takes an int64 tensor");
+  return key.contiguous().view(torch::kInt16).reshape({key.size(0), 4}).clone();
+}
+
+Tensor convert_key(Tensor in, int depth, bool to_key, const char* what) {
+  TORCH_CHECK(in.scalar_type() == torch::kInt64 && in.numel() >= 1, what,
+              ": The numel of the input int64 tensor must be larger than 1.");
+  TORCH_CHECK(in.is_cuda(), what, ": the tensor must be a CUDA tensor (there is no CPU path)");
+  c10::cuda::CUDAGuard guard(in.device());
+  Tensor src = in.contiguous();
+  Tensor out = torch::empty_like(src);
+  OCNN_CALL(ocnn_convert_key(src.data_ptr(), out.data_ptr(), src.numel(), depth, 64, to_key ? 1 : 0,
+                             current_stream()));
+  return out;
+}
+Tensor octree_xyz2key(Tensor xyz, int depth) { return convert_key(xyz, depth, true, "octree_xyz2key"); }
+Tensor octree_key2xyz(Tensor key, int depth) { return convert_key(key, depth, false, "octree_key2xyz"); }
+
+// The ascending Morton keys of a level: its Key block (converted when the octree stores xyz), or the
+// keys of its non-empty nodes only.  `hold` keeps temporaries alive.
+const void* level_keys(const OctreeRef& o, const Tensor& octree, int depth, bool nempty, int* n_key,
+                       vector<Tensor>& hold, const char* what) {
+  TORCH_CHECK(depth >= 1 && depth <= o.meta.depth, what, ": depth ", depth, " outside the octree");
+  const int64_t off = ocnn_prop_offset(&o.meta, OCNN_PROP_KEY, depth);
+  TORCH_CHECK(off >= 0, what, ": the octree has no keys at depth ", depth);
+  const void* keys = o.base + off;
+  *n_key = o.meta.nnum[depth];
+  const int kb = o.meta.key_bits / 8;
+  auto opts = octree.options().dtype(torch::kUInt8);
+  if (nempty) {
+    const int nne = o.meta.nnum_nempty[depth];
+    Tensor t = torch::zeros({(int64_t)std::max(nne, 1) * kb}, opts);
+    OCNN_CALL(ocnn_key_depad(keys, level_ptr(o, OCNN_PROP_CHILD, depth, what), *n_key, t.data_ptr(),
+                             o.meta.key_bits, current_stream()));
+    hold.push_back(t);
+    keys = t.data_ptr();
+    *n_key = nne;
+  }
+  if (o.meta.key2xyz) {
+    Tensor t = torch::empty({(int64_t)std::max(*n_key, 1) * kb}, opts);
+    OCNN_CALL(ocnn_convert_key(keys, t.data_ptr(), *n_key, depth, o.meta.key_bits, 1, current_stream()));
+    hold.push_back(t);
+    keys = t.data_ptr();
+  }
+  return keys;
+}
+
+Tensor octree_search_key(Tensor key, Tensor octree, int depth, bool key_is_xyz, bool nempty) {
+  TORCH_CHECK(key.scalar_type() == torch::kInt64 && key.numel() >= 1,
+              "The numel of the input tensor must be larger than 1.");
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda && key.is_cuda(), "octree_search_key: key and octree must be CUDA tensors");
+  need_key64(o, "octree_search_key");
+  c10::cuda::CUDAGuard guard(key.device());
+  Tensor q = key.contiguous();
+  vector<Tensor> hold;
+  int n_key = 0;
+  const void* keys = level_keys(o, octree, depth, nempty, &n_key, hold, "octree_search_key");
+  Tensor idx = torch::empty({q.numel()}, q.options().dtype(torch::kInt32));
+  OCNN_CALL(ocnn_search_key(keys, n_key, q.data_ptr(), q.numel(), idx.data_ptr<int32_t>(),
+                            key_is_xyz ? 1 : 0, depth, 64, current_stream()));
+  return idx;
+}
+
+// OctreeInterp in one kernel: data [1,C,H,1] at `depth` sampled at pts [N,4] = (x,y,z in
+// [0, 2^depth], batch id).  method: "nearest" or "linear".  Returns [1,C,N,1].
+Tensor octree_interp(Tensor data_in, Tensor octree, int depth, Tensor pts, string method, bool nempty) {
+  TORCH_CHECK(method == "nearest" || method == "linear", "octree_interp: unknown method ", method);
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, "octree_interp: the octree must be a CUDA tensor");
+  need_cuda(data_in, "octree_interp");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "octree_interp");
+  TORCH_CHECK(pts.is_cuda() && pts.dim() == 2 && pts.size(1) == 4, "octree_interp: pts must be a CUDA "
+              "tensor of shape [N, 4]");
+  Tensor p = pts.to(torch::kFloat32).contiguous();
+  vector<Tensor> hold;
+  int n_key = 0;
+  const void* keys = level_keys(o, octree, depth, nempty, &n_key, hold, "octree_interp");
+  TORCH_CHECK(x.H == n_key, "octree_interp: data height ", x.H, " != ", nempty ? "non-empty " : "",
+              "node number ", n_key);
+  const int64_t n = p.size(0);
+  Tensor out = new_data(x.C, (int)n, x);
+  OCNN_CALL(ocnn_octree_interp(x.t.data_ptr(), out.data_ptr(), p.data_ptr<float>(), keys, n_key, x.C,
+                               x.H, n, depth, o.meta.key_bits, method == "linear" ? 1 : 0, x.dtype,
+                               x.layout, current_stream()));
+  return out;
+}
+
+vector<Tensor> octree_align(Tensor src_data, Tensor src_octree, Tensor des_octree, int depth) {
+  OctreeRef so = get_octree(src_octree), dso = get_octree(des_octree);
+  TORCH_CHECK(so.cuda && dso.cuda, "octree_align: the octrees must be CUDA tensors");
+  TORCH_CHECK(so.meta.key_bits == dso.meta.key_bits, "octree_align: the octrees differ in key width");
+  need_cuda(src_data, "octree_align");
+  c10::cuda::CUDAGuard guard(src_data.device());
+  DataRef x = get_data(src_data, "octree_align");
+  TORCH_CHECK(depth >= 1 && depth <= so.meta.depth && depth <= dso.meta.depth,
+              "octree_align: depth outside the octrees");
+  TORCH_CHECK(so.meta.nnum[depth] == x.H, "octree_align: data height ", x.H, " != node number ",
+              so.meta.nnum[depth]);
+  vector<Tensor> hold;
+  int n_src = 0, n_des = 0;
+  const void* skeys = level_keys(so, src_octree, depth, false, &n_src, hold, "octree_align");
+  const void* dkeys = level_keys(dso, des_octree, depth, false, &n_des, hold, "octree_align");
+  Tensor idx = torch::empty({x.H}, x.t.options().dtype(torch::kInt32));
+  OCNN_CALL(ocnn_search_key(dkeys, n_des, skeys, n_src, idx.data_ptr<int32_t>(), 0, depth,
+                            so.meta.key_bits, current_stream()));
+  Tensor des = new_data(x.C, n_des, x);
+  OCNN_CALL(ocnn_octree_align(x.t.data_ptr(), des.data_ptr(), idx.data_ptr<int32_t>(), x.C, x.H, n_des,
+                              x.dtype, x.layout, current_stream()));
+  return {des, idx};
+}
+
+// Backward of octree_align: src_grad[., h] = idx[h] < 0 ? 0 : des_grad[., idx[h]]
+// (align_backward_gpu, octree/octree/octree_nn.cu:734-752).
+Tensor octree_align_grad(Tensor des_grad, Tensor idx_tensor) {
+  need_cuda(des_grad, "octree_align_grad");
+  c10::cuda::CUDAGuard guard(des_grad.device());
+  DataRef g = get_data(des_grad, "octree_align_grad");
+  TORCH_CHECK(idx_tensor.is_cuda() && idx_tensor.scalar_type() == torch::kInt32 && idx_tensor.dim() == 1,
+              "octree_align_grad: idx must be a 1-D int32 CUDA tensor");
+  Tensor idx = idx_tensor.contiguous();
+  const int src_h = (int)idx.numel();
+  Tensor out = new_data(g.C, src_h, g);
+  OCNN_CALL(ocnn_octree_align_backward(g.t.data_ptr(), out.data_ptr(), idx.data_ptr<int32_t>(), g.C,
+                                       src_h, g.H, g.dtype, g.layout, current_stream()));
+  return out;
 }
 
 // ---- points ------------------------------------------------------------------------------------------
@@ -804,9 +1184,16 @@ Tensor octree_property(Tensor octree, string property, int depth) {
                            : key.bitwise_right_shift(24).bitwise_and(0xff);
       return idx.to(torch::kInt32);
     }
-    TORCH_CHECK((property == "key") == (m.key2xyz == 0),
-                "octree_property('", property, "'): converting between Morton keys and packed xyz "
-                "is not implemented");
+    if ((property == "key") != (m.key2xyz == 0)) {
+      // the octree stores the other form: convert (octree_property.cpp:58-75 of the reference)
+      TORCH_CHECK(octree.is_cuda() && kb == 8, "octree_property('", property, "'): converting between "
+                  "Morton keys and packed xyz needs a CUDA octree with 64-bit keys");
+      c10::cuda::CUDAGuard guard(octree.device());
+      Tensor out = torch::empty_like(key);
+      OCNN_CALL(ocnn_convert_key(key.data_ptr(), out.data_ptr(), key.numel(), depth, 64,
+                                 property == "key" ? 1 : 0, current_stream()));
+      return out;
+    }
     return key;
   }
   if (property == "child") return block(OCNN_PROP_CHILD, 4, 1).view(torch::kInt32).clone();
@@ -840,7 +1227,8 @@ vector<int64_t> octree_info(Tensor octree) {
   return out;
 }
 
-Tensor feature_node_major(Tensor octree, int c_pad, bool bf16) {
+Tensor feature_node_major(Tensor octree, int c_pad, bool bf16, bool half) {
+  TORCH_CHECK(!(bf16 && half), "feature_node_major: choose one of bf16 / half");
   OctreeRef o = get_octree(octree);
   TORCH_CHECK(o.cuda, "feature_node_major: the octree must be a CUDA tensor");
   const ocnn_octree_meta& m = o.meta;
@@ -849,12 +1237,12 @@ Tensor feature_node_major(Tensor octree, int c_pad, bool bf16) {
   TORCH_CHECK(off >= 0 && ch > 0, "the octree has no features at its finest level");
   TORCH_CHECK(c_pad >= ch, "c_pad must be at least the feature channel count ", ch);
   c10::cuda::CUDAGuard guard(octree.device());
-  auto opts = octree.options().dtype(bf16 ? torch::kBFloat16 : torch::kFloat32)
+  auto opts = octree.options().dtype(bf16 ? torch::kBFloat16 : (half ? torch::kFloat16 : torch::kFloat32))
                   .memory_format(at::MemoryFormat::ChannelsLast);
   Tensor out = torch::empty({1, c_pad, m.nnum[d], 1}, opts);
   OCNN_CALL(ocnn_feature_to_node_major(reinterpret_cast<const float*>(o.base + off), out.data_ptr(),
-                                       ch, c_pad, m.nnum[d], bf16 ? OCNN_BF16 : OCNN_F32,
-                                       current_stream()));
+                                       ch, c_pad, m.nnum[d],
+                                       bf16 ? OCNN_BF16 : (half ? OCNN_F16 : OCNN_F32), current_stream()));
   return out;
 }
 
@@ -1072,7 +1460,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("property"), py::arg("depth") = 0);
   m.def("points2octree", &points2octree, "convert points to octree");
   m.def("octree2col", &octree2col, "octree2col");
+  m.def("col2octree", &col2octree, "col2octree");
   m.def("octree_conv", &octree_conv, "octree based convolution");
+  m.def("octree_deconv", &octree_deconv, "octree based deconvolution");
   m.def("octree_pad", &octree_pad, "octree pad", py::arg("data_in"), py::arg("octree"),
         py::arg("depth"), py::arg("val") = 0.0f);
   m.def("octree_depad", &octree_depad, "octree depad");
@@ -1101,9 +1491,39 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
         py::arg("scale") = py::none(), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
+  m.def("octree_conv_general", &octree_conv_general, py::arg("data_in"), py::arg("weights"),
+        py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
+        py::arg("stride") = 1, py::arg("nempty") = false, py::arg("transposed") = false,
+        py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false);
+  m.def("conv_pack_weights_general", &conv_pack_weights_general, py::arg("weights"), py::arg("cin"),
+        py::arg("cout"), py::arg("kernel_size"), py::arg("stride") = 1,
+        py::arg("transposed") = false, py::arg("nempty") = false, py::arg("half") = false);
+  m.def("octree_conv_tc_general", &octree_conv_tc_general, py::arg("data_in"), py::arg("packed"),
+        py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
+        py::arg("stride") = 1, py::arg("nempty") = false, py::arg("transposed") = false,
+        py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
+  m.def("pointwise_conv", &pointwise_conv, py::arg("data_in"), py::arg("weights"),
+        py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false);
+  m.def("pointwise_conv_tc", &pointwise_conv_tc, py::arg("data_in"), py::arg("packed"),
+        py::arg("num_output"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
+  m.def("octree_encode_key", &octree_encode_key, "encode xyz-id to octree key");
+  m.def("octree_decode_key", &octree_decode_key, "decode octree key to xyz-id");
+  m.def("octree_xyz2key", &octree_xyz2key, "convert key from xyz order");
+  m.def("octree_key2xyz", &octree_key2xyz, "convert key to xyz order");
+  m.def("octree_search_key", &octree_search_key, "search key from octree", py::arg("key"),
+        py::arg("octree"), py::arg("depth"), py::arg("key_is_xyz") = true, py::arg("nempty") = false);
+  m.def("octree_interp", &octree_interp, py::arg("data_in"), py::arg("octree"), py::arg("depth"),
+        py::arg("pts"), py::arg("method") = "linear", py::arg("nempty") = false);
+  m.def("octree_align", &octree_align, "align octree data", py::arg("src_data"),
+        py::arg("src_octree"), py::arg("des_octree"), py::arg("depth"));
+  m.def("octree_align_grad", &octree_align_grad, "backward of align-octree-data");
   m.def("octree_info", &octree_info);
   m.def("feature_node_major", &feature_node_major, py::arg("octree"), py::arg("c_pad"),
-        py::arg("bf16") = true);
+        py::arg("bf16") = true, py::arg("half") = false);
   m.def("set_key_bits", &set_key_bits);
   m.def("get_key_bits", &get_key_bits);
   py::class_<NetExecutor>(m, "NetExecutor")

@@ -493,6 +493,21 @@ long oc_octree_batch(const uint8_t *const *in, int batch, uint8_t *out, long cap
   return total;
 }
 
+/* top[m, h] = sum_k w[m, k] * src[k, h], k ascending, in fp32 without fused multiply-add: the
+ * same sequence of operations per output element as a plain dot-product loop, arranged so that the
+ * inner loop runs along h (contiguous) instead of along k. */
+static void gemm_rows(float *top, const float *w, const float *src, int M, long K, long H) {
+  for (int m = 0; m < M; ++m) {
+    float *row = top + (long)m * H;
+    for (long h = 0; h < H; ++h) row[h] = 0.0f;
+    for (long k = 0; k < K; ++k) {
+      const float a = w[(long)m * K + k];
+      const float *s = src + k * H;
+      for (long h = 0; h < H; ++h) row[h] += a * s[h];
+    }
+  }
+}
+
 /* ---- octree2col / convolution ----------------------------------------------------------- */
 /* col[(c*K + k)*H + h] = data[c*octree_h + neigh[...]] or 0:
  * octree2col_cpu, octree/octree/octree_nn.cpp:188-214 (single workspace chunk, n = 0). */
@@ -542,12 +557,7 @@ long oc_octree_conv(float *top, long cap, const float *bottom, const float *weig
     free(tmp);
     src = col;
   }
-  for (int m = 0; m < cout; ++m)
-    for (long h = 0; h < top_h; ++h) {
-      float acc = 0.0f;
-      for (long k = 0; k < kd; ++k) acc += weights[m * kd + k] * src[k * top_h + h];
-      top[m * top_h + h] = acc;
-    }
+  gemm_rows(top, weights, src, cout, kd, top_h);
   free(col);
   return count;
 }
@@ -605,13 +615,8 @@ long oc_octree_conv_nempty(float *top, long cap, const float *bottom, const floa
     free(ichild);
     src = col;
   }
-  for (int m = 0; m < cout; ++m)
-    for (long h = 0; h < top_h; ++h) {
-      float acc = 0.0f;
-      if (h_ne > 0)
-        for (long k = 0; k < kd; ++k) acc += weights[m * kd + k] * src[k * top_h + h];
-      top[m * top_h + h] = acc;
-    }
+  if (h_ne > 0) gemm_rows(top, weights, src, cout, kd, top_h);
+  else memset(top, 0, sizeof(float) * (size_t)count);
   free(col);
   return count;
 }
@@ -727,12 +732,7 @@ long oc_octree_conv_general(float *top, long cap, const float *bottom, const flo
         oc_octree2col(col, bottom, conv_in, (int)work_h, K, stride, neigh, ni);
       src = col;
     }
-    for (int m = 0; m < conv_out; ++m)
-      for (long h = 0; h < work_h; ++h) {
-        float acc = 0.0f;
-        for (long k = 0; k < kd; ++k) acc += weights[m * kd + k] * src[k * work_h + h];
-        top[m * work_h + h] = acc;
-      }
+    gemm_rows(top, weights, src, conv_out, kd, work_h);
   } else {
     float *dst = one ? top : col;
     for (long m = 0; m < kd; ++m)
@@ -751,6 +751,41 @@ long oc_octree_conv_general(float *top, long cap, const float *bottom, const flo
   free(col);
   free(ichild);
   return count;
+}
+
+/* ---- keys ------------------------------------------------------------------------------------- */
+/* xyz2key_cpu / key2xyz_cpu / search_key_cpu, octree/octree/octree_nn.cpp:540-620, for 64-bit keys
+ * (four 16-bit lanes x, y, z, id) or 32-bit keys (four bytes).  Only `depth` bits of each
+ * coordinate enter the key (compute_key, :551-560). */
+void oc_xyz2key(uint64_t *key, const uint64_t *xyz, long num, int depth, int key_bits) {
+  const int B = key_bits == 64 ? 16 : 8;
+  const uint64_t lane = (1ull << B) - 1, low3 = (1ull << (3 * B)) - 1;
+  for (long i = 0; i < num; ++i) {
+    const uint64_t v = xyz[i], pt[3] = {v & lane, (v >> B) & lane, (v >> (2 * B)) & lane};
+    uint64_t k = 0;
+    for (int b = 0; b < depth; ++b)
+      for (int j = 0; j < 3; ++j) k |= (pt[j] & (1ull << b)) << (2 * b + 2 - j);
+    key[i] = (k & low3) | (v & ~low3);
+  }
+}
+
+void oc_key2xyz(uint64_t *xyz, const uint64_t *key, long num, int depth, int key_bits) {
+  const int B = key_bits == 64 ? 16 : 8;
+  const uint64_t lane = (1ull << B) - 1, low3 = (1ull << (3 * B)) - 1;
+  for (long i = 0; i < num; ++i) {
+    uint64_t pt[3] = {0, 0, 0};
+    for (int b = 0; b < depth; ++b)
+      for (int j = 0; j < 3; ++j) pt[j] |= (key[i] & (1ull << (3 * b + 2 - j))) >> (2 * b + 2 - j);
+    xyz[i] = (pt[0] & lane) | ((pt[1] & lane) << B) | ((pt[2] & lane) << (2 * B)) | (key[i] & ~low3);
+  }
+}
+
+void oc_search_key(int32_t *idx, const uint64_t *key, long n_key, const uint64_t *query, long n_query) {
+  for (long i = 0; i < n_query; ++i) {
+    long lo = 0, hi = n_key;
+    while (lo < hi) { long mid = (lo + hi) / 2; if (key[mid] < query[i]) lo = mid + 1; else hi = mid; }
+    idx[i] = (lo >= n_key || key[lo] != query[i]) ? -1 : (int32_t)lo;
+  }
 }
 
 /* ---- pool / pad ------------------------------------------------------------------------- */

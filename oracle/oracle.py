@@ -63,6 +63,9 @@ def lib():
     L.oc_col2octree.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 4 + [c_int_p, c_int_p]
     L.oc_octree2col_p2.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 5 + [c_int_p] * 4
     L.oc_col2octree_p.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 5 + [c_int_p] * 4
+    L.oc_xyz2key.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_int, ctypes.c_int]
+    L.oc_key2xyz.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_int, ctypes.c_int]
+    L.oc_search_key.argtypes = [c_int_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p, ctypes.c_long]
     L.oc_max_pool.argtypes = [c_float_p, ctypes.c_int, c_int_p, c_float_p, ctypes.c_int,
                               ctypes.c_int]
     L.oc_pad.argtypes = [c_float_p, ctypes.c_int, ctypes.c_int, c_float_p, ctypes.c_int, c_int_p,
@@ -339,6 +342,81 @@ def col2octree_general(col, neigh, ksize, stride, octree_h, child=None):
     lib().oc_col2octree_p(_fp(col), _fp(data), channel, height, octree_h, kdim, stride,
                           _ip(neigh), _ip(ni), _ip(child), _ip(ichild))
   return data
+
+
+def _u64(a):
+  return np.ascontiguousarray(np.asarray(a).astype(np.uint64, copy=False), dtype=np.uint64)
+
+
+def xyz2key(xyz, depth, key_bits=64):
+  """Packed (x, y, z, id) lanes -> Morton key with the id lane kept; uint64 arrays either width."""
+  xyz = _u64(xyz)
+  out = np.empty_like(xyz)
+  lib().oc_xyz2key(out.ctypes.data_as(ctypes.c_void_p), xyz.ctypes.data_as(ctypes.c_void_p), xyz.size,
+                   depth, key_bits)
+  return out
+
+
+def key2xyz(key, depth, key_bits=64):
+  key = _u64(key)
+  out = np.empty_like(key)
+  lib().oc_key2xyz(out.ctypes.data_as(ctypes.c_void_p), key.ctypes.data_as(ctypes.c_void_p), key.size,
+                   depth, key_bits)
+  return out
+
+
+def search_key(keys, query):
+  keys, query = _u64(keys), _u64(query)
+  idx = np.empty(query.size, np.int32)
+  lib().oc_search_key(_ip(idx), keys.ctypes.data_as(ctypes.c_void_p), keys.size,
+                      query.ctypes.data_as(ctypes.c_void_p), query.size)
+  return idx
+
+
+def level_keys(octree, depth, nempty=False):
+  """Ascending Morton keys (batch id in the top lane) of a level, as uint64; of its non-empty nodes
+  only when nempty (pytorch/cpp/octree_key.cpp:96-108)."""
+  v = OctreeView(octree)
+  keys = v.prop('key', depth).astype(np.uint64)
+  if nempty:
+    child = v.prop('child', depth)
+    keys = keys[child >= 0]
+  return keys
+
+
+def octree_interp(data, octree, depth, pts, method='linear', nempty=False):
+  """The reference's octree_nearest_pts / octree_trilinear_pts (pytorch/ocnn/modules.py:209-275)
+  restated in numpy over xyz2key / search_key.  data: [C, H]; pts: [N, 4] float32 with xyz already
+  scaled to [0, 2^depth]; returns [C, N] float32.  64-bit keys."""
+  data = _f32(data)
+  pts = _f32(pts)
+  keys = level_keys(octree, depth, nempty)
+  n = pts.shape[0]
+  if method == 'nearest':
+    lanes = pts.astype(np.int16).astype(np.uint16).astype(np.uint64)       # Tensor.short()
+    word = lanes[:, 0] | (lanes[:, 1] << 16) | (lanes[:, 2] << 32) | (lanes[:, 3] << 48)
+    idx = search_key(keys, xyz2key(word, depth))
+    ok = idx > -1
+    out = data[:, idx * ok] * ok.astype(np.float32)
+    return np.ascontiguousarray(out, np.float32)
+  xyzf = pts[:, :3] - np.float32(0.5)
+  xyzi = np.floor(xyzf)
+  frac = xyzf - xyzi
+  lanes = np.concatenate([xyzi, pts[:, 3:4]], axis=1).astype(np.int16).astype(np.uint16).astype(np.uint64)
+  word = lanes[:, 0] | (lanes[:, 1] << 16) | (lanes[:, 2] << 32) | (lanes[:, 3] << 48)
+  mask = np.array([[0, 0, 0], [0, 0, 1], [0, 1, 0], [0, 1, 1], [1, 0, 0], [1, 0, 1], [1, 1, 0], [1, 1, 1]],
+                  np.float32)
+  masku = np.array([0, 4294967296, 65536, 4295032832, 1, 4294967297, 65537, 4295032833], np.uint64)
+  word8 = (word[:, None] + masku[None, :]).reshape(-1)           # packed addition: lanes may carry
+  idx = search_key(keys, xyz2key(word8, depth)).reshape(n, 8)
+  w = np.abs(np.prod((1 - mask)[None, :, :] - frac[:, None, :], axis=2)).astype(np.float32)
+  ok = idx > -1
+  w = w * ok
+  out = np.zeros((data.shape[0], n), np.float32)
+  for j in range(8):
+    out += data[:, idx[:, j] * ok[:, j]] * w[:, j][None, :]
+  norm = w.sum(axis=1)
+  return (out / (norm + np.float32(1e-10))[None, :]).astype(np.float32)
 
 
 def max_pool(btm):

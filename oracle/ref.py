@@ -87,6 +87,9 @@ class Ref:
         c_int_p, c_int_p, ctypes.c_int, ctypes.c_int]
     L.ref_col2octreeP.argtypes = [c_float_p, c_float_p] + [ctypes.c_int] * 5 + [
         c_int_p, c_int_p, c_int_p, c_int_p, ctypes.c_int, ctypes.c_int]
+    L.ref_xyz2key.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    L.ref_key2xyz.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    L.ref_search_key.argtypes = [c_int_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
     L.ref_set_gemm.argtypes = [ctypes.c_void_p]
     self._gemm_cb = None
 
@@ -281,6 +284,31 @@ def _general_methods():
                                _ip(neigh), _ip(ni), _ip(child), _ip(ichild), height, 0)
     return data
 
+  def _keys(self, a):
+    return np.ascontiguousarray(a, dtype=np.uint64 if self.key_bits == 64 else np.uint32)
+
+  def xyz2key(self, xyz, depth):
+    xyz = self._keys(xyz)
+    out = np.empty_like(xyz)
+    self.lib.ref_xyz2key(out.ctypes.data_as(ctypes.c_void_p), xyz.ctypes.data_as(ctypes.c_void_p),
+                         xyz.size, depth)
+    return out
+
+  def key2xyz(self, key, depth):
+    key = self._keys(key)
+    out = np.empty_like(key)
+    self.lib.ref_key2xyz(out.ctypes.data_as(ctypes.c_void_p), key.ctypes.data_as(ctypes.c_void_p),
+                         key.size, depth)
+    return out
+
+  def search_key(self, keys, query):
+    keys, query = self._keys(keys), self._keys(query)
+    idx = np.empty(query.size, np.int32)
+    self.lib.ref_search_key(_ip(idx), keys.ctypes.data_as(ctypes.c_void_p), keys.size,
+                            query.ctypes.data_as(ctypes.c_void_p), query.size)
+    return idx
+
+  Ref._keys, Ref.xyz2key, Ref.key2xyz, Ref.search_key = _keys, xyz2key, key2xyz, search_key
   Ref.octree_conv_general = octree_conv_general
   Ref._ichild = _ichild
   Ref.octree2col_general = octree2col_general

@@ -18,6 +18,7 @@
 //   OctreeBaseConv<float>::forward_cpu_gemm  octree/octree/octree_conv.cpp:158-180
 //   OctreeBaseConv<float>::backward_cpu_gemm (the deconvolution's forward)  octree_conv.cpp:182-206
 //   col2octree_cpu / col2octreeP_cpu   octree/octree/octree_nn.cpp:216-241, 273-298
+//   xyz2key_cpu / key2xyz_cpu / search_key_cpu   octree/octree/octree_nn.cpp:540-620
 //   NeighHelper tables            octree/octree/octree_nn.cpp:6-108
 //   octree::get_one_octree        octree/octree/octree_samples.cpp:2168-2178
 
@@ -299,6 +300,12 @@ void ref_col2octreeP(const float* col, float* data, int channel, int height, int
                      const int* ichild, int height_col, int n) {
   col2octreeP_cpu<float>(col, data, channel, height, octree_h, kernel_sdim, stride, neigh, ni, child,
                          ichild, height_col, n);
+}
+
+void ref_xyz2key(uintk* key, const uintk* xyz, int num, int depth) { xyz2key_cpu<uintk>(key, xyz, num, depth); }
+void ref_key2xyz(uintk* xyz, const uintk* key, int num, int depth) { key2xyz_cpu<uintk>(xyz, key, num, depth); }
+void ref_search_key(int* idx, const uintk* key, int n_key, const uintk* query, int n_query) {
+  search_key_cpu<uintk>(idx, key, n_key, query, n_query);
 }
 
 }  // extern "C"

@@ -10,11 +10,13 @@ def to_cuda_u8(buf):
   return torch.from_numpy(np.ascontiguousarray(buf, np.uint8)).cuda()
 
 
-def data_cuda(x, node_major=False, bf16=False):
+def data_cuda(x, node_major=False, bf16=False, half=False):
   """[C,H] numpy -> [1,C,H,1] CUDA tensor in the requested dtype / memory layout."""
   t = torch.from_numpy(np.ascontiguousarray(x, np.float32)).cuda().view(1, x.shape[0], x.shape[1], 1)
   if bf16:
     t = t.to(torch.bfloat16)
+  if half:
+    t = t.to(torch.float16)
   if node_major:
     t = t.contiguous(memory_format=torch.channels_last)
   return t
@@ -27,6 +29,10 @@ def to_np(t):
 
 def bf16_round(x):
   return torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def half_round(x):
+  return torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(torch.float16).float().numpy()
 
 
 def rel_err(a, b):

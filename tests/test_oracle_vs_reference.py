@@ -235,3 +235,28 @@ def test_deconv_identities(batch):
       dense = oc.octree_conv_general(dense_in, w, merged_o, d, cout, ks, stride, False, True)
       want = oc.depad(dense, child_out, nne_out)
       assert np.allclose(got, want, atol=1e-6), (ks, stride)
+
+
+def test_keys_and_search(batch):
+  """xyz2key / key2xyz / search_key against the reference's CPU functions, and the known answers
+  of pytorch/test/test_octree_key.py:43-52 (round trip of coordinates wider than 32 key bits)."""
+  kb, R, merged_r, merged_o = batch
+  v = oc.OctreeView(merged_o)
+  rng = np.random.default_rng(4)
+  depth = 6
+  keys = v.prop('key', depth)
+  lane = 16 if kb == 64 else 8
+  xyz = R.key2xyz(keys, depth)
+  assert np.array_equal(xyz.astype(np.uint64), oc.key2xyz(keys, depth, kb))
+  assert np.array_equal(R.xyz2key(xyz, depth).astype(np.uint64), oc.xyz2key(xyz, depth, kb))
+  assert np.array_equal(oc.xyz2key(oc.key2xyz(keys, depth, kb), depth, kb), keys.astype(np.uint64))
+  # coordinates outside [0, 2^depth) wrap: only `depth` bits of each lane are used
+  wild = rng.integers(0, 1 << (4 * lane - 1), size=200).astype(np.uint64)
+  assert np.array_equal(R.xyz2key(wild, depth).astype(np.uint64), oc.xyz2key(wild, depth, kb))
+  query = np.concatenate([keys[::7], keys[:5] + 1, rng.integers(0, 1 << 20, size=50).astype(keys.dtype)])
+  assert np.array_equal(R.search_key(keys, query), oc.search_key(keys, query))
+  if kb == 64:
+    xyz64 = np.array([[2049, 4095, 8011, 1], [511, 4095, 8011, 0]], np.uint64)
+    word = xyz64[:, 0] | (xyz64[:, 1] << 16) | (xyz64[:, 2] << 32) | (xyz64[:, 3] << 48)
+    assert np.array_equal(oc.key2xyz(oc.xyz2key(word, 13), 13), word)
+    assert np.array_equal(R.xyz2key(word, 13), oc.xyz2key(word, 13))
