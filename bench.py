@@ -41,6 +41,8 @@ def parse_args():
   ap.add_argument('--no-tensor-core', action='store_true',
                   help='run every convolution on the CUDA-core kernel')
   ap.add_argument('--cpu-sample', type=int, default=32, help='shapes in the CPU baseline sample')
+  ap.add_argument('--forward-streams', type=int, default=2,
+                  help='network executors (each on its own stream) that consecutive batches alternate over')
   ap.add_argument('--conv-iters', type=int, default=50,
                   help='timed launches per shape of the OctreeConv TFLOP/s measurement')
   return ap.parse_args()
@@ -56,8 +58,9 @@ def workload_config(n_gpus):
           'l2': 'every timed step reads its points from the next of several device copies, together '
                 'larger than the 126 MB L2, and builds a fresh octree; nothing is flushed inside the '
                 'timed region',
-          'pipeline': 'octree build of step k+1 on a second CUDA stream while step k runs through '
-                      'the network; K builds and K forwards inside one event pair',
+          'pipeline': 'the octree builds run on their own CUDA stream, issued by a second host thread, '
+                      'up to three batches ahead; consecutive batches run through the network on '
+                      'alternating streams; K builds and K forwards inside one event pair',
           'deviation_from_reference_resnet': 'the named configuration puts blocks on depths 6..2 '
               '(512 channels at depth 2); the reference class pytorch/ocnn/resnet.py stops at depth 3 '
               '(256 channels)'}
@@ -416,36 +419,63 @@ def run_ours(args):
   build_stream = torch.cuda.Stream(device=dev)
   main_stream = torch.cuda.current_stream(dev)
 
+  # two network executors on two streams: consecutive batches alternate between them, so the few-CTA
+  # kernels of one batch's coarse levels share the GPU with the other batch's kernels
+  fwd_streams = [torch.cuda.Stream(device=dev) for _ in range(args.forward_streams)]
+  fwd_nets = [net] + [models.GpuNet(params, 'bf16', tensor_core=not args.no_tensor_core, device=dev)
+                      for _ in range(args.forward_streams - 1)]
+
   def pipelined(steps, src_of, on_result=None):
-    """K builds on build_stream, K forwards on the current stream; returns the device time from the
-    first build's start to the last forward's end."""
-    built = [torch.cuda.Event() for _ in range(steps)]
-    keep = []
+    """K builds on build_stream, issued by a builder thread; K forwards issued by this thread,
+    alternating over the forward streams.  The builder's one blocking read-back per build (the
+    node counts) then stalls neither the enqueueing of the network's kernels nor the GPU.  Returns
+    the device time from the first build's start to the last forward's end."""
+    import queue
+    import threading
+    ready = queue.Queue(maxsize=3)          # at most three octrees built ahead
+    failure = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(main_stream)
     build_stream.wait_event(e0)
+    for fs in fwd_streams:
+      fs.wait_event(e0)
 
-    def enqueue_build(k):
-      with torch.cuda.stream(build_stream):
-        oct_k = build(src_of(k))
-        built[k].record(build_stream)
-      oct_k.record_stream(main_stream)
-      return oct_k
+    def builder():
+      try:
+        torch.cuda.set_device(dev)
+        for k in range(steps):
+          with torch.cuda.stream(build_stream):
+            oct_k = build(src_of(k))
+            done = torch.cuda.Event()
+            done.record(build_stream)
+          ready.put((oct_k, done))
+      except BaseException as err:        # surface the error in the main thread
+        failure.append(err)
+        ready.put(None)
 
-    nxt = enqueue_build(0)
+    thread = threading.Thread(target=builder, daemon=True)
+    thread.start()
+    keep = []
     for k in range(steps):
-      cur = nxt
-      if k + 1 < steps:
-        nxt = enqueue_build(k + 1)
-      main_stream.wait_event(built[k])
-      out = net.forward(cur)
-      if on_result is not None:
-        on_result(k, out)
-      keep.append(cur)
-      if len(keep) > 3:
+      item = ready.get()
+      if item is None:
+        raise failure[0]
+      cur, done = item
+      fs = fwd_streams[k % len(fwd_streams)]
+      cur.record_stream(fs)
+      with torch.cuda.stream(fs):
+        fs.wait_event(done)
+        out = fwd_nets[k % len(fwd_nets)].forward(cur)
+        if on_result is not None:
+          on_result(k, out)
+      keep.append((cur, out))
+      if len(keep) > 4:
         keep.pop(0)
+    for fs in fwd_streams:
+      main_stream.wait_stream(fs)
     e1.record(main_stream)
+    thread.join()
     barrier()
     return max_over_ranks(e0.elapsed_time(e1))
 
@@ -455,19 +485,19 @@ def run_ours(args):
   total_ms = pipelined(args.steps, lambda k: inputs[k % nbuf])
   host_ms = (time.perf_counter() - t_host0) * 1e3
   launches = ocnn.nn.launch_count() - launches0
-  assert net.error_status() == 0, 'a kernel reported an error status'
+  assert all(n.error_status() == 0 for n in fwd_nets), 'a kernel reported an error status'
 
   # ---- end to end: pinned host points -> H2D -> build -> forward -> logits D2H, every step ----
   copy_stream = torch.cuda.Stream(device=dev)
-  stage = [torch.empty_like(packed_dev) for _ in range(3)]
-  copied = [torch.cuda.Event() for _ in range(3)]
-  logits_host = [torch.empty((BATCH, 40), dtype=torch.float32).pin_memory() for _ in range(2)]
+  stage = [torch.empty_like(packed_dev) for _ in range(6)]
+  copied = [torch.cuda.Event() for _ in range(6)]
+  logits_host = [torch.empty((BATCH, 40), dtype=torch.float32).pin_memory() for _ in range(4)]
 
   def e2e_src(k):
     # the H2D copy of batch k runs on the copy stream; the build waits for it.  A staging buffer is
-    # reused three steps later, when the build that read it has long finished (the builds are
-    # ordered on one stream and the host waits for each build's read-back).
-    slot = k % 3
+    # reused six steps later: the builder runs at most three octrees ahead of the network and each
+    # build has finished reading its input when its successor's read-back returns.
+    slot = k % 6
     with torch.cuda.stream(copy_stream):
       stage[slot].copy_(packed_host, non_blocking=True)
       copied[slot].record(copy_stream)
@@ -475,7 +505,7 @@ def run_ours(args):
     return stage[slot]
 
   def e2e_result(k, out):
-    logits_host[k & 1].copy_(out.float().reshape(BATCH, 40), non_blocking=True)
+    logits_host[k % 4].copy_(out.float().reshape(BATCH, 40), non_blocking=True)
 
   pipelined(3, e2e_src, e2e_result)
   e2e_ms = pipelined(args.steps, e2e_src, e2e_result)

@@ -401,6 +401,35 @@ int ocnn_octree_align_backward(const void* dst_grad_dev, void* src_grad_dev, con
                                int channels, int src_h, int dst_h, int dtype, int layout,
                                void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Point-cloud preparation on the device (the reference runs these on the CPU in its DataLoader
+ * workers before points2octree).  Replace PointsParser::displace / rotate / translate / scale /
+ * orient_normal / clip, octree/octree/points_parser.cpp:42-259, and bounding_box,
+ * octree/octree/math_functions.cpp:113-128 (bindings pytorch/cpp/transform_points.cpp:7-125).
+ * ------------------------------------------------------------------------------------------ */
+/* In place, in the reference's order: p += normal * offset (when offset > 1e-10 and normals
+ * exist); p, normal = R p, R normal (rot9: out[m] = sum_k rot9[k*3 + m] * in[k], or NULL);
+ * p += shift3 (or NULL); p *= scale3 (or NULL; with unequal factors the normals are divided by
+ * them and renormalised); normals flipped so that component orient-1 is >= 0 (orient 1..3), made
+ * non-negative per component (4) or left alone (0). */
+int ocnn_points_transform(float* xyz_dev, float* normal_dev, int64_t n, float offset,
+                          const float* rot9, const float* shift3, const float* scale3, int orient,
+                          void* stream);
+/* Keep, in order, the points strictly inside (bbmin, bbmax).  src/dst/channels: the four property
+ * blocks (xyz, normal, feature, label; channels[t] == 0 = absent) of the source and of the
+ * destination buffer (distinct memory).  mask_dev[i] = 1 for kept points; *pt_num_out_dev = their
+ * number — it may point at the pt_num field of the destination's header.  If no point is inside,
+ * one point at bbmin is kept (points_parser.cpp:169-175). */
+size_t ocnn_points_clip_workspace_bytes(int64_t n);
+int ocnn_points_clip(const float* const src_dev[4], float* const dst_dev[4], const int channels[4],
+                     int64_t n, const float bbmin[3], const float bbmax[3], int32_t* mask_dev,
+                     int32_t* pt_num_out_dev, void* workspace_dev, size_t workspace_bytes,
+                     void* stream);
+/* out6_dev = (min x, y, z, max x, y, z) of the n points. */
+size_t ocnn_points_bbox_workspace_bytes(void);
+int ocnn_points_bbox(const float* xyz_dev, int64_t n, float* out6_dev, void* workspace_dev,
+                     size_t workspace_bytes, void* stream);
+
 /* Feature block of the finest level (fp32 [C, nnum] channel-major, as stored in the octree) to the
  * bf16 node-major tensor [nnum, c_pad] the tensor-core convolution reads (channels >= C are 0).
  * Replaces the octree_property('feature') copy, pytorch/cpp/octree_property.cpp:89-97. */

@@ -24,7 +24,7 @@ struct PwArgs {
   int f16;                 // the 16-bit elements are fp16 instead of bf16
 };
 
-template <int COUT, int ROWS>
+template <int COUT, int ROWS, bool HALF>
 __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
   extern __shared__ float ws[];                      // [cin][COUT]
   grid_dependency_trigger();
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
         const uint32_t* p = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 f = unpack2(p[k], a.f16 != 0);
+          const float2 f = unpack2(p[k], HALF);
           xv[r][2 * k] = f.x;
           xv[r][2 * k + 1] = f.y;
         }
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
           const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rv);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float2 rf = unpack2(rp[j], a.f16 != 0);
+            const float2 rf = unpack2(rp[j], HALF);
             f[2 * j] += rf.x;
             f[2 * j + 1] += rf.y;
           }
@@ -106,15 +106,15 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
         uint4 ov;
         uint32_t* op = reinterpret_cast<uint32_t*>(&ov);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) op[j] = pack2(f[2 * j], f[2 * j + 1], a.f16 != 0);
+        for (int j = 0; j < 4; ++j) op[j] = pack2(f[2 * j], f[2 * j + 1], HALF);
         *reinterpret_cast<uint4*>(a.y + at) = ov;
       }
     }
   }
 }
 
-template <int COUT, int ROWS>
-int launch_pw(const PwArgs& a, cudaStream_t st) {
+template <int COUT, int ROWS, bool HALF>
+int launch_pw_t(const PwArgs& a, cudaStream_t st) {
   const size_t smem = (size_t)a.cin * COUT * sizeof(float);
   static PerDeviceOnce attr_once;      // one per template instance
   int device = 0;
@@ -123,15 +123,20 @@ int launch_pw(const PwArgs& a, cudaStream_t st) {
     std::lock_guard<std::mutex> lock(attr_once.mutex);
     const bool known = device >= 0 && device < 64;
     if (!known || !attr_once.done[device]) {
-      OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<COUT, ROWS>,
+      OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<COUT, ROWS, HALF>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
       if (known) attr_once.done[device] = true;
     }
   }
   const int grid = grid_for(((long long)a.h + ROWS - 1) / ROWS, 256, 4);
-  OCNN_CUDA_OK(launch_chained(conv_pw_kernel<COUT, ROWS>, dim3(grid), dim3(256), smem, st, a));
+  OCNN_CUDA_OK(launch_chained(conv_pw_kernel<COUT, ROWS, HALF>, dim3(grid), dim3(256), smem, st, a));
   OCNN_LAUNCH_OK("conv_pw_kernel");
   return OCNN_OK;
+}
+
+template <int COUT, int ROWS>
+int launch_pw(const PwArgs& a, cudaStream_t st) {
+  return a.f16 ? launch_pw_t<COUT, ROWS, true>(a, st) : launch_pw_t<COUT, ROWS, false>(a, st);
 }
 
 }  // namespace

@@ -242,7 +242,7 @@ __device__ __forceinline__ void chunk_src(int cpt, int kb, int chunk, int& t, ui
   }
 }
 
-template <int CPT>
+template <int CPT, bool HALF>
 __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of address bits [4,10)
@@ -522,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     // the wait for the accumulator.
     const int h = h0 + r;
     const bool row_ok = r < a.tile_rows && h < a.rows;
-    const bool f16 = a.f16 != 0;
+    constexpr bool f16 = HALF;
     const __nv_bfloat16* res_row =
         (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + co_base : nullptr;
     uint4 res_nxt[4];
@@ -619,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
       // instruction descriptor: D = F32 (bit 4), A = B = BF16 (bits 7, 10), both K-major,
       // N >> 3 at bit 17, M >> 4 at bit 24
       // (A/B format field: 0 = F16, 1 = BF16)
-      const uint32_t ab = a.f16 ? 0u : 1u;
+      const uint32_t ab = HALF ? 0u : 1u;
       const uint32_t idesc = (1u << 4) | (ab << 7) | (ab << 10) | ((uint32_t)(a.npad >> 3) << 17) |
                              ((uint32_t)(kTileM >> 4) << 24);
       bool alive = true;
@@ -999,26 +999,34 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   static PerDeviceOnce attr_once;
   int device = 0;
   OCNN_CUDA_OK(cudaGetDevice(&device));
-  void (*kernel)(const TcArgs) = conv_tc_kernel<0>;
+  typedef void (*KernelFn)(const TcArgs);
+  static const KernelFn table[2][8] = {
+      {conv_tc_kernel<0, false>, conv_tc_kernel<1, false>, conv_tc_kernel<2, false>,
+       conv_tc_kernel<4, false>, conv_tc_kernel<8, false>, conv_tc_kernel<16, false>,
+       conv_tc_kernel<32, false>, conv_tc_kernel<64, false>},
+      {conv_tc_kernel<0, true>, conv_tc_kernel<1, true>, conv_tc_kernel<2, true>,
+       conv_tc_kernel<4, true>, conv_tc_kernel<8, true>, conv_tc_kernel<16, true>,
+       conv_tc_kernel<32, true>, conv_tc_kernel<64, true>}};
+  int slot = 0;
   switch (a.cin >> 3) {
-    case 1: kernel = conv_tc_kernel<1>; break;
-    case 2: kernel = conv_tc_kernel<2>; break;
-    case 4: kernel = conv_tc_kernel<4>; break;
-    case 8: kernel = conv_tc_kernel<8>; break;
-    case 16: kernel = conv_tc_kernel<16>; break;
-    case 32: kernel = conv_tc_kernel<32>; break;
-    case 64: kernel = conv_tc_kernel<64>; break;
+    case 1: slot = 1; break;
+    case 2: slot = 2; break;
+    case 4: slot = 3; break;
+    case 8: slot = 4; break;
+    case 16: slot = 5; break;
+    case 32: slot = 6; break;
+    case 64: slot = 7; break;
     default: break;
   }
+  KernelFn kernel = table[a.f16][slot];
   {
     std::lock_guard<std::mutex> lock(attr_once.mutex);
     const bool known = device >= 0 && device < 64;
     if (!known || !attr_once.done[device]) {
-      void (*all[])(const TcArgs) = {conv_tc_kernel<0>, conv_tc_kernel<1>, conv_tc_kernel<2>,
-                                     conv_tc_kernel<4>, conv_tc_kernel<8>, conv_tc_kernel<16>,
-                                     conv_tc_kernel<32>, conv_tc_kernel<64>};
-      for (auto k : all)
-        OCNN_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+      for (int h = 0; h < 2; ++h)
+        for (int k = 0; k < 8; ++k)
+          OCNN_CUDA_OK(cudaFuncSetAttribute(table[h][k], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            220 * 1024));
       if (known) attr_once.done[device] = true;
     }
   }

@@ -21,7 +21,11 @@ from .nn import (octree_batch, octree_property, points2octree, points2octree_bat
                  points_pack, points2octree_packed, octree_info, set_key_bits, get_key_bits,
                  octree_encode_key, octree_decode_key, octree_search_key, octree_xyz2key,
                  octree_key2xyz)
-from .transforms import Points2Octree, collate_octrees
+from .nn import (transform_points, clip_points, normalize_points, bounding_sphere, points_property,
+                 points_batch_property, points_set_property)
+from .transforms import (Points2Octree, collate_octrees, NormalizePoints, TransformPoints,
+                         TransformCompose)
+from .io import read_points, write_points, read_octree, write_octree
 from .octree2voxel import FullOctree2Voxel
 from .octree2col import octree2col, Octree2Col, col2octree, Col2Octree
 from .octree_align import octree_align, OctreeAlign

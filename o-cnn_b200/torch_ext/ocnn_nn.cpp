@@ -17,6 +17,7 @@
 #include <torch/extension.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -932,6 +933,180 @@ Tensor points_new(Tensor pts, Tensor normals, Tensor features, Tensor labels) {
   return out;
 }
 
+// ---- transform_points / normalize_points / clip_points / bounding_sphere / points_property ----------
+// (pytorch/cpp/transform_points.cpp:7-125, points_property.cpp:90-190).  CPU point buffers are
+// uploaded; the results are CUDA tensors that points2octree takes as they are.
+PointsHeader read_points_header(const Tensor& points) {
+  TORCH_CHECK(points.scalar_type() == torch::kUInt8 && points.dim() == 1 && points.numel() >= 88,
+              "a points tensor must be a 1-D uint8 tensor with an 88-byte header");
+  Tensor head = points.slice(0, 0, 88).to(torch::kCPU).contiguous();
+  PointsHeader h;
+  memcpy(&h, head.data_ptr<uint8_t>(), 88);
+  TORCH_CHECK(strncmp(h.magic, "_POINTS_1.0_", 13) == 0, "The version of points format is not _POINTS_1.0_.");
+  TORCH_CHECK(h.pt_num > 0, "The pt_num_ should be larger than 0.");
+  TORCH_CHECK((h.content_flags & 1) && h.channels[0] == 3, "points need xyz coordinates");
+  TORCH_CHECK(h.ptr_dis[4] <= points.numel(), "the points tensor is shorter than its header says");
+  return h;
+}
+
+float* points_block(Tensor& buf, const PointsHeader& h, int t) {
+  return h.channels[t] > 0 ? reinterpret_cast<float*>(buf.data_ptr<uint8_t>() + h.ptr_dis[t]) : nullptr;
+}
+
+vector<float> three(vector<float> v, const char* what) {
+  TORCH_CHECK(!v.empty() && v.size() <= 3, what, " must hold 1 to 3 values");
+  while (v.size() < 3) v.push_back(v.back());
+  return v;
+}
+
+// rotation_matrix(rot, angles), octree/octree/math_functions.cpp:148-158: Rx * Ry * Rz in the
+// reference's column-major 3x3 product
+void euler_rotation(const float* angle, float* rot) {
+  // (the reference evaluates cos / sin in double and rounds the result)
+  const float cx = (float)cos((double)angle[0]), sx = (float)sin((double)angle[0]);
+  const float cy = (float)cos((double)angle[1]), sy = (float)sin((double)angle[1]);
+  const float cz = (float)cos((double)angle[2]), sz = (float)sin((double)angle[2]);
+  const float rx[9] = {1.f, 0, 0, 0, cx, sx, 0, -sx, cx};
+  const float ry[9] = {cy, 0, -sy, 0, 1.f, 0, sy, 0, cy};
+  const float rz[9] = {cz, sz, 0, -sz, cz, 0, 0, 0, 1.f};
+  auto prod = [](float* C, const float* A, const float* B) {
+    for (int n = 0; n < 3; ++n)
+      for (int m = 0; m < 3; ++m) {
+        C[n * 3 + m] = 0;
+        for (int k = 0; k < 3; ++k) C[n * 3 + m] += A[k * 3 + m] * B[n * 3 + k];
+      }
+  };
+  float tmp[9];
+  prod(tmp, rx, ry);
+  prod(rot, tmp, rz);
+}
+
+Tensor transform_points(Tensor data_in, vector<float> angle, vector<float> scale, vector<float> jitter,
+                        float offset, string normal_axis) {
+  PointsHeader h = read_points_header(data_in);
+  Tensor out = data_in.to(torch::kCUDA).contiguous().clone();
+  c10::cuda::CUDAGuard guard(out.device());
+  angle = three(angle, "angle"); scale = three(scale, "scale"); jitter = three(jitter, "jitter");
+  const float eps = 1.0e-10f;
+  float rot[9];
+  const bool do_rot = fabsf(angle[0]) > eps || fabsf(angle[1]) > eps || fabsf(angle[2]) > eps;
+  if (do_rot) euler_rotation(angle.data(), rot);
+  const bool do_jit = fabsf(jitter[0]) > eps || fabsf(jitter[1]) > eps || fabsf(jitter[2]) > eps;
+  const bool do_scale = scale[0] != 1.0f || scale[1] != 1.0f || scale[2] != 1.0f;
+  int orient = 0;
+  if (normal_axis == "x") orient = 1;
+  else if (normal_axis == "y") orient = 2;
+  else if (normal_axis == "z") orient = 3;
+  else if (normal_axis == "xyz") orient = 4;
+  OCNN_CALL(ocnn_points_transform(points_block(out, h, 0), points_block(out, h, 1), h.pt_num, offset,
+                                  do_rot ? rot : nullptr, do_jit ? jitter.data() : nullptr,
+                                  do_scale ? scale.data() : nullptr, orient, current_stream()));
+  return out;
+}
+
+Tensor normalize_points(Tensor data_in, float radius, vector<float> center) {
+  TORCH_CHECK(radius >= 0.0f, "normalize_points: the radius must not be negative");
+  TORCH_CHECK(center.size() == 3, "normalize_points: center must hold 3 values");
+  PointsHeader h = read_points_header(data_in);
+  Tensor out = data_in.to(torch::kCUDA).contiguous().clone();
+  c10::cuda::CUDAGuard guard(out.device());
+  const float dis[3] = {-center[0], -center[1], -center[2]};
+  const bool do_shift = dis[0] != 0.0f || dis[1] != 0.0f || dis[2] != 0.0f;
+  const float inv = 1.0f / radius;
+  const float sc[3] = {inv, inv, inv};
+  OCNN_CALL(ocnn_points_transform(points_block(out, h, 0), points_block(out, h, 1), h.pt_num, 0.f, nullptr,
+                                  do_shift ? dis : nullptr, inv != 1.0f ? sc : nullptr, 0, current_stream()));
+  return out;
+}
+
+vector<Tensor> clip_points(Tensor data_in, vector<float> bbmin, vector<float> bbmax) {
+  TORCH_CHECK(bbmin.size() == 3 && bbmax.size() == 3, "clip_points: bbmin / bbmax must hold 3 values");
+  PointsHeader h = read_points_header(data_in);
+  Tensor src = data_in.to(torch::kCUDA).contiguous();
+  c10::cuda::CUDAGuard guard(src.device());
+  Tensor out = src.clone();      // header and (for an all-inside cloud) every block already in place
+  const float* sp[4]; float* dp[4]; int ch[4];
+  for (int t = 0; t < 4; ++t) {
+    ch[t] = h.channels[t];
+    sp[t] = points_block(src, h, t);
+    dp[t] = points_block(out, h, t);
+  }
+  Tensor mask = torch::empty({(int64_t)h.pt_num}, src.options().dtype(torch::kInt32));
+  const size_t ws_bytes = ocnn_points_clip_workspace_bytes(h.pt_num);
+  Tensor ws = torch::empty({(int64_t)ws_bytes}, src.options());
+  int32_t* pt_num_dev = reinterpret_cast<int32_t*>(out.data_ptr<uint8_t>() + 16);   // PointsInfo::pt_num_
+  OCNN_CALL(ocnn_points_clip(sp, dp, ch, h.pt_num, bbmin.data(), bbmax.data(), mask.data_ptr<int32_t>(),
+                             pt_num_dev, ws.data_ptr(), ws_bytes, current_stream()));
+  return {out, mask};
+}
+
+vector<float> bounding_sphere(Tensor data_in, string method) {
+  TORCH_CHECK(method != "sphere", "bounding_sphere(method='sphere') needs the reference's external "
+              "Miniball code and is not implemented; use method='box'");
+  PointsHeader h = read_points_header(data_in);
+  Tensor src = data_in.to(torch::kCUDA).contiguous();
+  c10::cuda::CUDAGuard guard(src.device());
+  const size_t ws_bytes = ocnn_points_bbox_workspace_bytes();
+  Tensor ws = torch::empty({(int64_t)ws_bytes}, src.options());
+  Tensor box = torch::empty({6}, src.options().dtype(torch::kFloat32));
+  OCNN_CALL(ocnn_points_bbox(points_block(src, h, 0), h.pt_num, box.data_ptr<float>(), ws.data_ptr(),
+                             ws_bytes, current_stream()));
+  Tensor b = box.cpu();
+  const float* p = b.data_ptr<float>();
+  float radius = 0.f, center[3];
+  for (int j = 0; j < 3; ++j) {
+    center[j] = (p[3 + j] + p[j]) / 2.0f;
+    const float width = (p[3 + j] - p[j]) / 2.0f;
+    radius += width * width;
+  }
+  radius = sqrtf(radius + 1.0e-20f);
+  return {radius, center[0], center[1], center[2]};
+}
+
+int points_prop_index(const string& property) {
+  if (property == "xyz" || property == "xyzi") return 0;
+  if (property == "normal") return 1;
+  if (property == "feature") return 2;
+  if (property == "label") return 3;
+  TORCH_CHECK(false, "Unsupported Property: ", property);
+  return -1;
+}
+
+Tensor points_property(Tensor points, string property) {
+  PointsHeader h = read_points_header(points);
+  const int t = points_prop_index(property);
+  if (h.channels[t] == 0) return Tensor();
+  Tensor buf = points.contiguous();
+  return buf.slice(0, h.ptr_dis[t], h.ptr_dis[t] + (int64_t)4 * h.pt_num * h.channels[t])
+      .clone().view(torch::kFloat32).view({h.pt_num, h.channels[t]});
+}
+
+Tensor points_batch_property(vector<Tensor> tensors, string property) {
+  TORCH_CHECK(!tensors.empty(), "points_batch_property: empty input");
+  vector<Tensor> parts;
+  for (size_t i = 0; i < tensors.size(); ++i) {
+    Tensor p = points_property(tensors[i], property);
+    TORCH_CHECK(p.defined(), "The specified property does not exist.");
+    if (property == "xyzi")
+      p = torch::cat({p, torch::full({p.size(0), 1}, (double)i, p.options())}, 1);
+    parts.push_back(p);
+  }
+  return torch::cat(parts, 0);
+}
+
+Tensor points_set_property(Tensor points_in, Tensor data, string property) {
+  TORCH_CHECK(data.dim() == 2, "points_set_property: data must be [N, C]");
+  PointsHeader h = read_points_header(points_in);
+  const int t = points_prop_index(property);
+  TORCH_CHECK(h.channels[t] > 0, "The property does not exist.");
+  TORCH_CHECK(data.size(1) == h.channels[t], "The channel is wrong.");
+  TORCH_CHECK(data.size(0) == h.pt_num, "The point number is wrong.");
+  Tensor out = points_in.contiguous().clone();
+  Tensor bytes = data.to(out.device(), torch::kFloat32).contiguous().view({-1}).view(torch::kUInt8);
+  out.slice(0, h.ptr_dis[t], h.ptr_dis[t] + bytes.numel()).copy_(bytes);
+  return out;
+}
+
 struct CloudInfo { int64_t byte_offset; PointsHeader h; };
 
 void check_points_header(const PointsHeader& h, int64_t nbytes) {
@@ -1470,11 +1645,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("octree_max_pool", &octree_max_pool, "octree max pooling");
   m.def("octree_max_pool_pad", &octree_max_pool_pad, "octree max pooling + pad to depth - 1 (bf16 node-major)");
   m.def("points_new", &points_new, "create a point cloud");
+  m.def("transform_points", &transform_points, "transform the point cloud");
+  m.def("clip_points", &clip_points, "clip the points with unit boundingbox");
+  m.def("normalize_points", &normalize_points, "normalize the point cloud");
+  m.def("bounding_sphere", &bounding_sphere, "calc the bounding sphere");
+  m.def("points_property", &points_property, "get the points' property");
+  m.def("points_batch_property", &points_batch_property, "get batch of points' property");
+  m.def("points_set_property", &points_set_property, "set the points' property");
   // additions of this implementation
   m.def("points2octree_batch", &points2octree_batch,
         "build the merged batch octree of a list of point clouds in one pass");
   m.def("points_pack", &points_pack, py::arg("points"), py::arg("pin") = false);
-  m.def("points2octree_packed", &points2octree_packed);
+  // (the GIL is released: the build blocks once on its stream, and a second Python thread may be
+  // enqueueing a forward pass meanwhile)
+  m.def("points2octree_packed", &points2octree_packed, py::call_guard<py::gil_scoped_release>());
   m.def("octree_conv_fused", &octree_conv_fused, py::arg("data_in"), py::arg("weights"),
         py::arg("octree"), py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"),
         py::arg("stride"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
@@ -1536,7 +1720,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("output") = 0, py::arg("residual") = -1, py::arg("pointwise_above") = -1)
       .def("add_pool", &NetExecutor::add_pool)
       .def("set_trace", &NetExecutor::set_trace)
-      .def("forward", &NetExecutor::forward)
+      .def("forward", &NetExecutor::forward, py::call_guard<py::gil_scoped_release>())
       .def("trace_ms", &NetExecutor::trace_ms)
       .def("op_names", &NetExecutor::op_names)
       .def("status", &NetExecutor::status);

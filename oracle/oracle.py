@@ -419,6 +419,112 @@ def octree_interp(data, octree, depth, pts, method='linear', nempty=False):
   return (out / (norm + np.float32(1e-10))[None, :]).astype(np.float32)
 
 
+# ---- point-cloud preparation (octree/octree/points_parser.cpp:42-259) -------------------------------
+def _points_blocks(buf):
+  """Views (xyz, normal, feature, label) into a points buffer, None where absent; and pt_num."""
+  npt = int(buf[16:20].view(np.int32)[0])
+  channels = buf[24:56].view(np.int32)
+  ptr_dis = buf[56:88].view(np.int32)
+  out = []
+  for t in range(4):
+    c = int(channels[t])
+    out.append(None if c == 0 else buf[ptr_dis[t]:ptr_dis[t] + 4 * npt * c].view(np.float32).reshape(npt, c))
+  return out, npt
+
+
+def _matrix_prod3(A, B):
+  """matrix_prod of two column-major 3x3 matrices, math_functions.cpp:185-196, in fp32."""
+  C = np.zeros(9, np.float32)
+  for n in range(3):
+    for m in range(3):
+      acc = np.float32(0)
+      for k in range(3):
+        acc = np.float32(acc + np.float32(A[k * 3 + m] * B[n * 3 + k]))
+      C[n * 3 + m] = acc
+  return C
+
+
+def rotation_matrix(angle):
+  """rotation_matrix(rot, angles), math_functions.cpp:148-158 (cos / sin evaluated in double)."""
+  c = [np.float32(np.cos(np.float64(np.float32(a)))) for a in angle]
+  s = [np.float32(np.sin(np.float64(np.float32(a)))) for a in angle]
+  z, o = np.float32(0), np.float32(1)
+  rx = np.array([o, z, z, z, c[0], s[0], z, -s[0], c[0]], np.float32)
+  ry = np.array([c[1], z, -s[1], z, o, z, s[1], z, c[1]], np.float32)
+  rz = np.array([c[2], s[2], z, -s[2], c[2], z, z, z, o], np.float32)
+  return _matrix_prod3(_matrix_prod3(rx, ry), rz)
+
+
+def _apply3(rot, v):
+  out = np.zeros_like(v)
+  for m in range(3):
+    acc = np.zeros(v.shape[0], np.float32)
+    for k in range(3):
+      acc = acc + rot[k * 3 + m] * v[:, k]
+    out[:, m] = acc
+  return out
+
+
+def transform_points(points, angle, scale, jitter, offset, normal_axis=''):
+  """transform_points, pytorch/cpp/transform_points.cpp:71-108, on a copy of the buffer."""
+  buf = np.array(points, dtype=np.uint8, copy=True)
+  (xyz, nrm, _, _), npt = _points_blocks(buf)
+  eps = np.float32(1.0e-10)
+  angle, scale, jitter = _f32(angle), _f32(scale), _f32(jitter)
+  offset = np.float32(offset)
+  if offset > eps and nrm is not None:
+    xyz += nrm * offset
+  if np.any(np.abs(angle) > eps):
+    rot = rotation_matrix(angle)
+    xyz[:] = _apply3(rot, xyz)
+    if nrm is not None:
+      nrm[:] = _apply3(rot, nrm)
+  if np.any(np.abs(jitter) > eps):
+    xyz += jitter[None, :]
+  if np.any(scale != 1) and not np.any(scale == 0):
+    xyz *= scale[None, :]
+    if not (scale[0] == scale[1] == scale[2]) and nrm is not None:
+      nrm *= (np.float32(1.0) / scale)[None, :]
+      length = np.zeros(npt, np.float32)
+      for m in range(3):
+        length = length + nrm[:, m] * nrm[:, m]
+      inv = np.float32(1.0) / (np.sqrt(length) + np.float32(1.0e-15))
+      nrm *= inv[:, None]
+  if nrm is not None and normal_axis in ('x', 'y', 'z'):
+    j = 'xyz'.index(normal_axis)
+    nrm[nrm[:, j] < 0] *= np.float32(-1)
+  elif nrm is not None and normal_axis == 'xyz':
+    nrm[:] = np.where(nrm < 0, -nrm, nrm)
+  return buf
+
+
+def clip_points(points, bbmin, bbmax):
+  """clip_points, transform_points.cpp:110-125 / PointsParser::clip: (buffer, in-box mask)."""
+  buf = np.array(points, dtype=np.uint8, copy=True)
+  blocks, npt = _points_blocks(buf)
+  xyz = blocks[0]
+  lo, hi = _f32(bbmin), _f32(bbmax)
+  inside = np.all((lo[None, :] < xyz) & (xyz < hi[None, :]), axis=1)
+  mask = inside.astype(np.int32)
+  if inside.all():
+    return buf, mask
+  if not inside.any():
+    mask[0] = 1
+    inside = mask.astype(bool)
+    xyz[0] = lo
+  kept = int(inside.sum())
+  for b in blocks:
+    if b is not None:
+      b[:kept] = b[inside]
+  buf[16:20].view(np.int32)[0] = kept
+  return buf, mask
+
+
+def bounding_box(xyz):
+  xyz = _f32(xyz).reshape(-1, 3)
+  return np.concatenate([xyz.min(axis=0), xyz.max(axis=0)]).astype(np.float32)
+
+
 def max_pool(btm):
   btm = _f32(btm)
   channel, btm_h = btm.shape

@@ -90,6 +90,10 @@ class Ref:
     L.ref_xyz2key.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     L.ref_key2xyz.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     L.ref_search_key.argtypes = [c_int_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    L.ref_transform_points.argtypes = [ctypes.c_char_p, c_float_p, c_float_p, c_float_p,
+                                       ctypes.c_float, ctypes.c_char_p]
+    L.ref_clip_points.argtypes = [ctypes.c_char_p, c_float_p, c_float_p, c_int_p]
+    L.ref_bounding_box.argtypes = [c_float_p, ctypes.c_int, c_float_p]
     L.ref_set_gemm.argtypes = [ctypes.c_void_p]
     self._gemm_cb = None
 
@@ -308,6 +312,28 @@ def _general_methods():
                             query.ctypes.data_as(ctypes.c_void_p), query.size)
     return idx
 
+  def transform_points(self, points, angle, scale, jitter, offset, normal_axis=''):
+    buf = ctypes.create_string_buffer(np.ascontiguousarray(points, np.uint8).tobytes())
+    a, sc, j = _f32(angle), _f32(scale), _f32(jitter)
+    self.lib.ref_transform_points(buf, _fp(a), _fp(sc), _fp(j), ctypes.c_float(offset),
+                                  normal_axis.encode())
+    return np.frombuffer(buf.raw[:len(points)], np.uint8).copy()
+
+  def clip_points(self, points, bbmin, bbmax):
+    buf = ctypes.create_string_buffer(np.ascontiguousarray(points, np.uint8).tobytes())
+    npt = int(np.frombuffer(buf.raw[16:20], np.int32)[0])
+    mask = np.zeros(npt, np.int32)
+    lo, hi = _f32(bbmin), _f32(bbmax)
+    self.lib.ref_clip_points(buf, _fp(lo), _fp(hi), _ip(mask))
+    return np.frombuffer(buf.raw[:len(points)], np.uint8).copy(), mask
+
+  def bounding_box(self, xyz):
+    xyz = _f32(xyz)
+    out = np.zeros(6, np.float32)
+    self.lib.ref_bounding_box(_fp(xyz), xyz.size // 3, _fp(out))
+    return out
+
+  Ref.transform_points, Ref.clip_points, Ref.bounding_box = transform_points, clip_points, bounding_box
   Ref._keys, Ref.xyz2key, Ref.key2xyz, Ref.search_key = _keys, xyz2key, key2xyz, search_key
   Ref.octree_conv_general = octree_conv_general
   Ref._ichild = _ichild

@@ -19,9 +19,13 @@
 //   OctreeBaseConv<float>::backward_cpu_gemm (the deconvolution's forward)  octree_conv.cpp:182-206
 //   col2octree_cpu / col2octreeP_cpu   octree/octree/octree_nn.cpp:216-241, 273-298
 //   xyz2key_cpu / key2xyz_cpu / search_key_cpu   octree/octree/octree_nn.cpp:540-620
+//   PointsParser::displace / rotate / translate / scale / orient_normal / clip
+//                                 octree/octree/points_parser.cpp:42-259
+//   bounding_box                  octree/octree/math_functions.cpp:113-128
 //   NeighHelper tables            octree/octree/octree_nn.cpp:6-108
 //   octree::get_one_octree        octree/octree/octree_samples.cpp:2168-2178
 
+#include <cmath>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -31,6 +35,7 @@
 #include "octree_conv.h"
 #include "octree_nn.h"
 #include "octree_samples.h"
+#include "math_functions.h"
 #include "points.h"
 
 // OctreeBaseConv's CPU im2col wrapper names OctreeParser::neighbor_gpu on its non-empty branch
@@ -307,5 +312,30 @@ void ref_key2xyz(uintk* xyz, const uintk* key, int num, int depth) { key2xyz_cpu
 void ref_search_key(int* idx, const uintk* key, int n_key, const uintk* query, int n_query) {
   search_key_cpu<uintk>(idx, key, n_key, query, n_query);
 }
+
+// transform_points as pytorch/cpp/transform_points.cpp:71-108 drives the Points methods, in place on
+// a copy of the buffer the caller made.
+void ref_transform_points(char* buf, const float* angle, const float* scale, const float* jitter,
+                          float offset, const char* normal_axis) {
+  Points pts;
+  pts.set(buf);
+  const float kEPS = 1.0e-10f;
+  if (offset > kEPS) pts.displace(offset);
+  if (std::fabs(angle[0]) > kEPS || std::fabs(angle[1]) > kEPS || std::fabs(angle[2]) > kEPS) pts.rotate(angle);
+  if (std::fabs(jitter[0]) > kEPS || std::fabs(jitter[1]) > kEPS || std::fabs(jitter[2]) > kEPS) pts.translate(jitter);
+  if (scale[0] != 1.0f || scale[1] != 1.0f || scale[2] != 1.0f) pts.scale(scale);
+  std::string axis(normal_axis);
+  if (!axis.empty()) pts.orient_normal(axis);
+}
+
+// clip_points (transform_points.cpp:110-125): in place; mask receives the in-box flags.
+void ref_clip_points(char* buf, const float* bbmin, const float* bbmax, int* mask) {
+  Points pts;
+  pts.set(buf);
+  const std::vector<int> in = pts.clip(bbmin, bbmax);
+  memcpy(mask, in.data(), in.size() * sizeof(int));
+}
+
+void ref_bounding_box(const float* pt, int npt, float* out6) { bounding_box(out6, out6 + 3, pt, npt); }
 
 }  // extern "C"

@@ -123,9 +123,8 @@ def test_conv_errors(ocnn, batch):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [4], 1)
   with pytest.raises(RuntimeError, match='stride'):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [3], 3)
-  with pytest.raises(RuntimeError, match='stride 1'):       # nempty: stride 1 only
-    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[5]), 1, device='cuda'), w, octree, 5, 4,
-                     [3], 2, True)
+  with pytest.raises(RuntimeError, match='data height'):    # nempty: rows = non-empty nodes
+    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[5]), 1, device='cuda'), w, octree, 5, 4, [3], 2, True)
 
 
 # ---- tensor-core (tcgen05) path -----------------------------------------------------------------

@@ -260,3 +260,36 @@ def test_keys_and_search(batch):
     word = xyz64[:, 0] | (xyz64[:, 1] << 16) | (xyz64[:, 2] << 32) | (xyz64[:, 3] << 48)
     assert np.array_equal(oc.key2xyz(oc.xyz2key(word, 13), 13), word)
     assert np.array_equal(R.xyz2key(word, 13), oc.xyz2key(word, 13))
+
+
+def test_point_preparation():
+  """transform_points / clip_points / bounding_box: the numpy restatement against the reference's
+  Points methods, bit for bit."""
+  R = ref.get(64)
+  rng = np.random.default_rng(12)
+  p, q = synth.primitive_union(3000, 31)
+  f = rng.normal(size=(3000, 2)).astype(np.float32)
+  lab = rng.integers(0, 5, size=3000).astype(np.float32)
+  for normals in (q, None):
+    pts = oc.points_new(p, normals, f, lab)
+    cases = [([0.3, -0.2, 1.1], [1.0, 1.0, 1.0], [0.0, 0.0, 0.0], 0.0, ''),
+             ([0.0, 0.0, 0.0], [0.8, 0.8, 0.8], [0.01, -0.02, 0.03], 0.02, 'x'),
+             ([0.5, 0.25, -0.75], [0.9, 1.1, 0.7], [0.05, 0.0, 0.0], 0.0, 'xyz'),
+             ([0.0, 0.0, 0.2], [1.0, 2.0, 1.0], [0.0, 0.0, 0.0], 0.001, 'z')]
+    for angle, scale, jitter, offset, axis in cases:
+      a = R.transform_points(pts, angle, scale, jitter, offset, axis)
+      b = oc.transform_points(pts, angle, scale, jitter, offset, axis)
+      assert same_bits(a, b), (angle, scale, jitter, offset, axis, normals is None)
+    for lo, hi in (([-1, -1, -1], [1, 1, 1]), ([-0.3, -0.5, -0.2], [0.4, 0.6, 0.9]), ([2, 2, 2], [3, 3, 3])):
+      a, ma = R.clip_points(pts, lo, hi)
+      b, mb = oc.clip_points(pts, lo, hi)
+      assert np.array_equal(ma, mb)
+      kept = int(b[16:20].view(np.int32)[0])
+      assert int(a[16:20].view(np.int32)[0]) == kept == max(1, int(mb.sum()))
+      (xa, na, fa, la), _ = oc._points_blocks(a)
+      (xb, nb, fb, lb), _ = oc._points_blocks(b)
+      for u, v in ((xa, xb), (na, nb), (fa, fb), (la, lb)):
+        assert (u is None) == (v is None)
+        if u is not None:
+          assert same_bits(u[:kept], v[:kept])
+  assert same_bits(R.bounding_box(p), oc.bounding_box(p))
