@@ -41,6 +41,8 @@ def parse_args():
   ap.add_argument('--no-tensor-core', action='store_true',
                   help='run every convolution on the CUDA-core kernel')
   ap.add_argument('--cpu-sample', type=int, default=32, help='shapes in the CPU baseline sample')
+  ap.add_argument('--build-streams', type=int, default=2,
+                  help='builder threads, each with its own high-priority stream')
   ap.add_argument('--forward-streams', type=int, default=2,
                   help='network executors (each on its own stream) that consecutive batches alternate over')
   ap.add_argument('--conv-iters', type=int, default=50,
@@ -58,8 +60,8 @@ def workload_config(n_gpus):
           'l2': 'every timed step reads its points from the next of several device copies, together '
                 'larger than the 126 MB L2, and builds a fresh octree; nothing is flushed inside the '
                 'timed region',
-          'pipeline': 'the octree builds run on their own CUDA stream, issued by a second host thread, '
-                      'up to three batches ahead; consecutive batches run through the network on '
+          'pipeline': 'the octree builds are issued by builder threads on their own high-priority CUDA '
+                      'streams, a few batches ahead; consecutive batches run through the network on '
                       'alternating streams; K builds and K forwards inside one event pair',
           'deviation_from_reference_resnet': 'the named configuration puts blocks on depths 6..2 '
               '(512 channels at depth 2); the reference class pytorch/ocnn/resnet.py stops at depth 3 '
@@ -416,7 +418,6 @@ def run_ours(args):
   l2_bytes = 126 << 20
   nbuf = max(2, -(-int(1.25 * l2_bytes) // int(packed_dev.numel())))
   inputs = [packed_dev] + [packed_dev.clone() for _ in range(nbuf - 1)]
-  build_stream = torch.cuda.Stream(device=dev)
   main_stream = torch.cuda.current_stream(dev)
 
   # two network executors on two streams: consecutive batches alternate between them, so the few-CTA
@@ -425,40 +426,48 @@ def run_ours(args):
   fwd_nets = [net] + [models.GpuNet(params, 'bf16', tensor_core=not args.no_tensor_core, device=dev)
                       for _ in range(args.forward_streams - 1)]
 
+  build_streams = [torch.cuda.Stream(device=dev, priority=-1) for _ in range(args.build_streams)]
+  host_split = {}
+
   def pipelined(steps, src_of, on_result=None):
-    """K builds on build_stream, issued by a builder thread; K forwards issued by this thread,
-    alternating over the forward streams.  The builder's one blocking read-back per build (the
-    node counts) then stalls neither the enqueueing of the network's kernels nor the GPU.  Returns
-    the device time from the first build's start to the last forward's end."""
+    """K builds issued by builder threads (batch k by thread k mod B, each on its own
+    high-priority stream: the builder is a chain of short dependent kernels with one blocking
+    read-back, so its latency, not its work, limits how fast octrees arrive); K forwards issued by
+    this thread, alternating over the forward streams.  Returns the device time from the first
+    build's start to the last forward's end."""
     import queue
     import threading
-    ready = queue.Queue(maxsize=3)          # at most three octrees built ahead
+    nb = len(build_streams)
+    ready = [queue.Queue(maxsize=2) for _ in range(nb)]      # octrees built ahead, per builder
     failure = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(main_stream)
-    build_stream.wait_event(e0)
-    for fs in fwd_streams:
-      fs.wait_event(e0)
+    for st in build_streams + fwd_streams:
+      st.wait_event(e0)
 
-    def builder():
+    def builder(b):
       try:
         torch.cuda.set_device(dev)
-        for k in range(steps):
-          with torch.cuda.stream(build_stream):
-            oct_k = build(src_of(k))
+        for k in range(b, steps, nb):
+          with torch.cuda.stream(build_streams[b]):
+            oct_k = build(src_of(k, build_streams[b]))
             done = torch.cuda.Event()
-            done.record(build_stream)
-          ready.put((oct_k, done))
+            done.record(build_streams[b])
+          ready[b].put((oct_k, done))
       except BaseException as err:        # surface the error in the main thread
         failure.append(err)
-        ready.put(None)
+        ready[b].put(None)
 
-    thread = threading.Thread(target=builder, daemon=True)
-    thread.start()
+    threads = [threading.Thread(target=builder, args=(b,), daemon=True) for b in range(nb)]
+    for t in threads:
+      t.start()
     keep = []
+    waited = enq = 0.0
     for k in range(steps):
-      item = ready.get()
+      t0 = time.perf_counter()
+      item = ready[k % nb].get()
+      t1 = time.perf_counter()
       if item is None:
         raise failure[0]
       cur, done = item
@@ -472,36 +481,42 @@ def run_ours(args):
       keep.append((cur, out))
       if len(keep) > 4:
         keep.pop(0)
+      waited += t1 - t0
+      enq += time.perf_counter() - t1
     for fs in fwd_streams:
       main_stream.wait_stream(fs)
     e1.record(main_stream)
-    thread.join()
+    for t in threads:
+      t.join()
     barrier()
+    host_split.update({'wait_for_octree_ms_per_step': 1e3 * waited / steps,
+                       'forward_enqueue_ms_per_step': 1e3 * enq / steps})
     return max_over_ranks(e0.elapsed_time(e1))
 
-  pipelined(max(args.warmup, 3), lambda k: inputs[k % nbuf])
+  pipelined(max(args.warmup, 3), lambda k, st: inputs[k % nbuf])
   launches0 = ocnn.nn.launch_count()
   t_host0 = time.perf_counter()
-  total_ms = pipelined(args.steps, lambda k: inputs[k % nbuf])
+  total_ms = pipelined(args.steps, lambda k, st: inputs[k % nbuf])
+  host_split_timed = dict(host_split)
   host_ms = (time.perf_counter() - t_host0) * 1e3
   launches = ocnn.nn.launch_count() - launches0
   assert all(n.error_status() == 0 for n in fwd_nets), 'a kernel reported an error status'
 
   # ---- end to end: pinned host points -> H2D -> build -> forward -> logits D2H, every step ----
   copy_stream = torch.cuda.Stream(device=dev)
-  stage = [torch.empty_like(packed_dev) for _ in range(6)]
-  copied = [torch.cuda.Event() for _ in range(6)]
+  stage = [torch.empty_like(packed_dev) for _ in range(8)]
+  copied = [torch.cuda.Event() for _ in range(8)]
   logits_host = [torch.empty((BATCH, 40), dtype=torch.float32).pin_memory() for _ in range(4)]
 
-  def e2e_src(k):
+  def e2e_src(k, bstream):
     # the H2D copy of batch k runs on the copy stream; the build waits for it.  A staging buffer is
-    # reused six steps later: the builder runs at most three octrees ahead of the network and each
-    # build has finished reading its input when its successor's read-back returns.
-    slot = k % 6
+    # reused eight steps later, when the build that read it has long been consumed (the builders run
+    # at most two octrees ahead each).
+    slot = k % 8
     with torch.cuda.stream(copy_stream):
       stage[slot].copy_(packed_host, non_blocking=True)
       copied[slot].record(copy_stream)
-    build_stream.wait_event(copied[slot])
+    bstream.wait_event(copied[slot])
     return stage[slot]
 
   def e2e_result(k, out):
@@ -514,7 +529,7 @@ def run_ours(args):
 
   # ---- sustained: the pipelined step back to back for about two seconds (clocks sampled over it) ----
   sustained_steps = int(max(200, min(4000, 2000.0 / max(total_ms / args.steps, 0.05))))
-  sustained_ms = pipelined(sustained_steps, lambda k: inputs[k % nbuf])
+  sustained_ms = pipelined(sustained_steps, lambda k, st: inputs[k % nbuf])
 
   extras = {}
   if rank == 0:
@@ -662,6 +677,8 @@ def run_ours(args):
           'tensor_core_layers': sum(1 for _, p in models.conv_layers(net.net) if p.get('_packed') is not None),
           'layer_ms': {k: round(v, 4) for k, v in layer_ms.items()},
           'finest_nodes': int(nnum[DEPTH]), 'host_ms_per_step': host_ms / args.steps,
+          'host_split': host_split_timed,
+          'streams': {'build': args.build_streams, 'forward': args.forward_streams},
           'input_rotation': {'device_copies': nbuf, 'bytes_each': int(packed_dev.numel()),
                              'l2_bytes': l2_bytes}}
   line.update(extras)

@@ -239,6 +239,29 @@ int ocnn_octree_conv_general(const void* x_dev, const float* weights_dev, void* 
                              const int kernel_size[3], int dtype, int layout,
                              const ocnn_conv_epilogue* epilogue, void* stream);
 
+/* Training support.  The gradient with respect to the data of a convolution is the deconvolution
+ * with the same weights and vice versa (ocnn_octree_conv_general with `transposed` flipped).  The
+ * gradient with respect to the weights, replacing OctreeBaseConv::weight_gpu_gemm
+ * (octree/octree/octree_conv.cpp:332-360: octree2col_gpu + GEMM), is
+ *     dw[m, c*K + k] = sum_h a[m, h] * x[c, nbr(h, k)]
+ * where `geometry` is the CONVOLUTION-type gather (transposed = 0) of the layer's column matrix:
+ * x has geometry->h_in rows, a has geometry->h_out rows.  Convolution: a = output gradient
+ * [Cout, h_out], x = layer input [Cin, h_in], dw = [Cout, Cin*K].  Deconvolution at depth d: a =
+ * layer input [Cin, .], x = output gradient [Cout, .], geometry = that of the convolution from the
+ * output level back to the input level, dw = [Cin, Cout*K].  fp32 data in either layout; dw is
+ * cleared and then accumulated with atomic additions. */
+int ocnn_octree_conv_weight_grad(const float* a_dev, const float* x_dev, float* dw_dev,
+                                 const ocnn_conv_geometry* geometry, int m_channels, int x_channels,
+                                 const int kernel_size[3], int layout, void* stream);
+/* The transposes of the max-pool through its argmax mask.  Replace octree_max_unpool_gpu /
+ * octree_mask_pool_gpu, octree/octree/octree_nn.cu:293-329 (bindings pytorch/cpp/octree_pool.cpp:
+ * 36-95).  top, mask: [C, top_h]; btm: [C, 8*top_h]; fp32.  unpool: btm = 0, btm[., mask] = top;
+ * mask_pool: top = btm[., mask]. */
+int ocnn_octree_max_unpool(const float* top_dev, const int32_t* mask_dev, float* btm_dev, int channels,
+                           int top_h, int layout, void* stream);
+int ocnn_octree_mask_pool(const float* btm_dev, const int32_t* mask_dev, float* top_dev, int channels,
+                          int top_h, int layout, void* stream);
+
 /* Tensor-core path: weights packed once per layer into bf16 K-major tiles.  The packed image
  * depends on the kernel shape AND the stride the layer will run with (stride-1 neighbourhood
  * convolutions with few channels use a per-sibling-group formulation with expanded weights). */

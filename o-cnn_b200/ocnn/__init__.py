@@ -33,7 +33,8 @@ from .octree_pad import (octree_pad, OctreePad, octree_depad, OctreeDepad, octre
                          OctreeTile)
 from .octree_conv import (octree_conv, OctreeConv, OctreeConvFast, octree_deconv, OctreeDeconv,
                           OctreeDeconvFast, tc_status)
-from .octree_pool import octree_max_pool, OctreeMaxPool, OctreeAvgPool, FullOctreeGlobalPool
+from .octree_pool import (octree_max_pool, OctreeMaxPool, octree_max_unpool, OctreeMaxUnpool,
+                          octree_mask_pool, OctreeAvgPool, FullOctreeGlobalPool)
 
 from .modules import (OctreeConvBn, OctreeConvBnRelu, OctreeDeConvBnRelu, FcBnRelu, OctreeConv1x1,
                       OctreeConv1x1Bn, OctreeConv1x1BnRelu, OctreeResBlock, OctreeResBlock2,

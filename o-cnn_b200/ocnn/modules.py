@@ -91,6 +91,17 @@ class OctreeConv1x1(_nn.Module):
     self._packed = {}
 
   def run(self, data_in, scale=None, bias=None, residual=None, relu=False):
+    if torch.is_grad_enabled() and (data_in.requires_grad or
+                                    (self.training and self.conv1x1.weight.requires_grad)):
+      # training: torch's own 1x1 convolution (as the reference), which autograd differentiates
+      out = self.conv1x1(data_in.squeeze(-1)).unsqueeze(-1)
+      if scale is not None:
+        out = out * scale.view(1, -1, 1, 1)
+      if bias is not None and self.conv1x1.bias is None:
+        out = out + bias.view(1, -1, 1, 1)
+      if residual is not None:
+        out = out + residual
+      return torch.relu(out) if relu else out
     w = self.conv1x1.weight.detach()
     cout, cin = w.shape[0], w.shape[1]
     w2 = w.reshape(cout, cin).float()

@@ -1,4 +1,4 @@
-"""OctreeConv / OctreeDeconv (pytorch/ocnn/octree_conv.py:8-158 of the reference), forward only.
+"""OctreeConv / OctreeDeconv (pytorch/ocnn/octree_conv.py:8-158 of the reference).
 
 The modules hold their weights exactly as the reference's do — float32 [channel_out,
 channel_in * K] for the convolution, [channel_in, channel_out * K] for the deconvolution, column
@@ -7,7 +7,9 @@ nodes or non-empty nodes only) is one implicit-GEMM CUDA kernel; no column buffe
 
 Data in bfloat16 / float16 with torch's channels_last memory format runs on the tensor-core
 kernel (weights are packed once per module and dtype and cached); float32 data, or the
-reference's contiguous [1,C,H,1] layout, runs on the CUDA-core kernel.
+reference's contiguous [1,C,H,1] layout, runs on the CUDA-core kernel.  float32 data that takes
+part in autograd (training) goes through `OctreeConvFunction` / `OctreeDeconvFunction`, whose
+backward is the transposed operator for the data and a node-reduction kernel for the weights.
 """
 import torch
 from torch import nn as _nn
@@ -41,7 +43,55 @@ def _tensor_core_ready(data):
           data.shape[1] % 8 == 0 and data.is_contiguous(memory_format=torch.channels_last))
 
 
+class _ConvFunctionBase(torch.autograd.Function):
+  deconv = False
+
+  @classmethod
+  def _forward(cls, ctx, data_in, weights, octree, depth, channel_out, kernel_size, stride, nempty):
+    data_in = data_in.contiguous()
+    ctx.save_for_backward(data_in, weights, octree)
+    ctx.args = (depth, channel_out, resize_with_last_val(list(kernel_size)), stride, nempty)
+    op = nn.octree_deconv if cls.deconv else nn.octree_conv
+    return op(data_in, weights, octree, *ctx.args)
+
+  @classmethod
+  def _backward(cls, ctx, grad_in):
+    data_in, weights, octree = ctx.saved_tensors
+    op = nn.octree_deconv_grad if cls.deconv else nn.octree_conv_grad
+    grad_out, grad_w = op(data_in, weights, octree, grad_in.contiguous(), *ctx.args)
+    return (grad_out, grad_w) + (None,) * 6
+
+
+class OctreeConvFunction(_ConvFunctionBase):
+  @staticmethod
+  def forward(ctx, *args):
+    return OctreeConvFunction._forward(ctx, *args)
+
+  @staticmethod
+  def backward(ctx, grad_in):
+    return OctreeConvFunction._backward(ctx, grad_in)
+
+
+class OctreeDeconvFunction(_ConvFunctionBase):
+  deconv = True
+
+  @staticmethod
+  def forward(ctx, *args):
+    return OctreeDeconvFunction._forward(ctx, *args)
+
+  @staticmethod
+  def backward(ctx, grad_in):
+    return OctreeDeconvFunction._backward(ctx, grad_in)
+
+
+def _wants_grad(*tensors):
+  return torch.is_grad_enabled() and any(t.requires_grad for t in tensors)
+
+
 def octree_conv(data_in, weights, octree, depth, channel_out, kernel_size, stride=1, nempty=False):
+  if _wants_grad(data_in, weights):
+    return OctreeConvFunction.apply(data_in, weights, octree, depth, channel_out, kernel_size, stride,
+                                    nempty)
   with torch.no_grad():
     return nn.octree_conv(data_in, weights, octree, depth, channel_out,
                           resize_with_last_val(list(kernel_size)), stride, nempty)
@@ -49,6 +99,9 @@ def octree_conv(data_in, weights, octree, depth, channel_out, kernel_size, strid
 
 def octree_deconv(data_in, weights, octree, depth, channel_out, kernel_size, stride=1,
                   nempty=False):
+  if _wants_grad(data_in, weights):
+    return OctreeDeconvFunction.apply(data_in, weights, octree, depth, channel_out, kernel_size,
+                                      stride, nempty)
   with torch.no_grad():
     return nn.octree_deconv(data_in, weights, octree, depth, channel_out,
                             resize_with_last_val(list(kernel_size)), stride, nempty)
@@ -78,6 +131,11 @@ class OctreeConvBase(_nn.Module):
     """One kernel for the layer; `fused` = (scale, bias, residual, relu) applied in its epilogue."""
     scale, bias, residual, relu = fused if fused is not None else (None, None, None, False)
     transposed = not self.is_conv_layer()
+    if (fused is None and data.dtype == torch.float32 and torch.is_grad_enabled() and
+        (data.requires_grad or (self.training and self.weights.requires_grad))):
+      fn = OctreeDeconvFunction if transposed else OctreeConvFunction
+      return fn.apply(data, self.weights, octree, self.depth, self.channel_out, self.kernel_size,
+                      self.stride, self.nempty)
     w = self.weights.detach()
     with torch.no_grad():
       if _tensor_core_ready(data) and self.channel_out % 8 == 0:
@@ -138,7 +196,7 @@ class OctreeConvFast(OctreeConvBase):
   def forward(self, data, octree):
     col = octree2col(data, octree, self.depth, self.kernel_size, self.stride, False)
     col = col.view([self.cdim, -1])
-    conv = torch.mm(self.weights.detach(), col)
+    conv = torch.mm(self.weights, col)
     conv = torch.unsqueeze(torch.unsqueeze(conv, 0), -1)
     if self.stride == 2:
       conv = octree_pad(conv, octree, self.depth - 1)
@@ -155,7 +213,7 @@ class OctreeDeconvFast(OctreeConvBase):
     if self.stride == 2:
       data = octree_depad(data, octree, self.depth)
     data = data.contiguous().view(self.channel_in, -1)
-    col = torch.mm(self.weights.detach().t(), data)
+    col = torch.mm(self.weights.t(), data)
     col = col.view(self.channel_out, self.kdim, -1)
     depth = self.depth + 1 if self.stride == 2 else self.depth
     return col2octree(col, octree, depth, self.kernel_size, self.stride, False)

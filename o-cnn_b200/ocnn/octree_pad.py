@@ -1,19 +1,40 @@
 """octree_pad / octree_depad as functions and modules (pytorch/ocnn/octree_pad.py:7-71 of the
-reference).  Forward only: this package serves inference."""
+reference).  Each is the other's backward."""
 import torch
 from torch import nn as _nn
 
 from . import nn
 
 
+class _PadFunction(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, data_in, octree, depth, val, pad):
+    ctx.save_for_backward(octree)
+    ctx.depth, ctx.pad = depth, pad
+    if pad:
+      return nn.octree_pad(data_in, octree, depth, val)
+    return nn.octree_depad(data_in, octree, depth)
+
+  @staticmethod
+  def backward(ctx, grad_in):
+    octree, = ctx.saved_tensors
+    if ctx.pad:
+      return nn.octree_depad(grad_in.contiguous(), octree, ctx.depth), None, None, None, None
+    return nn.octree_pad(grad_in.contiguous(), octree, ctx.depth, 0.0), None, None, None, None
+
+
 def octree_pad(data_in, octree, depth, val=0.0):
   """[1,C,nnum_nempty[depth],1] -> [1,C,nnum[depth],1]; rows of empty nodes get `val`."""
+  if torch.is_grad_enabled() and data_in.requires_grad:
+    return _PadFunction.apply(data_in, octree, depth, val, True)
   with torch.no_grad():
     return nn.octree_pad(data_in, octree, depth, val)
 
 
 def octree_depad(data_in, octree, depth):
   """[1,C,nnum[depth],1] -> [1,C,nnum_nempty[depth],1]: keep the rows of non-empty nodes."""
+  if torch.is_grad_enabled() and data_in.requires_grad:
+    return _PadFunction.apply(data_in, octree, depth, 0.0, False)
   with torch.no_grad():
     return nn.octree_depad(data_in, octree, depth)
 

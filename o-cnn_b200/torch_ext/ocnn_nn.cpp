@@ -697,6 +697,100 @@ Tensor octree_conv_tc_general(Tensor data_in, Tensor packed, Tensor octree, int 
   return y;
 }
 
+// ---- gradients (pytorch/cpp/octree_conv.cpp:159-189, 219-253, 262-298; octree_pool.cpp:36-95) ---------
+// Returns {gradient of the data, gradient of the weights} of OctreeConv (deconv = false) or
+// OctreeDeconv (deconv = true) given the gradient of its output.  fp32.
+vector<Tensor> conv_grad_impl(Tensor data_in, Tensor weights, Tensor octree, Tensor grad_in, int depth,
+                              int num_output, vector<int> kernel_size, int stride, bool nempty,
+                              bool deconv) {
+  const char* what = deconv ? "octree_deconv_grad" : "octree_conv_grad";
+  vector<int> ks = kernel3(kernel_size);
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(o.cuda, what, ": the octree must be a CUDA tensor");
+  need_cuda(data_in, what);
+  need_cuda(grad_in, what);
+  c10::cuda::CUDAGuard guard(data_in.device());
+  TORCH_CHECK(data_in.scalar_type() == torch::kFloat32 && grad_in.scalar_type() == torch::kFloat32,
+              what, ": float32 data only");
+  DataRef x = get_data(data_in, what);
+  DataRef gy = get_data(x.layout == OCNN_NODE_MAJOR ? grad_in.contiguous(at::MemoryFormat::ChannelsLast)
+                                                    : grad_in.contiguous(), what);
+  const int kdim = ks[0] * ks[1] * ks[2];
+  check_weights(weights, x.C, num_output, kdim);
+  TORCH_CHECK(gy.C == num_output, what, ": the gradient has ", gy.C, " channels, expected ", num_output);
+  Tensor w = weights.contiguous();
+  // forward geometry: checks the data height and gives the output height
+  Geometry fwd = make_geometry(o, x, depth, ks, stride, nempty, deconv, what);
+  TORCH_CHECK(gy.H == fwd.g.h_out, what, ": the gradient has ", gy.H, " rows, expected ", fwd.g.h_out);
+  // data gradient: the transposed operator with the same weights, from the output level back
+  const int back_depth = stride == 1 ? depth : (deconv ? depth + 1 : depth - 1);
+  Geometry back = make_geometry(o, gy, back_depth, ks, stride, nempty, !deconv, what);
+  TORCH_CHECK(back.g.h_out == x.H, what, ": inconsistent octree");
+  Tensor gx = new_data(x.C, x.H, x);
+  OCNN_CALL(ocnn_octree_conv_general(gy.t.data_ptr(), w.data_ptr<float>(), gx.data_ptr(), &back.g, gy.C,
+                                     x.C, ks.data(), OCNN_F32, x.layout, nullptr, current_stream()));
+  // weight gradient: reduction over the rows of the convolution-type column matrix
+  Tensor gw = torch::empty_like(w);
+  const Geometry& conv_geo = deconv ? back : fwd;
+  const DataRef& a = deconv ? x : gy;      // the operand with one row per column-matrix row
+  const DataRef& src = deconv ? gy : x;    // the operand that is gathered
+  OCNN_CALL(ocnn_octree_conv_weight_grad(a.t.data_ptr<float>(), src.t.data_ptr<float>(),
+                                         gw.data_ptr<float>(), &conv_geo.g, a.C, src.C, ks.data(),
+                                         x.layout, current_stream()));
+  return {gx, gw};
+}
+
+vector<Tensor> octree_conv_grad(Tensor data_in, Tensor weights, Tensor octree, Tensor grad_in, int depth,
+                                int num_output, vector<int> kernel_size, int stride, bool nempty) {
+  return conv_grad_impl(data_in, weights, octree, grad_in, depth, num_output, kernel_size, stride,
+                        nempty, false);
+}
+
+vector<Tensor> octree_deconv_grad(Tensor data_in, Tensor weights, Tensor octree, Tensor grad_in,
+                                  int depth, int num_output, vector<int> kernel_size, int stride,
+                                  bool nempty) {
+  return conv_grad_impl(data_in, weights, octree, grad_in, depth, num_output, kernel_size, stride,
+                        nempty, true);
+}
+
+Tensor octree_max_unpool(Tensor top_data, Tensor mask, Tensor octree, int depth) {
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(depth > 1 && depth <= o.meta.depth, "octree_max_unpool: depth out of range");
+  need_cuda(top_data, "octree_max_unpool");
+  c10::cuda::CUDAGuard guard(top_data.device());
+  TORCH_CHECK(top_data.scalar_type() == torch::kFloat32, "octree_max_unpool: float32 data only");
+  DataRef t = get_data(top_data, "octree_max_unpool");
+  TORCH_CHECK(t.H == o.meta.nnum_nempty[depth - 1], "octree_max_unpool: data height ", t.H,
+              " != non-empty node number ", o.meta.nnum_nempty[depth - 1]);
+  TORCH_CHECK(mask.is_cuda() && mask.scalar_type() == torch::kInt32 && mask.sizes() == top_data.sizes(),
+              "octree_max_unpool: mask must be an int32 CUDA tensor shaped like the data");
+  Tensor m = t.layout == OCNN_NODE_MAJOR ? mask.contiguous(at::MemoryFormat::ChannelsLast) : mask.contiguous();
+  Tensor btm = new_data(t.C, t.H * 8, t);
+  OCNN_CALL(ocnn_octree_max_unpool(t.t.data_ptr<float>(), m.data_ptr<int32_t>(), btm.data_ptr<float>(),
+                                   t.C, t.H, t.layout, current_stream()));
+  return btm;
+}
+
+Tensor octree_mask_pool(Tensor btm_data, Tensor mask, Tensor octree, int depth) {
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(depth > 1 && depth <= o.meta.depth, "octree_mask_pool: depth out of range");
+  need_cuda(btm_data, "octree_mask_pool");
+  c10::cuda::CUDAGuard guard(btm_data.device());
+  TORCH_CHECK(btm_data.scalar_type() == torch::kFloat32, "octree_mask_pool: float32 data only");
+  DataRef b = get_data(btm_data, "octree_mask_pool");
+  TORCH_CHECK(b.H == o.meta.nnum[depth], "octree_mask_pool: data height ", b.H, " != node number ",
+              o.meta.nnum[depth]);
+  const int top_h = b.H >> 3;
+  TORCH_CHECK(mask.is_cuda() && mask.scalar_type() == torch::kInt32 && mask.dim() == 4 &&
+                  mask.size(1) == b.C && mask.size(2) == top_h,
+              "octree_mask_pool: mask must be an int32 CUDA tensor [1, C, H/8, 1]");
+  Tensor m = b.layout == OCNN_NODE_MAJOR ? mask.contiguous(at::MemoryFormat::ChannelsLast) : mask.contiguous();
+  Tensor top = new_data(b.C, top_h, b);
+  OCNN_CALL(ocnn_octree_mask_pool(b.t.data_ptr<float>(), m.data_ptr<int32_t>(), top.data_ptr<float>(),
+                                  b.C, top_h, b.layout, current_stream()));
+  return top;
+}
+
 // ---- 1x1x1 convolution without an octree -------------------------------------------------------------
 // The reference's OctreeConv1x1 is a torch Conv1d over [1,C,H] (pytorch/ocnn/modules.py:71-83): a
 // per-node matrix product that needs no octree.  weights: float32 [Cout, Cin].
@@ -1638,6 +1732,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("col2octree", &col2octree, "col2octree");
   m.def("octree_conv", &octree_conv, "octree based convolution");
   m.def("octree_deconv", &octree_deconv, "octree based deconvolution");
+  m.def("octree_conv_grad", &octree_conv_grad, "octree based convolution");
+  m.def("octree_deconv_grad", &octree_deconv_grad, "octree based deconvolution");
+  m.def("octree_max_unpool", &octree_max_unpool, "octree max unpooling");
+  m.def("octree_mask_pool", &octree_mask_pool, "octree mask pooling");
   m.def("octree_pad", &octree_pad, "octree pad", py::arg("data_in"), py::arg("octree"),
         py::arg("depth"), py::arg("val") = 0.0f);
   m.def("octree_depad", &octree_depad, "octree depad");

@@ -271,9 +271,9 @@ def test_conv_nempty(ocnn, batch, ks, nm, bf16):
 def test_conv_nempty_errors(ocnn, batch):
   _, octree, v = batch
   w = torch.zeros(4, 3 * 8, device='cuda')
-  with pytest.raises(RuntimeError, match='stride 1'):
-    ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[4]), 1, device='cuda'), w, octree, 4, 4,
-                     [2], 2, True)
+  out = ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum_nempty[4]), 1, device='cuda'), w, octree, 4, 4,
+                         [2], 2, True)                      # stride 2 on non-empty nodes
+  assert out.shape == (1, 4, int(v.nnum_nempty[3]), 1)
   with pytest.raises(RuntimeError, match='non-empty node number'):
     ocnn.octree_conv(torch.zeros(1, 3, int(v.nnum[4]), 1, device='cuda'),
                      torch.zeros(4, 81, device='cuda'), octree, 4, 4, [3], 1, True)
