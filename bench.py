@@ -43,7 +43,7 @@ def parse_args():
   ap.add_argument('--cpu-sample', type=int, default=32, help='shapes in the CPU baseline sample')
   ap.add_argument('--build-streams', type=int, default=2,
                   help='builder threads, each with its own high-priority stream')
-  ap.add_argument('--forward-streams', type=int, default=2,
+  ap.add_argument('--forward-streams', type=int, default=4,
                   help='network executors (each on its own stream) that consecutive batches alternate over')
   ap.add_argument('--conv-iters', type=int, default=50,
                   help='timed launches per shape of the OctreeConv TFLOP/s measurement')
@@ -62,7 +62,8 @@ def workload_config(n_gpus):
                 'timed region',
           'pipeline': 'the octree builds are issued by builder threads on their own high-priority CUDA '
                       'streams, a few batches ahead; consecutive batches run through the network on '
-                      'alternating streams; K builds and K forwards inside one event pair',
+                      'alternating executors, each with its own stream and host thread; K builds and '
+                      'K forwards inside one event pair',
           'deviation_from_reference_resnet': 'the named configuration puts blocks on depths 6..2 '
               '(512 channels at depth 2); the reference class pytorch/ocnn/resnet.py stops at depth 3 '
               '(256 channels)'}
@@ -430,16 +431,19 @@ def run_ours(args):
   host_split = {}
 
   def pipelined(steps, src_of, on_result=None):
-    """K builds issued by builder threads (batch k by thread k mod B, each on its own
+    """K builds issued by builder threads (batch k by builder k mod B, each on its own
     high-priority stream: the builder is a chain of short dependent kernels with one blocking
-    read-back, so its latency, not its work, limits how fast octrees arrive); K forwards issued by
-    this thread, alternating over the forward streams.  Returns the device time from the first
-    build's start to the last forward's end."""
-    import queue
+    read-back, so its latency, not its work, limits how fast octrees arrive) and K forwards issued
+    by forward threads (batch k by thread k mod F, each with its own executor and stream: enqueueing
+    a forward's ~45 launches costs the host about half a step).  Returns the device time from the
+    first build's start to the last forward's end."""
     import threading
-    nb = len(build_streams)
-    ready = [queue.Queue(maxsize=2) for _ in range(nb)]      # octrees built ahead, per builder
+    nb, nf = len(build_streams), len(fwd_streams)
+    built = [None] * steps
+    is_built = [threading.Event() for _ in range(steps)]
+    ahead = [threading.Semaphore(2) for _ in range(nb)]       # octrees built ahead, per builder
     failure = []
+    stats = [[0.0, 0.0] for _ in range(nf)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(main_stream)
@@ -450,50 +454,70 @@ def run_ours(args):
       try:
         torch.cuda.set_device(dev)
         for k in range(b, steps, nb):
+          ahead[b].acquire()
+          if failure:
+            return
           with torch.cuda.stream(build_streams[b]):
             oct_k = build(src_of(k, build_streams[b]))
             done = torch.cuda.Event()
             done.record(build_streams[b])
-          ready[b].put((oct_k, done))
+          built[k] = (oct_k, done)
+          is_built[k].set()
       except BaseException as err:        # surface the error in the main thread
         failure.append(err)
-        ready[b].put(None)
+        for ev in is_built:
+          ev.set()
+
+    def forwarder(f):
+      try:
+        torch.cuda.set_device(dev)
+        fs, fnet = fwd_streams[f], fwd_nets[f]
+        keep = []
+        for k in range(f, steps, nf):
+          t0 = time.perf_counter()
+          is_built[k].wait()
+          t1 = time.perf_counter()
+          if failure:
+            return
+          cur, done = built[k]
+          built[k] = None
+          ahead[k % nb].release()
+          cur.record_stream(fs)
+          with torch.cuda.stream(fs):
+            fs.wait_event(done)
+            out = fnet.forward(cur)
+            if on_result is not None:
+              on_result(k, out)
+          keep.append((cur, out))
+          if len(keep) > 2:
+            keep.pop(0)
+          stats[f][0] += t1 - t0
+          stats[f][1] += time.perf_counter() - t1
+      except BaseException as err:
+        failure.append(err)
+        for sem in ahead:
+          sem.release()
 
     threads = [threading.Thread(target=builder, args=(b,), daemon=True) for b in range(nb)]
+    threads += [threading.Thread(target=forwarder, args=(f,), daemon=True) for f in range(nf)]
     for t in threads:
       t.start()
-    keep = []
-    waited = enq = 0.0
-    for k in range(steps):
-      t0 = time.perf_counter()
-      item = ready[k % nb].get()
-      t1 = time.perf_counter()
-      if item is None:
-        raise failure[0]
-      cur, done = item
-      fs = fwd_streams[k % len(fwd_streams)]
-      cur.record_stream(fs)
-      with torch.cuda.stream(fs):
-        fs.wait_event(done)
-        out = fwd_nets[k % len(fwd_nets)].forward(cur)
-        if on_result is not None:
-          on_result(k, out)
-      keep.append((cur, out))
-      if len(keep) > 4:
-        keep.pop(0)
-      waited += t1 - t0
-      enq += time.perf_counter() - t1
+    for t in threads:
+      t.join()
+    if failure:
+      raise failure[0]
     for fs in fwd_streams:
       main_stream.wait_stream(fs)
     e1.record(main_stream)
-    for t in threads:
-      t.join()
     barrier()
-    host_split.update({'wait_for_octree_ms_per_step': 1e3 * waited / steps,
-                       'forward_enqueue_ms_per_step': 1e3 * enq / steps})
+    host_split.update({'wait_for_octree_ms_per_step': 1e3 * sum(s[0] for s in stats) / steps,
+                       'forward_enqueue_ms_per_step': 1e3 * sum(s[1] for s in stats) / steps})
     return max_over_ranks(e0.elapsed_time(e1))
 
-  pipelined(max(args.warmup, 3), lambda k, st: inputs[k % nbuf])
+  # (as many warm-up steps as timed ones, twice: the allocator's pools and the threads' working sets
+  # reach their steady state before the timed region)
+  for _ in range(2):
+    pipelined(max(args.warmup, 3, args.steps), lambda k, st: inputs[k % nbuf])
   launches0 = ocnn.nn.launch_count()
   t_host0 = time.perf_counter()
   total_ms = pipelined(args.steps, lambda k, st: inputs[k % nbuf])
@@ -522,7 +546,8 @@ def run_ours(args):
   def e2e_result(k, out):
     logits_host[k % 4].copy_(out.float().reshape(BATCH, 40), non_blocking=True)
 
-  pipelined(3, e2e_src, e2e_result)
+  for _ in range(2):
+    pipelined(max(3, args.steps), e2e_src, e2e_result)
   e2e_ms = pipelined(args.steps, e2e_src, e2e_result)
   torch.cuda.synchronize()
   assert all(bool(torch.isfinite(t).all()) for t in logits_host), 'end-to-end logits are not finite'
@@ -645,7 +670,7 @@ def run_ours(args):
 
   cfg = workload_config(world)
   line = {'metric': METRIC, 'value': shapes / (total_ms * 1e-3), 'unit': UNIT, 'n_gpus': world,
-          'steps': args.steps, 'warmup': args.warmup, 'warmup_run': max(args.warmup, 3) + 2,
+          'steps': args.steps, 'warmup': args.warmup, 'warmup_run': 2 * max(args.warmup, 3, args.steps),
           'ms_per_step': total_ms / args.steps,
           'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16',
           'data': 'synthetic', 'config': cfg,

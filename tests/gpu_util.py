@@ -24,7 +24,7 @@ def data_cuda(x, node_major=False, bf16=False, half=False):
 
 def to_np(t):
   """[1,C,H,1] tensor (any layout / dtype) -> [C,H] float32 numpy."""
-  return t.float().contiguous().view(t.shape[1], t.shape[2]).cpu().numpy()
+  return t.detach().float().contiguous().view(t.shape[1], t.shape[2]).cpu().numpy()
 
 
 def bf16_round(x):
