@@ -48,8 +48,7 @@ class _ConvFunctionBase(torch.autograd.Function):
 
   @classmethod
   def _forward(cls, ctx, data_in, weights, octree, depth, channel_out, kernel_size, stride, nempty):
-    data_in = data_in.contiguous()
-    ctx.save_for_backward(data_in, weights, octree)
+    ctx.save_for_backward(data_in, weights, octree)     # (either memory layout is taken as it is)
     ctx.args = (depth, channel_out, resize_with_last_val(list(kernel_size)), stride, nempty)
     op = nn.octree_deconv if cls.deconv else nn.octree_conv
     return op(data_in, weights, octree, *ctx.args)
