@@ -41,6 +41,9 @@ def parse_args():
   ap.add_argument('--no-tensor-core', action='store_true',
                   help='run every convolution on the CUDA-core kernel')
   ap.add_argument('--cpu-sample', type=int, default=32, help='shapes in the CPU baseline sample')
+  ap.add_argument('--serial-only', action='store_true',
+                  help='only the serial steps (one stream, one batch at a time): the launch sequence '
+                       'of one step, for profiler captures')
   ap.add_argument('--build-streams', type=int, default=2,
                   help='builder threads, each with its own high-priority stream')
   ap.add_argument('--forward-streams', type=int, default=4,
@@ -410,7 +413,17 @@ def run_ours(args):
   top_ms = statistics.mean(top_times) if top_times else None
   net.exec.set_trace(-2)
 
-  # ---- headline: the same K steps as a two-stream pipeline ----
+  if args.serial_only:
+    if rank == 0:
+      print(json.dumps({'metric': METRIC, 'mode': 'serial-only', 'n_gpus': world, 'steps': args.steps,
+                        'ms_per_step': serial_ms / args.steps,
+                        'value': BATCH * world * args.steps / (serial_ms * 1e-3), 'unit': UNIT,
+                        'layer_ms': {k: round(v, 4) for k, v in layer_ms.items()}}))
+    if world > 1:
+      dist.destroy_process_group()
+    return
+
+  # ---- headline: the same K steps as a multi-stream pipeline ----
   # The octree of batch k+1 is built on a second stream while batch k runs through the network:
   # the builder's short dependent kernels fill the SMs that the network's coarse levels leave idle,
   # and its one blocking read-back (the node counts) stalls only that stream's host thread.  Every

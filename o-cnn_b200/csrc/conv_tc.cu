@@ -28,8 +28,11 @@
 // that read the stage have retired).  A level too small to fill the SMs runs 64- or 32-row tiles:
 // the MMA is still 128 rows, the rows a tile does not have are neither gathered nor stored.
 //
-// Every wait is bounded: a wait that runs out sets *status (and a CTA-wide abort flag), the CTA
-// drains its own copies, frees its TMEM and returns — the launch never hangs the GPU.
+// Every wait is bounded: a wait that runs out sets *status (and a CTA-wide abort flag); the other
+// roles see the flag at their next wait and stop issuing.  Before the CTA frees its TMEM and
+// returns, the gather threads wait for their own cp.async copies, the MMA thread commits what it
+// has issued and waits (bounded) for that commit, and the weight thread gives the bulk copies it
+// has in flight a bounded time to land — the launch never hangs the GPU.
 #include "common.cuh"
 
 namespace ocnn {
@@ -242,7 +245,10 @@ __device__ __forceinline__ void chunk_src(int cpt, int kb, int chunk, int& t, ui
   }
 }
 
-template <int CPT, bool HALF>
+// GENERAL compiles in the rarely used layer kinds (stride-2 deconvolution in gather form, the
+// expanded kernel-2 deconvolution with its scattered epilogue); the convolutions of the
+// classification networks run the variant without them.
+template <int CPT, bool HALF, bool GENERAL>
 __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of address bits [4,10)
@@ -292,8 +298,8 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   grid_dependency_wait();
   for (int n = tid; n < a.npad; n += kThreads) {
     // output channel of column n: columns are (octant, channel) pairs in group mode
-    const int co = a.group ? (n & (a.cout - 1))
-                           : (a.expand_cout ? (co_base + n) % a.expand_cout : co_base + n);
+    int co = a.group ? (n & (a.cout - 1)) : co_base + n;
+    if (GENERAL && a.expand_cout) co = (co_base + n) % a.expand_cout;
     const bool live = n < a.row_elems;
     s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
     s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
@@ -338,7 +344,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
         if (t < a.T && live) {
           // a.tap[t] holds (tx<<4)|(ty<<2)|tz; adding the octant's (ox<<4)|(oy<<2)|oz gives the
           // position in the sibling group's 4x4x4 block (no field can carry: each sum is <= 3)
-          if (a.up) {
+          if (GENERAL && a.up) {
             const int code = a.tap[t];
             p = up_source_group(a.neigh, hn, (code >> 4) * 9 + ((code >> 2) & 3) * 3 + (code & 3));
           } else {
@@ -549,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
     if (alive) {
       __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + co_base;
       const bool has_sb = a.scale != nullptr || a.bias != nullptr;
-      const bool scatter = a.scatter_child != nullptr;
+      const bool scatter = GENERAL && a.scatter_child != nullptr;
       for (int c0 = 0; c0 < a.npad; c0 += 32) {
         uint4 res_cur[4];
 #pragma unroll
@@ -643,7 +649,13 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
         umma_commit(smem_u32(&empty[s]));     // stage reusable once these MMAs retire
         if (++s == a.stages) { s = 0; pf ^= 1u; }
       }
-      if (alive) umma_commit(smem_u32(accum));
+      umma_commit(smem_u32(accum));
+      if (!alive) {
+        // gave up: nobody may be waiting on `accum` any more; make sure the MMAs already issued have
+        // retired before TMEM is freed
+        for (unsigned it = 0; it < kSpinLimit; ++it)
+          if (mbar_try_wait(smem_u32(accum), 0)) break;
+      }
     }
   } else {
     // ---------------- weight tiles: one thread, one bulk copy per K-block ----------------
@@ -676,6 +688,11 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
               "r"((uint32_t)stage_b), "r"(bar)
             : "memory");
         if (++s == a.stages) { s = 0; pe ^= 1u; }
+      }
+      if (!alive) {
+        // gave up with up to `stages` bulk copies in flight into this CTA's shared memory: they
+        // complete on their own; leave them time to (bounded) before the CTA exits
+        for (int it = 0; it < 64; ++it) __nanosleep(1000);
       }
     }
   }
@@ -1001,12 +1018,13 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   OCNN_CUDA_OK(cudaGetDevice(&device));
   typedef void (*KernelFn)(const TcArgs);
   static const KernelFn table[2][8] = {
-      {conv_tc_kernel<0, false>, conv_tc_kernel<1, false>, conv_tc_kernel<2, false>,
-       conv_tc_kernel<4, false>, conv_tc_kernel<8, false>, conv_tc_kernel<16, false>,
-       conv_tc_kernel<32, false>, conv_tc_kernel<64, false>},
-      {conv_tc_kernel<0, true>, conv_tc_kernel<1, true>, conv_tc_kernel<2, true>,
-       conv_tc_kernel<4, true>, conv_tc_kernel<8, true>, conv_tc_kernel<16, true>,
-       conv_tc_kernel<32, true>, conv_tc_kernel<64, true>}};
+      {conv_tc_kernel<0, false, false>, conv_tc_kernel<1, false, false>, conv_tc_kernel<2, false, false>,
+       conv_tc_kernel<4, false, false>, conv_tc_kernel<8, false, false>, conv_tc_kernel<16, false, false>,
+       conv_tc_kernel<32, false, false>, conv_tc_kernel<64, false, false>},
+      {conv_tc_kernel<0, true, false>, conv_tc_kernel<1, true, false>, conv_tc_kernel<2, true, false>,
+       conv_tc_kernel<4, true, false>, conv_tc_kernel<8, true, false>, conv_tc_kernel<16, true, false>,
+       conv_tc_kernel<32, true, false>, conv_tc_kernel<64, true, false>}};
+  static const KernelFn general[2] = {conv_tc_kernel<0, false, true>, conv_tc_kernel<0, true, true>};
   int slot = 0;
   switch (a.cin >> 3) {
     case 1: slot = 1; break;
@@ -1018,15 +1036,19 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
     case 64: slot = 7; break;
     default: break;
   }
-  KernelFn kernel = table[a.f16][slot];
+  const bool needs_general = a.up || a.expand_cout > 0;
+  KernelFn kernel = needs_general ? general[a.f16] : table[a.f16][slot];
   {
     std::lock_guard<std::mutex> lock(attr_once.mutex);
     const bool known = device >= 0 && device < 64;
     if (!known || !attr_once.done[device]) {
-      for (int h = 0; h < 2; ++h)
+      for (int h = 0; h < 2; ++h) {
         for (int k = 0; k < 8; ++k)
           OCNN_CUDA_OK(cudaFuncSetAttribute(table[h][k], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             220 * 1024));
+        OCNN_CUDA_OK(cudaFuncSetAttribute(general[h], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          220 * 1024));
+      }
       if (known) attr_once.done[device] = true;
     }
   }

@@ -25,7 +25,7 @@ from .nn import (transform_points, clip_points, normalize_points, bounding_spher
                  points_batch_property, points_set_property)
 from .transforms import (Points2Octree, collate_octrees, NormalizePoints, TransformPoints,
                          TransformCompose)
-from .io import read_points, write_points, read_octree, write_octree
+from .io import read_points, write_points, read_octree, write_octree, octree_samples
 from .octree2voxel import FullOctree2Voxel
 from .octree2col import octree2col, Octree2Col, col2octree, Col2Octree
 from .octree_align import octree_align, OctreeAlign
@@ -43,6 +43,8 @@ from .modules import (OctreeConvBn, OctreeConvBnRelu, OctreeDeConvBnRelu, FcBnRe
 from .lenet import LeNet
 from .resnet import ResNet
 from .unet import UNet
+
+nn.octree_samples = octree_samples      # the reference exposes it on the extension module too
 
 LIBRARY = _os.path.join(_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))),
                         'libocnn_b200.so')

@@ -41,3 +41,23 @@ def write_points(points, filename):
 
 def write_octree(octree, filename):
   _write(octree, filename)
+
+
+_SAMPLES = {}
+
+
+def octree_samples(names):
+  """The small octrees the reference library carries for its own tests (`octree_1` .. `octree_6`,
+  octree/octree/octree_samples.cpp; binding pytorch/cpp/octree_samples.cpp:5-22), as CPU uint8
+  tensors in the current key width (`ocnn.set_key_bits`)."""
+  import os
+  if not _SAMPLES:
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'data', 'octree_samples.npz')
+    _SAMPLES.update(np.load(path))
+  out = []
+  for name in names:
+    key = 'k%d_%s' % (nn.get_key_bits(), name)
+    if key not in _SAMPLES:
+      raise ValueError('unknown octree sample %r' % (name,))
+    out.append(torch.from_numpy(_SAMPLES[key].copy()))
+  return out

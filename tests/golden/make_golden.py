@@ -6,6 +6,7 @@ Run in a container that has the reference checkout (it is compiled unmodified by
 
     python tests/golden/make_golden.py            # both files
     python tests/golden/make_golden.py general    # only reference_vectors_general.npz
+    python tests/golden/make_golden.py samples    # only o-cnn_b200/ocnn/data/octree_samples.npz
 
 Every array written here is an input fed to, or an output produced by, the reference
 (``oracle/_ref/libocnn_ref{32,64}.so``); nothing is computed by this repository's own oracle or
@@ -133,7 +134,26 @@ def main_general():
   print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
 
 
+def main_samples():
+  """The six small octrees the reference library embeds for its own tests
+  (octree/octree/octree_samples.cpp, read through octree::get_one_octree), in both key widths, as
+  the package data behind `ocnn.octree_samples`."""
+  out = {}
+  for kb in (32, 64):
+    R = ref.get(kb)
+    for i in range(1, 7):
+      out['k%d_octree_%d' % (kb, i)] = R.octree_sample('octree_%d' % i)
+  path = os.path.join(ROOT, 'o-cnn_b200', 'ocnn', 'data', 'octree_samples.npz')
+  os.makedirs(os.path.dirname(path), exist_ok=True)
+  np.savez_compressed(path, **out)
+  print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
+
+
 if __name__ == '__main__':
-  if len(sys.argv) < 2 or sys.argv[1] != 'general':
+  what = sys.argv[1] if len(sys.argv) > 1 else 'all'
+  if what == 'all':
     main()
-  main_general()
+  if what in ('all', 'general'):
+    main_general()
+  if what in ('all', 'samples'):
+    main_samples()

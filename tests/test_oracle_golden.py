@@ -274,3 +274,20 @@ def test_conv_general_matches_reference_fixture(golden, golden_general, ks):
         got = oc.octree_conv_general(x, w, merged, 3, 5, ks, stride, bool(nempty), bool(deconv))
         assert same_bits(got, g['g_y%s_s%d_n%d_t%d' % (name, stride, nempty, deconv)]), \
             (ks, stride, nempty, deconv)
+
+
+def test_octree_samples_api(golden):
+  """`ocnn.octree_samples` hands out the reference's embedded test octrees in the current key
+  width (pytorch/cpp/octree_samples.cpp:5-22)."""
+  import ocnn
+  for kb in (64, 32):
+    ocnn.set_key_bits(kb)
+    try:
+      got = ocnn.octree_samples(['octree_1', 'octree_2'])
+      for t, name in zip(got, ('octree_1', 'octree_2')):
+        assert same_bits(t.numpy(), golden['k%d_%s' % (kb, name)])
+      assert len(ocnn.nn.octree_samples(['octree_%d' % i for i in range(1, 7)])) == 6
+    finally:
+      ocnn.set_key_bits(64)
+  with pytest.raises(ValueError):
+    ocnn.octree_samples(['octree_7'])
