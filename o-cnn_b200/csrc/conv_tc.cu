@@ -706,6 +706,355 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   }
 }
 
+// ---- persistent variant ------------------------------------------------------------------------
+// For layers whose Cin is a multiple of 64 (whole-row gathers) on levels of many tiles.  While an
+// MMA runs it reads its A and B slices from shared memory at about the rate shared memory can
+// deliver (M = N = 128, K = 16: 8 KB in 64 cycles), and every byte it reads was written there
+// once by the gather or the weight copy, so with one 128-row tile per weight tile the tensor pipe
+// cannot be busy more than about half of the time.  This variant computes R = 2 tiles of 128 rows
+// against every weight tile (B is written once per 256 rows: a third less shared-memory traffic
+// per flop at Cout = 128), which needs all of an SM: one CTA per SM walks many 256-row tiles
+// (tile = blockIdx.x, += gridDim.x) and overlaps everything inside itself.  Set-up (barriers,
+// TMEM, scale / bias) happens once; the accumulator set is double buffered in TMEM where it fits
+// and four extra warps run the epilogue, so tile i's TMEM read-out, scale / bias / residual /
+// ReLU and stores run under tile i+1's gathers and MMAs.  Roles (32 * (4R + 6) threads): warps
+// 0 .. 4R-1 fill the tile's neighbour table and gather A (warp w: rows 32w .. 32w+31); warp 4R
+// lane 0 issues the MMAs; warp 4R+1 lane 0 streams the weight tiles; the last four warps are the
+// epilogue (TMEM lane quarter = warp & 3).  The {A, B} ring and its phase bits run on across
+// tiles; tfull[b] / tempty[b] hand accumulator set b between the MMA thread and the epilogue.
+// Same packed weights and the same whole-row gather mapping as conv_tc_kernel's rowsplit 2.
+template <int R>
+__device__ __forceinline__ void gather_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(128 * R) : "memory");
+}
+
+template <int CPT, bool HALF, int R>
+__global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(const TcArgs a, const int ntiles,
+                                                                             const int acc_bufs) {
+  constexpr int kRows = kTileM * R;              // rows of one tile
+  constexpr int kGatherWarps = 4 * R;
+  constexpr int kThreadsP = 32 * (4 * R + 6);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stage_b = a.npad * 128;
+  uint8_t* sA = smem;                            // stage s: R sub-tiles of 128 rows back to back
+  uint8_t* sB = sA + a.stages * (R * kStageA);
+  int* nbr = reinterpret_cast<int*>(sB + a.stages * stage_b);      // [taps][kRows]
+  float* s_scale = reinterpret_cast<float*>(nbr + a.T * kRows);
+  float* s_bias = s_scale + a.npad;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + a.npad);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + a.stages;
+  uint64_t* tfull = bars + 2 * a.stages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int co_base = blockIdx.y * a.cout;
+  const uint8_t* wpacked = a.wpacked + (size_t)blockIdx.y * a.nkb * (a.npad * 128);
+  const int acc_cols = R * a.tmem_cols;          // TMEM columns of one accumulator set
+  grid_dependency_trigger();
+
+  if (tid == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(&full[s]), kRows + 1);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tfull[b]), 1);
+      mbar_init(smem_u32(&tempty[b]), kTileM);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kGatherWarps) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)), "r"((uint32_t)(acc_cols * acc_bufs))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  grid_dependency_wait();
+  for (int n = tid; n < a.npad; n += kThreadsP) {
+    const bool live = n < a.row_elems;
+    s_scale[n] = (live && a.scale) ? a.scale[co_base + n] : 1.f;
+    s_bias[n] = (live && a.bias) ? a.bias[co_base + n] : 0.f;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp < kGatherWarps) {
+    // ---------------- neighbour table + A gather, tile after tile ----------------
+    bool alive = true;
+    int s = 0;
+    uint32_t pe = 1;
+    long long gk = 0;                  // K-blocks issued so far by this CTA (all tiles)
+    const char* xb = reinterpret_cast<const char*>(a.x);
+    const uint32_t row_bytes = (uint32_t)a.cin * 2u;
+    const int kBlocksPerTap = CPT >= 8 ? CPT / 8 : a.cin >> 6;
+    const int sub = lane >> 3, chunk = lane & 7;
+    const int rbase = warp * 32 + sub;             // this thread gathers rows rbase + 4i, i = 0..7
+    // table slot of row tid: the eight rows of one gather thread sit side by side
+    const int slot = (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7);
+    const int* my_idx = nbr + warp * 32 + sub * 8;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+      const int h0 = tile * kRows;
+      gather_bar<R>();                 // every gather thread has finished reading the previous table
+      {
+        const int h = h0 + tid;
+        const bool live = h < a.rows;
+        const int hn = (a.ichild != nullptr && live) ? a.ichild[h] : h;
+        const int oct_code = ((hn & 4) << 2) | ((hn & 2) << 1) | (hn & 1);
+        if (a.identity) {
+          nbr[slot] = live ? h : -1;
+        } else {
+          int pv[27];
+#pragma unroll
+          for (int t = 0; t < 27; ++t) {
+            int p = -1;
+            if (t < a.T && live) {
+              const long long at = a.stride == 2 ? ((long long)hn << 6) + a.tap[t]
+                                                 : ((long long)(hn >> 3) << 6) + a.tap[t] + oct_code;
+              p = a.neigh[at];
+            }
+            pv[t] = p;
+          }
+          if (a.child != nullptr) {
+#pragma unroll
+            for (int t = 0; t < 27; ++t)
+              if (t < a.T && pv[t] >= 0) pv[t] = a.child[pv[t]];
+          }
+#pragma unroll
+          for (int t = 0; t < 27; ++t)
+            if (t < a.T) nbr[t * kRows + slot] = pv[t];
+        }
+      }
+      gather_bar<R>();
+
+      uint32_t row_mask = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
+      int p[8];
+      int t = 0, part = 0;
+      for (int kb = 0; kb < a.nkb; ++kb, ++gk) {
+        if (part == 0) {
+          const int4 lo = *reinterpret_cast<const int4*>(my_idx + t * kRows);
+          const int4 hi = *reinterpret_cast<const int4*>(my_idx + t * kRows + 4);
+          p[0] = lo.x; p[1] = lo.y; p[2] = lo.z; p[3] = lo.w;
+          p[4] = hi.x; p[5] = hi.y; p[6] = hi.z; p[7] = hi.w;
+        }
+        if (alive && gk >= a.stages)
+          alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
+        if (alive) {
+          const uint32_t stage_base = smem_u32(sA + s * (R * kStageA));
+          const uint32_t off = (uint32_t)part * 128u + (uint32_t)chunk * 16u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = rbase + 4 * i;
+            const uint32_t dst = stage_base + (uint32_t)row * 128u +
+                                 (((uint32_t)chunk ^ (uint32_t)(row & 7)) << 4);
+            const int pi = p[i];
+            const char* src = pi >= 0 ? xb + (size_t)((uint32_t)pi * row_bytes) + off : xb;
+            if ((row_mask >> i) & 1u) cp_async16(dst, src, pi >= 0 ? 16u : 0u);
+          }
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
+                     : "memory");
+        if (++s == a.stages) { s = 0; pe ^= 1u; }
+        if (++part == kBlocksPerTap) { part = 0; ++t; }
+      }
+      // a thread that gave up keeps walking the tiles (without waiting or copying): the named
+      // barrier above needs every gather thread every time
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (warp == kGatherWarps) {
+    // ---------------- MMA issue: one thread ----------------
+    if (lane == 0) {
+      const uint32_t ab = HALF ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (ab << 7) | (ab << 10) | ((uint32_t)(a.npad >> 3) << 17) |
+                             ((uint32_t)(kTileM >> 4) << 24);
+      bool alive = true;
+      int s = 0;
+      uint32_t pf = 0;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++it) {
+        const int b = it % acc_bufs;
+        const uint32_t use = (uint32_t)(it / acc_bufs);
+        // the epilogue must have drained accumulator set b (first use: passes at once)
+        alive = mbar_wait(smem_u32(&tempty[b]), (use & 1u) ^ 1u, abort_flag, a.status, kErrAccumWait);
+        if (!alive) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(b * acc_cols);
+        for (int kb = 0; kb < a.nkb && alive; ++kb) {
+          alive = mbar_wait(smem_u32(&full[s]), pf, abort_flag, a.status, kErrFullWait);
+          if (!alive) break;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(sA + s * (R * kStageA));
+          const uint32_t b_addr = smem_u32(sB + s * stage_b);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int k4 = 0; k4 < kBlockK / 16; ++k4) {
+              umma_bf16(tmem_d + (uint32_t)(r * a.tmem_cols), smem_desc_sw128(a_addr + r * kStageA + k4 * 32),
+                        smem_desc_sw128(b_addr + k4 * 32), idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(smem_u32(&empty[s]));
+          if (++s == a.stages) { s = 0; pf ^= 1u; }
+        }
+        umma_commit(smem_u32(&tfull[b]));
+      }
+      if (!alive) {
+        // gave up: wait (bounded) until the MMAs already issued have retired before TMEM is freed
+        umma_commit(smem_u32(&tfull[0]));
+        for (int w = 0; w < 64; ++w) __nanosleep(1000);
+      }
+    }
+  } else if (warp == kGatherWarps + 1) {
+    // ---------------- weight tiles ----------------
+    {
+      const int wave = gridDim.x < kSMs ? (int)gridDim.x : kSMs;
+      if ((int)blockIdx.x < wave) {
+        for (int kb = blockIdx.x + lane * wave; kb < a.nkb; kb += 32 * wave)
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wpacked + (size_t)kb * stage_b),
+                       "r"((uint32_t)stage_b)
+                       : "memory");
+      }
+    }
+    if (lane == 0) {
+      bool alive = true;
+      int s = 0;
+      uint32_t pe = 1;
+      long long gk = 0;
+      for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+        for (int kb = 0; kb < a.nkb && alive; ++kb, ++gk) {
+          if (gk >= a.stages)
+            alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrWeightWait);
+          if (!alive) break;
+          const uint32_t bar = smem_u32(&full[s]);
+          mbar_arrive_expect_tx(bar, (uint32_t)stage_b);
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+              ::"r"(smem_u32(sB + s * stage_b)), "l"(wpacked + (size_t)kb * stage_b),
+                "r"((uint32_t)stage_b), "r"(bar)
+              : "memory");
+          if (++s == a.stages) { s = 0; pe ^= 1u; }
+        }
+      }
+      if (!alive) {
+        for (int w = 0; w < 64; ++w) __nanosleep(1000);
+      }
+    }
+  } else {
+    // ---------------- epilogue warps: TMEM -> registers -> global, tile after tile ----------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    constexpr bool f16 = HALF;
+    bool alive = true;
+    const bool has_sb = a.scale != nullptr || a.bias != nullptr;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+      const int b = it % acc_bufs;
+      const uint32_t use = (uint32_t)(it / acc_bufs);
+      alive = mbar_wait(smem_u32(&tfull[b]), use & 1u, abort_flag, a.status, kErrAccumWait);
+      alive = __all_sync(0xffffffffu, alive);
+      if (!alive) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int r = 0; r < R; ++r) {
+        const int h = tile * kRows + r * kTileM + q * 32 + lane;
+        const bool row_ok = h < a.rows;
+        const __nv_bfloat16* res_row =
+            (a.residual && row_ok) ? a.residual + (long long)h * a.y_stride + co_base : nullptr;
+        uint4 res_nxt[4];
+        auto load_line = [&](int c0) {
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) res_nxt[qq] = make_uint4(0, 0, 0, 0);
+          if (res_row == nullptr) return;
+          if (a.wide) {
+#pragma unroll
+            for (int qq = 0; qq < 4; qq += 2)
+              if (c0 + 8 * qq < a.row_elems) ld_global_32B(res_row + c0 + 8 * qq, res_nxt[qq], res_nxt[qq + 1]);
+          } else {
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq)
+              if (c0 + 8 * qq < a.row_elems)
+                res_nxt[qq] = *reinterpret_cast<const uint4*>(res_row + c0 + 8 * qq);
+          }
+        };
+        load_line(0);
+        const uint32_t lane_base = tmem_base + (uint32_t)(b * acc_cols + r * a.tmem_cols) + ((uint32_t)(q * 32) << 16);
+        __nv_bfloat16* y_row = a.y + (long long)h * a.y_stride + co_base;
+        for (int c0 = 0; c0 < a.npad; c0 += 32) {
+          uint4 res_cur[4];
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) res_cur[qq] = res_nxt[qq];
+          if (c0 + 32 < a.npad) load_line(c0 + 32);
+#pragma unroll
+          for (int step = 0; step < 2; ++step) {
+            const int n0 = c0 + 16 * step;
+            if (n0 >= a.npad) break;
+            uint32_t v[16];
+            tmem_ld16(lane_base + (uint32_t)n0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint4 ov[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int n = n0 + 8 * half;
+              if (!row_ok || n >= a.row_elems) continue;
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[8 * half + j]);
+              if (has_sb) {
+                const float4 sc0 = *reinterpret_cast<const float4*>(s_scale + n);
+                const float4 sc1 = *reinterpret_cast<const float4*>(s_scale + n + 4);
+                const float4 bi0 = *reinterpret_cast<const float4*>(s_bias + n);
+                const float4 bi1 = *reinterpret_cast<const float4*>(s_bias + n + 4);
+                const float sc[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
+                const float bi[8] = {bi0.x, bi0.y, bi0.z, bi0.w, bi1.x, bi1.y, bi1.z, bi1.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], bi[j]);
+              }
+              if (res_row != nullptr) {
+                const uint32_t* rp = reinterpret_cast<const uint32_t*>(&res_cur[2 * step + half]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 rf = unpack2(rp[j], f16);
+                  f[2 * j] += rf.x;
+                  f[2 * j + 1] += rf.y;
+                }
+              }
+              if (a.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+              }
+              uint32_t* op = reinterpret_cast<uint32_t*>(&ov[half]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) op[j] = pack2(f[2 * j], f[2 * j + 1], f16);
+              if (!a.wide) *reinterpret_cast<uint4*>(y_row + n) = ov[half];
+            }
+            if (a.wide && row_ok && n0 < a.row_elems) st_global_32B(y_row + n0, ov[0], ov[1]);
+          }
+        }
+      }
+      // accumulator set b has been read out: hand it back to the MMA thread
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(smem_u32(&tempty[b]));
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kGatherWarps) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)(acc_cols * acc_bufs))
+                 : "memory");
+  }
+}
+
 // ---- weight packing -------------------------------------------------------------------------
 // packed: per K-block a [npad x 64] tile of 16-bit floats in the swizzled K-major image: element
 // (n, kk) at (n/8)*1024 + (n%8)*128 + (((kk/8) ^ (n%8)) * 16) + (kk%8)*2, k = kb*64 + kk.
@@ -811,6 +1160,8 @@ struct TcShape {
   int fold_in, expand_out;   // kernel 2, stride 2 as a dense product (see WeightView)
   int cin_eff, cout_eff;     // channel counts the kernel sees: 8*Cin when folded, 8*Cout when expanded
   size_t smem;
+  size_t fixed_bytes, stage_bytes;   // shared memory outside the ring / per ring stage
+  bool small_grid;                   // the tiles do not fill the SMs once
 };
 
 int tc_shape(int cin, int cout, const int ks[3], const LayerKind& kind, TcShape* s,
@@ -893,7 +1244,41 @@ int tc_shape(int cin, int cout, const int ks[3], const LayerKind& kind, TcShape*
   if (st > s->nkb) st = s->nkb < 2 ? 2 : s->nkb;
   s->stages = st;
   s->smem = fixed + (size_t)s->stages * stage_bytes;
+  s->fixed_bytes = fixed;
+  s->stage_bytes = stage_bytes;
+  s->small_grid = small_grid;
   return OCNN_OK;
+}
+
+// 0: one tile per CTA always; 1: the persistent kernel where it pays (default).
+int persist_mode() {
+  static const int mode = [] {
+    const char* e = getenv("OCNN_CONV_PERSIST");
+    return e ? atoi(e) : 1;
+  }();
+  return mode;
+}
+
+// Launch shape of the persistent kernel: 128-row tiles per weight tile, ring depth, accumulator
+// sets in TMEM, dynamic shared memory.  stages == 0: it does not fit.
+struct PersistShape {
+  int R, stages, acc_bufs;
+  size_t smem;
+};
+
+PersistShape persist_shape(const TcShape& s, int R) {
+  PersistShape p;
+  p.R = R;
+  p.acc_bufs = 2 * R * s.tmem_cols <= 512 ? 2 : 1;
+  const size_t budget = 226 * 1024;           // one CTA per SM
+  const size_t fixed = 1024 + (size_t)s.T * 128 * R * 4 + (size_t)s.npad * 8 + 256;
+  const size_t stage = (size_t)R * kStageA + (size_t)s.npad * 128;
+  int st = budget > fixed ? (int)((budget - fixed) / stage) : 0;
+  if (st > 8) st = 8;
+  if (st < 3 || R * s.tmem_cols > 512) st = 0;
+  p.stages = st;
+  p.smem = fixed + (size_t)st * stage;
+  return p;
 }
 
 size_t packed_bytes_impl(int cin, int cout, const int kernel_size[3], const LayerKind& kind) {
@@ -1025,6 +1410,15 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
        conv_tc_kernel<4, true, false>, conv_tc_kernel<8, true, false>, conv_tc_kernel<16, true, false>,
        conv_tc_kernel<32, true, false>, conv_tc_kernel<64, true, false>}};
   static const KernelFn general[2] = {conv_tc_kernel<0, false, true>, conv_tc_kernel<0, true, true>};
+  // persistent variant (two 128-row tiles per weight tile): Cin = any multiple of 64, 64, 128, 256, 512
+  typedef void (*PersistFn)(const TcArgs, const int, const int);
+  static const PersistFn persist[2][5] = {
+      {conv_tc_persist_kernel<0, false, 2>, conv_tc_persist_kernel<8, false, 2>,
+       conv_tc_persist_kernel<16, false, 2>, conv_tc_persist_kernel<32, false, 2>,
+       conv_tc_persist_kernel<64, false, 2>},
+      {conv_tc_persist_kernel<0, true, 2>, conv_tc_persist_kernel<8, true, 2>,
+       conv_tc_persist_kernel<16, true, 2>, conv_tc_persist_kernel<32, true, 2>,
+       conv_tc_persist_kernel<64, true, 2>}};
   int slot = 0;
   switch (a.cin >> 3) {
     case 1: slot = 1; break;
@@ -1046,6 +1440,9 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
         for (int k = 0; k < 8; ++k)
           OCNN_CUDA_OK(cudaFuncSetAttribute(table[h][k], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             220 * 1024));
+        for (int k = 0; k < 5; ++k)
+          OCNN_CUDA_OK(cudaFuncSetAttribute(persist[h][k], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            227 * 1024));
         OCNN_CUDA_OK(cudaFuncSetAttribute(general[h], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           220 * 1024));
       }
@@ -1055,7 +1452,28 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
                "%s: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses", who,
                (long long)h_in * cin * 2);
-  OCNN_CUDA_OK(launch_chained(kernel, dim3(ceil_div(a.rows, a.tile_rows), s.slices), dim3(kThreads), s.smem,
+  const int ntiles = ceil_div(a.rows, a.tile_rows);
+  // The persistent kernel pays where the weight tile is the larger part of a stage (256 output
+  // columns: 1.1 -> 1.5 PFLOP/s at 256 -> 256 channels); with 128 columns or fewer the gather of A
+  // from L2 bounds both kernels alike and the lighter one-tile kernel is as fast or faster.
+  if (!needs_general && a.rowsplit == 2 && s.npad >= 256 && persist_mode() != 0) {
+    const PersistShape ps = persist_shape(s, 2);
+    const int sms = sm_count();
+    const int big_tiles = ceil_div(a.rows, kTileM * ps.R);
+    // from a few tiles per CTA on: a CTA's first tile pays the set-up alone
+    if (ps.stages > 0 && big_tiles >= 3 * sms) {
+      a.stages = ps.stages;
+      // the same number of tiles (within one) for every CTA
+      const int waves = ceil_div(big_tiles, sms);
+      const int ctas = ceil_div(big_tiles, waves);
+      const int pslot = slot >= 4 ? slot - 3 : 0;      // Cin = 64, 128, 256, 512 -> 1..4
+      OCNN_CUDA_OK(launch_chained(persist[a.f16][pslot], dim3(ctas, s.slices), dim3(32 * (4 * ps.R + 6)),
+                                  ps.smem, static_cast<cudaStream_t>(stream), a, big_tiles, ps.acc_bufs));
+      OCNN_LAUNCH_OK("conv_tc_persist_kernel");
+      return OCNN_OK;
+    }
+  }
+  OCNN_CUDA_OK(launch_chained(kernel, dim3(ntiles, s.slices), dim3(kThreads), s.smem,
                               static_cast<cudaStream_t>(stream), a));
   OCNN_LAUNCH_OK("conv_tc_kernel");
   return OCNN_OK;

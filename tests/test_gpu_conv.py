@@ -154,6 +154,18 @@ TC_CASES = [
     (4, 64, 48, [2, 2, 2], 2),
     (3, 128, 128, [1, 1, 1], 1),
     (4, 320, 16, [1, 1, 1], 1),
+    # sibling-product mode (full 3x3x3 kernel, weight set resident in shared memory), every channel
+    # family, on levels from a single tile to many tiles per CTA
+    (6, 8, 16, [3, 3, 3], 1),
+    (2, 8, 32, [3, 3, 3], 1),
+    (6, 16, 32, [3, 3, 3], 1),
+    (3, 16, 16, [3, 3, 3], 1),
+    (6, 16, 64, [3, 3, 3], 1),
+    (6, 32, 32, [3, 3, 3], 1),
+    (5, 32, 64, [3, 3, 3], 1),
+    (6, 64, 32, [3, 3, 3], 1),
+    (4, 64, 16, [3, 3, 3], 1),
+    (6, 8, 64, [3, 3, 3], 1),
 ]
 
 

@@ -192,13 +192,15 @@ def test_full_size_per_layer_parity(full_batch):
 
 
 BENCH_SIZE_TC = [(8, 32, [3, 3, 3]), (32, 32, [3, 3, 3]), (24, 40, [3, 3, 3]), (64, 64, [3, 3, 3]),
-                 (128, 128, [3, 3, 3])]
+                 (128, 128, [3, 3, 3]), (192, 64, [3, 3, 3]), (64, 512, [3, 3, 3]), (128, 256, [3, 3, 3]),
+                 (192, 256, [3, 3, 3])]
 
 
 @pytest.mark.parametrize('case', BENCH_SIZE_TC, ids=lambda c: '%dto%d' % (c[0], c[1]))
 def test_tensor_core_at_benchmark_size(full_batch, case):
-  """The launch configuration the benchmark runs (many waves, two or three CTAs per SM, two-stage
-  rings, 128-row tiles) on the depth-6 level of the benchmark batch: the tensor-core kernel with
+  """The launch configurations the benchmark runs (many waves; two or three CTAs per SM with
+  two-stage rings and 128-row tiles, or, where Cin is a multiple of 64, the persistent kernel with
+  256-row tiles and a ragged last tile) on the depth-6 level of the benchmark batch: the tensor-core kernel with
   its fused epilogue against the fp32 kernel on the same GPU (every row) and against the CPU oracle
   on a sample of rows."""
   import ocnn
@@ -238,3 +240,43 @@ def test_tensor_core_at_benchmark_size(full_batch, case):
     col = np.where(nb[None, :] >= 0, xn[:, np.maximum(nb, 0)], 0.0)          # [cin, 27]
     y = np.maximum(np.einsum('oct,ct->o', wn, col) * sc + bi + rn[:, h], 0)
     assert np.abs(gn[:, h] - y).max() < 2e-2 * max(1.0, np.abs(y).max()), h
+
+
+PERSISTENT_CASES = [
+    # (depth of the output, cin, cout, kernel, stride, nempty, fp16)
+    (6, 64, 256, [3, 3, 3], 1, True, False),     # non-empty nodes only: rows through ichild / child
+    (5, 64, 256, [3, 3, 3], 2, False, True),     # stride 2 (output on depth 5), fp16
+    (6, 128, 256, [1, 1, 1], 1, False, False),   # 1x1: the identity table
+    (5, 128, 512, [3, 3, 3], 1, False, True),    # two slices of 256 columns, fp16
+]
+
+
+@pytest.mark.parametrize('case', PERSISTENT_CASES, ids=lambda c: 'd%d_%dto%d_k%s_s%d_ne%d_h%d' % (
+    c[0], c[1], c[2], ''.join(map(str, c[3])), c[4], c[5], c[6]))
+def test_persistent_kernel_layer_kinds(full_batch, case):
+  """The persistent tensor-core kernel (256 output columns, levels of many tiles) on the layer kinds
+  it serves besides the plain convolution, against the CUDA-core fp32-accumulating kernel on the
+  same 16-bit data (that kernel is checked against the CPU code on the small batch)."""
+  import ocnn
+  pts, merged, _, _, _ = full_batch
+  d_out, cin, cout, ks, stride, nempty, half = case
+  d_in = d_out + 1 if stride == 2 else d_out
+  octree = gu.to_cuda_u8(merged)
+  v = oc.OctreeView(merged)
+  H = int(v.nnum_nempty[d_in]) if nempty else int(v.nnum[d_in])
+  dt = torch.float16 if half else torch.bfloat16
+  g = torch.Generator(device='cuda').manual_seed(cin + cout + stride)
+  x = (torch.rand(1, cin, H, 1, device='cuda', generator=g) * 2 - 1).to(dt)
+  x = x.contiguous(memory_format=torch.channels_last)
+  kd = int(np.prod(ks))
+  w = (torch.randn(cout, cin * kd, device='cuda', generator=g) * 0.1)
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights_general(w, cin, cout, ks, stride, False, nempty, half)
+  got = ocnn.nn.octree_conv_tc_general(x, packed, octree, d_in, cout, ks, stride, nempty, False,
+                                       None, None, None, False, status)
+  ref = ocnn.nn.octree_conv_general(x, w, octree, d_in, cout, ks, stride, nempty, False)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  assert got.shape == ref.shape and got.shape[2] >= 3 * 148 * 256
+  err = float((got.float() - ref.float()).abs().max()) / float(ref.float().abs().max())
+  assert err < 1.2e-2, err
