@@ -22,9 +22,14 @@ struct PwArgs {
   const __nv_bfloat16* residual;
   int relu;
   int f16;                 // the 16-bit elements are fp16 instead of bf16
+  int wide;                // x, y and the residual start on 32-byte boundaries
 };
 
-template <int COUT, int ROWS, bool HALF>
+// CIN > 0: the channel count is a compile-time constant and a thread requests its whole rows
+// (and the residual rows) before it starts on the arithmetic, 32 bytes per load where the row
+// allows: with one 16-byte piece in flight per thread the kernel waited on memory latency (42 %
+// of the HBM copy rate).  CIN == 0: any Cin % 8 == 0, one 16-byte piece at a time.
+template <int CIN, int COUT, int ROWS, bool HALF>
 __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
   extern __shared__ float ws[];                      // [cin][COUT]
   grid_dependency_trigger();
@@ -34,7 +39,6 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
     ws[ci * COUT + co] = a.w[(long long)a.co_base * a.cin + i];
   }
   __syncthreads();
-  const int chunks = a.cin >> 3;
   const long long stride = (long long)gridDim.x * blockDim.x;
   // thread t of the grid handles rows t, t + stride, ... in packets of ROWS rows spaced by the
   // grid size, so that a warp always touches 32 consecutive rows
@@ -44,14 +48,32 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
     for (int r = 0; r < ROWS; ++r)
 #pragma unroll
       for (int co = 0; co < COUT; ++co) acc[r][co] = 0.f;
-    for (int c8 = 0; c8 < chunks; ++c8) {
-      float xv[ROWS][8];
+    constexpr int kResPieces = COUT / 8;
+    uint4 rres[ROWS][kResPieces];
+    auto load_residual = [&]() {
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
         const long long h = h0 + r * stride;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (h < a.h) raw = reinterpret_cast<const uint4*>(a.x + h * a.cin)[c8];
-        const uint32_t* p = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+        for (int q = 0; q < kResPieces; ++q) rres[r][q] = make_uint4(0, 0, 0, 0);
+        if (a.residual == nullptr || h >= a.h) continue;
+        const __nv_bfloat16* rp = a.residual + h * a.y_stride + a.co_base;
+        if constexpr (COUT % 16 == 0) {
+          if (a.wide) {
+#pragma unroll
+            for (int q = 0; q < kResPieces; q += 2) ld_global_32B(rp + 8 * q, rres[r][q], rres[r][q + 1]);
+            continue;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < kResPieces; ++q) rres[r][q] = *reinterpret_cast<const uint4*>(rp + 8 * q);
+      }
+    };
+    auto fma_piece = [&](const uint4 (&raw)[ROWS], int c8) {
+      float xv[ROWS][8];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&raw[r]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float2 f = unpack2(p[k], HALF);
@@ -74,11 +96,49 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
           }
         }
       }
+    };
+    if constexpr (CIN > 0) {
+      constexpr int kPieces = CIN / 8;
+      uint4 xr[kPieces][ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const long long h = h0 + r * stride;
+#pragma unroll
+        for (int c8 = 0; c8 < kPieces; ++c8) xr[c8][r] = make_uint4(0, 0, 0, 0);
+        if (h >= a.h) continue;
+        const __nv_bfloat16* xp = a.x + h * CIN;
+        if constexpr (CIN % 16 == 0) {
+          if (a.wide) {
+#pragma unroll
+            for (int c8 = 0; c8 < kPieces; c8 += 2) ld_global_32B(xp + 8 * c8, xr[c8][r], xr[c8 + 1][r]);
+            continue;
+          }
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < kPieces; ++c8) xr[c8][r] = reinterpret_cast<const uint4*>(xp)[c8];
+      }
+      load_residual();
+#pragma unroll
+      for (int c8 = 0; c8 < kPieces; ++c8) fma_piece(xr[c8], c8);
+    } else {
+      load_residual();
+      const int chunks = a.cin >> 3;
+      for (int c8 = 0; c8 < chunks; ++c8) {
+        uint4 raw[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          const long long h = h0 + r * stride;
+          raw[r] = make_uint4(0, 0, 0, 0);
+          if (h < a.h) raw[r] = reinterpret_cast<const uint4*>(a.x + h * a.cin)[c8];
+        }
+        fma_piece(raw, c8);
+      }
     }
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       const long long h = h0 + r * stride;
       if (h >= a.h) continue;
+      uint4 ov[kResPieces];
 #pragma unroll
       for (int q = 0; q < COUT / 8; ++q) {
         float f[8];
@@ -88,10 +148,8 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
           if (a.scale) f[j] *= a.scale[a.co_base + 8 * q + j];
           if (a.bias) f[j] += a.bias[a.co_base + 8 * q + j];
         }
-        const long long at = h * a.y_stride + a.co_base + 8 * q;
         if (a.residual) {
-          const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + at);
-          const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rv);
+          const uint32_t* rp = reinterpret_cast<const uint32_t*>(&rres[r][q]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float2 rf = unpack2(rp[j], HALF);
@@ -103,17 +161,25 @@ __global__ void __launch_bounds__(256) conv_pw_kernel(const PwArgs a) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
         }
-        uint4 ov;
-        uint32_t* op = reinterpret_cast<uint32_t*>(&ov);
+        uint32_t* op = reinterpret_cast<uint32_t*>(&ov[q]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) op[j] = pack2(f[2 * j], f[2 * j + 1], HALF);
-        *reinterpret_cast<uint4*>(a.y + at) = ov;
       }
+      __nv_bfloat16* yp = a.y + h * a.y_stride + a.co_base;
+      if constexpr (COUT % 16 == 0) {
+        if (a.wide) {
+#pragma unroll
+          for (int q = 0; q < kResPieces; q += 2) st_global_32B(yp + 8 * q, ov[q], ov[q + 1]);
+          continue;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kResPieces; ++q) *reinterpret_cast<uint4*>(yp + 8 * q) = ov[q];
     }
   }
 }
 
-template <int COUT, int ROWS, bool HALF>
+template <int CIN, int COUT, int ROWS, bool HALF>
 int launch_pw_t(const PwArgs& a, cudaStream_t st) {
   const size_t smem = (size_t)a.cin * COUT * sizeof(float);
   static PerDeviceOnce attr_once;      // one per template instance
@@ -123,20 +189,30 @@ int launch_pw_t(const PwArgs& a, cudaStream_t st) {
     std::lock_guard<std::mutex> lock(attr_once.mutex);
     const bool known = device >= 0 && device < 64;
     if (!known || !attr_once.done[device]) {
-      OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<COUT, ROWS, HALF>,
+      OCNN_CUDA_OK(cudaFuncSetAttribute(conv_pw_kernel<CIN, COUT, ROWS, HALF>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
       if (known) attr_once.done[device] = true;
     }
   }
   const int grid = grid_for(((long long)a.h + ROWS - 1) / ROWS, 256, 4);
-  OCNN_CUDA_OK(launch_chained(conv_pw_kernel<COUT, ROWS, HALF>, dim3(grid), dim3(256), smem, st, a));
+  OCNN_CUDA_OK(launch_chained(conv_pw_kernel<CIN, COUT, ROWS, HALF>, dim3(grid), dim3(256), smem, st, a));
   OCNN_LAUNCH_OK("conv_pw_kernel");
   return OCNN_OK;
 }
 
 template <int COUT, int ROWS>
 int launch_pw(const PwArgs& a, cudaStream_t st) {
-  return a.f16 ? launch_pw_t<COUT, ROWS, true>(a, st) : launch_pw_t<COUT, ROWS, false>(a, st);
+  // the channel counts of the reference's bottleneck blocks get the whole-row variant
+  switch (a.cin) {
+    case 8:
+      return a.f16 ? launch_pw_t<8, COUT, ROWS, true>(a, st) : launch_pw_t<8, COUT, ROWS, false>(a, st);
+    case 16:
+      return a.f16 ? launch_pw_t<16, COUT, ROWS, true>(a, st) : launch_pw_t<16, COUT, ROWS, false>(a, st);
+    case 32:
+      return a.f16 ? launch_pw_t<32, COUT, ROWS, true>(a, st) : launch_pw_t<32, COUT, ROWS, false>(a, st);
+    default:
+      return a.f16 ? launch_pw_t<0, COUT, ROWS, true>(a, st) : launch_pw_t<0, COUT, ROWS, false>(a, st);
+  }
 }
 
 }  // namespace
@@ -160,6 +236,8 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
   a.relu = ep ? ep->relu : 0;
   a.f16 = f16 ? 1 : 0;
+  a.wide = (((uintptr_t)x % 32) == 0 && ((uintptr_t)y % 32) == 0 &&
+            (!(ep && ep->residual_dev) || ((uintptr_t)ep->residual_dev % 32) == 0)) ? 1 : 0;
   switch (cout) {
     case 8: return launch_pw<8, 2>(a, st);
     case 16: return launch_pw<16, 2>(a, st);

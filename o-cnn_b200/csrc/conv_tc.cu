@@ -74,6 +74,9 @@ struct TcArgs {
   int f16;          // the 16-bit elements are fp16 instead of bf16
   int expand_cout;  // > 0: the kernel-2 stride-2 deconvolution as a dense product: tile row = a
                     // parent, its row_elems = 8 * expand_cout columns are (octant, channel) pairs
+  int fold_cout;    // > 0: a 1x1x1 layer with Cin < 64 run on rows of 64/Cin nodes (one 128-byte
+                    // line) against block-diagonal weights: column n is channel n % fold_cout of
+                    // node n / fold_cout of the row
   const int* scatter_child;   // with expand_cout: Child block of the finer level; octant o of tile
                               // row h is written to row scatter_child[8h + o] (skipped when < 0)
   const float* scale;
@@ -299,6 +302,7 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
   for (int n = tid; n < a.npad; n += kThreads) {
     // output channel of column n: columns are (octant, channel) pairs in group mode
     int co = a.group ? (n & (a.cout - 1)) : co_base + n;
+    if (a.fold_cout) co = n % a.fold_cout;
     if (GENERAL && a.expand_cout) co = (co_base + n) % a.expand_cout;
     const bool live = n < a.row_elems;
     s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
@@ -747,24 +751,29 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
   uint64_t* empty = bars + a.stages;
   uint64_t* tfull = bars + 2 * a.stages;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* wfull = tempty + 2;                  // single K-block: the one weight tile has landed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(wfull + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int co_base = blockIdx.y * a.cout;
   const uint8_t* wpacked = a.wpacked + (size_t)blockIdx.y * a.nkb * (a.npad * 128);
   const int acc_cols = R * a.tmem_cols;          // TMEM columns of one accumulator set
+  // A layer of one K-block (a 1x1x1 layer on 64 channels) uses the same weight tile for every
+  // tile of rows: it is fetched once into slot 0 of the B ring and stays there.
+  const bool b_resident = a.nkb == 1;
   grid_dependency_trigger();
 
   if (tid == 0) {
     for (int s = 0; s < a.stages; ++s) {
-      mbar_init(smem_u32(&full[s]), kRows + 1);
+      mbar_init(smem_u32(&full[s]), b_resident ? kRows : kRows + 1);
       mbar_init(smem_u32(&empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tfull[b]), 1);
       mbar_init(smem_u32(&tempty[b]), kTileM);
     }
+    mbar_init(smem_u32(wfull), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -777,8 +786,9 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
   grid_dependency_wait();
   for (int n = tid; n < a.npad; n += kThreadsP) {
     const bool live = n < a.row_elems;
-    s_scale[n] = (live && a.scale) ? a.scale[co_base + n] : 1.f;
-    s_bias[n] = (live && a.bias) ? a.bias[co_base + n] : 0.f;
+    const int co = a.fold_cout ? n % a.fold_cout : co_base + n;
+    s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
+    s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -880,6 +890,7 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
       int s = 0;
       uint32_t pf = 0;
       int it = 0;
+      if (b_resident) alive = mbar_wait(smem_u32(wfull), 0, abort_flag, a.status, kErrWeightWait);
       for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++it) {
         const int b = it % acc_bufs;
         const uint32_t use = (uint32_t)(it / acc_bufs);
@@ -894,7 +905,7 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = smem_u32(sA + s * (R * kStageA));
-          const uint32_t b_addr = smem_u32(sB + s * stage_b);
+          const uint32_t b_addr = smem_u32(sB + (b_resident ? 0 : s * stage_b));
 #pragma unroll
           for (int r = 0; r < R; ++r) {
 #pragma unroll
@@ -925,7 +936,16 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
                        : "memory");
       }
     }
-    if (lane == 0) {
+    if (lane == 0 && b_resident) {
+      const uint32_t bar = smem_u32(wfull);
+      mbar_arrive_expect_tx(bar, (uint32_t)stage_b);
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+          ::"r"(smem_u32(sB)), "l"(wpacked), "r"((uint32_t)stage_b), "r"(bar)
+          : "memory");
+      // stay until it has landed (bounded): the CTA must not retire under the copy
+      mbar_wait(bar, 0, abort_flag, a.status, kErrWeightWait);
+    } else if (lane == 0) {
       bool alive = true;
       int s = 0;
       uint32_t pe = 1;
@@ -1069,6 +1089,8 @@ struct WeightView {
   int cin, cout, T;      // of the layer as the reference sees it
   int transposed;
   int fold_in, expand_out;
+  int fold_nodes;        // > 1: 1x1x1 layer on rows of fold_nodes nodes: block-diagonal weights,
+                         // K index k = node*Cin + ci, column n = node*Cout + co
   int co_base;           // first output column of this 256-column slice
 };
 
@@ -1102,7 +1124,9 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, uint16_t* __res
     float val = 0.f;
     if (n < ncols && k < kdim) {
       const int col = v.co_base + n;
-      if (v.expand_out) {
+      if (v.fold_nodes > 1) {
+        val = (col / v.cout == k / v.cin) ? weight_at(w, v, col % v.cout, k % v.cin, 0) : 0.f;
+      } else if (v.expand_out) {
         // column = octant * Cout + channel; the only tap that reaches octant o is tap o
         val = weight_at(w, v, col % v.cout, k, col / v.cout);
       } else {
@@ -1149,15 +1173,52 @@ __global__ void pack_weights_group_kernel(const float* __restrict__ w, uint16_t*
   }
 }
 
+// The last h % fold nodes of a folded 1x1x1 layer (a node count that does not fill its last row;
+// only data on non-empty nodes can have one): one thread per (node, output channel), weights read
+// back from the first diagonal block of the packed image.
+template <bool HALF>
+__global__ void fold_tail_kernel(const __nv_bfloat16* __restrict__ x, const uint16_t* __restrict__ packed,
+                                 __nv_bfloat16* __restrict__ y, long long first, int count, int cin,
+                                 int cout, const float* __restrict__ scale, const float* __restrict__ bias,
+                                 const __nv_bfloat16* __restrict__ residual, int relu) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count * cout) return;
+  const int node = i / cout, co = i % cout;
+  const uint16_t* xr = reinterpret_cast<const uint16_t*>(x) + (first + node) * cin;
+  float acc = 0.f;
+  for (int ci = 0; ci < cin; ++ci) {
+    const uint16_t wv = packed[(co >> 3) * 512 + (co & 7) * 64 + (((ci >> 3) ^ (co & 7)) << 3) + (ci & 7)];
+    const float2 xf = unpack2((uint32_t)xr[ci], HALF), wf = unpack2((uint32_t)wv, HALF);
+    acc = fmaf(xf.x, wf.x, acc);
+  }
+  if (scale) acc *= scale[co];
+  if (bias) acc += bias[co];
+  const long long at = (first + node) * cout + co;
+  if (residual) acc += unpack2((uint32_t)reinterpret_cast<const uint16_t*>(residual)[at], HALF).x;
+  if (relu) acc = fmaxf(acc, 0.f);
+  reinterpret_cast<uint16_t*>(y)[at] = (uint16_t)(pack2(acc, 0.f, HALF) & 0xffffu);
+}
+
 // What kind of layer a launch serves (the reference's OctreeConv / OctreeDeconv flags).
 struct LayerKind {
   int stride;
   bool transposed, nempty;
 };
 
+// 0: never fold nodes of 1x1x1 layers into 128-byte rows; 1: fold where it applies (default).
+// Read once: the packed weight image depends on it.
+int fold_mode() {
+  static const int mode = [] {
+    const char* e = getenv("OCNN_CONV_FOLD");
+    return e ? atoi(e) : 1;
+  }();
+  return mode;
+}
+
 struct TcShape {
   int T, npad, nkb, tmem_cols, stages, group, slices, tile_rows, gtable, ntable_stride;
   int fold_in, expand_out;   // kernel 2, stride 2 as a dense product (see WeightView)
+  int fold_nodes;            // 1x1x1 with Cin < 64: 64/Cin nodes per tile row (1 = not folded)
   int cin_eff, cout_eff;     // channel counts the kernel sees: 8*Cin when folded, 8*Cout when expanded
   size_t smem;
   size_t fixed_bytes, stage_bytes;   // shared memory outside the ring / per ring stage
@@ -1182,8 +1243,16 @@ int tc_shape(int cin, int cout, const int ks[3], const LayerKind& kind, TcShape*
   // nodes).  Both are then plain dense products with no gather.
   s->fold_in = (k222s2 && !kind.transposed && !kind.nempty) ? 1 : 0;
   s->expand_out = (k222s2 && kind.transposed && (cout * 8 <= 256 || cout % 32 == 0) && cout * 8 <= 4096) ? 1 : 0;
-  s->cin_eff = s->fold_in ? 8 * cin : cin;
-  s->cout_eff = s->expand_out ? 8 * cout : cout;
+  // 1x1x1, stride 1, fewer than 64 channels in: a K-block of one node would be mostly padding and
+  // a tile of 128 nodes only 128*Cin*2 bytes.  64/Cin consecutive nodes are one 128-byte line, so
+  // the layer runs on rows of 64/Cin nodes with block-diagonal weights (K = 64 exactly, N =
+  // 64/Cin * Cout): a plain stream of full lines through one K-block per tile.
+  s->fold_nodes = 1;
+  if (tl.count == 1 && stride == 1 && !kind.transposed && !kind.nempty && cin < 64 && 64 % cin == 0 &&
+      cout % 8 == 0 && (64 / cin) * cout <= 256 && fold_mode() != 0)
+    s->fold_nodes = 64 / cin;
+  s->cin_eff = s->fold_in ? 8 * cin : (s->fold_nodes > 1 ? 64 : cin);
+  s->cout_eff = s->expand_out ? 8 * cout : (s->fold_nodes > 1 ? s->fold_nodes * cout : cout);
   cout = s->cout_eff;
   if (cout <= 0 || cout % 8 != 0 || (cout > 256 && cout % 256 != 0) || cout > 4096)
     return fail(OCNN_ERR_UNSUPPORTED,
@@ -1219,7 +1288,7 @@ int tc_shape(int cin, int cout, const int ks[3], const LayerKind& kind, TcShape*
   int st = two_cta > fixed ? (int)((two_cta - fixed) / stage_bytes) : 0;
   // a grid that does not even fill the SMs once gains nothing from co-residency: give the lone CTA
   // of each SM the deepest ring instead (its K loop is a pure latency chain)
-  const long long rows = rows_hint < 0 ? -1 : (s->group ? rows_hint / 8 : rows_hint);
+  const long long rows = rows_hint < 0 ? -1 : (s->group ? rows_hint / 8 : rows_hint / s->fold_nodes);
   // A level too small to give even half of the SMs a 128-row tile is cut into 64- or 32-row
   // tiles: the gather is then spread over more SMs.  Every CTA still streams the whole weight
   // image, so halving stops where a K-block's gather (about 8 cycles per row of 16-byte copies)
@@ -1308,7 +1377,7 @@ int pack_weights_impl(const float* w, void* packed, int cin, int cout, const int
     // one packed image per slice of (at most) 256 output columns
     WeightView v;
     v.cin = cin; v.cout = cout; v.T = tl.count; v.transposed = kind.transposed ? 1 : 0;
-    v.fold_in = s.fold_in; v.expand_out = s.expand_out;
+    v.fold_in = s.fold_in; v.expand_out = s.expand_out; v.fold_nodes = s.fold_nodes;
     const int cslice = s.slices > 1 ? 256 : s.cout_eff;
     const int kdim = s.cin_eff * s.T;
     for (int sl = 0; sl < s.slices; ++sl) {
@@ -1365,13 +1434,35 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   a.up = (plain_gather && kind.transposed && stride == 2) ? 1 : 0;
   a.f16 = dtype == OCNN_F16 ? 1 : 0;
   a.expand_cout = s.expand_out ? cout : 0;
+  a.fold_cout = s.fold_nodes > 1 ? cout : 0;
+  const int fold_tail = s.fold_nodes > 1 ? h_out % s.fold_nodes : 0;
+  if (fold_tail > 0) {
+    // the nodes that do not fill a row
+    const long long first = h_out - fold_tail;
+    const int threads = fold_tail * cout;
+    if (dtype == OCNN_F16)
+      fold_tail_kernel<true><<<ceil_div(threads, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<const uint16_t*>(packed),
+          static_cast<__nv_bfloat16*>(y), first, fold_tail, cin, cout, ep ? ep->scale_dev : nullptr,
+          ep ? ep->bias_dev : nullptr, ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr,
+          ep ? ep->relu : 0);
+    else
+      fold_tail_kernel<false><<<ceil_div(threads, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<const uint16_t*>(packed),
+          static_cast<__nv_bfloat16*>(y), first, fold_tail, cin, cout, ep ? ep->scale_dev : nullptr,
+          ep ? ep->bias_dev : nullptr, ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr,
+          ep ? ep->relu : 0);
+    OCNN_LAUNCH_OK("fold_tail_kernel");
+    note_launches(1);
+    if (h_out < s.fold_nodes) return OCNN_OK;
+  }
   a.scatter_child = scatter ? g->child_dev : nullptr;
   a.h_in = h_in; a.h_out = h_out; a.cin = s.cin_eff; a.npad = s.npad; a.T = s.T;
   a.stride = (s.fold_in || s.expand_out) ? 1 : stride;
   a.identity = identity ? 1 : 0; a.nkb = s.nkb; a.stages = s.stages;
   a.tmem_cols = s.tmem_cols;
   a.group = s.group;
-  a.rows = s.group ? h_out / 8 : (s.expand_out ? h_in : h_out);
+  a.rows = s.group ? h_out / 8 : (s.expand_out ? h_in : h_out / s.fold_nodes);
   const int cslice = s.slices > 1 ? 256 : s.cout_eff;
   a.cout = cslice;
   a.row_elems = s.group ? 8 * cout : cslice;
@@ -1456,7 +1547,10 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   // The persistent kernel pays where the weight tile is the larger part of a stage (256 output
   // columns: 1.1 -> 1.5 PFLOP/s at 256 -> 256 channels); with 128 columns or fewer the gather of A
   // from L2 bounds both kernels alike and the lighter one-tile kernel is as fast or faster.
-  if (!needs_general && a.rowsplit == 2 && s.npad >= 256 && persist_mode() != 0) {
+  // ... and for single-K-block layers (1x1x1 on 64 channels, folded or not), which are plain
+  // streams: its weight tile stays resident and nothing is set up per 128 rows.
+  if (!needs_general && a.rowsplit == 2 && (s.npad >= 256 || (s.nkb == 1 && identity)) &&
+      persist_mode() != 0) {
     const PersistShape ps = persist_shape(s, 2);
     const int sms = sm_count();
     const int big_tiles = ceil_div(a.rows, kTileM * ps.R);

@@ -343,7 +343,10 @@ class GpuNet:
     # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
     # else that fits goes to the tensor-core kernel
     cout = p['_cout']
-    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin <= 32)
+    # (from 32 channels in, the tensor-core kernel on rows of two nodes is the faster stream:
+    # 32 -> 8 at 972 k nodes 0.026 ms against 0.031 ms; with 8 or 16 channels in its rows hold
+    # 8 or 4 nodes and the block-diagonal product costs more than it saves)
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin <= 16)
     if self.tc and cin % 8 == 0 and cout % 8 == 0 and (cout <= 256 or cout % 256 == 0):
       try:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, cout, p['ks'])

@@ -215,6 +215,33 @@ def test_conv_tensor_core_epilogue(ocnn, batch):
   assert gu.rel_err(gu.to_np(got), want) < 8e-3
 
 
+@pytest.mark.parametrize('half', [False, True], ids=['bf16', 'fp16'])
+@pytest.mark.parametrize('shape', [(1001, 8, 32), (1003, 16, 64), (77, 32, 8), (5, 8, 8), (2048, 32, 16),
+                                   (300007, 8, 32), (300001, 32, 8)])
+def test_pointwise_tensor_core_any_height(ocnn, shape, half):
+  """1x1x1 layers with fewer than 64 input channels run on rows of 64/Cin nodes; a node count that
+  does not fill the last row (data on non-empty nodes) is finished by a separate small launch."""
+  H, cin, cout = shape
+  rng = np.random.default_rng(H + cin)
+  rnd = gu.half_round if half else gu.bf16_round
+  x = rnd(rng.uniform(-1, 1, size=(cin, H)).astype(np.float32))
+  w = rng.normal(scale=0.2, size=(cout, cin)).astype(np.float32)
+  scale = rng.uniform(0.5, 1.5, size=cout).astype(np.float32)
+  bias = rng.normal(size=cout).astype(np.float32)
+  res = rnd(rng.normal(size=(cout, H)).astype(np.float32))
+  want = np.maximum((rnd(w) @ x) * scale[:, None] + bias[:, None] + res, 0)
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights_general(torch.from_numpy(w).cuda(), cin, cout, [1, 1, 1], 1, False,
+                                             False, half)
+  got = ocnn.nn.pointwise_conv_tc(gu.data_cuda(x, True, not half, half), packed, cout,
+                                  torch.from_numpy(scale).cuda(), torch.from_numpy(bias).cuda(),
+                                  gu.data_cuda(res, True, not half, half), True, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  assert got.shape == (1, cout, H, 1)
+  assert gu.rel_err(gu.to_np(got), want) < (3e-3 if half else 8e-3)
+
+
 def test_conv_tensor_core_rejects_unsupported_shapes(ocnn, batch):
   _, octree, v = batch
   w = torch.zeros(16, 3 * 27, device='cuda')
