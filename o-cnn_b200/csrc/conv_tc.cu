@@ -811,15 +811,15 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
     const int* my_idx = nbr + warp * 32 + sub * 8;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const int h0 = tile * kRows;
+      // 1x1x1: a tile row reads its own row, no table and no barriers
+      if (!a.identity) {
       gather_bar<R>();                 // every gather thread has finished reading the previous table
       {
         const int h = h0 + tid;
         const bool live = h < a.rows;
         const int hn = (a.ichild != nullptr && live) ? a.ichild[h] : h;
         const int oct_code = ((hn & 4) << 2) | ((hn & 2) << 1) | (hn & 1);
-        if (a.identity) {
-          nbr[slot] = live ? h : -1;
-        } else {
+        {
           int pv[27];
 #pragma unroll
           for (int t = 0; t < 27; ++t) {
@@ -842,15 +842,18 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
         }
       }
       gather_bar<R>();
+      }
 
       uint32_t row_mask = 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         if (h0 + rbase + 4 * i < a.rows) row_mask |= 1u << i;
       int p[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) p[i] = h0 + rbase + 4 * i;      // (identity; masked rows are not copied)
       int t = 0, part = 0;
       for (int kb = 0; kb < a.nkb; ++kb, ++gk) {
-        if (part == 0) {
+        if (part == 0 && !a.identity) {
           const int4 lo = *reinterpret_cast<const int4*>(my_idx + t * kRows);
           const int4 hi = *reinterpret_cast<const int4*>(my_idx + t * kRows + 4);
           p[0] = lo.x; p[1] = lo.y; p[2] = lo.z; p[3] = lo.w;
