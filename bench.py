@@ -332,6 +332,9 @@ def run_ours(args):
   world = int(os.environ.get('WORLD_SIZE', '1'))
   local = int(os.environ.get('LOCAL_RANK', '0'))
   torch.cuda.set_device(local)
+  # the pipeline's host threads hand the interpreter lock to each other between their (lock-free)
+  # launch calls: a thread that wants it should not wait out the default 5 ms switch interval
+  sys.setswitchinterval(1e-4)
   if world > 1:
     import torch.distributed as dist
     dist.init_process_group('nccl', device_id=torch.device('cuda', local))
@@ -531,12 +534,18 @@ def run_ours(args):
   # reach their steady state before the timed region)
   for _ in range(2):
     pipelined(max(args.warmup, 3, args.steps), lambda k, st: inputs[k % nbuf])
-  launches0 = ocnn.nn.launch_count()
-  t_host0 = time.perf_counter()
-  total_ms = pipelined(args.steps, lambda k, st: inputs[k % nbuf])
-  host_split_timed = dict(host_split)
-  host_ms = (time.perf_counter() - t_host0) * 1e3
-  launches = ocnn.nn.launch_count() - launches0
+  # Three timed regions of exactly K steps each, back to back; the median one is reported (all three
+  # are listed).  Six host threads feed the GPU here, and a single host-side stall of a few tens of
+  # milliseconds (seen once in about ten runs) would otherwise decide the figure of a 35 ms region.
+  regions = []
+  for _ in range(3):
+    launches0 = ocnn.nn.launch_count()
+    t_host0 = time.perf_counter()
+    ms = pipelined(args.steps, lambda k, st: inputs[k % nbuf])
+    regions.append((ms, dict(host_split), (time.perf_counter() - t_host0) * 1e3,
+                    ocnn.nn.launch_count() - launches0))
+  total_ms, host_split_timed, host_ms, launches = sorted(regions, key=lambda r: r[0])[1]
+  timed_regions_ms = [r[0] for r in regions]
   assert all(n.error_status() == 0 for n in fwd_nets), 'a kernel reported an error status'
 
   # ---- end to end: pinned host points -> H2D -> build -> forward -> logits D2H, every step ----
@@ -561,7 +570,8 @@ def run_ours(args):
 
   for _ in range(2):
     pipelined(max(3, args.steps), e2e_src, e2e_result)
-  e2e_ms = pipelined(args.steps, e2e_src, e2e_result)
+  e2e_regions_ms = [pipelined(args.steps, e2e_src, e2e_result) for _ in range(3)]
+  e2e_ms = sorted(e2e_regions_ms)[1]
   torch.cuda.synchronize()
   assert all(bool(torch.isfinite(t).all()) for t in logits_host), 'end-to-end logits are not finite'
 
@@ -685,12 +695,15 @@ def run_ours(args):
   line = {'metric': METRIC, 'value': shapes / (total_ms * 1e-3), 'unit': UNIT, 'n_gpus': world,
           'steps': args.steps, 'warmup': args.warmup, 'warmup_run': 2 * max(args.warmup, 3, args.steps),
           'ms_per_step': total_ms / args.steps,
+          'timed_regions_ms': [round(v, 4) for v in timed_regions_ms],
+          'timed_region_reported': 'the median of three back-to-back regions of `steps` steps each',
           'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16',
           'data': 'synthetic', 'config': cfg,
           'e2e': {'value': shapes / (e2e_ms * 1e-3), 'unit': UNIT,
                   'h2d_bytes_per_step': int(packed_host.numel()) * world,
                   'd2h_bytes_per_step': BATCH * 40 * 4 * world,
                   'ms_per_step': e2e_ms / args.steps,
+                  'timed_regions_ms': [round(v, 4) for v in e2e_regions_ms],
                   'pipeline': 'pinned host buffers; the H2D copy of every batch on a copy stream, its '
                               'build on the build stream, the network on the main stream; logits '
                               'copied back to pinned memory every step'},
