@@ -285,6 +285,14 @@ int ocnn_octree_conv_tc(const void* x_dev, const void* packed_weights_dev, void*
                         const int kernel_size[3], int stride,
                         const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
 
+/* Self-test of the bounded waits of the tensor-core kernels (no reference counterpart: the
+ * reference has no such kernels).  Launches one small CTA whose two waiting threads wait on a
+ * barrier that nobody arrives on.  status_dev: two int32, zero before the call; afterwards
+ * status_dev[0] = 1 or 2 (the code of the wait that ran out of polls first) and status_dev[1] = 1
+ * (the second waiter came back with "stop").  The kernel returns by itself after about 2^20 polls (well under a
+ * second); the context stays usable. */
+int ocnn_conv_tc_wait_selftest(int32_t* status_dev, void* stream);
+
 /* The tensor-core kernel for every layer kind ocnn_octree_conv_general takes, on bf16 or fp16
  * node-major data (dtype = OCNN_BF16 / OCNN_F16; fp32 accumulation in TMEM either way).  The packed
  * image depends on (cin, cout, kernel, stride, transposed, nempty, dtype): pack with the same

@@ -1078,6 +1078,28 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
   }
 }
 
+// ---- self-test of the bounded waits -------------------------------------------------------------
+// One CTA, two waiting threads, a barrier that nobody ever arrives on: the first waiter must run
+// out of polls, write its code to status[0] and raise the abort flag; the second must come back
+// from its own wait with "stop" (status[1] = 1).  Exactly the mbar_wait the convolution kernels use.
+__global__ void wait_selftest_kernel(int* status) {
+  __shared__ uint64_t never;
+  __shared__ int abort_flag_s;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&never), 1);
+    abort_flag_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abort_flag = &abort_flag_s;
+  if (threadIdx.x == 0) {
+    mbar_wait(smem_u32(&never), 0, abort_flag, status, kErrFullWait);
+  } else if (threadIdx.x == 32) {
+    const bool ok = mbar_wait(smem_u32(&never), 0, abort_flag, status, kErrEmptyWait);
+    status[1] = ok ? 0 : 1;
+  }
+}
+
 // ---- weight packing -------------------------------------------------------------------------
 // packed: per K-block a [npad x 64] tile of 16-bit floats in the swizzled K-major image: element
 // (n, kk) at (n/8)*1024 + (n%8)*128 + (((kk/8) ^ (n%8)) * 16) + (kk%8)*2, k = kb*64 + kk.
@@ -1621,6 +1643,14 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   g.stride = stride; g.h_in = h_in; g.h_out = h_out; g.neigh_dev = neigh;
   return ocnn::conv_tc_impl(x, packed, y, &g, cin, cout, kernel_size, OCNN_BF16, ep, status, stream,
                             "ocnn_octree_conv_tc");
+}
+
+int ocnn_conv_tc_wait_selftest(int32_t* status, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(status != nullptr, "ocnn_conv_tc_wait_selftest: null status");
+  wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status);
+  OCNN_LAUNCH_OK("wait_selftest_kernel");
+  return OCNN_OK;
 }
 
 int ocnn_octree_conv_tc_nempty(const void* x, const void* packed, void* y, const int32_t* neigh,

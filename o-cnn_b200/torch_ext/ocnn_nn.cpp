@@ -519,6 +519,13 @@ Tensor octree_conv_tc(Tensor data_in, Tensor packed, Tensor octree, int depth, i
   return y;
 }
 
+// ocnn_conv_tc_wait_selftest: [code of the expired wait, second waiter stopped] on the current device.
+Tensor conv_tc_wait_selftest() {
+  Tensor status = torch::zeros({2}, torch::dtype(torch::kInt32).device(torch::kCUDA));
+  OCNN_CALL(ocnn_conv_tc_wait_selftest(status.data_ptr<int32_t>(), current_stream()));
+  return status;
+}
+
 // Tensor-core convolution on the non-empty nodes only (nempty = True, stride 1).
 Tensor conv_pack_weights_nempty(Tensor weights, int cin, int cout, vector<int> kernel_size) {
   vector<int> ks = kernel3(kernel_size);
@@ -1763,6 +1770,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("residual") = py::none(), py::arg("relu") = false);
   m.def("conv_pack_weights", &conv_pack_weights, py::arg("weights"), py::arg("cin"), py::arg("cout"),
         py::arg("kernel_size"), py::arg("stride") = 1);
+  m.def("conv_tc_wait_selftest", &conv_tc_wait_selftest);
   m.def("octree_conv_tc", &octree_conv_tc, py::arg("data_in"), py::arg("packed"), py::arg("octree"),
         py::arg("depth"), py::arg("num_output"), py::arg("kernel_size"), py::arg("stride"),
         py::arg("scale") = py::none(), py::arg("bias") = py::none(),

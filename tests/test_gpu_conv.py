@@ -242,6 +242,28 @@ def test_pointwise_tensor_core_any_height(ocnn, shape, half):
   assert gu.rel_err(gu.to_np(got), want) < (3e-3 if half else 8e-3)
 
 
+def test_bounded_wait_runs_out_and_reports(ocnn, batch):
+  """A wait that nothing completes ends by itself: the waiter writes its code to the status word
+  and raises the abort flag, a second waiter is told to stop, the kernel returns, and the next
+  convolution on the same context works."""
+  merged, octree, v = batch
+  st = ocnn.nn.conv_tc_wait_selftest()
+  torch.cuda.synchronize()
+  code, stopped = st.cpu().tolist()
+  assert code in (1, 2) and stopped == 1
+  d, cin, cout, ks = 4, 32, 32, [3, 3, 3]
+  rng = np.random.default_rng(5)
+  x = gu.bf16_round(rng.uniform(-1, 1, size=(cin, int(v.nnum[d]))).astype(np.float32))
+  w = rng.normal(scale=0.1, size=(cout, cin * 27)).astype(np.float32)
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights(torch.from_numpy(w).cuda(), cin, cout, ks)
+  got = ocnn.nn.octree_conv_tc(gu.data_cuda(x, True, True), packed, octree, d, cout, ks, 1,
+                               None, None, None, False, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  assert gu.rel_err(gu.to_np(got), oc.octree_conv(x, w, merged, d, cout, ks, 1)) < BF16_TOL
+
+
 def test_conv_tensor_core_rejects_unsupported_shapes(ocnn, batch):
   _, octree, v = batch
   w = torch.zeros(16, 3 * 27, device='cuda')
