@@ -82,7 +82,7 @@ Layout make_layout(int64_t n, int batch, int depth, int full) {
   L.off_counts = take(sizeof(int) * 32);
   L.off_blockcnt = take(sizeof(int) * kMaxScanGrid);
   L.off_hist = take(sizeof(int) * 256 * (size_t)L.nvb);
-  L.off_bintot = take(sizeof(int) * 256);
+  L.off_bintot = take(sizeof(int) * 256 * 8);      // one row of digit totals per sort pass (<= 8)
   for (int i = 0; i < 2; ++i) L.off_keys[i] = take((size_t)L.key_bytes_sort * (size_t)n);
   for (int i = 0; i < 2; ++i) L.off_idx[i] = take(sizeof(uint32_t) * (size_t)n);
   for (int d = full; d <= depth; ++d) {
@@ -129,7 +129,12 @@ __device__ __forceinline__ int cloud_of(const CloudRef* clouds, int batch, long 
 // normalize_pts + sort_keys' key computation (octree.cpp:155-170, 180-186): cell = trunc((p -
 // bbmin) * mul), only `depth` bits per axis enter the key.
 template <typename KeyT>
-__global__ void encode_kernel(EncodeArgs a, KeyT* __restrict__ keys) {
+__global__ void encode_kernel(EncodeArgs a, KeyT* __restrict__ keys, int* __restrict__ bintot,
+                              int bintot_n) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
+  // the sort's per-pass digit totals start at zero (the histogram kernels add into them)
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < bintot_n; i += blockDim.x) bintot[i] = 0;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < a.n;
        i += (long long)gridDim.x * blockDim.x) {
     const int b = cloud_of(a.clouds, a.batch, i);
@@ -144,6 +149,7 @@ __global__ void encode_kernel(EncodeArgs a, KeyT* __restrict__ keys) {
     const uint64_t key = (spread3(c[0]) << 2) | (spread3(c[1]) << 1) | spread3(c[2]);
     keys[i] = (KeyT)(((uint64_t)b << (3 * a.depth)) | key);
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // ---- stable LSD radix sort, 8 bits per pass -------------------------------------------------------
@@ -156,7 +162,9 @@ __global__ void encode_kernel(EncodeArgs a, KeyT* __restrict__ keys) {
 template <typename KeyT>
 __global__ void __launch_bounds__(kThreads) sort_hist_kernel(const KeyT* __restrict__ keys,
                                                              long long n, int shift, int vchunk,
-                                                             int nvb, int* __restrict__ hist) {
+                                                             int nvb, int* __restrict__ hist,
+                                                             int* __restrict__ bintot) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   // one private histogram per warp (shared-memory atomics never cross warps), summed at the end
   __shared__ int sh[kThreads / 32][256];
   const int warp = threadIdx.x >> 5;
@@ -198,25 +206,14 @@ __global__ void __launch_bounds__(kThreads) sort_hist_kernel(const KeyT* __restr
 #pragma unroll
   for (int w = 0; w < kThreads / 32; ++w) total += sh[w][threadIdx.x];
   hist[(long long)threadIdx.x * nvb + blockIdx.x] = total;
+  // digit totals over all CTAs (integer additions: the order does not matter); bintot was cleared
+  // by the encode kernel
+  if (total) atomicAdd(&bintot[threadIdx.x], total);
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
-// Exclusive scan of hist[256][nvb] in (digit, CTA) order: one CTA per digit row.
-__global__ void __launch_bounds__(kThreads) sort_rowsum_kernel(const int* __restrict__ hist,
-                                                               int nvb, int* __restrict__ bintot) {
-  __shared__ int red[kThreads / 32];
-  const int* row = hist + (long long)blockIdx.x * nvb;
-  int s = 0;
-  for (int i = threadIdx.x; i < nvb; i += kThreads) s += row[i];
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int t = 0;
-    for (int w = 0; w < kThreads / 32; ++w) t += red[w];
-    bintot[blockIdx.x] = t;
-  }
-}
-
+// Exclusive scan of hist[256][nvb] in (digit, CTA) order: one CTA per digit row (sort_rowscan_kernel
+// below); the digit totals it starts from were accumulated by the histogram kernel.
 __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
   // exclusive prefix of v over the CTA's kThreads threads
   __shared__ int wsum[kThreads / 32];
@@ -247,6 +244,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
 
 __global__ void __launch_bounds__(kThreads) sort_rowscan_kernel(int* __restrict__ hist, int nvb,
                                                                 const int* __restrict__ bintot) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   // first slot of this digit = number of keys with a smaller digit (kThreads == 256 digits)
   int below_total;
   block_exclusive_scan(threadIdx.x < blockIdx.x ? bintot[threadIdx.x] : 0, &below_total);
@@ -260,6 +258,7 @@ __global__ void __launch_bounds__(kThreads) sort_rowscan_kernel(int* __restrict_
     if (i < nvb) row[i] = base + ex;
     base += total;
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // The lanes of `mask` whose 8-bit digit equals this lane's: eight ballots, one per bit.  (Measured
@@ -280,6 +279,7 @@ __global__ void __launch_bounds__(kThreads) sort_scatter_kernel(
     const KeyT* __restrict__ keys_in, const uint32_t* __restrict__ idx_in,
     KeyT* __restrict__ keys_out, uint32_t* __restrict__ idx_out, long long n, int shift,
     int vchunk, int nvb, const int* __restrict__ hist) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   constexpr int kWarps = kThreads / 32;
   __shared__ int cnt[kWarps][256];        // per-warp digit counts, then per-warp digit bases
   __shared__ int tile_start[256];         // first slot of each digit inside the sorted tile
@@ -362,6 +362,7 @@ __global__ void __launch_bounds__(kThreads) sort_scatter_kernel(
     gofs[threadIdx.x] += total_d;
     __syncthreads();
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // ---- segmented unique (reduce, then scan) ---------------------------------------------------------
@@ -386,6 +387,7 @@ __global__ void __launch_bounds__(kThreads) unique_count_kernel(const InT* __res
                                                                 const int* __restrict__ n_ptr,
                                                                 long long n_host, int shift,
                                                                 int* __restrict__ blockcnt) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   __shared__ int red[kThreads / 32];
   const long long n = n_ptr ? (long long)*n_ptr : n_host;
   long long beg, end;
@@ -400,6 +402,7 @@ __global__ void __launch_bounds__(kThreads) unique_count_kernel(const InT* __res
     for (int w = 0; w < kThreads / 32; ++w) t += red[w];
     blockcnt[blockIdx.x] = t;
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 template <typename InT>
@@ -407,6 +410,7 @@ __global__ void __launch_bounds__(kThreads) unique_compact_kernel(
     const InT* __restrict__ in, const int* __restrict__ n_ptr, long long n_host, int shift,
     const int* __restrict__ blockcnt, uint64_t* __restrict__ out, int* __restrict__ start,
     int* __restrict__ count_out) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   __shared__ int red[kThreads / 32];
   __shared__ int base_s;
   const long long n = n_ptr ? (long long)*n_ptr : n_host;
@@ -450,6 +454,7 @@ __global__ void __launch_bounds__(kThreads) unique_compact_kernel(
     *count_out = base;
     start[base] = (int)n;
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // ---- emit ------------------------------------------------------------------------------------
@@ -473,60 +478,78 @@ __device__ __forceinline__ void store_key(uint8_t* base, long long off, long lon
 
 // levels 0..full: every node exists; key = index inside its octree; child = itself below the
 // full level, -1 at the full level (filled from K_full afterwards) — octree.cpp:210-224.
-__global__ void emit_full_level_kernel(EmitLevelArgs a, int batch, int full) {
+// All levels in one launch: a block serves one level (EmitAll::block0 is the first block of each).
+struct EmitAll {
+  int nlev, batch, full;
+  int block0[OCNN_MAX_DEPTH + 2];
+  long long nnum[OCNN_MAX_DEPTH + 1];
+  EmitLevelArgs a[OCNN_MAX_DEPTH + 1];
+  const uint64_t* Kp[OCNN_MAX_DEPTH + 1];     // K(d-1), levels above the full ones only
+  const uint64_t* Kc[OCNN_MAX_DEPTH + 1];     // Kd
+  const int* start[OCNN_MAX_DEPTH + 1];       // first entry of Kc under each parent
+};
+
+__device__ __forceinline__ void emit_full_node(const EmitLevelArgs& a, long long i, int batch, int full) {
   const long long per = 1LL << (3 * a.d);
-  const long long total = per * batch;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int b = (int)(i / per);
-    store_key(a.out, a.off_key, i, (uint64_t)(i - b * per), b, a.key_bytes);
-    const int ch = a.d < full ? (int)i : -1;
-    reinterpret_cast<int*>(a.out + a.off_child)[i] = ch;
-    if (a.off_split >= 0) reinterpret_cast<float*>(a.out + a.off_split)[i] = ch < 0 ? 0.f : 1.f;
-  }
+  const int b = (int)(i / per);
+  store_key(a.out, a.off_key, i, (uint64_t)(i - b * per), b, a.key_bytes);
+  const int ch = a.d < full ? (int)i : -1;
+  reinterpret_cast<int*>(a.out + a.off_child)[i] = ch;
+  if (a.off_split >= 0) reinterpret_cast<float*>(a.out + a.off_split)[i] = ch < 0 ? 0.f : 1.f;
 }
 
 // children of the full level: the composite key of a level-`full` node IS its batch-wide node
 // index, so child[K_full[r]] = r (octree.cpp:277-282 + the rebasing of merge_octrees.cpp:136-144).
 __global__ void emit_full_children_kernel(EmitLevelArgs a, const uint64_t* __restrict__ K,
                                           const int* __restrict__ count) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   const int n = *count;
   for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
     const long long node = (long long)K[r];
     reinterpret_cast<int*>(a.out + a.off_child)[node] = r;
     if (a.off_split >= 0) reinterpret_cast<float*>(a.out + a.off_split)[node] = 1.f;
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // level d > full: node 8a+j is the j-th child slot of the a-th non-empty node of level d-1
 // (octree.cpp:226-273).  Kp = K(d-1), Kc = Kd, start = first entry of Kc under each parent.
-__global__ void emit_level_kernel(EmitLevelArgs a, const uint64_t* __restrict__ Kp,
-                                  const uint64_t* __restrict__ Kc, const int* __restrict__ start,
-                                  long long nnum) {
-  const uint64_t local_mask = (1ULL << (3 * (a.d - 1))) - 1ULL;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nnum;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long p = i >> 3;
-    const int j = (int)(i & 7);
-    const uint64_t pk = Kp[p];
-    const int b = (int)(pk >> (3 * (a.d - 1)));
-    store_key(a.out, a.off_key, i, ((pk & local_mask) << 3) | (uint64_t)j, b, a.key_bytes);
-    // The group's children are the s1 - s0 <= 8 keys Kc[s0..s1): lane j of the group's 8 lanes
-    // fetches Kc[s0 + j], and each lane then picks, among the group's lanes, the one whose key
-    // ends in its own octant.  (The level's node count is a multiple of 8 and so is the grid's
-    // stride, so the 8 lanes of a group always run together.)
-    const int s0 = start[p], s1 = start[p + 1];
-    const int mine = s0 + j < s1 ? (int)(Kc[s0 + j] & 7) : -1;
-    const unsigned group_mask = 0xffu << (threadIdx.x & 24);
-    int ch = -1;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int oct = __shfl_sync(group_mask, mine, u, 8);
-      if (oct == j) ch = s0 + u;
-    }
-    reinterpret_cast<int*>(a.out + a.off_child)[i] = ch;
-    if (a.off_split >= 0) reinterpret_cast<float*>(a.out + a.off_split)[i] = ch < 0 ? 0.f : 1.f;
+__global__ void __launch_bounds__(kThreads) emit_levels_kernel(const EmitAll A) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
+  int l = 0;
+  while (l + 1 < A.nlev && (int)blockIdx.x >= A.block0[l + 1]) ++l;
+  const EmitLevelArgs& a = A.a[l];
+  const long long i = (long long)((int)blockIdx.x - A.block0[l]) * kThreads + threadIdx.x;
+  if (i >= A.nnum[l]) return;          // (whole sibling groups leave together: nnum is a multiple of 8)
+  if (a.d <= A.full) {
+    emit_full_node(a, i, A.batch, A.full);
+    return;
   }
+  const uint64_t* __restrict__ Kp = A.Kp[l];
+  const uint64_t* __restrict__ Kc = A.Kc[l];
+  const int* __restrict__ start = A.start[l];
+  const uint64_t local_mask = (1ULL << (3 * (a.d - 1))) - 1ULL;
+  const long long p = i >> 3;
+  const int j = (int)(i & 7);
+  const uint64_t pk = Kp[p];
+  const int b = (int)(pk >> (3 * (a.d - 1)));
+  store_key(a.out, a.off_key, i, ((pk & local_mask) << 3) | (uint64_t)j, b, a.key_bytes);
+  // The group's children are the s1 - s0 <= 8 keys Kc[s0..s1): lane j of the group's 8 lanes
+  // fetches Kc[s0 + j], and each lane then picks, among the group's lanes, the one whose key
+  // ends in its own octant.  (A level above the full ones holds whole sibling groups and a block
+  // starts on a multiple of 8, so the 8 lanes of a group always run together.)
+  const int s0 = start[p], s1 = start[p + 1];
+  const int mine = s0 + j < s1 ? (int)(Kc[s0 + j] & 7) : -1;
+  const unsigned group_mask = 0xffu << (threadIdx.x & 24);
+  int ch = -1;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int oct = __shfl_sync(group_mask, mine, u, 8);
+    if (oct == j) ch = s0 + u;
+  }
+  reinterpret_cast<int*>(a.out + a.off_child)[i] = ch;
+  if (a.off_split >= 0) reinterpret_cast<float*>(a.out + a.off_split)[i] = ch < 0 ? 0.f : 1.f;
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // finest-level signal, octree.cpp:312-452 restated per node.  Rows of the feature block, in
@@ -554,6 +577,7 @@ struct SignalArgs {
 // general kernel below is a latency loop: ~5 dependent reads per node).  The arithmetic and its
 // order are those of the general kernel, so the results are bit-identical.
 __global__ void __launch_bounds__(256) signal_normals_kernel(SignalArgs a) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   constexpr int U = 4;
   const long long nn = a.nnum;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -620,9 +644,11 @@ __global__ void __launch_bounds__(256) signal_normals_kernel(SignalArgs a) {
       for (int c = 0; c < 3; ++c) { nrm[c] = nrm[c] / factor; f_normal[c * nn + i] = nrm[c]; }
     }
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 __global__ void signal_kernel(SignalArgs a) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   const long long nn = a.nnum;
   const int cn = a.has_normal ? 3 : 0;
   const int cdis = a.node_dis ? (a.has_normal ? 1 : 4) : 0;
@@ -706,6 +732,7 @@ __global__ void signal_kernel(SignalArgs a) {
       }
     }
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // ---- host drivers -----------------------------------------------------------------------------
@@ -729,7 +756,7 @@ int sort_and_unique(const ocnn_points_batch* pts, const ocnn_build_params* prm, 
   if (width == 0.0f) width = 1.0e-10f;
   ea.mul = (float)(1 << prm->depth) / width;
   for (int j = 0; j < 3; ++j) ea.bbmin[j] = prm->bbmin[j];
-  encode_kernel<KeyT><<<grid_for(n, kThreads), kThreads, 0, st>>>(ea, keys[0]);
+  OCNN_CUDA_OK(launch_chained(encode_kernel<KeyT>, dim3(grid_for(n, kThreads)), dim3(kThreads), 0, st, ea, keys[0], bintot, 256 * 8));
   OCNN_LAUNCH_OK("encode_kernel");
 
   const int nbits = 3 * prm->depth + bits_for(pts->batch);
@@ -738,16 +765,13 @@ int sort_and_unique(const ocnn_points_batch* pts, const ocnn_build_params* prm, 
   int cur = 0;
   for (int p = 0; p < passes; ++p) {
     const int shift = 8 * p;
-    sort_hist_kernel<KeyT><<<sort_grid, kThreads, 0, st>>>(keys[cur], n, shift, L.vchunk, L.nvb, hist);
-    sort_rowsum_kernel<<<256, kThreads, 0, st>>>(hist, L.nvb, bintot);
-    sort_rowscan_kernel<<<256, kThreads, 0, st>>>(hist, L.nvb, bintot);
+    OCNN_CUDA_OK(launch_chained(sort_hist_kernel<KeyT>, dim3(sort_grid), dim3(kThreads), 0, st, keys[cur], n, shift, L.vchunk, L.nvb, hist, bintot + 256 * p));
+    OCNN_CUDA_OK(launch_chained(sort_rowscan_kernel, dim3(256), dim3(kThreads), 0, st, hist, L.nvb, bintot + 256 * p));
     if (p == 0)
-      sort_scatter_kernel<KeyT, true><<<sort_grid, kThreads, 0, st>>>(
-          keys[cur], nullptr, keys[cur ^ 1], idx[cur ^ 1], n, shift, L.vchunk, L.nvb, hist);
+      OCNN_CUDA_OK(launch_chained(sort_scatter_kernel<KeyT, true>, dim3(sort_grid), dim3(kThreads), 0, st, keys[cur], nullptr, keys[cur ^ 1], idx[cur ^ 1], n, shift, L.vchunk, L.nvb, hist));
     else
-      sort_scatter_kernel<KeyT, false><<<sort_grid, kThreads, 0, st>>>(
-          keys[cur], idx[cur], keys[cur ^ 1], idx[cur ^ 1], n, shift, L.vchunk, L.nvb, hist);
-    OCNN_LAUNCHES_OK("radix sort pass", 4);
+      OCNN_CUDA_OK(launch_chained(sort_scatter_kernel<KeyT, false>, dim3(sort_grid), dim3(kThreads), 0, st, keys[cur], idx[cur], keys[cur ^ 1], idx[cur ^ 1], n, shift, L.vchunk, L.nvb, hist));
+    OCNN_LAUNCHES_OK("radix sort pass", 3);
     cur ^= 1;
   }
   *final_buf = cur;
@@ -756,18 +780,14 @@ int sort_and_unique(const ocnn_points_batch* pts, const ocnn_build_params* prm, 
   int* blockcnt = reinterpret_cast<int*>(ws + L.off_blockcnt);
   const int D = prm->depth, F = prm->full_depth;
   const int g0 = grid_for(n, kScanTile, 4);
-  unique_count_kernel<KeyT><<<g0, kThreads, 0, st>>>(keys[cur], nullptr, n, 0, blockcnt);
-  unique_compact_kernel<KeyT><<<g0, kThreads, 0, st>>>(
-      keys[cur], nullptr, n, 0, blockcnt, reinterpret_cast<uint64_t*>(ws + L.off_K[D]),
-      reinterpret_cast<int*>(ws + L.off_start[D]), counts + D);
+  OCNN_CUDA_OK(launch_chained(unique_count_kernel<KeyT>, dim3(g0), dim3(kThreads), 0, st, keys[cur], nullptr, n, 0, blockcnt));
+  OCNN_CUDA_OK(launch_chained(unique_compact_kernel<KeyT>, dim3(g0), dim3(kThreads), 0, st, keys[cur], nullptr, n, 0, blockcnt, reinterpret_cast<uint64_t*>(ws + L.off_K[D]), reinterpret_cast<int*>(ws + L.off_start[D]), counts + D));
   OCNN_LAUNCHES_OK("unique (finest level)", 2);
   for (int d = D; d > F; --d) {
     const uint64_t* Kd = reinterpret_cast<const uint64_t*>(ws + L.off_K[d]);
     const int g = grid_for(L.cap[d], kScanTile, 4);
-    unique_count_kernel<uint64_t><<<g, kThreads, 0, st>>>(Kd, counts + d, 0, 3, blockcnt);
-    unique_compact_kernel<uint64_t><<<g, kThreads, 0, st>>>(
-        Kd, counts + d, 0, 3, blockcnt, reinterpret_cast<uint64_t*>(ws + L.off_K[d - 1]),
-        reinterpret_cast<int*>(ws + L.off_start[d - 1]), counts + d - 1);
+    OCNN_CUDA_OK(launch_chained(unique_count_kernel<uint64_t>, dim3(g), dim3(kThreads), 0, st, Kd, counts + d, 0, 3, blockcnt));
+    OCNN_CUDA_OK(launch_chained(unique_compact_kernel<uint64_t>, dim3(g), dim3(kThreads), 0, st, Kd, counts + d, 0, 3, blockcnt, reinterpret_cast<uint64_t*>(ws + L.off_K[d - 1]), reinterpret_cast<int*>(ws + L.off_start[d - 1]), counts + d - 1));
     OCNN_LAUNCHES_OK("unique (parent level)", 2);
   }
   return OCNN_OK;
@@ -928,6 +948,12 @@ int ocnn_octree_build_emit(const ocnn_points_batch* pts, const ocnn_build_params
   OCNN_CUDA_OK(cudaMemcpyAsync(o, hdr, OCNN_HEADER_BYTES, cudaMemcpyHostToDevice, st));
 
   const int* counts = reinterpret_cast<const int*>(ws + L.off_counts);
+  EmitAll all;
+  memset(&all, 0, sizeof(all));
+  all.batch = B; all.full = F;
+  int blocks = 0;
+  EmitLevelArgs full_args;
+  memset(&full_args, 0, sizeof(full_args));
   for (int d = 0; d <= D; ++d) {
     EmitLevelArgs a;
     a.out = o;
@@ -936,22 +962,31 @@ int ocnn_octree_build_emit(const ocnn_points_batch* pts, const ocnn_build_params
     a.off_split = meta->channels[OCNN_PROP_SPLIT] ? ocnn_prop_offset(meta, OCNN_PROP_SPLIT, d) : -1;
     a.key_bytes = prm->key_bits / 8;
     a.d = d;
+    if (d == F) full_args = a;
     const long long nnum = meta->nnum[d];
     if (nnum == 0) continue;
-    if (d <= F) {
-      emit_full_level_kernel<<<grid_for(nnum, kThreads), kThreads, 0, st>>>(a, B, F);
-      if (d == F && D > F) {
-        emit_full_children_kernel<<<grid_for(meta->nnum_nempty[F], kThreads), kThreads, 0, st>>>(
-            a, reinterpret_cast<const uint64_t*>(ws + L.off_K[F]), counts + F);
-        note_launches(1);
-      }
-    } else {
-      emit_level_kernel<<<grid_for(nnum, kThreads), kThreads, 0, st>>>(
-          a, reinterpret_cast<const uint64_t*>(ws + L.off_K[d - 1]),
-          reinterpret_cast<const uint64_t*>(ws + L.off_K[d]),
-          reinterpret_cast<const int*>(ws + L.off_start[d - 1]), nnum);
+    const int l = all.nlev++;
+    all.a[l] = a;
+    all.nnum[l] = nnum;
+    all.block0[l] = blocks;
+    blocks += (int)((nnum + kThreads - 1) / kThreads);
+    if (d > F) {
+      all.Kp[l] = reinterpret_cast<const uint64_t*>(ws + L.off_K[d - 1]);
+      all.Kc[l] = reinterpret_cast<const uint64_t*>(ws + L.off_K[d]);
+      all.start[l] = reinterpret_cast<const int*>(ws + L.off_start[d - 1]);
     }
-    OCNN_LAUNCH_OK("emit level");
+  }
+  all.block0[all.nlev] = blocks;
+  if (blocks > 0) {
+    OCNN_CUDA_OK(launch_chained(emit_levels_kernel, dim3(blocks), dim3(kThreads), 0, st, all));
+    OCNN_LAUNCH_OK("emit_levels_kernel");
+  }
+  if (D > F && meta->nnum_nempty[F] > 0) {
+    // (after the level itself: it overwrites the -1 the full level wrote for every node)
+    OCNN_CUDA_OK(launch_chained(emit_full_children_kernel, dim3(grid_for(meta->nnum_nempty[F], kThreads)),
+                                dim3(kThreads), 0, st, full_args,
+                                reinterpret_cast<const uint64_t*>(ws + L.off_K[F]), counts + F));
+    OCNN_LAUNCH_OK("emit_full_children_kernel");
   }
 
   if (meta->nnum[D] > 0) {
@@ -981,9 +1016,9 @@ int ocnn_octree_build_emit(const ocnn_points_batch* pts, const ocnn_build_params
     sa.mul = (float)(1 << D) / width;
     for (int j = 0; j < 3; ++j) sa.bbmin[j] = prm->bbmin[j];
     if (sa.has_normal && sa.cf == 0 && sa.l_out == nullptr && !sa.node_dis && !sa.save_pts)
-      signal_normals_kernel<<<grid_for((sa.nnum + 3) / 4, 256, 8), 256, 0, st>>>(sa);
+      OCNN_CUDA_OK(launch_chained(signal_normals_kernel, dim3(grid_for((sa.nnum + 3) / 4, 256, 8)), dim3(256), 0, st, sa));
     else
-      signal_kernel<<<grid_for(sa.nnum, 256, 8), 256, 0, st>>>(sa);
+      OCNN_CUDA_OK(launch_chained(signal_kernel, dim3(grid_for(sa.nnum, 256, 8)), dim3(256), 0, st, sa));
     OCNN_LAUNCH_OK("signal_kernel");
   }
 

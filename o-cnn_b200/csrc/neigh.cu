@@ -27,6 +27,7 @@ __device__ __forceinline__ unsigned gather3(unsigned key) {
 // Restates calc_neigh_cpu(neigh, depth, batch), octree/octree/octree_nn.cpp:382-424.
 __global__ void neigh_full_kernel(int* __restrict__ out, int depth, long long per,
                                   long long total) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   const int side = 1 << depth;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -42,6 +43,7 @@ __global__ void neigh_full_kernel(int* __restrict__ out, int depth, long long pe
       v = (int)((spread3(x) << 2) | (spread3(y) << 1) | spread3(z)) + (int)(n * per);
     out[i] = v;
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 // Split level, one warp per sibling group of PARENT nodes.  The eight parents of a group share one
@@ -58,6 +60,7 @@ constexpr int kNeighWarps = 8;
 __global__ void __launch_bounds__(kNeighWarps * 32) neigh_split_kernel(
     int* __restrict__ out, const int* __restrict__ neigh, const int* __restrict__ child,
     long long ngroups) {
+  grid_dependency_wait();       // launched as a programmatic dependent: see common.cuh
   __shared__ int cblk[kNeighWarps][64];     // child group of each cell of the parents' block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // child-level block position j = (x,y,z) in 0..3 -> which parent-level cell (tap, as a
@@ -95,6 +98,7 @@ __global__ void __launch_bounds__(kNeighWarps * 32) neigh_split_kernel(
     }
     __syncwarp();
   }
+  grid_dependency_trigger();    // at the end: the successor's blocks should not sit on SM slots early
 }
 
 }  // namespace
@@ -110,8 +114,7 @@ int ocnn_calc_neigh_full(int32_t* neigh, int depth, int batch, void* stream) {
   const long long per = 1LL << (3 * depth);
   const long long total = per * batch * 8;
   OCNN_REQUIRE(per * batch < (1LL << 31), "ocnn_calc_neigh_full: level too large for int32 indices");
-  neigh_full_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      neigh, depth, per, total);
+  OCNN_CUDA_OK(launch_chained(neigh_full_kernel, dim3(grid_for(total, 256)), dim3(256), 0, static_cast<cudaStream_t>(stream), neigh, depth, per, total));
   OCNN_LAUNCH_OK("neigh_full_kernel");
   return OCNN_OK;
 }
@@ -125,8 +128,7 @@ int ocnn_calc_neigh_split(int32_t* neigh_child, const int32_t* neigh, const int3
                "ocnn_calc_neigh_split: parent level must hold whole sibling groups (got %d nodes)",
                nnum_parent);
   const long long ngroups = nnum_parent / 8;
-  neigh_split_kernel<<<grid_for(ngroups, kNeighWarps, 16), kNeighWarps * 32, 0,
-                       static_cast<cudaStream_t>(stream)>>>(neigh_child, neigh, child, ngroups);
+  OCNN_CUDA_OK(launch_chained(neigh_split_kernel, dim3(grid_for(ngroups, kNeighWarps, 16)), dim3(kNeighWarps * 32), 0, static_cast<cudaStream_t>(stream), neigh_child, neigh, child, ngroups));
   OCNN_LAUNCH_OK("neigh_split_kernel");
   return OCNN_OK;
 }
