@@ -217,8 +217,10 @@ class ClockSampler:
     self.gpu_index = gpu_index
     self.proc = None
     try:
-      self.proc = subprocess.Popen(['nvidia-smi', '--query-gpu=' + self.QUERY,
-                                    '--format=csv,noheader,nounits', '-lms', '100'],
+      # this GPU only: a query over all GPUs of the box takes the driver several times as long,
+      # and kernel launches issued meanwhile were seen to stall for 10-15 ms
+      self.proc = subprocess.Popen(['nvidia-smi', '-i', str(gpu_index), '--query-gpu=' + self.QUERY,
+                                    '--format=csv,noheader,nounits', '-lms', '200'],
                                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     except OSError:
       self.proc = None
