@@ -312,6 +312,36 @@ int ocnn_octree_conv_tc_general(const void* x_dev, const void* packed_dev, void*
                                 const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Octree editing for the generative networks.  Replace octree_new / octree_grow / octree_update
+ * (pytorch/cpp/octree_grow.cpp:108-148, 8-104, 150-177).  Headers are passed and returned as the
+ * OCNN_HEADER_BYTES the caller holds on the host; results are byte-identical to the reference's.
+ *
+ * ocnn_octree_new: `batch_size` root nodes (depth 0, xyz keys, Key / Child / Neigh(8) /
+ *   Feature(channel) on every level, box [0,2]^3), written into HOST memory as the reference does;
+ *   the caller uploads it.
+ * ocnn_octree_grow: a copy of the octree with level target_depth (<= depth + 1) added: eight
+ *   children under every non-empty node of the level above, with their xyz keys
+ *   (generate_key, octree/octree/octree_nn.cpp:428-464), child = 0..n-1 and the neighbour table
+ *   (calc_neigh); full_octree: the level is complete (every node above must be non-empty).  First
+ *   ocnn_octree_grow_header (host only) gives the new header, whose total size
+ *   (ocnn_parse_header -> ptr_dis[6]) the caller allocates; then ocnn_octree_grow fills it.
+ * ocnn_octree_update: in place, child[depth][i] = rank of node i among the nodes whose label equals
+ *   `split`, -1 for the others (generate_label, octree_nn.cpp:466-473), and their number becomes
+ *   nnum_nempty[depth] (1 with child[0] = 0 when there is none).  Synchronises the stream once (the
+ *   number goes into the header).  workspace_dev: ocnn_octree_update_workspace_bytes() bytes.
+ * ------------------------------------------------------------------------------------------ */
+size_t ocnn_octree_new_bytes(int batch_size, int channel, int key_bits);
+int ocnn_octree_new(int batch_size, int channel, int node_dis, int adaptive_layer, int key_bits,
+                    void* out_host, size_t capacity);
+int ocnn_octree_grow_header(const void* header_host_in, int target_depth, int full_octree,
+                            void* header_host_out);
+int ocnn_octree_grow(const void* octree_in_dev, const void* header_host_in, void* octree_out_dev,
+                     const void* header_host_out, int target_depth, int full_octree, void* stream);
+size_t ocnn_octree_update_workspace_bytes(void);
+int ocnn_octree_update(void* octree_dev, const void* header_host_in, const int32_t* label_dev, int depth,
+                       int split, void* workspace_dev, void* header_host_out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * points -> octree, batched, on the device.  Replaces Octree::build
  * (octree/octree/octree.cpp:74-121, binding pytorch/cpp/point2octree.cpp:5-34) and, when
  * `merged` is set, the merge_octrees call that follows it in the reference pipeline

@@ -87,10 +87,11 @@ int ocnn_parse_header(const void* header_host, size_t nbytes, ocnn_octree_meta* 
   meta->save_pts = h[kOffSavePts] != 0;
   const int max_depth = meta->key_bits == 64 ? 16 : 8;
   OCNN_REQUIRE(meta->batch_size >= 0, "octree header: negative batch size %d", meta->batch_size);
-  OCNN_REQUIRE(meta->depth >= 1 && meta->depth <= max_depth && meta->depth < OCNN_MAX_DEPTH,
-               "octree header: depth %d outside [1, %d]", meta->depth,
+  // (depth 0 with full layer 1 is what octree_new makes: pytorch/cpp/octree_grow.cpp:108-148)
+  OCNN_REQUIRE(meta->depth >= 0 && meta->depth <= max_depth && meta->depth < OCNN_MAX_DEPTH,
+               "octree header: depth %d outside [0, %d]", meta->depth,
                max_depth < OCNN_MAX_DEPTH ? max_depth : OCNN_MAX_DEPTH - 1);
-  OCNN_REQUIRE(meta->full_depth >= 0 && meta->full_depth <= meta->depth,
+  OCNN_REQUIRE(meta->full_depth >= 0 && meta->full_depth <= (meta->depth > 1 ? meta->depth : 1),
                "octree header: full layer %d outside [0, depth]", meta->full_depth);
   const int flags = *i32(kOffFlags);
   for (int d = 0; d < OCNN_MAX_DEPTH; ++d) {

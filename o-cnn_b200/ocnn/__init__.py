@@ -23,6 +23,7 @@ from .nn import (octree_batch, octree_property, points2octree, points2octree_bat
                  octree_key2xyz)
 from .nn import (transform_points, clip_points, normalize_points, bounding_sphere, points_property,
                  points_batch_property, points_set_property)
+from .nn import octree_new, octree_grow, octree_update
 from .transforms import (Points2Octree, collate_octrees, NormalizePoints, TransformPoints,
                          TransformCompose)
 from .io import read_points, write_points, read_octree, write_octree, octree_samples
@@ -39,7 +40,7 @@ from .octree_pool import (octree_max_pool, OctreeMaxPool, octree_max_unpool, Oct
 from .modules import (OctreeConvBn, OctreeConvBnRelu, OctreeDeConvBnRelu, FcBnRelu, OctreeConv1x1,
                       OctreeConv1x1Bn, OctreeConv1x1BnRelu, OctreeResBlock, OctreeResBlock2,
                       OctreeResBlocks, octree_trilinear_pts, octree_trilinear, octree_nearest_pts,
-                      OctreeTrilinear, OctreeInterp, octree_feature)
+                      OctreeTrilinear, OctreeInterp, octree_feature, create_full_octree)
 from .lenet import LeNet
 from .resnet import ResNet
 from .unet import UNet

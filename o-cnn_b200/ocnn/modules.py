@@ -225,6 +225,16 @@ class OctreeResBlocks(_nn.Module):
     return data
 
 
+def create_full_octree(depth, channel, batch_size=1, node_dis=True):
+  """A full octree of the given depth, grown level by level from octree_new
+  (pytorch/ocnn/modules.py:325-330)."""
+  assert depth > 1
+  octree = nn.octree_new(batch_size, channel, node_dis)
+  for target_depth in range(1, depth + 1):
+    octree = nn.octree_grow(octree, target_depth, full_octree=True)
+  return octree
+
+
 def octree_feature(octree, depth, nempty=False):
   """The octree's stored signal at `depth` as [1,C,H,1] (on the non-empty nodes when nempty)."""
   out = nn.octree_property(octree, 'feature', depth)

@@ -1718,6 +1718,54 @@ void set_key_bits(int bits) {
 }
 int get_key_bits() { return g_key_bits; }
 
+// ---- octree editing for the generative networks (pytorch/cpp/octree_grow.cpp) --------------------
+// octree_new builds on the host and uploads, as the reference does; its keys follow the
+// binding's key width (ocnn.nn.set_key_bits, 64 like the reference's build).
+Tensor octree_new(int batch_size, int channel, bool node_dis, int adaptive_layer) {
+  const size_t bytes = ocnn_octree_new_bytes(batch_size, channel, g_key_bits);
+  TORCH_CHECK(bytes > 0, "octree_new: batch_size must be at least 1 and channel non-negative");
+  Tensor host = torch::zeros({(int64_t)bytes}, torch::kUInt8);
+  OCNN_CALL(ocnn_octree_new(batch_size, channel, node_dis ? 1 : 0, adaptive_layer, g_key_bits,
+                            host.data_ptr<uint8_t>(), bytes));
+  return host.cuda();
+}
+
+Tensor octree_grow(Tensor octree_in, int target_depth, bool full_octree) {
+  OctreeRef o = get_octree(octree_in);
+  TORCH_CHECK(o.cuda, "octree_grow: the octree must be a CUDA tensor");
+  c10::cuda::CUDAGuard guard(octree_in.device());
+  uint8_t header_out[OCNN_HEADER_BYTES];
+  OCNN_CALL(ocnn_octree_grow_header(o.raw, target_depth, full_octree ? 1 : 0, header_out));
+  ocnn_octree_meta mo;
+  OCNN_CALL(ocnn_parse_header(header_out, OCNN_HEADER_BYTES, &mo));
+  Tensor out = torch::empty({(int64_t)mo.ptr_dis[OCNN_PROP_COUNT]}, octree_in.options());
+  OCNN_CALL(ocnn_octree_grow(octree_in.data_ptr<uint8_t>(), o.raw, out.data_ptr<uint8_t>(), header_out,
+                             target_depth, full_octree ? 1 : 0, current_stream()));
+  remember_header(out, mo, header_out);
+  return out;
+}
+
+Tensor octree_update(Tensor octree_in, Tensor label_in, int depth, int split) {
+  OctreeRef o = get_octree(octree_in);
+  TORCH_CHECK(o.cuda, "octree_update: the octree must be a CUDA tensor");
+  c10::cuda::CUDAGuard guard(octree_in.device());
+  TORCH_CHECK(depth >= 0 && depth <= o.meta.depth, "octree_update: depth ", depth, " outside the octree");
+  TORCH_CHECK(label_in.is_cuda() && label_in.scalar_type() == torch::kInt32,
+              "octree_update: the label must be an int32 CUDA tensor");
+  TORCH_CHECK(label_in.numel() == o.meta.nnum[depth], "octree_update: ", label_in.numel(),
+              " labels for ", o.meta.nnum[depth], " nodes");
+  Tensor label = label_in.contiguous();
+  Tensor out = octree_in.clone();
+  Tensor ws = torch::empty({(int64_t)ocnn_octree_update_workspace_bytes()}, octree_in.options());
+  uint8_t header_out[OCNN_HEADER_BYTES];
+  OCNN_CALL(ocnn_octree_update(out.data_ptr<uint8_t>(), o.raw, label.data_ptr<int32_t>(), depth, split,
+                               ws.data_ptr<uint8_t>(), header_out, current_stream()));
+  ocnn_octree_meta mo;
+  OCNN_CALL(ocnn_parse_header(header_out, OCNN_HEADER_BYTES, &mo));
+  remember_header(out, mo, header_out);
+  return out;
+}
+
 template <typename... Args>
 Tensor not_built(const char* name) {
   TORCH_CHECK(false, "ocnn.nn.", name, " is outside the inference hot path and is not implemented "
@@ -1812,6 +1860,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("src_octree"), py::arg("des_octree"), py::arg("depth"));
   m.def("octree_align_grad", &octree_align_grad, "backward of align-octree-data");
   m.def("octree_info", &octree_info);
+  // (pytorch/cpp/pybind.cpp:35-41)
+  m.def("octree_grow", &octree_grow, "octree growing", py::arg("octree"), py::arg("target_depth"),
+        py::arg("full_octree") = false);
+  m.def("octree_update", &octree_update, "update octree via splitting labels", py::arg("octree"),
+        py::arg("label"), py::arg("depth"), py::arg("split") = 1);
+  m.def("octree_new", &octree_new, "create a new octree", py::arg("batch_size") = 1,
+        py::arg("channel") = 4, py::arg("node_dis") = true, py::arg("adaptive_layer") = 0);
   m.def("feature_node_major", &feature_node_major, py::arg("octree"), py::arg("c_pad"),
         py::arg("bf16") = true, py::arg("half") = false);
   m.def("set_key_bits", &set_key_bits);

@@ -549,3 +549,160 @@ def depad(y, child, hx):
   x = np.zeros((channel, hx), np.float32)
   lib().oc_depad(_fp(x), hx, channel, _fp(y), child.size, _ip(child))
   return x
+
+
+# -- the generative path's octree editing ----------------------------------------------------------
+# Restated from pytorch/cpp/octree_grow.cpp and the OctreeInfo setters it calls
+# (octree/octree/octree_info.cpp:188-268).  Header field offsets: octree_info.h:93-116.
+_OFF = dict(batch=16, depth=20, full=24, adp_layer=28, is_adaptive=32, key2xyz=44, node_dis=45,
+            nnum=48, nnum_cum=112, nnum_nempty=176, flags=240, channels=244, locations=308,
+            bbmin=372, bbmax=384, ptr_dis=652)
+
+
+def _hdr_i32(hdr, name, n=1):
+  off = _OFF[name]
+  return hdr[off:off + 4 * n].view(np.int32)
+
+
+def _finish_header(hdr, key_bits):
+  """set_nnum_cum() (capacity 0) and set_ptr_dis() (octree_info.cpp:216-223, 254-268)."""
+  depth = int(_hdr_i32(hdr, 'depth')[0])
+  nnum, cum = _hdr_i32(hdr, 'nnum', 16), _hdr_i32(hdr, 'nnum_cum', 16)
+  cum[0] = 0
+  for d in range(1, depth + 2):
+    cum[d] = cum[d - 1] + nnum[d - 1]
+  cum[depth + 2] = cum[depth + 1]
+  ch, lc, dis = _hdr_i32(hdr, 'channels', 6), _hdr_i32(hdr, 'locations', 6), _hdr_i32(hdr, 'ptr_dis', 7)
+  dis[0] = 720
+  for p in range(6):
+    n = int(cum[depth + 2]) if lc[p] == -1 else int(nnum[lc[p]])
+    esz = key_bits // 8 if p == 0 else 4
+    dis[p + 1] = dis[p] + esz * n * ch[p]
+
+
+def octree_new(batch_size, channel, node_dis=False, adaptive_layer=0, key_bits=64):
+  """octree_new (octree_grow.cpp:108-148): `batch_size` root nodes, depth 0 (full_layer clamps to
+  1, octree_info.cpp:192-194), xyz keys, Key/Child/Neigh(8)/Feature(channel) on every level, box
+  [0,2]^3; key and child of level 0 are 0..batch-1, neigh and feature stay zero."""
+  hdr = np.zeros(720, np.uint8)
+  hdr[:12] = np.frombuffer(b'_OCTREE_2.0_' if key_bits == 64 else b'_OCTREE_1.0_', np.uint8)
+  _hdr_i32(hdr, 'batch')[0] = batch_size
+  _hdr_i32(hdr, 'depth')[0] = 0
+  _hdr_i32(hdr, 'full')[0] = 1
+  hdr[_OFF['node_dis']] = 1 if node_dis else 0
+  if adaptive_layer > 1:
+    hdr[_OFF['is_adaptive']] = 1
+    _hdr_i32(hdr, 'adp_layer')[0] = adaptive_layer
+  hdr[_OFF['key2xyz']] = 1
+  ch, lc = _hdr_i32(hdr, 'channels', 6), _hdr_i32(hdr, 'locations', 6)
+  flags = 0
+  for p, c in enumerate((1, 1, 8, channel)):
+    ch[p] = c
+    lc[p] = -1
+    # set_channel records the property in content_flags when it has channels (octree_info.cpp:232-243)
+    if c != 0:
+      flags |= 1 << p
+  _hdr_i32(hdr, 'flags')[0] = flags
+  hdr[_OFF['bbmax']:_OFF['bbmax'] + 12].view(np.float32)[:] = 2.0
+  _hdr_i32(hdr, 'nnum', 16)[0] = batch_size
+  _hdr_i32(hdr, 'nnum_nempty', 16)[0] = batch_size
+  _finish_header(hdr, key_bits)
+  size = int(_hdr_i32(hdr, 'ptr_dis', 7)[6])
+  out = np.zeros(size, np.uint8)
+  out[:720] = hdr
+  v = OctreeView(out)
+  kdt = np.uint64 if key_bits == 64 else np.uint32
+  out[v.ptr_dis[0]:v.ptr_dis[0] + batch_size * (key_bits // 8)].view(kdt)[:] = np.arange(batch_size)
+  out[v.ptr_dis[1]:v.ptr_dis[1] + 4 * batch_size].view(np.int32)[:] = np.arange(batch_size)
+  return out
+
+
+def _lanes(keys, key_bits):
+  """[n, 4] view of the four lanes of xyz keys (uint8 lanes for 32-bit keys, uint16 for 64-bit)."""
+  return keys.view(np.uint16 if key_bits == 64 else np.uint8).reshape(-1, 4)
+
+
+def octree_grow(octree, target_depth, full_octree):
+  """octree_grow (octree_grow.cpp:8-104): a copy of the octree with level `target_depth` added —
+  eight children under every non-empty node of the level above (all nodes when full_octree).
+  New keys are xyz keys: child j of a node doubles the parent's x,y,z lanes and appends the bits of
+  j (generate_key_cpu, octree_nn.cpp:428-444), or, for a full level, de-interleaves the node's
+  index (:446-464) with the batch index in lane 3; child = 0..n-1; neigh from the level above
+  (calc_neigh_cpu)."""
+  vin = OctreeView(octree)
+  kb = vin.key_bits
+  hdr = np.array(vin.buf[:720], copy=True)
+  node_num = int(vin.nnum_nempty[target_depth - 1]) << 3
+  full_old = int(_hdr_i32(hdr, 'full')[0])
+  _hdr_i32(hdr, 'depth')[0] = max(full_old, target_depth)          # set_depth, octree_info.cpp:188-190
+  if full_octree:
+    _hdr_i32(hdr, 'full')[0] = max(1, target_depth)
+  hdr[_OFF['bbmin']:_OFF['bbmin'] + 12].view(np.float32)[:] = 0.0
+  hdr[_OFF['bbmax']:_OFF['bbmax'] + 12].view(np.float32)[:] = float(1 << target_depth)
+  _hdr_i32(hdr, 'nnum', 16)[target_depth] = node_num
+  _hdr_i32(hdr, 'nnum_nempty', 16)[target_depth] = node_num
+  _finish_header(hdr, kb)
+  size = int(_hdr_i32(hdr, 'ptr_dis', 7)[6])
+  out = np.zeros(size, np.uint8)
+  out[:720] = hdr
+  vo = OctreeView(out)
+  cum = int(vin.nnum_cum[target_depth])
+  for p, esz in ((0, kb // 8), (1, 4), (2, 4), (3, 4)):
+    nbytes = cum * int(vin.channels[p]) * esz
+    out[vo.ptr_dis[p]:vo.ptr_dis[p] + nbytes] = vin.buf[vin.ptr_dis[p]:vin.ptr_dis[p] + nbytes]
+  vo = OctreeView(out)
+  kdt = np.uint64 if kb == 64 else np.uint32
+  key_off = int(vo.ptr_dis[0]) + int(vo.nnum_cum[target_depth]) * (kb // 8)
+  child_off = int(vo.ptr_dis[1]) + int(vo.nnum_cum[target_depth]) * 4
+  neigh_off = int(vo.ptr_dis[2]) + int(vo.nnum_cum[target_depth]) * 8 * 4
+  new_keys = np.zeros(node_num, kdt)
+  if full_octree:
+    per = 1 << (3 * target_depth)
+    k = np.arange(node_num, dtype=np.uint64) % per
+    lanes = np.zeros((node_num, 4), np.uint64)
+    for d in range(target_depth):
+      lanes[:, 0] |= (k & np.uint64(1 << (3 * d + 2))) >> np.uint64(2 * d + 2)
+      lanes[:, 1] |= (k & np.uint64(1 << (3 * d + 1))) >> np.uint64(2 * d + 1)
+      lanes[:, 2] |= (k & np.uint64(1 << (3 * d + 0))) >> np.uint64(2 * d + 0)
+    lanes[:, 3] = np.arange(node_num, dtype=np.uint64) // per
+    _lanes(new_keys, kb)[:] = lanes
+    neigh = calc_neigh_full(target_depth, vo.batch_size)
+  else:
+    parent_keys = np.array(vo.prop('key', target_depth - 1), copy=True)
+    child = vo.prop('child', target_depth - 1)
+    pl = _lanes(parent_keys, kb).astype(np.uint64)
+    nl = np.zeros((node_num, 4), np.uint64)
+    for i in np.nonzero(child >= 0)[0]:
+      for j in range(8):
+        r = 8 * int(child[i]) + j
+        nl[r, 0] = (pl[i, 0] << 1) | ((j & 4) >> 2)
+        nl[r, 1] = (pl[i, 1] << 1) | ((j & 2) >> 1)
+        nl[r, 2] = (pl[i, 2] << 1) | (j & 1)
+        nl[r, 3] = pl[i, 3]
+    _lanes(new_keys, kb)[:] = nl      # (lanes wrap to their width, as the reference's typed stores do)
+    neigh = calc_neigh_split(vo.prop('neigh', target_depth - 1).reshape(-1), child, node_num, fill=0)
+  out[key_off:key_off + node_num * (kb // 8)] = new_keys.view(np.uint8)
+  out[child_off:child_off + 4 * node_num].view(np.int32)[:] = np.arange(node_num)
+  out[neigh_off:neigh_off + 4 * neigh.size] = neigh.view(np.uint8)
+  return out
+
+
+def octree_update(octree, label, depth, split):
+  """octree_update (octree_grow.cpp:150-177): child[depth][i] = rank among the nodes whose label
+  equals `split`, -1 for the others (generate_label, octree_nn.cpp:466-473); their number becomes
+  nnum_nempty[depth] (1, with child[0] = 0, when there is none)."""
+  out = np.array(octree, dtype=np.uint8, copy=True)
+  v = OctreeView(out)
+  label = _i32(label)
+  n = int(v.nnum[depth])
+  assert label.size == n
+  hit = label == split
+  child = np.where(hit, np.cumsum(hit) - 1, -1).astype(np.int32)
+  split_num = int(hit.sum())
+  if split_num == 0:
+    split_num = 1
+    child[0] = 0
+  off = int(v.ptr_dis[1]) + int(v.nnum_cum[depth]) * 4
+  out[off:off + 4 * n].view(np.int32)[:] = child
+  _hdr_i32(out, 'nnum_nempty', 16)[depth] = split_num
+  return out

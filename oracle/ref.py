@@ -95,6 +95,11 @@ class Ref:
     L.ref_clip_points.argtypes = [ctypes.c_char_p, c_float_p, c_float_p, c_int_p]
     L.ref_bounding_box.argtypes = [c_float_p, ctypes.c_int, c_float_p]
     L.ref_set_gemm.argtypes = [ctypes.c_void_p]
+    L.ref_octree_new.restype = ctypes.c_long
+    L.ref_octree_new.argtypes = [ctypes.c_int] * 4 + [ctypes.c_char_p, ctypes.c_long]
+    L.ref_octree_grow.restype = ctypes.c_long
+    L.ref_octree_grow.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_long]
+    L.ref_octree_update.argtypes = [ctypes.c_char_p, c_int_p, ctypes.c_int, ctypes.c_int]
     self._gemm_cb = None
 
   # -- buffers ---------------------------------------------------------------------------
@@ -130,6 +135,22 @@ class Ref:
     bufs = [np.ascontiguousarray(o, dtype=np.uint8).tobytes() for o in octrees]
     arr = (ctypes.c_char_p * len(bufs))(*bufs)
     return self._sized(lambda o, c: self.lib.ref_octree_batch(arr, len(bufs), o, c))
+
+  # -- the generative path's octree editing (pytorch/cpp/octree_grow.cpp) ----------------------
+  def octree_new(self, batch_size, channel, node_dis=False, adaptive_layer=0):
+    return self._sized(lambda o, c: self.lib.ref_octree_new(batch_size, channel, int(node_dis),
+                                                            adaptive_layer, o, c))
+
+  def octree_grow(self, octree, target_depth, full_octree):
+    buf = np.ascontiguousarray(octree, dtype=np.uint8).tobytes()
+    return self._sized(lambda o, c: self.lib.ref_octree_grow(buf, target_depth, int(full_octree), o, c))
+
+  def octree_update(self, octree, label, depth, split):
+    buf = ctypes.create_string_buffer(np.ascontiguousarray(octree, dtype=np.uint8).tobytes(),
+                                      len(octree))
+    label = _i32(label)
+    self.lib.ref_octree_update(buf, _ip(label), depth, split)
+    return np.frombuffer(buf.raw, dtype=np.uint8).copy()
 
   def octree_sample(self, name):
     return self._sized(lambda o, c: self.lib.ref_octree_sample(name.encode(), o, c))

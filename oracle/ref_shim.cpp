@@ -338,4 +338,101 @@ void ref_clip_points(char* buf, const float* bbmin, const float* bbmax, int* mas
 
 void ref_bounding_box(const float* pt, int npt, float* out6) { bounding_box(out6, out6 + 3, pt, npt); }
 
+// octree_new (pytorch/cpp/octree_grow.cpp:108-148): the same OctreeInfo calls in the same order.
+long ref_octree_new(int batch_size, int channel, int node_dis, int adaptive_layer, char* out, long cap) {
+  const int node_num = batch_size, depth = 0;
+  OctreeInfo oct_info;
+  oct_info.set_batch_size(batch_size);
+  oct_info.set_depth(depth);
+  oct_info.set_full_layer(depth);
+  oct_info.set_node_dis(node_dis != 0);
+  if (adaptive_layer > 1) {
+    oct_info.set_adaptive(true);
+    oct_info.set_adaptive_layer(adaptive_layer);
+  } else {
+    oct_info.set_adaptive(false);
+  }
+  oct_info.set_key2xyz(true);
+  oct_info.set_property(OctreeInfo::kKey, 1, -1);
+  oct_info.set_property(OctreeInfo::kChild, 1, -1);
+  oct_info.set_property(OctreeInfo::kNeigh, 8, -1);
+  oct_info.set_property(OctreeInfo::kFeature, channel, -1);
+  float bbmin[] = {0, 0, 0};
+  float bbmax[] = {2, 2, 2};
+  oct_info.set_bbox(bbmin, bbmax);
+  oct_info.set_nnum(depth, node_num);
+  oct_info.set_nnum_cum();
+  oct_info.set_nempty(depth, node_num);
+  oct_info.set_ptr_dis();
+  std::vector<char> buf(oct_info.sizeof_octree(), 0);
+  OctreeParser octree_out;
+  octree_out.set_cpu(buf.data(), &oct_info);
+  sequence_cpu(octree_out.mutable_key_cpu(depth), node_num);
+  sequence_cpu(octree_out.mutable_children_cpu(depth), node_num);
+  return emit(buf, out, cap);
+}
+
+// octree_grow (pytorch/cpp/octree_grow.cpp:8-104) with the CPU versions of the functions the
+// binding calls on the GPU (calc_neigh_cpu, generate_key_cpu, sequence_cpu: octree_nn.cpp).
+long ref_octree_grow(const char* octree_in_buf, int target_depth, int full_octree, char* out, long cap) {
+  OctreeParser octree_in;
+  octree_in.set_cpu(octree_in_buf);
+  const int batch_size = octree_in.info().batch_size();
+  const int node_num = octree_in.info().node_num_nempty(target_depth - 1) << 3;
+  OctreeInfo oct_info = octree_in.info();
+  oct_info.set_depth(target_depth);
+  if (full_octree) oct_info.set_full_layer(target_depth);
+  float width = 1 << target_depth;
+  float bbmin[] = {0, 0, 0};
+  float bbmax[] = {width, width, width};
+  oct_info.set_bbox(bbmin, bbmax);
+  oct_info.set_nnum(target_depth, node_num);
+  oct_info.set_nempty(target_depth, node_num);
+  oct_info.set_nnum_cum();
+  oct_info.set_ptr_dis();
+  std::vector<char> buf(oct_info.sizeof_octree(), 0);
+  OctreeParser octree_out;
+  octree_out.set_cpu(buf.data(), &oct_info);
+  const int node_num_cum = octree_in.info().node_num_cum(target_depth);
+  memcpy(octree_out.mutable_key_cpu(0), octree_in.key_cpu(0),
+         sizeof(uintk) * node_num_cum * octree_in.info().channel(OctreeInfo::kKey));
+  memcpy(octree_out.mutable_children_cpu(0), octree_in.children_cpu(0),
+         sizeof(int) * node_num_cum * octree_in.info().channel(OctreeInfo::kChild));
+  memcpy(octree_out.mutable_neighbor_cpu(0), octree_in.neighbor_cpu(0),
+         sizeof(int) * node_num_cum * octree_in.info().channel(OctreeInfo::kNeigh));
+  if (octree_in.info().channel(OctreeInfo::kFeature) > 0)
+    memcpy(octree_out.mutable_feature_cpu(0), octree_in.feature_cpu(0),
+           sizeof(float) * node_num_cum * octree_in.info().channel(OctreeInfo::kFeature));
+  if (full_octree) {
+    calc_neigh_cpu(octree_out.mutable_neighbor_cpu(target_depth), target_depth, batch_size);
+    generate_key_cpu(octree_out.mutable_key_cpu(target_depth), target_depth, batch_size);
+    sequence_cpu(octree_out.mutable_children_cpu(target_depth), node_num);
+  } else {
+    const int* label_ptr = octree_out.children_cpu(target_depth - 1);
+    calc_neigh_cpu(octree_out.mutable_neighbor_cpu(target_depth),
+                   octree_out.neighbor_cpu(target_depth - 1), label_ptr,
+                   octree_out.info().node_num(target_depth - 1));
+    generate_key_cpu(octree_out.mutable_key_cpu(target_depth),
+                     octree_out.key_cpu(target_depth - 1), label_ptr,
+                     octree_out.info().node_num(target_depth - 1));
+    sequence_cpu(octree_out.mutable_children_cpu(target_depth), node_num);
+  }
+  return emit(buf, out, cap);
+}
+
+// octree_update (pytorch/cpp/octree_grow.cpp:150-177) with generate_label_cpu.  In place.
+void ref_octree_update(char* octree_buf, const int* label, int depth, int split) {
+  OctreeParser octree_;
+  octree_.set_cpu(octree_buf);
+  const int node_num = octree_.info().node_num(depth);
+  int split_num = 0;
+  int* children = octree_.mutable_children_cpu(depth);
+  generate_label_cpu(children, split_num, label, node_num, split);
+  if (split_num == 0) {
+    split_num = 1;
+    children[0] = 0;
+  }
+  octree_.mutable_info().set_nempty(depth, split_num);
+}
+
 }  // extern "C"

@@ -149,6 +149,30 @@ def main_samples():
   print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
 
 
+def main_grow():
+  """octree_new / octree_grow / octree_update (pytorch/cpp/octree_grow.cpp) through the compiled
+  reference: two octrees grown full to depth 2, then three label-driven levels."""
+  here = os.path.dirname(os.path.abspath(__file__))
+  out = {}
+  for kb in (32, 64):
+    R = ref.get(kb)
+    rng = np.random.default_rng(77 + kb)
+    cur = R.octree_new(2, 4, True, 0)
+    out['k%d_new' % kb] = cur
+    for d in range(1, 5):
+      cur = R.octree_grow(cur, d, d <= 2)
+      out['k%d_grow%d' % (kb, d)] = cur
+      if d >= 2:
+        n = int(R.octree_info(cur)['nnum'][d])
+        label = (rng.random(n) < 0.45).astype(np.int32)
+        out['k%d_label%d' % (kb, d)] = label
+        cur = R.octree_update(cur, label, d, 1)
+        out['k%d_update%d' % (kb, d)] = cur
+  path = os.path.join(here, 'reference_vectors_grow.npz')
+  np.savez_compressed(path, **out)
+  print('wrote %s: %d arrays, %d bytes' % (path, len(out), os.path.getsize(path)))
+
+
 if __name__ == '__main__':
   what = sys.argv[1] if len(sys.argv) > 1 else 'all'
   if what == 'all':
@@ -157,3 +181,5 @@ if __name__ == '__main__':
     main_general()
   if what in ('all', 'samples'):
     main_samples()
+  if what in ('all', 'grow'):
+    main_grow()

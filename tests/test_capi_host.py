@@ -151,3 +151,36 @@ def test_extension_loads_and_fails_loudly_without_gpu():
     ocnn.points2octree(pts, 4, 2, False, False, False, False, 4, 0.1, 2.0, False, False, False)
   with pytest.raises(RuntimeError):
     ocnn.nn.octree_pad(torch.zeros(1, 2, 8, 1), torch.zeros(2000, dtype=torch.uint8), 1, 0.0)
+
+
+@pytest.mark.parametrize('kb', [32, 64])
+def test_octree_new_and_grow_header_on_the_host(lib, kb):
+  """ocnn_octree_new and ocnn_octree_grow_header are host code: bytes equal to the oracle's
+  (itself pinned on the compiled reference), incl. the depth-0 / full-layer-1 header and a
+  Feature block without channels."""
+  lib.ocnn_octree_new_bytes.restype = ctypes.c_size_t
+  for batch, channel, node_dis, adp in ((1, 3, 0, 0), (2, 4, 1, 0), (3, 0, 0, 4)):
+    want = oc.octree_new(batch, channel, bool(node_dis), adp, kb)
+    n = lib.ocnn_octree_new_bytes(batch, channel, kb)
+    assert n == want.size
+    buf = ctypes.create_string_buffer(n)
+    assert lib.ocnn_octree_new(batch, channel, node_dis, adp, kb, buf, ctypes.c_size_t(n)) == 0, \
+        lib.ocnn_last_error()
+    assert np.array_equal(np.frombuffer(buf.raw, np.uint8), want)
+    cur = want
+    for d in (1, 2, 3):
+      grown = oc.octree_grow(cur, d, True)
+      hdr = ctypes.create_string_buffer(720)
+      assert lib.ocnn_octree_grow_header(cur[:720].tobytes(), d, 1, hdr) == 0, lib.ocnn_last_error()
+      assert np.array_equal(np.frombuffer(hdr.raw, np.uint8), grown[:720]), d
+      cur = grown
+    # a partly split level, then a label-driven level
+    label = (np.arange(int(oc.OctreeView(cur).nnum[3])) % 3 == 0).astype(np.int32)
+    cur = oc.octree_update(cur, label, 3, 1)
+    grown = oc.octree_grow(cur, 4, False)
+    hdr = ctypes.create_string_buffer(720)
+    assert lib.ocnn_octree_grow_header(cur[:720].tobytes(), 4, 0, hdr) == 0, lib.ocnn_last_error()
+    assert np.array_equal(np.frombuffer(hdr.raw, np.uint8), grown[:720])
+  # a full level cannot follow a level with empty nodes
+  assert lib.ocnn_octree_grow_header(cur[:720].tobytes(), 4, 1, hdr) != 0
+  assert b'non-empty' in lib.ocnn_last_error()

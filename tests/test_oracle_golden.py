@@ -1,6 +1,8 @@
 """Pins the CPU oracle (oracle/ocnn_oracle.c) on (1) the known-answer vectors held by the
 reference's own tests and (2) fixtures produced by the reference's compiled CPU code
 (tests/golden/reference_vectors.npz).  Runs without a GPU and without the reference checkout."""
+import os
+
 import numpy as np
 import pytest
 
@@ -291,3 +293,19 @@ def test_octree_samples_api(golden):
       ocnn.set_key_bits(64)
   with pytest.raises(ValueError):
     ocnn.octree_samples(['octree_7'])
+
+
+@pytest.mark.parametrize('kb', [32, 64])
+def test_octree_new_grow_update_match_reference_fixture(kb):
+  """octree_new / octree_grow / octree_update against outputs of the compiled reference
+  (tests/golden/reference_vectors_grow.npz, made by make_golden.py grow)."""
+  g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden',
+                           'reference_vectors_grow.npz'))
+  cur = oc.octree_new(2, 4, True, 0, kb)
+  assert np.array_equal(cur, g['k%d_new' % kb])
+  for d in range(1, 5):
+    cur = oc.octree_grow(cur, d, d <= 2)
+    assert np.array_equal(cur, g['k%d_grow%d' % (kb, d)]), d
+    if d >= 2:
+      cur = oc.octree_update(cur, g['k%d_label%d' % (kb, d)], d, 1)
+      assert np.array_equal(cur, g['k%d_update%d' % (kb, d)]), d

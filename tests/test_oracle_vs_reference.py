@@ -293,3 +293,27 @@ def test_point_preparation():
         if u is not None:
           assert same_bits(u[:kept], v[:kept])
   assert same_bits(R.bounding_box(p), oc.bounding_box(p))
+
+
+@pytest.mark.parametrize('kb', [32, 64])
+@pytest.mark.parametrize('setup', [(1, 3, False, 0), (2, 4, True, 0), (3, 0, False, 4)])
+def test_octree_new_grow_update(kb, setup):
+  """The generative path's octree editing (pytorch/cpp/octree_grow.cpp): octree_new, full and
+  label-driven octree_grow, octree_update incl. the degenerate all-empty case."""
+  R = ref.get(kb)
+  batch, channel, node_dis, adp = setup
+  cur = R.octree_new(batch, channel, node_dis, adp)
+  assert same_bits(cur, oc.octree_new(batch, channel, node_dis, adp, kb))
+  rng = np.random.default_rng(batch)
+  for d in range(1, 6):
+    full = d <= 2
+    grown = R.octree_grow(cur, d, full)
+    assert same_bits(grown, oc.octree_grow(cur, d, full)), (d, full)
+    cur = grown
+    if d >= 2:
+      n = int(oc.OctreeView(grown).nnum[d])
+      label = (rng.random(n) < 0.4).astype(np.int32)
+      if d == 5 and batch == 1:
+        label[:] = 0                       # nothing splits: one node is kept
+      cur = R.octree_update(grown, label, d, 1)
+      assert same_bits(cur, oc.octree_update(grown, label, d, 1)), d
