@@ -136,7 +136,9 @@ def run_build(args):
   flush = torch.empty(256 << 20, dtype=torch.uint8, device='cuda') if args.flush else None
   ms, best = time_op(fn, args.iters, flush=flush)
   info = ocnn.octree_info(octree)
-  report('points2octree+neigh (plan + emit, %d kernels)' % 0, ms, best, byts, 0,
+  n0 = ocnn.nn.launch_count()
+  fn()
+  report('points2octree+neigh (plan + emit, %d kernels)' % (ocnn.nn.launch_count() - n0), ms, best, byts, 0,
          {'clouds': len(clouds), 'points': n, 'depth': depth, 'key_bits': kb,
           'octree_bytes': int(octree.numel()), 'finest_nodes': int(info[4 + depth]),
           'clouds_per_s': len(clouds) / (ms * 1e-3), 'points_per_s': n / (ms * 1e-3)})
