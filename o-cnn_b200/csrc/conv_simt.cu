@@ -19,7 +19,7 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 16, THREADS = 256;
+constexpr int BK = 16;
 
 struct ConvArgs {
   const void* x;
@@ -46,10 +46,19 @@ __device__ __forceinline__ void st(__half* p, long long i, float v) { p[i] = __f
 __device__ __forceinline__ void st(float* p, long long i, float v) { p[i] = v; }
 __device__ __forceinline__ void st(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
 
-template <typename T, int LAYOUT>
-__global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
-  __shared__ float As[BK][BM + 4];
-  __shared__ float Bs[BK][BN + 4];
+// Tile BM nodes x BN output channels, BM*BN/16 threads, 4x4 outputs per thread.  64x64 (256
+// threads) where the level gives the GPU enough of them; 32x32 (64 threads) on small levels, where
+// a 64x64 grid would leave SMs without a CTA and every CTA alone with its latency chain.  The K
+// loop is software-pipelined: the global loads of slice k+1 (weights and gathered inputs) are
+// issued before the FMAs of slice k and land in the other half of a double-buffered pair of
+// shared-memory tiles, so a slice costs one barrier.  A thread's (channel, tap) position advances
+// by BK per slice and is kept incrementally (no division in the loop).
+template <typename T, int LAYOUT, int BM, int BN>
+__global__ void __launch_bounds__(BM* BN / 16) conv_simt_kernel(const ConvArgs a) {
+  constexpr int THREADS = BM * BN / 16;
+  constexpr int RA = (BK * BM) / THREADS, RB = (BK * BN) / THREADS;
+  __shared__ __align__(16) float As[2][BK][BM + 4];
+  __shared__ __align__(16) float Bs[2][BK][BN + 4];
   __shared__ int nbr[27][BM];
 
   const T* __restrict__ x = static_cast<const T*>(a.x);
@@ -91,54 +100,97 @@ __global__ void __launch_bounds__(THREADS) conv_simt_kernel(const ConvArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  const int tm = tid % 16, tn = tid / 16;
+  const int tm = tid % (BM / 4), tn = tid / (BM / 4);
 
-  for (int k0 = 0; k0 < KD; k0 += BK) {
+  // this thread's slots in the A and B tiles: (kl, m) / (kl, n) are fixed, the K position of kl
+  // advances by BK per slice; (ci, t) of that position is carried along
+  int a_kl[RA], a_m[RA], b_kl[RB], b_n[RB];
 #pragma unroll
-    for (int r = 0; r < (BK * BM) / THREADS; ++r) {
-      const int e = tid + THREADS * r;
-      int m, kl;
-      if (LAYOUT == OCNN_CHANNEL_MAJOR) { m = e % BM; kl = e / BM; } else { kl = e % BK; m = e / BK; }
-      const int kk = k0 + kl;
+  for (int r = 0; r < RA; ++r) {
+    const int e = tid + THREADS * r;
+    if (LAYOUT == OCNN_CHANNEL_MAJOR) { a_m[r] = e % BM; a_kl[r] = e / BM; } else { a_kl[r] = e % BK; a_m[r] = e / BK; }
+  }
+#pragma unroll
+  for (int r = 0; r < RB; ++r) {
+    const int e = tid + THREADS * r;
+    b_kl[r] = e % BK;
+    b_n[r] = e / BK;
+  }
+  auto split = [&](int kk, int& ci, int& t) {
+    if (LAYOUT == OCNN_CHANNEL_MAJOR) { ci = kk / a.K; t = kk - ci * a.K; } else { t = kk / a.cin; ci = kk - t * a.cin; }
+  };
+  int a_ci[RA], a_t[RA], b_ci[RB], b_t[RB];
+#pragma unroll
+  for (int r = 0; r < RA; ++r) split(a_kl[r], a_ci[r], a_t[r]);
+#pragma unroll
+  for (int r = 0; r < RB; ++r) split(b_kl[r], b_ci[r], b_t[r]);
+  auto advance = [&](int& ci, int& t) {
+    // K position += BK
+    if (LAYOUT == OCNN_CHANNEL_MAJOR) {
+      t += BK;
+      while (t >= a.K) { t -= a.K; ++ci; }
+    } else {
+      ci += BK;
+      while (ci >= a.cin) { ci -= a.cin; ++t; }
+    }
+  };
+  auto in_range = [&](int ci, int t) {
+    return LAYOUT == OCNN_CHANNEL_MAJOR ? ci < a.cin : t < a.K;
+  };
+
+  float ra[RA], rb[RB];
+  auto fetch = [&]() {
+#pragma unroll
+    for (int r = 0; r < RA; ++r) {
       float v = 0.f;
-      if (kk < KD) {
-        int ci, t;
-        if (LAYOUT == OCNN_CHANNEL_MAJOR) { ci = kk / a.K; t = kk % a.K; } else { t = kk / a.cin; ci = kk % a.cin; }
-        const int p = nbr[t][m];
+      if (in_range(a_ci[r], a_t[r])) {
+        const int p = nbr[a_t[r]][a_m[r]];
         if (p >= 0)
-          v = LAYOUT == OCNN_CHANNEL_MAJOR ? ld(x, (long long)ci * a.h_in + p)
-                                           : ld(x, (long long)p * a.cin + ci);
+          v = LAYOUT == OCNN_CHANNEL_MAJOR ? ld(x, (long long)a_ci[r] * a.h_in + p)
+                                           : ld(x, (long long)p * a.cin + a_ci[r]);
       }
-      As[kl][m] = v;
+      ra[r] = v;
+      advance(a_ci[r], a_t[r]);
     }
 #pragma unroll
-    for (int r = 0; r < (BK * BN) / THREADS; ++r) {
-      const int e = tid + THREADS * r;
-      const int kl = e % BK, n = e / BK;
-      const int kk = k0 + kl, co = n0 + n;
+    for (int r = 0; r < RB; ++r) {
       float v = 0.f;
-      if (kk < KD && co < a.cout) {
-        int ci, t;
-        if (LAYOUT == OCNN_CHANNEL_MAJOR) { ci = kk / a.K; t = kk % a.K; } else { t = kk / a.cin; ci = kk % a.cin; }
-        v = a.transposed ? a.w[((long long)ci * a.cout + co) * a.K + t]
-                         : a.w[(long long)co * KD + ci * a.K + t];
-      }
-      Bs[kl][n] = v;
+      const int co = n0 + b_n[r];
+      if (in_range(b_ci[r], b_t[r]) && co < a.cout)
+        v = a.transposed ? a.w[((long long)b_ci[r] * a.cout + co) * a.K + b_t[r]]
+                         : a.w[(long long)co * KD + b_ci[r] * a.K + b_t[r]];
+      rb[r] = v;
+      advance(b_ci[r], b_t[r]);
     }
-    __syncthreads();
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int r = 0; r < RA; ++r) As[buf][a_kl[r]][a_m[r]] = ra[r];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) Bs[buf][b_kl[r]][b_n[r]] = rb[r];
+  };
+
+  fetch();
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < KD; k0 += BK) {
+    const bool more = k0 + BK < KD;
+    if (more) fetch();                 // in flight during the FMAs below
 #pragma unroll
     for (int kl = 0; kl < BK; ++kl) {
-      float av[4], bv[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) av[i] = As[kl][tm * 4 + i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) bv[j] = Bs[kl][tn * 4 + j];
+      const float4 av4 = *reinterpret_cast<const float4*>(&As[buf][kl][tm * 4]);
+      const float4 bv4 = *reinterpret_cast<const float4*>(&Bs[buf][kl][tn * 4]);
+      const float av[4] = {av4.x, av4.y, av4.z, av4.w};
+      const float bv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
+    if (more) stash(buf ^ 1);
     __syncthreads();
+    buf ^= 1;
   }
 
   T* __restrict__ y = static_cast<T*>(a.y);
@@ -195,18 +247,28 @@ int conv_simt_launch(const void* x, const float* w, void* y, const int32_t* neig
   // with p = h + offset(t), i.e. h = p - offset(t)
   for (int i = 0; i < 27; ++i)
     a.tap[i] = i < tl.count ? (signed char)((transposed && stride == 1) ? 26 - tl.tap[i] : tl.tap[i]) : 0;
-  dim3 grid(ceil_div(h_out, BM), ceil_div(cout, BN));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // 64x64 tiles unless they would not even give every SM one CTA: then 32x32 tiles
+  const long long big_ctas = (long long)ceil_div(h_out, 64) * ceil_div(cout, 64);
+  const bool small = big_ctas < (long long)sm_count();
+#define OCNN_SIMT_LAUNCH(TYPE, LAY)                                                                   \
+  do {                                                                                                \
+    if (small)                                                                                        \
+      conv_simt_kernel<TYPE, LAY, 32, 32><<<dim3(ceil_div(h_out, 32), ceil_div(cout, 32)), 64, 0, s>>>(a); \
+    else                                                                                              \
+      conv_simt_kernel<TYPE, LAY, 64, 64><<<dim3(ceil_div(h_out, 64), ceil_div(cout, 64)), 256, 0, s>>>(a); \
+  } while (0)
   if (dtype == OCNN_F32) {
-    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<float, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
-    else conv_simt_kernel<float, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    if (layout == OCNN_CHANNEL_MAJOR) OCNN_SIMT_LAUNCH(float, OCNN_CHANNEL_MAJOR);
+    else OCNN_SIMT_LAUNCH(float, OCNN_NODE_MAJOR);
   } else if (dtype == OCNN_F16) {
-    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__half, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
-    else conv_simt_kernel<__half, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    if (layout == OCNN_CHANNEL_MAJOR) OCNN_SIMT_LAUNCH(__half, OCNN_CHANNEL_MAJOR);
+    else OCNN_SIMT_LAUNCH(__half, OCNN_NODE_MAJOR);
   } else {
-    if (layout == OCNN_CHANNEL_MAJOR) conv_simt_kernel<__nv_bfloat16, OCNN_CHANNEL_MAJOR><<<grid, THREADS, 0, s>>>(a);
-    else conv_simt_kernel<__nv_bfloat16, OCNN_NODE_MAJOR><<<grid, THREADS, 0, s>>>(a);
+    if (layout == OCNN_CHANNEL_MAJOR) OCNN_SIMT_LAUNCH(__nv_bfloat16, OCNN_CHANNEL_MAJOR);
+    else OCNN_SIMT_LAUNCH(__nv_bfloat16, OCNN_NODE_MAJOR);
   }
+#undef OCNN_SIMT_LAUNCH
   OCNN_LAUNCH_OK("conv_simt_kernel");
   return OCNN_OK;
 }
