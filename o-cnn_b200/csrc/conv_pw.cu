@@ -215,6 +215,156 @@ int launch_pw(const PwArgs& a, cudaStream_t st) {
   }
 }
 
+// ---- the same layer on warp-level tensor-core instructions ------------------------------------
+// With 8..64 channels the CUDA-core kernel above is bound by instruction issue (Cin*Cout FMAs and
+// Cin*Cout/4 shared-memory reads per node), not by memory.  Here a warp owns 16 consecutive node
+// rows at a time and multiplies them with mma.sync (m16n8k16, or m16n8k8 for 8 input channels;
+// bf16 or fp16 operands, fp32 accumulation): the A fragments are 4-byte loads straight from the
+// node-major rows (consecutive rows are consecutive memory), the weights live in registers for the
+// whole launch as a (hi, lo) pair of 16-bit values per element, so the product is that of the fp32
+// weights to about 2^-17, and the output (and shortcut) are accessed as 16-bit pairs in the
+// accumulator's own layout.  What is left per node is the memory traffic.
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                          bool half) {
+  if (half)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, bool half) {
+  if (half)
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+  else
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+
+// (hi, lo) 16-bit split of two fp32 weights, packed as the low / high half of a register each
+__device__ __forceinline__ void split2(float w0, float w1, bool half, uint32_t& hi, uint32_t& lo) {
+  hi = pack2(w0, w1, half);
+  const float2 h = unpack2(hi, half);
+  lo = pack2(w0 - h.x, w1 - h.y, half);
+}
+
+template <int CIN, int COUT, bool HALF>
+__global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
+  constexpr int KS = CIN >= 16 ? CIN / 16 : 1;     // 16-wide (8-wide for CIN = 8) K slices
+  constexpr int NT = COUT / 8;                      // 8-column accumulator tiles
+  constexpr int BR = CIN >= 16 ? 2 : 1;             // B registers per (slice, tile)
+  grid_dependency_trigger();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  // weights: B[k = ci][n = co] = w[co][ci]; this lane's elements of every (slice, tile)
+  uint32_t bh[KS][NT][BR], bl[KS][NT][BR];
+#pragma unroll
+  for (int s = 0; s < KS; ++s)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int r = 0; r < BR; ++r) {
+        const float* wp = a.w + (long long)(8 * j + g) * CIN + 16 * s + 8 * r + 2 * q;
+        split2(wp[0], wp[1], HALF, bh[s][j][r], bl[s][j][r]);
+      }
+  float sc[NT][2], bi[NT][2];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      sc[j][e] = a.scale ? a.scale[8 * j + 2 * q + e] : 1.f;
+      bi[j][e] = a.bias ? a.bias[8 * j + 2 * q + e] : 0.f;
+    }
+  const long long tiles = ((long long)a.h + 15) >> 4;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const uint32_t* x32 = reinterpret_cast<const uint32_t*>(a.x);
+  const uint32_t* r32 = reinterpret_cast<const uint32_t*>(a.residual);
+  uint32_t* y32 = reinterpret_cast<uint32_t*>(a.y);
+  constexpr int XW = CIN / 2, YW = COUT / 2;        // 32-bit words per row
+  for (long long tile = warp0; tile < tiles; tile += nwarps) {
+    const long long r0 = (tile << 4) + g, r1 = r0 + 8;
+    const bool ok0 = r0 < a.h, ok1 = r1 < a.h;
+    // A fragments of every slice (all loads before the first MMA)
+    uint32_t af[KS][4];
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      af[s][0] = ok0 ? x32[r0 * XW + 8 * s + q] : 0u;
+      af[s][1] = ok1 ? x32[r1 * XW + 8 * s + q] : 0u;
+      if (CIN >= 16) {
+        af[s][2] = ok0 ? x32[r0 * XW + 8 * s + 4 + q] : 0u;
+        af[s][3] = ok1 ? x32[r1 * XW + 8 * s + 4 + q] : 0u;
+      } else {
+        af[s][2] = af[s][3] = 0u;
+      }
+    }
+    uint32_t rw[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      rw[j][0] = (r32 && ok0) ? r32[r0 * YW + 4 * j + q] : 0u;
+      rw[j][1] = (r32 && ok1) ? r32[r1 * YW + 4 * j + q] : 0u;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll
+      for (int s = 0; s < KS; ++s) {
+        if (CIN >= 16) {
+          mma_16816(acc[j], af[s], bl[s][j][0], bl[s][j][BR - 1], HALF);
+          mma_16816(acc[j], af[s], bh[s][j][0], bh[s][j][BR - 1], HALF);
+        } else {
+          mma_1688(acc[j], af[s][0], af[s][1], bl[s][j][0], HALF);
+          mma_1688(acc[j], af[s][0], af[s][1], bh[s][j][0], HALF);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      float v0 = fmaf(acc[j][0], sc[j][0], bi[j][0]), v1 = fmaf(acc[j][1], sc[j][1], bi[j][1]);
+      float v2 = fmaf(acc[j][2], sc[j][0], bi[j][0]), v3 = fmaf(acc[j][3], sc[j][1], bi[j][1]);
+      if (r32) {
+        const float2 ra = unpack2(rw[j][0], HALF), rb = unpack2(rw[j][1], HALF);
+        v0 += ra.x; v1 += ra.y; v2 += rb.x; v3 += rb.y;
+      }
+      if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
+      if (ok0) y32[r0 * YW + 4 * j + q] = pack2(v0, v1, HALF);
+      if (ok1) y32[r1 * YW + 4 * j + q] = pack2(v2, v3, HALF);
+    }
+  }
+}
+
+template <int CIN, int COUT>
+int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
+  const long long warps = ((long long)a.h + 15) / 16;
+  const int grid = grid_for(warps * 32, 256, 8);
+  if (a.f16)
+    OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, true>, dim3(grid), dim3(256), 0, st, a));
+  else
+    OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, false>, dim3(grid), dim3(256), 0, st, a));
+  OCNN_LAUNCH_OK("conv_pw_mma_kernel");
+  return OCNN_OK;
+}
+
+// -1: not a shape the mma kernel is built for
+int try_pw_mma(const PwArgs& a, int cout, cudaStream_t st) {
+  if (a.y_stride != cout || a.co_base != 0) return -1;
+#define OCNN_PW_CASE(CI, CO) if (a.cin == CI && cout == CO) return launch_pw_mma<CI, CO>(a, st);
+  OCNN_PW_CASE(8, 8) OCNN_PW_CASE(8, 16) OCNN_PW_CASE(8, 32) OCNN_PW_CASE(8, 64)
+  OCNN_PW_CASE(16, 8) OCNN_PW_CASE(16, 16) OCNN_PW_CASE(16, 32) OCNN_PW_CASE(16, 64)
+  OCNN_PW_CASE(32, 8) OCNN_PW_CASE(32, 16) OCNN_PW_CASE(32, 32) OCNN_PW_CASE(32, 64)
+  OCNN_PW_CASE(64, 8) OCNN_PW_CASE(64, 16) OCNN_PW_CASE(64, 32)
+#undef OCNN_PW_CASE
+  return -1;
+}
+
 }  // namespace
 
 // Used by ocnn_octree_conv for 1x1x1 stride-1 bf16 node-major convolutions.  Returns -1 when the
@@ -238,6 +388,13 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.f16 = f16 ? 1 : 0;
   a.wide = (((uintptr_t)x % 32) == 0 && ((uintptr_t)y % 32) == 0 &&
             (!(ep && ep->residual_dev) || ((uintptr_t)ep->residual_dev % 32) == 0)) ? 1 : 0;
+  {
+    static const int use_mma = [] { const char* e = getenv("OCNN_PW_MMA"); return e ? atoi(e) : 1; }();
+    if (use_mma) {
+      const int rc = try_pw_mma(a, cout, st);
+      if (rc != -1) return rc;
+    }
+  }
   switch (cout) {
     case 8: return launch_pw<8, 2>(a, st);
     case 16: return launch_pw<16, 2>(a, st);

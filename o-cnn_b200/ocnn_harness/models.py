@@ -343,10 +343,11 @@ class GpuNet:
     # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
     # else that fits goes to the tensor-core kernel
     cout = p['_cout']
-    # (from 32 channels in, the tensor-core kernel on rows of two nodes is the faster stream:
-    # 32 -> 8 at 972 k nodes 0.026 ms against 0.031 ms; with 8 or 16 channels in its rows hold
-    # 8 or 4 nodes and the block-diagonal product costs more than it saves)
-    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin <= 16)
+    # (the streaming mma.sync kernel behind octree_conv wins on big levels while Cin * Cout <= 512:
+    # 8 -> 32 + shortcut 0.030 ms against 0.045, 32 -> 8 0.022 against 0.026 at 972 k nodes; with 64
+    # channels on either side its 4-byte accesses and register count lose to the tensor-core kernel)
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin in (8, 16, 32) and
+                       cin * cout <= 512)
     if self.tc and cin % 8 == 0 and cout % 8 == 0 and (cout <= 256 or cout % 256 == 0):
       try:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, cout, p['ks'])
