@@ -565,13 +565,16 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) res_cur[q] = res_nxt[q];
         if (c0 + 32 < a.npad) load_line(c0 + 32);
+        // both 16-column reads of the line are in flight before the one wait
+        uint32_t v2[2][16];
+        tmem_ld16(lane_base + (uint32_t)c0, v2[0]);
+        if (c0 + 16 < a.npad) tmem_ld16(lane_base + (uint32_t)(c0 + 16), v2[1]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
         for (int step = 0; step < 2; ++step) {
           const int n0 = c0 + 16 * step;
           if (n0 >= a.npad) break;
-          uint32_t v[16];
-          tmem_ld16(lane_base + (uint32_t)n0, v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const uint32_t (&v)[16] = v2[step];
           uint4 ov[2];
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
