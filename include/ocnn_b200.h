@@ -285,6 +285,17 @@ int ocnn_octree_conv_tc(const void* x_dev, const void* packed_weights_dev, void*
                         const int kernel_size[3], int stride,
                         const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
 
+/* A 1x1x1 stride-1 convolution over the concatenated channels of two node-major tensors of the
+ * same h rows: y[h] = epilogue(W * [xa[h] | xb[h]]).  With W = [Wb | Wc] it is the sum of a residual
+ * block's last convolution and its shortcut convolution, conv1x1b(y) + conv1x1c(x) of
+ * pytorch/ocnn/modules.py OctreeResBlock.forward, in one launch and without the shortcut tensor
+ * (BatchNorm scales folded into the two halves of W by the caller, the biases added up).
+ * packed_weights_dev: ocnn_conv_pack_weights_general(W as fp32 [cout, cin_a + cin_b], 1x1x1,
+ * stride 1); cin_a, cin_b multiples of 8 with a sum that the packer does not fold (not 8, 16, 32). */
+int ocnn_octree_conv_tc_pair(const void* xa_dev, int cin_a, const void* xb_dev, int cin_b,
+                             const void* packed_weights_dev, void* y_dev, int h, int cout, int dtype,
+                             const ocnn_conv_epilogue* epilogue, int32_t* status_dev, void* stream);
+
 /* Self-test of the bounded waits of the tensor-core kernels (no reference counterpart: the
  * reference has no such kernels).  Launches one small CTA whose two waiting threads wait on a
  * barrier that nobody arrives on.  status_dev: two int32, zero before the call; afterwards

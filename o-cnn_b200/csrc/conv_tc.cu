@@ -50,6 +50,8 @@ enum : int { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccumWait = 3, kErrWeightW
 
 struct TcArgs {
   const __nv_bfloat16* x;
+  const __nv_bfloat16* x2;   // two-input 1x1x1 layer: the K row of node h is x[h] followed by x2[h]
+  int cpt_a;                 // ... and x's share of it in 16-byte chunks (0: one input)
   const uint8_t* wpacked;
   __nv_bfloat16* y;
   const int* neigh;
@@ -514,7 +516,24 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
       for (int kb = 0; kb < a.nkb; ++kb) {
         if (alive && kb >= a.stages)
           alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
-        if (alive && row_ok)
+        bool paired = false;
+        if constexpr (CPT == 0) paired = a.x2 != nullptr;
+        if (alive && row_ok && paired) {
+          // chunk g of the node's K row: the first cpt_a chunks are its row of x, the rest its row
+          // of x2, zeros beyond Cin
+          const uint32_t cpt_all = (uint32_t)a.cin >> 3, cpt_a = (uint32_t)a.cpt_a;
+          const char* row_a = reinterpret_cast<const char*>(a.x) + (size_t)(h0 + r) * (cpt_a * 16u);
+          const char* row_b =
+              reinterpret_cast<const char*>(a.x2) + (size_t)(h0 + r) * ((cpt_all - cpt_a) * 16u);
+          const uint32_t dst_row = smem_u32(sA + s * kStageA) + row_off;
+#pragma unroll
+          for (uint32_t c = 0; c < 8; ++c) {
+            const uint32_t g = (uint32_t)kb * 8u + c;
+            const char* src = g < cpt_a ? row_a + g * 16u : row_b + (g - cpt_a) * 16u;
+            const bool live = g < cpt_all;
+            cp_async16(dst_row + ((c ^ sw) << 4), live ? src : row_a, live ? 16u : 0u);
+          }
+        } else if (alive && row_ok)
           gather_block<CPT>(a, nbr_col, nbr_stride, T, kb, smem_u32(sA + s * kStageA) + row_off, sw,
                             t_run, cc_run);
         // Arrive on full[s] when this thread's copies of the block have landed; the thread itself
@@ -864,7 +883,27 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
         }
         if (alive && gk >= a.stages)
           alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
-        if (alive) {
+        bool paired = false;
+        if constexpr (CPT == 0) paired = a.x2 != nullptr;
+        if (alive && paired) {
+          // two-input 1x1x1 layer: chunk g of a node's K row is chunk g of its row of x while
+          // g < cpt_a, chunk g - cpt_a of its row of x2 after that, zeros beyond Cin
+          const uint32_t stage_base = smem_u32(sA + s * (R * kStageA));
+          const uint32_t g = (uint32_t)kb * 8u + (uint32_t)chunk;
+          const uint32_t cpt_all = (uint32_t)a.cin >> 3, cpt_a = (uint32_t)a.cpt_a;
+          const bool from_a = g < cpt_a, live = g < cpt_all;
+          const char* base = from_a ? xb : reinterpret_cast<const char*>(a.x2);
+          const uint32_t rb = (from_a ? cpt_a : cpt_all - cpt_a) * 16u;
+          const uint32_t off = (from_a ? g : g - cpt_a) * 16u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = rbase + 4 * i;
+            const uint32_t dst = stage_base + (uint32_t)row * 128u +
+                                 (((uint32_t)chunk ^ (uint32_t)(row & 7)) << 4);
+            const char* src = live ? base + (size_t)p[i] * rb + off : xb;
+            if ((row_mask >> i) & 1u) cp_async16(dst, src, live ? 16u : 0u);
+          }
+        } else if (alive) {
           const uint32_t stage_base = smem_u32(sA + s * (R * kStageA));
           const uint32_t off = (uint32_t)part * 128u + (uint32_t)chunk * 16u;
 #pragma unroll
@@ -1421,7 +1460,8 @@ int pack_weights_impl(const float* w, void* packed, int cin, int cout, const int
 
 int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geometry* g, int cin,
                  int cout, const int kernel_size[3], int dtype, const ocnn_conv_epilogue* ep,
-                 int32_t* status, void* stream, const char* who) {
+                 int32_t* status, void* stream, const char* who, const void* x2 = nullptr,
+                 int cin_a = 0) {
   OCNN_REQUIRE(kernel_size != nullptr, "%s: null kernel size", who);
   OCNN_REQUIRE(dtype == OCNN_BF16 || dtype == OCNN_F16, "%s: bf16 or fp16 data only (dtype %d)", who, dtype);
   const TapList tl = taps_for_kernel(kernel_size);
@@ -1453,6 +1493,15 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   }
   TcArgs a;
   a.x = static_cast<const __nv_bfloat16*>(x);
+  a.x2 = static_cast<const __nv_bfloat16*>(x2);
+  a.cpt_a = x2 != nullptr ? cin_a / 8 : 0;
+  if (x2 != nullptr) {
+    OCNN_REQUIRE(identity && !g->nempty && !g->transposed && s.fold_nodes == 1 && !s.fold_in && !s.expand_out,
+                 "%s: two inputs only for a plain 1x1x1 stride-1 layer", who);
+    OCNN_REQUIRE(cin_a > 0 && cin_a < cin && cin_a % 8 == 0 && (uintptr_t)x2 % 16 == 0,
+                 "%s: input channel split %d + %d must be multiples of 8, pointers 16-byte aligned", who,
+                 cin_a, cin - cin_a);
+  }
   a.wpacked = static_cast<const uint8_t*>(packed);
   a.y = static_cast<__nv_bfloat16*>(y);
   a.neigh = identity ? nullptr : g->neigh_dev;
@@ -1499,6 +1548,7 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   if (s.gtable) a.rowsplit = 3;
   if (!s.group && s.cin_eff % 64 == 0) a.rowsplit = 2;
   if (!s.group && s.ntable_stride == kGroupTableStride) a.rowsplit = 4;
+  if (x2 != nullptr) a.rowsplit = 0;       // the two-input gather is written for one row per thread
   a.tile_rows = s.tile_rows;
   // 32-byte epilogue accesses: rows and channel slices on 32-byte boundaries
   a.wide = (a.row_elems % 16 == 0 && a.y_stride % 16 == 0 && (uintptr_t)y % 32 == 0 &&
@@ -1550,6 +1600,7 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
     default: break;
   }
   const bool needs_general = a.up || a.expand_cout > 0;
+  if (x2 != nullptr) slot = 0;             // the variant with run-time channel counts
   KernelFn kernel = needs_general ? general[a.f16] : table[a.f16][slot];
   {
     std::lock_guard<std::mutex> lock(attr_once.mutex);
@@ -1568,7 +1619,7 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
       if (known) attr_once.done[device] = true;
     }
   }
-  OCNN_REQUIRE((long long)h_in * cin * 2 < (1LL << 32),
+  OCNN_REQUIRE(x2 != nullptr || (long long)h_in * cin * 2 < (1LL << 32),
                "%s: input tensor of %lld bytes exceeds the 4 GiB this kernel addresses", who,
                (long long)h_in * cin * 2);
   const int ntiles = ceil_div(a.rows, a.tile_rows);
@@ -1577,7 +1628,7 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   // from L2 bounds both kernels alike and the lighter one-tile kernel is as fast or faster.
   // ... and for single-K-block layers (1x1x1 on 64 channels, folded or not), which are plain
   // streams: its weight tile stays resident and nothing is set up per 128 rows.
-  if (!needs_general && a.rowsplit == 2 && (s.npad >= 256 || (s.nkb == 1 && identity)) &&
+  if (!needs_general && (a.rowsplit == 2 || x2 != nullptr) && (s.npad >= 256 || (s.nkb == 1 && identity)) &&
       persist_mode() != 0) {
     const PersistShape ps = persist_shape(s, 2);
     const int sms = sm_count();
@@ -1588,7 +1639,7 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
       // the same number of tiles (within one) for every CTA
       const int waves = ceil_div(big_tiles, sms);
       const int ctas = ceil_div(big_tiles, waves);
-      const int pslot = slot >= 4 ? slot - 3 : 0;      // Cin = 64, 128, 256, 512 -> 1..4
+      const int pslot = (slot >= 4 && x2 == nullptr) ? slot - 3 : 0;      // Cin = 64, 128, 256, 512 -> 1..4
       OCNN_CUDA_OK(launch_chained(persist[a.f16][pslot], dim3(ctas, s.slices), dim3(32 * (4 * ps.R + 6)),
                                   ps.smem, static_cast<cudaStream_t>(stream), a, big_tiles, ps.acc_bufs));
       OCNN_LAUNCH_OK("conv_tc_persist_kernel");
@@ -1646,6 +1697,19 @@ int ocnn_octree_conv_tc(const void* x, const void* packed, void* y, const int32_
   g.stride = stride; g.h_in = h_in; g.h_out = h_out; g.neigh_dev = neigh;
   return ocnn::conv_tc_impl(x, packed, y, &g, cin, cout, kernel_size, OCNN_BF16, ep, status, stream,
                             "ocnn_octree_conv_tc");
+}
+
+int ocnn_octree_conv_tc_pair(const void* xa, int cin_a, const void* xb, int cin_b, const void* packed,
+                             void* y, int h, int cout, int dtype, const ocnn_conv_epilogue* ep,
+                             int32_t* status, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(xa != nullptr && xb != nullptr, "ocnn_octree_conv_tc_pair: null input");
+  OCNN_REQUIRE(cin_a > 0 && cin_b > 0, "ocnn_octree_conv_tc_pair: channel counts must be positive");
+  const int ks[3] = {1, 1, 1};
+  ocnn_conv_geometry g = {};
+  g.stride = 1; g.h_in = h; g.h_out = h;
+  return conv_tc_impl(xa, packed, y, &g, cin_a + cin_b, cout, ks, dtype, ep, status, stream,
+                      "ocnn_octree_conv_tc_pair", xb, cin_a);
 }
 
 int ocnn_conv_tc_wait_selftest(int32_t* status, void* stream) {

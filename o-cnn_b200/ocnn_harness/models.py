@@ -17,6 +17,8 @@ import numpy as np
 # 1x1x1 layers with few channels go to the streaming pointwise kernel from this many nodes up
 # (below it the tensor-core kernel is faster)
 PW_MIN_NODES = int(os.environ.get('OCNN_PW_MIN_NODES', '100000'))
+# a residual block's conv1x1b + shortcut conv1x1c as one two-input layer (0: two launches)
+BLOCK_PAIR = int(os.environ.get('OCNN_BLOCK_PAIR', '1'))
 
 BN_EPS = 0.001   # pytorch/ocnn/modules.py:5
 
@@ -241,6 +243,10 @@ class GpuNet:
     self.tc = bool(tensor_core) and self.bf16
     for _, p in conv_layers(net):
       self._upload(p)
+    if self.tc and BLOCK_PAIR and net['kind'] == 'resnet':
+      for lv in net['levels']:
+        for blk in lv['blocks']:
+          self._pair(blk)
     if net['kind'] != 'unet':
       self.fc_w = torch.from_numpy(net['fc_w']).to(device)
       self.fc_b = torch.from_numpy(net['fc_b']).to(device)
@@ -292,6 +298,13 @@ class GpuNet:
           conv(blk['a'], d, cur, 2, True)
           conv(blk['conv'], d, 2, 3, True)
           skip = cur
+          pr = blk.get('_pair')
+          if pr is not None:
+            ex.add_conv_pair(pr['name'], d, pr['cb'], pr['cc'], pr['cout'], pr['packed'], None,
+                             pr['bias'], True, 3, cur, other)
+            self.exec_layers.append(pr['name'])
+            cur, other = other, cur
+            continue
           if blk['c'] is not None:
             conv(blk['c'], d, cur, 4, False)
             skip = 4
@@ -353,6 +366,41 @@ class GpuNet:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, cout, p['ks'])
       except RuntimeError:
         p['_packed'] = None
+
+  def _pair(self, blk):
+    """conv1x1b(y) + conv1x1c(x) of a block with a projected shortcut as ONE 1x1x1 layer over the
+    concatenated channels [y | x]: weights [diag(scale_b) Wb | diag(scale_c) Wc], bias_b + bias_c.
+    The shortcut tensor is neither written nor read and the block is three launches instead of
+    four."""
+    t = self.torch
+    blk['_pair'] = None
+    b, c = blk['b'], blk['c']
+    if c is None or b['_packed'] is None or c['_packed'] is None:
+      return
+    cb, cc, cout = b['_cin'], c['_cin'], b['_cout']
+    if cb % 8 or cc % 8 or (cb + cc) in (8, 16, 32) or c['_cout'] != cout:
+      return
+    if (cb, cc, cout) != (b['cin'], c['cin'], b['cout']):      # padded by _upload
+      return
+    def scaled(p):
+      w = p['w'].reshape(cout, -1).astype(np.float32)
+      return w if p['scale'] is None else w * p['scale'][:, None]
+    w = np.ascontiguousarray(np.concatenate([scaled(b), scaled(c)], axis=1))
+    bias = np.zeros(cout, np.float32)
+    for p in (b, c):
+      if p['bias'] is not None:
+        bias = bias + p['bias']
+    try:
+      packed = self.ocnn.nn.conv_pack_weights(t.from_numpy(w).to(self.device), cb + cc, cout, [1, 1, 1])
+    except RuntimeError:
+      return
+    blk['_pair'] = {'packed': packed, 'bias': t.from_numpy(bias.astype(np.float32)).to(self.device),
+                    'cb': cb, 'cc': cc, 'cout': cout, 'name': b['name']}
+
+  def _conv_pair(self, y, x, pr):
+    self.launches += 1
+    return self._traced(pr['name'], lambda: self.ocnn.nn.pointwise_conv_tc_pair(
+        y, x, pr['packed'], pr['cout'], None, pr['bias'], None, True, self.status))
 
   def _conv(self, x, p, octree, d, relu, residual=None):
     nn = self.ocnn.nn
@@ -423,6 +471,9 @@ class GpuNet:
           for blk in lv['blocks']:
             y = self._conv(x, blk['a'], octree, d, True)
             y = self._conv(y, blk['conv'], octree, d, True)
+            if blk.get('_pair') is not None:
+              x = self._conv_pair(y, x, blk['_pair'])
+              continue
             skip = x if blk['c'] is None else self._conv(x, blk['c'], octree, d, False)
             x = self._conv(y, blk['b'], octree, d, True, residual=skip)
           if lv['pool']:

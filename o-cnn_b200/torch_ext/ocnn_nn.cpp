@@ -844,6 +844,37 @@ Tensor pointwise_conv_tc(Tensor data_in, Tensor packed, int num_output, c10::opt
   return y;
 }
 
+// 1x1x1 convolution over the concatenated channels of two tensors of the same rows: the sum of a
+// residual block's conv1x1b and its shortcut conv1x1c (pytorch/ocnn/modules.py OctreeResBlock) in
+// one launch; `packed` = conv_pack_weights of [Wb | Wc] with cin = Cb + Cc.
+Tensor pointwise_conv_tc_pair(Tensor data_a, Tensor data_b, Tensor packed, int num_output,
+                              c10::optional<Tensor> scale, c10::optional<Tensor> bias,
+                              c10::optional<Tensor> residual, bool relu, Tensor status) {
+  need_cuda(data_a, "pointwise_conv_tc_pair");
+  need_cuda(data_b, "pointwise_conv_tc_pair");
+  c10::cuda::CUDAGuard guard(data_a.device());
+  DataRef xa = get_data(data_a, "pointwise_conv_tc_pair");
+  DataRef xb = get_data(data_b, "pointwise_conv_tc_pair");
+  TORCH_CHECK(xa.dtype != OCNN_F32 && xa.dtype == xb.dtype &&
+                  (xa.layout == OCNN_NODE_MAJOR || xa.C == 1 || xa.H == 1) &&
+                  (xb.layout == OCNN_NODE_MAJOR || xb.C == 1 || xb.H == 1),
+              "pointwise_conv_tc_pair takes two bfloat16 or two float16 channels_last tensors");
+  TORCH_CHECK(xa.H == xb.H, "pointwise_conv_tc_pair: the inputs have ", xa.H, " and ", xb.H, " rows");
+  xa.layout = OCNN_NODE_MAJOR;
+  const int ks[3] = {1, 1, 1};
+  TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == torch::kUInt8 &&
+                  (size_t)packed.numel() == ocnn_conv_packed_weight_bytes(xa.C + xb.C, num_output, ks, 1),
+              "packed weights do not match this convolution's shape");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32 && status.numel() >= 1,
+              "status must be an int32 CUDA tensor");
+  Tensor y = new_data(num_output, xa.H, xa);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, residual, relu, num_output, y);
+  OCNN_CALL(ocnn_octree_conv_tc_pair(xa.t.data_ptr(), xa.C, xb.t.data_ptr(), xb.C, packed.data_ptr(),
+                                     y.data_ptr(), xa.H, num_output, xa.dtype, &ep,
+                                     status.data_ptr<int32_t>(), current_stream()));
+  return y;
+}
+
 // ---- keys, search, interpolation, alignment (pytorch/cpp/octree_key.cpp, octree_align.cpp) ------------
 // The reference's binding is compiled with 64-bit keys only (pytorch/cpp/octree_key.cpp:1-3), so
 // key tensors are int64; a 32-bit-key octree is rejected here with a message.
@@ -1534,6 +1565,7 @@ struct ExecOp {
   std::string name;
   int depth = 0, cin = 0, cout = 0, stride = 1, relu = 0;
   int in = -1, out = -1, res = -1;
+  int in2 = -1, cin2 = 0;         // second input of a two-input 1x1x1 layer (cin = the first one's)
   int64_t pointwise_above = -1;   // >= 0: prefer the streaming pointwise kernel from this many nodes
   std::vector<int> ks;
   Tensor weights, packed, scale, bias;     // kept alive here
@@ -1560,6 +1592,20 @@ class NetExecutor {
     TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32, "weights: float32 CUDA");
     op.weights = weights.contiguous();
     if (op.kind == ExecOp::kConvTc) op.packed = *packed;
+    if (scale.has_value() && scale->defined()) op.scale = scale->contiguous();
+    if (bias.has_value() && bias->defined()) op.bias = bias->contiguous();
+    return push(op);
+  }
+  // conv1x1b(in) + conv1x1c(in2) of a residual block as one layer over [in | in2]
+  int add_conv_pair(string name, int depth, int cin_a, int cin_b, int cout, Tensor packed,
+                    c10::optional<Tensor> scale, c10::optional<Tensor> bias, bool relu, int in_a,
+                    int in_b, int out) {
+    ExecOp op;
+    op.kind = ExecOp::kConvTc;
+    op.name = name; op.depth = depth; op.cin = cin_a; op.cin2 = cin_b; op.cout = cout;
+    op.ks = {1, 1, 1}; op.relu = relu ? 1 : 0; op.in = in_a; op.in2 = in_b; op.out = out;
+    TORCH_CHECK(packed.defined() && packed.is_cuda(), "add_conv_pair: packed weights required");
+    op.packed = packed;
     if (scale.has_value() && scale->defined()) op.scale = scale->contiguous();
     if (bias.has_value() && bias->defined()) op.bias = bias->contiguous();
     return push(op);
@@ -1635,7 +1681,13 @@ class NetExecutor {
           const bool identity = op.ks[0] * op.ks[1] * op.ks[2] == 1;
           const int32_t* neigh = identity ? nullptr : level_ptr(o, OCNN_PROP_NEIGH, op.depth, "conv");
           const bool stream_pw = identity && op.pointwise_above >= 0 && h >= op.pointwise_above;
-          if (op.kind == ExecOp::kConvTc && !stream_pw) {
+          if (op.in2 >= 0) {
+            TORCH_CHECK(op.in2 != op.out && rows[op.in2] == h && chans[op.in2] == op.cin2,
+                        "NetExecutor: ", op.name, " second input slot does not match");
+            OCNN_CALL(ocnn_octree_conv_tc_pair(slot(op.in), op.cin, slot(op.in2), op.cin2,
+                                               op.packed.data_ptr(), slot(op.out), h, op.cout,
+                                               OCNN_BF16, &ep, status_.data_ptr<int32_t>(), st));
+          } else if (op.kind == ExecOp::kConvTc && !stream_pw) {
             OCNN_CALL(ocnn_octree_conv_tc(slot(op.in), op.packed.data_ptr(), slot(op.out), neigh, h, h,
                                           op.cin, op.cout, op.ks.data(), 1, &ep,
                                           status_.data_ptr<int32_t>(), st));
@@ -1848,6 +1900,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pointwise_conv_tc", &pointwise_conv_tc, py::arg("data_in"), py::arg("packed"),
         py::arg("num_output"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("relu") = false, py::arg("status"));
+  m.def("pointwise_conv_tc_pair", &pointwise_conv_tc_pair, py::arg("data_a"), py::arg("data_b"),
+        py::arg("packed"), py::arg("num_output"), py::arg("scale") = py::none(),
+        py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("relu") = false,
+        py::arg("status"));
   m.def("octree_encode_key", &octree_encode_key, "encode xyz-id to octree key");
   m.def("octree_decode_key", &octree_decode_key, "decode octree key to xyz-id");
   m.def("octree_xyz2key", &octree_xyz2key, "convert key from xyz order");
@@ -1879,6 +1935,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("packed") = py::none(), py::arg("scale") = py::none(),
            py::arg("bias") = py::none(), py::arg("relu") = false, py::arg("input") = 0,
            py::arg("output") = 0, py::arg("residual") = -1, py::arg("pointwise_above") = -1)
+      .def("add_conv_pair", &NetExecutor::add_conv_pair)
       .def("add_pool", &NetExecutor::add_pool)
       .def("set_trace", &NetExecutor::set_trace)
       .def("forward", &NetExecutor::forward, py::call_guard<py::gil_scoped_release>())

@@ -242,6 +242,50 @@ def test_pointwise_tensor_core_any_height(ocnn, shape, half):
   assert gu.rel_err(gu.to_np(got), want) < (3e-3 if half else 8e-3)
 
 
+@pytest.mark.parametrize('half', [False, True], ids=['bf16', 'fp16'])
+@pytest.mark.parametrize('shape', [(1001, 16, 32, 64), (50003, 32, 64, 128), (4099, 64, 128, 256),
+                                   (2048, 128, 256, 512), (37, 8, 40, 24), (260000, 16, 32, 64),
+                                   (130001, 64, 128, 256)])
+def test_pointwise_pair_is_the_sum_of_two_layers(ocnn, shape, half):
+  """conv1x1b(y) + conv1x1c(x) of a residual block as one layer over the concatenated channels
+  (pytorch/ocnn/modules.py OctreeResBlock.forward computes the two and adds them)."""
+  H, ca, cb, cout = shape
+  rng = np.random.default_rng(H + ca)
+  rnd = gu.half_round if half else gu.bf16_round
+  xa = rnd(rng.uniform(-1, 1, size=(ca, H)).astype(np.float32))
+  xb = rnd(rng.uniform(-1, 1, size=(cb, H)).astype(np.float32))
+  wa = rng.normal(scale=0.2, size=(cout, ca)).astype(np.float32)
+  wb = rng.normal(scale=0.2, size=(cout, cb)).astype(np.float32)
+  bias = rng.normal(size=cout).astype(np.float32)
+  want = np.maximum(rnd(wa) @ xa + rnd(wb) @ xb + bias[:, None], 0)
+  w = np.ascontiguousarray(np.concatenate([wa, wb], axis=1))
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  packed = ocnn.nn.conv_pack_weights_general(torch.from_numpy(w).cuda(), ca + cb, cout, [1, 1, 1], 1,
+                                             False, False, half)
+  got = ocnn.nn.pointwise_conv_tc_pair(gu.data_cuda(xa, True, not half, half),
+                                       gu.data_cuda(xb, True, not half, half), packed, cout, None,
+                                       torch.from_numpy(bias).cuda(), None, True, status)
+  torch.cuda.synchronize()
+  assert int(status.item()) == 0
+  assert got.shape == (1, cout, H, 1)
+  assert gu.rel_err(gu.to_np(got), want) < (3e-3 if half else 8e-3)
+
+
+def test_pointwise_pair_rejects_what_it_cannot_run(ocnn):
+  status = torch.zeros(1, dtype=torch.int32, device='cuda')
+  xa = gu.data_cuda(np.zeros((8, 64), np.float32), True, True)
+  xb = gu.data_cuda(np.zeros((8, 64), np.float32), True, True)
+  w = torch.zeros(16, 16, device='cuda')
+  packed = ocnn.nn.conv_pack_weights(w, 16, 16, [1, 1, 1])
+  with pytest.raises(RuntimeError, match='two inputs only'):      # 8 + 8 channels: a folded layer
+    ocnn.nn.pointwise_conv_tc_pair(xa, xb, packed, 16, None, None, None, False, status)
+  xc = gu.data_cuda(np.zeros((40, 63), np.float32), True, True)
+  w = torch.zeros(16, 48, device='cuda')
+  packed = ocnn.nn.conv_pack_weights(w, 48, 16, [1, 1, 1])
+  with pytest.raises(RuntimeError, match='rows'):
+    ocnn.nn.pointwise_conv_tc_pair(xa, xc, packed, 16, None, None, None, False, status)
+
+
 def test_bounded_wait_runs_out_and_reports(ocnn, batch):
   """A wait that nothing completes ends by itself: the waiter writes its code to the status word
   and raises the abort flag, a second waiter is told to stop, the kernel returns, and the next
