@@ -749,6 +749,13 @@ __global__ void __launch_bounds__(kThreads, 3) conv_tc_kernel(const TcArgs a) {
 // epilogue (TMEM lane quarter = warp & 3).  The {A, B} ring and its phase bits run on across
 // tiles; tfull[b] / tempty[b] hand accumulator set b between the MMA thread and the epilogue.
 // Same packed weights and the same whole-row gather mapping as conv_tc_kernel's rowsplit 2.
+//
+// The sibling-group layers with 8 or 16 channels run here too on levels of many tiles (R = 1: a
+// tile is 128 groups): the one-tile kernel's CTA spends most of its life in set-up, the latency of
+// its first gathers and weight tiles and its 64- to 256-column epilogue, none of which overlaps
+// anything of its own.  Their gather is conv_tc_kernel's rowsplit 1 (lane = row within four,
+// chunk; indices straight from the groups' neighbour blocks), the indices of four K-blocks read
+// ahead of the copies, across tile boundaries.
 template <int R>
 __device__ __forceinline__ void gather_bar() {
   asm volatile("bar.sync 1, %0;" ::"n"(128 * R) : "memory");
@@ -766,7 +773,7 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
   uint8_t* sA = smem;                            // stage s: R sub-tiles of 128 rows back to back
   uint8_t* sB = sA + a.stages * (R * kStageA);
   int* nbr = reinterpret_cast<int*>(sB + a.stages * stage_b);      // [taps][kRows]
-  float* s_scale = reinterpret_cast<float*>(nbr + a.T * kRows);
+  float* s_scale = reinterpret_cast<float*>(nbr + (a.group ? 0 : a.T * kRows));   // group mode: no table
   float* s_bias = s_scale + a.npad;
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + a.npad);
   uint64_t* full = bars;
@@ -808,7 +815,7 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
   grid_dependency_wait();
   for (int n = tid; n < a.npad; n += kThreadsP) {
     const bool live = n < a.row_elems;
-    const int co = a.fold_cout ? n % a.fold_cout : co_base + n;
+    const int co = a.group ? (n & (a.cout - 1)) : (a.fold_cout ? n % a.fold_cout : co_base + n);
     s_scale[n] = (live && a.scale) ? a.scale[co] : 1.f;
     s_bias[n] = (live && a.bias) ? a.bias[co] : 0.f;
   }
@@ -831,6 +838,78 @@ __global__ void __launch_bounds__(32 * (4 * R + 6), 1) conv_tc_persist_kernel(co
     // table slot of row tid: the eight rows of one gather thread sit side by side
     const int slot = (tid & ~31) + ((tid & 3) << 3) + ((tid >> 2) & 7);
     const int* my_idx = nbr + warp * 32 + sub * 8;
+    if (a.group) {
+      // Sibling-group mode with 8 or 16 channels: chunk `chunk` of K-block kb of tile row g is (a
+      // piece of) the row of the node at one position of group g's 4x4x4 neighbour block.  The
+      // indices come straight from the block in global memory, one K-block ahead of the copies,
+      // across tile boundaries too: the (tile, K-block) sequence of a CTA is one continuous stream.
+      const int cpt = a.cin >> 3;
+      // The neighbour blocks stream from HBM, so an index read takes longer than a K-block's
+      // copies: the indices are read four K-blocks at a time, one such batch ahead of the copies
+      // (the host only sends layers here whose K-block count is a multiple of four).
+      constexpr int kAhead = 4;
+      auto fetch = [&](int tile, int kb0, int (&p)[kAhead][8], uint32_t (&off)[kAhead]) {
+#pragma unroll
+        for (int j = 0; j < kAhead; ++j) {
+          int t;
+          chunk_src<CPT>(cpt, kb0 + j, chunk, t, off[j]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int g = tile * kRows + rbase + 4 * i;
+            p[j][i] = -1;
+            if (t < a.T && g < a.rows) p[j][i] = __ldg(a.neigh + ((long long)g << 6) + t);
+          }
+        }
+      };
+      int tile = blockIdx.x, kb0 = 0;
+      int p_cur[kAhead][8];
+      uint32_t off_cur[kAhead];
+      if (tile < ntiles) fetch(tile, 0, p_cur, off_cur);
+      while (tile < ntiles) {
+        int tile_nxt = tile, kb_nxt = kb0 + kAhead;
+        if (kb_nxt >= a.nkb) { kb_nxt = 0; tile_nxt += gridDim.x; }
+        int p_nxt[kAhead][8];
+        uint32_t off_nxt[kAhead];
+#pragma unroll
+        for (int j = 0; j < kAhead; ++j) {
+          off_nxt[j] = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) p_nxt[j][i] = -1;
+        }
+        if (tile_nxt < ntiles) fetch(tile_nxt, kb_nxt, p_nxt, off_nxt);
+#pragma unroll
+        for (int j = 0; j < kAhead; ++j) {
+          if (alive && gk >= a.stages)
+            alive = mbar_wait(smem_u32(&empty[s]), pe, abort_flag, a.status, kErrEmptyWait);
+          if (alive) {
+            const uint32_t stage_base = smem_u32(sA + s * (R * kStageA));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = rbase + 4 * i;
+              const uint32_t dst = stage_base + (uint32_t)row * 128u +
+                                   (((uint32_t)chunk ^ (uint32_t)(row & 7)) << 4);
+              const int pi = p_cur[j][i];
+              const char* src = pi >= 0 ? xb + (size_t)((uint32_t)pi * row_bytes) + off_cur[j] : xb;
+              // rows past the level's last group are left as they are: their accumulator lanes
+              // are never read
+              if (tile * kRows + row < a.rows) cp_async16(dst, src, pi >= 0 ? 16u : 0u);
+            }
+          }
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s]))
+                       : "memory");
+          if (++s == a.stages) { s = 0; pe ^= 1u; }
+          ++gk;
+        }
+#pragma unroll
+        for (int j = 0; j < kAhead; ++j) {
+          off_cur[j] = off_nxt[j];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) p_cur[j][i] = p_nxt[j][i];
+        }
+        tile = tile_nxt;
+        kb0 = kb_nxt;
+      }
+    } else
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const int h0 = tile * kRows;
       // 1x1x1: a tile row reads its own row, no table and no barriers
@@ -1395,6 +1474,15 @@ int persist_mode() {
   return mode;
 }
 
+// 0: few-channel sibling-group layers always on the one-tile kernel; 1: persistent on big levels.
+int persist_group_mode() {
+  static const int mode = [] {
+    const char* e = getenv("OCNN_CONV_PERSIST_GROUP");
+    return e ? atoi(e) : (persist_mode() != 0 ? 1 : 0);
+  }();
+  return mode;
+}
+
 // Launch shape of the persistent kernel: 128-row tiles per weight tile, ring depth, accumulator
 // sets in TMEM, dynamic shared memory.  stages == 0: it does not fit.
 struct PersistShape {
@@ -1407,7 +1495,7 @@ PersistShape persist_shape(const TcShape& s, int R) {
   p.R = R;
   p.acc_bufs = 2 * R * s.tmem_cols <= 512 ? 2 : 1;
   const size_t budget = 226 * 1024;           // one CTA per SM
-  const size_t fixed = 1024 + (size_t)s.T * 128 * R * 4 + (size_t)s.npad * 8 + 256;
+  const size_t fixed = 1024 + (s.group ? 0 : (size_t)s.T * 128 * R * 4) + (size_t)s.npad * 8 + 256;
   const size_t stage = (size_t)R * kStageA + (size_t)s.npad * 128;
   int st = budget > fixed ? (int)((budget - fixed) / stage) : 0;
   if (st > 8) st = 8;
@@ -1588,6 +1676,10 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
       {conv_tc_persist_kernel<0, true, 2>, conv_tc_persist_kernel<8, true, 2>,
        conv_tc_persist_kernel<16, true, 2>, conv_tc_persist_kernel<32, true, 2>,
        conv_tc_persist_kernel<64, true, 2>}};
+  // ... and for the few-channel sibling-group layers of big levels (one 128-row tile at a time)
+  static const PersistFn persist_group[2][2] = {
+      {conv_tc_persist_kernel<1, false, 1>, conv_tc_persist_kernel<2, false, 1>},
+      {conv_tc_persist_kernel<1, true, 1>, conv_tc_persist_kernel<2, true, 1>}};
   int slot = 0;
   switch (a.cin >> 3) {
     case 1: slot = 1; break;
@@ -1615,6 +1707,9 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
                                             227 * 1024));
         OCNN_CUDA_OK(cudaFuncSetAttribute(general[h], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           220 * 1024));
+        for (int k = 0; k < 2; ++k)
+          OCNN_CUDA_OK(cudaFuncSetAttribute(persist_group[h][k],
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
       }
       if (known) attr_once.done[device] = true;
     }
@@ -1642,6 +1737,26 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
       const int pslot = (slot >= 4 && x2 == nullptr) ? slot - 3 : 0;      // Cin = 64, 128, 256, 512 -> 1..4
       OCNN_CUDA_OK(launch_chained(persist[a.f16][pslot], dim3(ctas, s.slices), dim3(32 * (4 * ps.R + 6)),
                                   ps.smem, static_cast<cudaStream_t>(stream), a, big_tiles, ps.acc_bufs));
+      OCNN_LAUNCH_OK("conv_tc_persist_kernel");
+      return OCNN_OK;
+    }
+  }
+  // Sibling-group layers with 8 or 16 channels on a level of many tiles: a one-tile CTA spends
+  // most of its life in set-up, the latency of its first gathers and weight tiles, and its
+  // epilogue (an empty skeleton of the one-tile kernel -- no gathers, MMAs, weight bytes or stores
+  // -- runs 8 -> 8 at 972 k nodes in 0.026 ms of the full kernel's 0.044).  The persistent kernel
+  // pays these once per CTA and keeps gathers, MMAs and the epilogue of different tiles in flight
+  // together.
+  if (!needs_general && s.group && a.rowsplit == 1 && x2 == nullptr && persist_group_mode() != 0) {
+    const PersistShape ps = persist_shape(s, 1);
+    const int sms = sm_count();
+    const int tiles = ceil_div(a.rows, kTileM);
+    if (ps.stages > 0 && tiles >= 3 * sms && s.nkb % 4 == 0) {
+      a.stages = ps.stages;
+      const int waves = ceil_div(tiles, sms);
+      const int ctas = ceil_div(tiles, waves);
+      OCNN_CUDA_OK(launch_chained(persist_group[a.f16][a.cin == 8 ? 0 : 1], dim3(ctas, 1), dim3(32 * 10),
+                                  ps.smem, static_cast<cudaStream_t>(stream), a, tiles, ps.acc_bufs));
       OCNN_LAUNCH_OK("conv_tc_persist_kernel");
       return OCNN_OK;
     }

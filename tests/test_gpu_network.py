@@ -248,6 +248,11 @@ PERSISTENT_CASES = [
     (5, 64, 256, [3, 3, 3], 2, False, True),     # stride 2 (output on depth 5), fp16
     (6, 128, 256, [1, 1, 1], 1, False, False),   # 1x1: the identity table
     (5, 128, 512, [3, 3, 3], 1, False, True),    # two slices of 256 columns, fp16
+    # sibling-group layers with 8 / 16 channels: tile rows are groups, indices from the neighbour blocks
+    (6, 8, 32, [3, 3, 3], 1, False, False),
+    (6, 8, 8, [3, 3, 3], 1, False, True),
+    (6, 16, 16, [3, 3, 3], 1, False, False),
+    (6, 16, 32, [3, 1, 3], 1, False, False),     # 9 taps
 ]
 
 
