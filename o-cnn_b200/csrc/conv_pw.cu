@@ -219,11 +219,11 @@ int launch_pw(const PwArgs& a, cudaStream_t st) {
 // With 8..64 channels the CUDA-core kernel above is bound by instruction issue (Cin*Cout FMAs and
 // Cin*Cout/4 shared-memory reads per node), not by memory.  Here a warp owns 16 consecutive node
 // rows at a time and multiplies them with mma.sync (m16n8k16, or m16n8k8 for 8 input channels;
-// bf16 or fp16 operands, fp32 accumulation): the A fragments are 4-byte loads straight from the
-// node-major rows (consecutive rows are consecutive memory), the weights live in registers for the
-// whole launch as a (hi, lo) pair of 16-bit values per element, so the product is that of the fp32
-// weights to about 2^-17, and the output (and shortcut) are accessed as 16-bit pairs in the
-// accumulator's own layout.  What is left per node is the memory traffic.
+// bf16 or fp16 operands, fp32 accumulation): the A fragments come straight from the node-major
+// rows (consecutive rows are consecutive memory), the weights live in registers for the whole
+// launch as a (hi, lo) pair of 16-bit values per element, so the product is that of the fp32
+// weights to about 2^-17, and output and shortcut are accessed from the accumulator fragments.
+// What is left per node is the memory traffic.
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                           bool half) {
   if (half)
@@ -255,15 +255,52 @@ __device__ __forceinline__ void split2(float w0, float w1, bool half, uint32_t& 
   lo = pack2(w0 - h.x, w1 - h.y, half);
 }
 
+// W consecutive 32-bit words, as the widest accesses their count allows (W = 1, 2, 4, 8)
+template <int W>
+__device__ __forceinline__ void load_words(const uint32_t* p, uint32_t (&v)[W]) {
+  if constexpr (W == 1) {
+    v[0] = *p;
+  } else if constexpr (W == 2) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = t.x; v[1] = t.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; i += 4) {
+      const uint4 t = *reinterpret_cast<const uint4*>(p + i);
+      v[i] = t.x; v[i + 1] = t.y; v[i + 2] = t.z; v[i + 3] = t.w;
+    }
+  }
+}
+template <int W>
+__device__ __forceinline__ void store_words(uint32_t* p, const uint32_t (&v)[W]) {
+  if constexpr (W == 1) {
+    *p = v[0];
+  } else if constexpr (W == 2) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(v[0], v[1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; i += 4)
+      *reinterpret_cast<uint4*>(p + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  }
+}
+
+// Which channel an MMA operand element stands for is free as long as A and B agree on k and B and
+// D agree on n.  Here lane q of a quad owns a CONTIGUOUS quarter of the node's input row and of
+// its output row: logical k = 2q + {0, 1} (+ 8) of slice s is input channel q*CIN/4 + 4s + {0, 1}
+// (+ 2), logical column 2q + e of accumulator tile j is output channel q*COUT/4 + 2j + e.  A
+// lane then reads its CIN/4 input channels and writes its COUT/4 output channels (and reads the
+// shortcut's) of a row as one vector each, and a warp instruction covers 8 whole consecutive rows.
 template <int CIN, int COUT, bool HALF>
 __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   constexpr int KS = CIN >= 16 ? CIN / 16 : 1;     // 16-wide (8-wide for CIN = 8) K slices
   constexpr int NT = COUT / 8;                      // 8-column accumulator tiles
   constexpr int BR = CIN >= 16 ? 2 : 1;             // B registers per (slice, tile)
+  constexpr int KQ = CIN / 4, CQ = COUT / 4;        // channels per lane of a row: input, output
+  constexpr int XW = KQ / 2, YW = CQ / 2;           // ... in 32-bit words (YW == NT)
   grid_dependency_trigger();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  // weights: B[k = ci][n = co] = w[co][ci]; this lane's elements of every (slice, tile)
+  // weights: this lane's elements of every (slice, tile): column g of tile j, rows 2q + {0, 1} (+ 8)
   uint32_t bh[KS][NT][BR], bl[KS][NT][BR];
 #pragma unroll
   for (int s = 0; s < KS; ++s)
@@ -271,7 +308,9 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
     for (int j = 0; j < NT; ++j)
 #pragma unroll
       for (int r = 0; r < BR; ++r) {
-        const float* wp = a.w + (long long)(8 * j + g) * CIN + 16 * s + 8 * r + 2 * q;
+        const int co = (g >> 1) * CQ + 2 * j + (g & 1);
+        const int ci = q * KQ + (CIN >= 16 ? 4 * s + 2 * r : 0);
+        const float* wp = a.w + (long long)co * CIN + ci;
         split2(wp[0], wp[1], HALF, bh[s][j][r], bl[s][j][r]);
       }
   float sc[NT][2], bi[NT][2];
@@ -279,65 +318,60 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      sc[j][e] = a.scale ? a.scale[8 * j + 2 * q + e] : 1.f;
-      bi[j][e] = a.bias ? a.bias[8 * j + 2 * q + e] : 0.f;
+      sc[j][e] = a.scale ? a.scale[q * CQ + 2 * j + e] : 1.f;
+      bi[j][e] = a.bias ? a.bias[q * CQ + 2 * j + e] : 0.f;
     }
   const long long tiles = ((long long)a.h + 15) >> 4;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  const uint32_t* x32 = reinterpret_cast<const uint32_t*>(a.x);
-  const uint32_t* r32 = reinterpret_cast<const uint32_t*>(a.residual);
-  uint32_t* y32 = reinterpret_cast<uint32_t*>(a.y);
-  constexpr int XW = CIN / 2, YW = COUT / 2;        // 32-bit words per row
+  const uint32_t* x32 = reinterpret_cast<const uint32_t*>(a.x) + q * XW;
+  const uint32_t* r32 = a.residual ? reinterpret_cast<const uint32_t*>(a.residual) + q * YW : nullptr;
+  uint32_t* y32 = reinterpret_cast<uint32_t*>(a.y) + q * YW;
   for (long long tile = warp0; tile < tiles; tile += nwarps) {
     const long long r0 = (tile << 4) + g, r1 = r0 + 8;
     const bool ok0 = r0 < a.h, ok1 = r1 < a.h;
-    // A fragments of every slice (all loads before the first MMA)
-    uint32_t af[KS][4];
+    // this lane's quarter of rows r0 and r1 (all loads before the first MMA)
+    uint32_t xa[XW], xb[XW];
 #pragma unroll
-    for (int s = 0; s < KS; ++s) {
-      af[s][0] = ok0 ? x32[r0 * XW + 8 * s + q] : 0u;
-      af[s][1] = ok1 ? x32[r1 * XW + 8 * s + q] : 0u;
-      if (CIN >= 16) {
-        af[s][2] = ok0 ? x32[r0 * XW + 8 * s + 4 + q] : 0u;
-        af[s][3] = ok1 ? x32[r1 * XW + 8 * s + 4 + q] : 0u;
-      } else {
-        af[s][2] = af[s][3] = 0u;
-      }
-    }
-    uint32_t rw[NT][2];
+    for (int i = 0; i < XW; ++i) xa[i] = xb[i] = 0u;
+    if (ok0) load_words<XW>(x32 + r0 * (CIN / 2), xa);
+    if (ok1) load_words<XW>(x32 + r1 * (CIN / 2), xb);
+    uint32_t ra[YW], rb[YW];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      rw[j][0] = (r32 && ok0) ? r32[r0 * YW + 4 * j + q] : 0u;
-      rw[j][1] = (r32 && ok1) ? r32[r1 * YW + 4 * j + q] : 0u;
-    }
+    for (int i = 0; i < YW; ++i) ra[i] = rb[i] = 0u;
+    if (r32 && ok0) load_words<YW>(r32 + r0 * (COUT / 2), ra);
+    if (r32 && ok1) load_words<YW>(r32 + r1 * (COUT / 2), rb);
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 #pragma unroll
       for (int s = 0; s < KS; ++s) {
-        if (CIN >= 16) {
-          mma_16816(acc[j], af[s], bl[s][j][0], bl[s][j][BR - 1], HALF);
-          mma_16816(acc[j], af[s], bh[s][j][0], bh[s][j][BR - 1], HALF);
+        if constexpr (CIN >= 16) {
+          const uint32_t af[4] = {xa[2 * s], xb[2 * s], xa[2 * s + 1], xb[2 * s + 1]};
+          mma_16816(acc[j], af, bl[s][j][0], bl[s][j][BR - 1], HALF);
+          mma_16816(acc[j], af, bh[s][j][0], bh[s][j][BR - 1], HALF);
         } else {
-          mma_1688(acc[j], af[s][0], af[s][1], bl[s][j][0], HALF);
-          mma_1688(acc[j], af[s][0], af[s][1], bh[s][j][0], HALF);
+          mma_1688(acc[j], xa[0], xb[0], bl[s][j][0], HALF);
+          mma_1688(acc[j], xa[0], xb[0], bh[s][j][0], HALF);
         }
       }
     }
+    uint32_t oa[YW], ob[YW];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       float v0 = fmaf(acc[j][0], sc[j][0], bi[j][0]), v1 = fmaf(acc[j][1], sc[j][1], bi[j][1]);
       float v2 = fmaf(acc[j][2], sc[j][0], bi[j][0]), v3 = fmaf(acc[j][3], sc[j][1], bi[j][1]);
       if (r32) {
-        const float2 ra = unpack2(rw[j][0], HALF), rb = unpack2(rw[j][1], HALF);
-        v0 += ra.x; v1 += ra.y; v2 += rb.x; v3 += rb.y;
+        const float2 fa = unpack2(ra[j], HALF), fb = unpack2(rb[j], HALF);
+        v0 += fa.x; v1 += fa.y; v2 += fb.x; v3 += fb.y;
       }
       if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
-      if (ok0) y32[r0 * YW + 4 * j + q] = pack2(v0, v1, HALF);
-      if (ok1) y32[r1 * YW + 4 * j + q] = pack2(v2, v3, HALF);
+      oa[j] = pack2(v0, v1, HALF);
+      ob[j] = pack2(v2, v3, HALF);
     }
+    if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
+    if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
   }
 }
 
