@@ -297,10 +297,18 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   constexpr int BR = CIN >= 16 ? 2 : 1;             // B registers per (slice, tile)
   constexpr int KQ = CIN / 4, CQ = COUT / 4;        // channels per lane of a row: input, output
   constexpr int XW = KQ / 2, YW = CQ / 2;           // ... in 32-bit words (YW == NT)
+  constexpr int PAIRS = COUT * CIN / 2;             // weight pairs (w[co][2p], w[co][2p + 1])
+  // the (hi, lo) split of the layer's weights, made once per CTA
+  __shared__ uint32_t s_hi[PAIRS], s_lo[PAIRS];
   grid_dependency_trigger();
   grid_dependency_wait();
+  for (int p = threadIdx.x; p < PAIRS; p += blockDim.x) {
+    const float2 w2 = *reinterpret_cast<const float2*>(a.w + 2 * p);
+    split2(w2.x, w2.y, HALF, s_hi[p], s_lo[p]);
+  }
+  __syncthreads();
   const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  // weights: this lane's elements of every (slice, tile): column g of tile j, rows 2q + {0, 1} (+ 8)
+  // this lane's elements of every (slice, tile): column g of tile j, rows 2q + {0, 1} (+ 8)
   uint32_t bh[KS][NT][BR], bl[KS][NT][BR];
 #pragma unroll
   for (int s = 0; s < KS; ++s)
@@ -310,8 +318,9 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
       for (int r = 0; r < BR; ++r) {
         const int co = (g >> 1) * CQ + 2 * j + (g & 1);
         const int ci = q * KQ + (CIN >= 16 ? 4 * s + 2 * r : 0);
-        const float* wp = a.w + (long long)co * CIN + ci;
-        split2(wp[0], wp[1], HALF, bh[s][j][r], bl[s][j][r]);
+        const int p = (co * CIN + ci) >> 1;
+        bh[s][j][r] = s_hi[p];
+        bl[s][j][r] = s_lo[p];
       }
   float sc[NT][2], bi[NT][2];
 #pragma unroll
@@ -327,20 +336,28 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   const uint32_t* x32 = reinterpret_cast<const uint32_t*>(a.x) + q * XW;
   const uint32_t* r32 = a.residual ? reinterpret_cast<const uint32_t*>(a.residual) + q * YW : nullptr;
   uint32_t* y32 = reinterpret_cast<uint32_t*>(a.y) + q * YW;
+  // this lane's quarter of rows 16*tile + g and + 8, and of the shortcut's: the next tile's are
+  // requested before the current one is multiplied
+  uint32_t xa[XW], xb[XW], ra[YW], rb[YW];
+  auto load_tile = [&](long long tile, uint32_t (&pa)[XW], uint32_t (&pb)[XW], uint32_t (&qa)[YW],
+                       uint32_t (&qb)[YW]) {
+    const long long r0 = (tile << 4) + g, r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < XW; ++i) pa[i] = pb[i] = 0u;
+#pragma unroll
+    for (int i = 0; i < YW; ++i) qa[i] = qb[i] = 0u;
+    if (tile >= tiles) return;
+    if (r0 < a.h) load_words<XW>(x32 + r0 * (CIN / 2), pa);
+    if (r1 < a.h) load_words<XW>(x32 + r1 * (CIN / 2), pb);
+    if (r32 && r0 < a.h) load_words<YW>(r32 + r0 * (COUT / 2), qa);
+    if (r32 && r1 < a.h) load_words<YW>(r32 + r1 * (COUT / 2), qb);
+  };
+  load_tile(warp0, xa, xb, ra, rb);
   for (long long tile = warp0; tile < tiles; tile += nwarps) {
     const long long r0 = (tile << 4) + g, r1 = r0 + 8;
     const bool ok0 = r0 < a.h, ok1 = r1 < a.h;
-    // this lane's quarter of rows r0 and r1 (all loads before the first MMA)
-    uint32_t xa[XW], xb[XW];
-#pragma unroll
-    for (int i = 0; i < XW; ++i) xa[i] = xb[i] = 0u;
-    if (ok0) load_words<XW>(x32 + r0 * (CIN / 2), xa);
-    if (ok1) load_words<XW>(x32 + r1 * (CIN / 2), xb);
-    uint32_t ra[YW], rb[YW];
-#pragma unroll
-    for (int i = 0; i < YW; ++i) ra[i] = rb[i] = 0u;
-    if (r32 && ok0) load_words<YW>(r32 + r0 * (COUT / 2), ra);
-    if (r32 && ok1) load_words<YW>(r32 + r1 * (COUT / 2), rb);
+    uint32_t nxa[XW], nxb[XW], nra[YW], nrb[YW];
+    load_tile(tile + nwarps, nxa, nxb, nra, nrb);
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -372,13 +389,21 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
     }
     if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
     if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
+#pragma unroll
+    for (int i = 0; i < XW; ++i) { xa[i] = nxa[i]; xb[i] = nxb[i]; }
+#pragma unroll
+    for (int i = 0; i < YW; ++i) { ra[i] = nra[i]; rb[i] = nrb[i]; }
   }
 }
 
 template <int CIN, int COUT>
 int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
   const long long warps = ((long long)a.h + 15) / 16;
-  const int grid = grid_for(warps * 32, 256, 8);
+  // about six 16-row tiles per warp (a warp's set-up -- its weight fragments, scale and bias -- is
+  // then a small part of its life), up to eight CTAs per SM
+  const long long want = (warps + 47) / 48;
+  const long long cap = (long long)sm_count() * 8;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
   if (a.f16)
     OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, true>, dim3(grid), dim3(256), 0, st, a));
   else
@@ -390,6 +415,7 @@ int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
 // -1: not a shape the mma kernel is built for
 int try_pw_mma(const PwArgs& a, int cout, cudaStream_t st) {
   if (a.y_stride != cout || a.co_base != 0) return -1;
+  if ((uintptr_t)a.w % 8 != 0) return -1;          // the weights are read two at a time
 #define OCNN_PW_CASE(CI, CO) if (a.cin == CI && cout == CO) return launch_pw_mma<CI, CO>(a, st);
   OCNN_PW_CASE(8, 8) OCNN_PW_CASE(8, 16) OCNN_PW_CASE(8, 32) OCNN_PW_CASE(8, 64)
   OCNN_PW_CASE(16, 8) OCNN_PW_CASE(16, 16) OCNN_PW_CASE(16, 32) OCNN_PW_CASE(16, 64)

@@ -356,11 +356,12 @@ class GpuNet:
     # few-channel 1x1 layers stream through the pointwise kernel behind octree_conv; everything
     # else that fits goes to the tensor-core kernel
     cout = p['_cout']
-    # (the streaming mma.sync kernel behind octree_conv wins on big levels while Cin * Cout <= 512:
-    # 8 -> 32 + shortcut 0.030 ms against 0.045, 32 -> 8 0.022 against 0.026 at 972 k nodes; with 64
-    # channels on either side its 4-byte accesses and register count lose to the tensor-core kernel)
-    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32) and cin in (8, 16, 32) and
-                       cin * cout <= 512)
+    # (the streaming mma.sync kernel behind octree_conv wins on big levels while Cin * Cout <= 1024:
+    # 8 -> 32 + shortcut 0.030 ms against 0.045 and 32 -> 8 0.022 against 0.026 at 972 k nodes,
+    # 16 -> 64 + shortcut 0.025 against 0.035 and 64 -> 16 0.019 against 0.021 at 250 k nodes; beyond
+    # that its weight fragments no longer fit the registers beside the accumulators)
+    p['_pointwise'] = (p['ks'] == [1, 1, 1] and cout in (8, 16, 32, 64) and cin in (8, 16, 32, 64) and
+                       cin * cout <= int(os.environ.get('OCNN_PW_PRODUCT_MAX', '1024')))
     if self.tc and cin % 8 == 0 and cout % 8 == 0 and (cout <= 256 or cout % 256 == 0):
       try:
         p['_packed'] = self.ocnn.nn.conv_pack_weights(p['_w'], cin, cout, p['ks'])
