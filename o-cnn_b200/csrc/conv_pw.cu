@@ -396,6 +396,136 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   }
 }
 
+// The two-input layer (a residual block's conv1x1b + shortcut conv1x1c over [xa | xb]) on the same
+// scheme: K slices first over xa's channels, then over xb's, lane q owning a contiguous quarter of
+// each input row.  The weights are the 16-bit values of the tensor-core kernel's packed image
+// (element (k, n) of K-block kb sits at kb*npad*64 + (n>>3)*512 + (n&7)*64 + (((kk>>3)^(n&7))<<3)
+// + (kk&7), kk = k - 64*kb), so both kernels multiply the same numbers.
+struct PwPairArgs {
+  const __nv_bfloat16* xa;
+  const __nv_bfloat16* xb;
+  const uint16_t* packed;
+  __nv_bfloat16* y;
+  int h, npad;
+  const float* scale;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  int relu;
+};
+
+template <int CA, int CB, int COUT, bool HALF>
+__global__ void __launch_bounds__(256) conv_pw_pair_kernel(const PwPairArgs a) {
+  constexpr int KA = CA / 16, KB = CB / 16, KS = KA + KB;
+  constexpr int NT = COUT / 8;
+  constexpr int AQ = CA / 4, BQ = CB / 4, CQ = COUT / 4;      // channels per lane of a row
+  constexpr int AW = AQ / 2, BW = BQ / 2, YW = CQ / 2;        // ... in 32-bit words
+  constexpr int CIN = CA + CB;
+  __shared__ uint32_t s_w[COUT * CIN / 2];                    // [co][k pair], 16-bit values as packed
+  grid_dependency_trigger();
+  grid_dependency_wait();
+  for (int p = threadIdx.x; p < COUT * CIN / 2; p += blockDim.x) {
+    const int n = p / (CIN / 2), k = 2 * (p % (CIN / 2));
+    const int kb = k >> 6, kk = k & 63;
+    const long long off = (long long)kb * a.npad * 64 + (n >> 3) * 512 + (n & 7) * 64 +
+                          (((kk >> 3) ^ (n & 7)) << 3) + (kk & 7);
+    s_w[p] = *reinterpret_cast<const uint32_t*>(a.packed + off);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  uint32_t bw[KS][NT][2];
+#pragma unroll
+  for (int s = 0; s < KS; ++s)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int co = (g >> 1) * CQ + 2 * j + (g & 1);
+        const int ci = s < KA ? q * AQ + 4 * s + 2 * r : CA + q * BQ + 4 * (s - KA) + 2 * r;
+        bw[s][j][r] = s_w[(co * CIN + ci) >> 1];
+      }
+  float sc[NT][2], bi[NT][2];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      sc[j][e] = a.scale ? a.scale[q * CQ + 2 * j + e] : 1.f;
+      bi[j][e] = a.bias ? a.bias[q * CQ + 2 * j + e] : 0.f;
+    }
+  const long long tiles = ((long long)a.h + 15) >> 4;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(a.xa) + q * AW;
+  const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(a.xb) + q * BW;
+  const uint32_t* r32 = a.residual ? reinterpret_cast<const uint32_t*>(a.residual) + q * YW : nullptr;
+  uint32_t* y32 = reinterpret_cast<uint32_t*>(a.y) + q * YW;
+  // rows 16*tile + g (0) and + 8 (1) of both inputs and of the residual
+  uint32_t a0[AW], a1[AW], b0[BW], b1[BW], ra[YW], rb[YW];
+  auto load_tile = [&](long long tile, uint32_t (&pa0)[AW], uint32_t (&pa1)[AW], uint32_t (&pb0)[BW],
+                       uint32_t (&pb1)[BW], uint32_t (&qa)[YW], uint32_t (&qb)[YW]) {
+    const long long r0 = (tile << 4) + g, r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < AW; ++i) pa0[i] = pa1[i] = 0u;
+#pragma unroll
+    for (int i = 0; i < BW; ++i) pb0[i] = pb1[i] = 0u;
+#pragma unroll
+    for (int i = 0; i < YW; ++i) qa[i] = qb[i] = 0u;
+    if (tile >= tiles) return;
+    if (r0 < a.h) {
+      load_words<AW>(xa32 + r0 * (CA / 2), pa0);
+      load_words<BW>(xb32 + r0 * (CB / 2), pb0);
+      if (r32) load_words<YW>(r32 + r0 * (COUT / 2), qa);
+    }
+    if (r1 < a.h) {
+      load_words<AW>(xa32 + r1 * (CA / 2), pa1);
+      load_words<BW>(xb32 + r1 * (CB / 2), pb1);
+      if (r32) load_words<YW>(r32 + r1 * (COUT / 2), qb);
+    }
+  };
+  load_tile(warp0, a0, a1, b0, b1, ra, rb);
+  for (long long tile = warp0; tile < tiles; tile += nwarps) {
+    const long long r0 = (tile << 4) + g, r1 = r0 + 8;
+    uint32_t na0[AW], na1[AW], nb0[BW], nb1[BW], nra[YW], nrb[YW];
+    load_tile(tile + nwarps, na0, na1, nb0, nb1, nra, nrb);
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+#pragma unroll
+      for (int s = 0; s < KS; ++s) {
+        uint32_t af[4];
+        if (s < KA) {
+          af[0] = a0[2 * s]; af[1] = a1[2 * s]; af[2] = a0[2 * s + 1]; af[3] = a1[2 * s + 1];
+        } else {
+          af[0] = b0[2 * (s - KA)]; af[1] = b1[2 * (s - KA)];
+          af[2] = b0[2 * (s - KA) + 1]; af[3] = b1[2 * (s - KA) + 1];
+        }
+        mma_16816(acc[j], af, bw[s][j][0], bw[s][j][1], HALF);
+      }
+    }
+    uint32_t oa[YW], ob[YW];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      float v0 = fmaf(acc[j][0], sc[j][0], bi[j][0]), v1 = fmaf(acc[j][1], sc[j][1], bi[j][1]);
+      float v2 = fmaf(acc[j][2], sc[j][0], bi[j][0]), v3 = fmaf(acc[j][3], sc[j][1], bi[j][1]);
+      if (r32) {
+        const float2 fa = unpack2(ra[j], HALF), fb = unpack2(rb[j], HALF);
+        v0 += fa.x; v1 += fa.y; v2 += fb.x; v3 += fb.y;
+      }
+      if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
+      oa[j] = pack2(v0, v1, HALF);
+      ob[j] = pack2(v2, v3, HALF);
+    }
+    if (r0 < a.h) store_words<YW>(y32 + r0 * (COUT / 2), oa);
+    if (r1 < a.h) store_words<YW>(y32 + r1 * (COUT / 2), ob);
+#pragma unroll
+    for (int i = 0; i < AW; ++i) { a0[i] = na0[i]; a1[i] = na1[i]; }
+#pragma unroll
+    for (int i = 0; i < BW; ++i) { b0[i] = nb0[i]; b1[i] = nb1[i]; }
+#pragma unroll
+    for (int i = 0; i < YW; ++i) { ra[i] = nra[i]; rb[i] = nrb[i]; }
+  }
+}
+
 template <int CIN, int COUT>
 int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
   const long long warps = ((long long)a.h + 15) / 16;
@@ -468,6 +598,38 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
     }
     default: return -1;
   }
+}
+
+// The two-input 1x1x1 layer on the streaming kernel, for the shapes and sizes where it beats the
+// tensor-core kernels (a big level, few channels).  -1: not one of them.
+int conv_pointwise_pair_packed(const void* xa, int ca, const void* xb, int cb, const void* packed,
+                               int npad, void* y, int h, int cout, const ocnn_conv_epilogue* ep,
+                               cudaStream_t st, bool f16) {
+  static const int enabled = [] { const char* e = getenv("OCNN_PW_MMA"); return e ? atoi(e) : 1; }();
+  if (!enabled || h < 100000) return -1;
+  if (!(ca == 16 && cb == 32 && cout == 64)) return -1;
+  if (((uintptr_t)xa % 16) || ((uintptr_t)xb % 16) || ((uintptr_t)y % 16) || ((uintptr_t)packed % 4)) return -1;
+  if (ep && ep->residual_dev && ((uintptr_t)ep->residual_dev % 16) != 0) return -1;
+  PwPairArgs a;
+  a.xa = static_cast<const __nv_bfloat16*>(xa);
+  a.xb = static_cast<const __nv_bfloat16*>(xb);
+  a.packed = static_cast<const uint16_t*>(packed);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.h = h; a.npad = npad;
+  a.scale = ep ? ep->scale_dev : nullptr;
+  a.bias = ep ? ep->bias_dev : nullptr;
+  a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
+  a.relu = ep ? ep->relu : 0;
+  const long long warps = ((long long)h + 15) / 16;
+  const long long want = (warps + 47) / 48;
+  const long long cap = (long long)sm_count() * 8;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+  if (f16)
+    OCNN_CUDA_OK(launch_chained(conv_pw_pair_kernel<16, 32, 64, true>, dim3(grid), dim3(256), 0, st, a));
+  else
+    OCNN_CUDA_OK(launch_chained(conv_pw_pair_kernel<16, 32, 64, false>, dim3(grid), dim3(256), 0, st, a));
+  OCNN_LAUNCH_OK("conv_pw_pair_kernel");
+  return OCNN_OK;
 }
 
 }  // namespace ocnn

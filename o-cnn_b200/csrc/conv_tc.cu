@@ -36,6 +36,10 @@
 #include "common.cuh"
 
 namespace ocnn {
+// conv_pw.cu
+int conv_pointwise_pair_packed(const void* xa, int ca, const void* xb, int cb, const void* packed,
+                               int npad, void* y, int h, int cout, const ocnn_conv_epilogue* ep,
+                               cudaStream_t st, bool f16);
 namespace {
 
 constexpr int kTileM = 128;          // nodes per CTA = TMEM lanes
@@ -1578,6 +1582,13 @@ int conv_tc_impl(const void* x, const void* packed, void* y, const ocnn_conv_geo
   if (scatter) {
     OCNN_REQUIRE(g->child_dev != nullptr, "%s: child array of the finer level required", who);
     OCNN_REQUIRE(!(ep && ep->residual_dev), "%s: no residual on a scattered deconvolution", who);
+  }
+  if (x2 != nullptr && identity && !g->nempty && !g->transposed && s.fold_nodes == 1 && s.slices == 1 &&
+      cin_a > 0 && cin_a < cin) {
+    // few channels on a big level: the streaming kernel, on the same packed weights
+    const int rc = conv_pointwise_pair_packed(x, cin_a, x2, cin - cin_a, packed, s.npad, y, h_out, cout, ep,
+                                              static_cast<cudaStream_t>(stream), dtype == OCNN_F16);
+    if (rc != -1) return rc;
   }
   TcArgs a;
   a.x = static_cast<const __nv_bfloat16*>(x);
