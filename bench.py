@@ -538,9 +538,10 @@ def run_ours(args):
   # released now, which leaves it cached and splittable for everything the steps allocate.
   reserve = torch.empty(6 << 30, dtype=torch.uint8, device=dev)
   del reserve
-  # (as many warm-up steps as timed ones, twice: the allocator's pools and the threads' working sets
-  # reach their steady state before the timed region)
-  for _ in range(2):
+  # (as many warm-up steps as timed ones, four times: the allocator's pools and the threads' working
+  # sets reach their steady state before the timed region; on some boxes the first two or three
+  # regions after the serial phase ran 10-25 % longer than the following ones)
+  for _ in range(4):
     pipelined(max(args.warmup, 3, args.steps), lambda k, st: inputs[k % nbuf])
   # Five timed regions of exactly K steps each, back to back; the median one is reported (all five
   # are listed).  Six host threads feed the GPU here, and a single host-side stall of a few tens of
@@ -701,7 +702,7 @@ def run_ours(args):
 
   cfg = workload_config(world)
   line = {'metric': METRIC, 'value': shapes / (total_ms * 1e-3), 'unit': UNIT, 'n_gpus': world,
-          'steps': args.steps, 'warmup': args.warmup, 'warmup_run': 2 * max(args.warmup, 3, args.steps),
+          'steps': args.steps, 'warmup': args.warmup, 'warmup_run': 4 * max(args.warmup, 3, args.steps),
           'ms_per_step': total_ms / args.steps,
           'timed_regions_ms': [round(v, 4) for v in timed_regions_ms],
           'timed_region_reported': 'the median of five back-to-back regions of `steps` steps each',
