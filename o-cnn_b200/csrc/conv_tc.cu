@@ -1459,7 +1459,11 @@ int tc_shape(int cin, int cout, const int ks[3], const LayerKind& kind, TcShape*
   // a two-stage ring each beat two CTAs with deeper rings: more set-up and epilogue phases overlap
   // the others' main loops (8->8: 0.050 -> 0.042 ms, 64->64: 0.417 -> 0.351 ms at 931 k nodes).
   const size_t three_cta = 74 * 1024;
-  if (!small_grid && st > 2 && fixed + 2 * stage_bytes <= three_cta && 3 * s->tmem_cols <= 512) st = 2;
+  // (a level with at most two tiles per SM never has three CTAs on an SM: it keeps the deeper ring)
+  // (depth-5 3x3x3 16 -> 16 of the benchmark: 0.026 -> 0.024 ms in the step's trace)
+  const bool two_per_sm = rows >= 0 && (rows + s->tile_rows - 1) / s->tile_rows <= 2 * sms;
+  if (!small_grid && !two_per_sm && st > 2 && fixed + 2 * stage_bytes <= three_cta && 3 * s->tmem_cols <= 512)
+    st = 2;
   if (st > s->nkb) st = s->nkb < 2 ? 2 : s->nkb;
   s->stages = st;
   s->smem = fixed + (size_t)s->stages * stage_bytes;
