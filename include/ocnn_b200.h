@@ -508,6 +508,14 @@ int ocnn_points_bbox(const float* xyz_dev, int64_t n, float* out6_dev, void* wor
 int ocnn_feature_to_node_major(const float* feature_dev, void* out_dev, int channels, int c_pad,
                                int nnum, int dtype, void* stream);
 
+/* The classification header of the reference's networks in one launch: FullOctreeGlobalPool (the
+ * mean over the 8^d cells of each shape's full level, pytorch/ocnn/octree_pool.py:106-115) followed
+ * by the Linear layer (pytorch/ocnn/resnet.py:18-21, lenet.py).  x: 16-bit node-major
+ * [batch * per, channels] (a full level: per = 8^d rows per shape, shapes back to back);
+ * w: fp32 [nout, channels]; bias: fp32 [nout] or NULL; out: fp32 [batch, nout]. */
+int ocnn_global_pool_fc(const void* x_dev, const float* w_dev, const float* bias_dev, float* out_dev,
+                        int batch, int per, int channels, int nout, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

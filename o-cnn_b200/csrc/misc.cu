@@ -38,8 +38,64 @@ __global__ void __launch_bounds__(256) feature_to_nm_bf16x8_kernel(const float* 
   }
 }
 
+// Global average pool over each shape's `per` rows followed by a fully connected layer, one CTA per
+// shape: the channel means go to shared memory (threads stride over channels: a warp reads
+// consecutive channels of one row), then one warp per output computes its dot product.
+template <bool HALF>
+__global__ void __launch_bounds__(256) global_pool_fc_kernel(const uint16_t* __restrict__ x,
+                                                             const float* __restrict__ w,
+                                                             const float* __restrict__ bias,
+                                                             float* __restrict__ out, int per, int C,
+                                                             int nout) {
+  extern __shared__ float s_mean[];
+  grid_dependency_wait();
+  const int b = blockIdx.x;
+  const uint16_t* xb = x + (long long)b * per * C;
+  const float inv = 1.f / (float)per;
+  for (int c2 = threadIdx.x; 2 * c2 < C; c2 += blockDim.x) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int i = 0; i < per; ++i) {
+      const float2 v = unpack2(*reinterpret_cast<const uint32_t*>(xb + (long long)i * C + 2 * c2), HALF);
+      s0 += v.x;
+      s1 += v.y;
+    }
+    s_mean[2 * c2] = s0 * inv;
+    s_mean[2 * c2 + 1] = s1 * inv;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int o = warp; o < nout; o += blockDim.x >> 5) {
+    float acc = 0.f;
+    for (int c = lane; c < C; c += 32) acc = fmaf(w[(long long)o * C + c], s_mean[c], acc);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (lane == 0) out[(long long)b * nout + o] = acc + (bias ? bias[o] : 0.f);
+  }
+}
+
 }  // namespace
 }  // namespace ocnn
+
+extern "C" int ocnn_global_pool_fc(const void* x, const float* w, const float* bias, float* out, int batch,
+                                   int per, int channels, int nout, int dtype, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(x && w && out, "ocnn_global_pool_fc: null pointer");
+  OCNN_REQUIRE(dtype == OCNN_BF16 || dtype == OCNN_F16, "ocnn_global_pool_fc: bf16 or fp16 node-major data");
+  OCNN_REQUIRE(batch >= 0 && per > 0 && nout > 0 && channels > 0 && channels % 2 == 0 && channels <= 8192,
+               "ocnn_global_pool_fc: bad shape (batch %d, per %d, C %d, nout %d)", batch, per, channels, nout);
+  OCNN_REQUIRE((uintptr_t)x % 4 == 0, "ocnn_global_pool_fc: data must be 4-byte aligned");
+  if (batch == 0) return OCNN_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)channels * sizeof(float);
+  if (dtype == OCNN_F16)
+    OCNN_CUDA_OK(launch_chained(global_pool_fc_kernel<true>, dim3(batch), dim3(256), smem, st,
+                                static_cast<const uint16_t*>(x), w, bias, out, per, channels, nout));
+  else
+    OCNN_CUDA_OK(launch_chained(global_pool_fc_kernel<false>, dim3(batch), dim3(256), smem, st,
+                                static_cast<const uint16_t*>(x), w, bias, out, per, channels, nout));
+  OCNN_LAUNCH_OK("global_pool_fc_kernel");
+  return OCNN_OK;
+}
 
 extern "C" int ocnn_feature_to_node_major(const float* feature, void* out, int channels, int c_pad,
                                           int nnum, int dtype, void* stream) {

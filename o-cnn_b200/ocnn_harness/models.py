@@ -19,6 +19,8 @@ import numpy as np
 PW_MIN_NODES = int(os.environ.get('OCNN_PW_MIN_NODES', '100000'))
 # a residual block's conv1x1b + shortcut conv1x1c as one two-input layer (0: two launches)
 BLOCK_PAIR = int(os.environ.get('OCNN_BLOCK_PAIR', '1'))
+# global pool + FC of the classification networks as one launch of the executor (0: torch ops)
+HEAD_FUSED = int(os.environ.get('OCNN_HEAD_FUSED', '1'))
 
 BN_EPS = 0.001   # pytorch/ocnn/modules.py:5
 
@@ -315,6 +317,13 @@ class GpuNet:
           self.exec_layers.append('pool%d' % d)
           cur, other = other, cur
       self.exec_out_depth = net['min_depth'] if not net['levels'][-1]['pool'] else net['min_depth'] - 1
+    # global average pool over the (full) output level + the classifier's Linear layer: one launch
+    self.exec_head = False
+    if HEAD_FUSED and self.exec_out_depth <= net.get('full_depth', 2):
+      c_out = net['fc_w'].shape[1]
+      ex.add_head(self.exec_out_depth, c_out, net['fc_w'].shape[0], self.fc_w, self.fc_b, cur, other)
+      self.exec_layers.append('head')
+      self.exec_head = True
     return ex
 
   def _traced(self, name, fn):
@@ -448,6 +457,8 @@ class GpuNet:
     if self.exec is not None:
       with t.no_grad():
         x = self.exec.forward(octree)
+        if self.exec_head:
+          return x                                               # [batch, nout] fp32
         per = 8 ** self.exec_out_depth
         C = x.shape[1]
         pooled = x.permute(0, 2, 1, 3).reshape(-1, per, C).float().mean(dim=1)

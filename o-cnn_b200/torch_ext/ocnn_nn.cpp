@@ -875,6 +875,32 @@ Tensor pointwise_conv_tc_pair(Tensor data_a, Tensor data_b, Tensor packed, int n
   return y;
 }
 
+// FullOctreeGlobalPool + Linear (pytorch/ocnn/octree_pool.py:106-115, resnet.py:18-21) in one
+// launch: data [1, C, batch * per, 1] 16-bit channels_last over a full level -> [batch, nout] fp32.
+Tensor global_pool_fc(Tensor data_in, Tensor weights, c10::optional<Tensor> bias, int batch) {
+  need_cuda(data_in, "global_pool_fc");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "global_pool_fc");
+  TORCH_CHECK(x.dtype != OCNN_F32 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
+              "global_pool_fc takes bfloat16 or float16 channels_last data");
+  TORCH_CHECK(batch > 0 && x.H % batch == 0, "global_pool_fc: ", x.H, " rows for a batch of ", batch);
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 && weights.dim() == 2 &&
+                  weights.size(1) == x.C, "global_pool_fc: weights float32 [nout, C]");
+  Tensor w = weights.contiguous();
+  const int nout = (int)w.size(0);
+  Tensor b;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kFloat32 && bias->numel() == nout,
+                "global_pool_fc: bias float32 [nout]");
+    b = bias->contiguous();
+  }
+  Tensor out = torch::empty({batch, nout}, data_in.options().dtype(torch::kFloat32).memory_format(c10::MemoryFormat::Contiguous));
+  OCNN_CALL(ocnn_global_pool_fc(x.t.data_ptr(), w.data_ptr<float>(), b.defined() ? b.data_ptr<float>() : nullptr,
+                                out.data_ptr<float>(), batch, x.H / batch, x.C, nout, x.dtype,
+                                current_stream()));
+  return out;
+}
+
 // ---- keys, search, interpolation, alignment (pytorch/cpp/octree_key.cpp, octree_align.cpp) ------------
 // The reference's binding is compiled with 64-bit keys only (pytorch/cpp/octree_key.cpp:1-3), so
 // key tensors are int64; a 32-bit-key octree is rejected here with a message.
@@ -1561,7 +1587,7 @@ Tensor feature_node_major(Tensor octree, int c_pad, bool bf16, bool half) {
 // from C++, with every activation carved out of one arena that is reused across calls.
 // Activations are bf16 node-major ([H, C]); slot s at depth d holds nnum[d] rows.
 struct ExecOp {
-  enum Kind { kFeature, kConvTc, kConv, kPool } kind;
+  enum Kind { kFeature, kConvTc, kConv, kPool, kHead } kind;
   std::string name;
   int depth = 0, cin = 0, cout = 0, stride = 1, relu = 0;
   int in = -1, out = -1, res = -1;
@@ -1615,6 +1641,17 @@ class NetExecutor {
     op.cin = op.cout = channels; op.in = in; op.out = out;
     return push(op);
   }
+  // global average pool over the full level `depth` + Linear: the output is fp32 [batch, nout]
+  int add_head(int depth, int channels, int nout, Tensor weights, c10::optional<Tensor> bias, int in,
+               int out) {
+    ExecOp op; op.kind = ExecOp::kHead; op.name = "head"; op.depth = depth; op.cin = channels;
+    op.cout = nout; op.in = in; op.out = out;
+    TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 &&
+                    weights.numel() == (int64_t)channels * nout, "add_head: weights float32 [nout, channels]");
+    op.weights = weights.contiguous();
+    if (bias.has_value() && bias->defined()) op.bias = bias->contiguous();
+    return push(op);
+  }
   void set_trace(int op_index) { trace_ = op_index; }   // -2 none, -1 every op, >= 0 one op
 
   // Runs the recorded ops; returns the last op's output as a [1,C,H,1] channels_last tensor
@@ -1633,7 +1670,7 @@ class NetExecutor {
     for (auto& op : ops_) {
       const int d = op.kind == ExecOp::kPool ? op.depth - 1 : op.depth;
       TORCH_CHECK(d >= 1 && d <= o.meta.depth, "NetExecutor: op ", op.name, " outside the octree depth");
-      cap[op.out] = std::max<int64_t>(cap[op.out], (int64_t)o.meta.nnum[d] * op.cout * 2);
+      cap[op.out] = std::max<int64_t>(cap[op.out], (int64_t)o.meta.nnum[d] * op.cout * (op.kind == ExecOp::kHead ? 4 : 2));
     }
     int64_t total = 0, pool_tmp = 0;
     for (int s = 0; s < nslots; ++s) { offs[s] = total; total += (cap[s] + 255) / 256 * 256; }
@@ -1647,6 +1684,11 @@ class NetExecutor {
     uint8_t* base = arena_.data_ptr<uint8_t>();
     auto slot = [&](int s) { return s < 0 ? nullptr : base + offs[s]; };
 
+    // a classification head's logits outlive the arena's next use: they get a tensor of their own
+    Tensor head_out;
+    if (ops_.back().kind == ExecOp::kHead)
+      head_out = torch::empty({(int64_t)o.meta.batch_size, (int64_t)ops_.back().cout},
+                              octree.options().dtype(torch::kFloat32));
     int index = 0;     // (events of earlier forwards stay queued until trace_ms() collects them)
     for (auto& op : ops_) {
       const bool traced = trace_ == -1 || trace_ == index;
@@ -1698,6 +1740,20 @@ class NetExecutor {
           }
           break;
         }
+        case ExecOp::kHead: {
+          const int h = m.nnum[op.depth], batch = m.batch_size;
+          TORCH_CHECK(rows[op.in] == h && chans[op.in] == op.cin && batch > 0 &&
+                          (int64_t)h == ((int64_t)batch << (3 * op.depth)),
+                      "NetExecutor: the head needs a full level (depth ", op.depth, ": ", h,
+                      " nodes for a batch of ", batch, ")");
+          OCNN_CALL(ocnn_global_pool_fc(slot(op.in), op.weights.data_ptr<float>(),
+                                        op.bias.defined() ? op.bias.data_ptr<float>() : nullptr,
+                                        (&op == &ops_.back() && head_out.defined())
+                                            ? head_out.data_ptr<float>()
+                                            : reinterpret_cast<float*>(slot(op.out)),
+                                        batch, h / batch, op.cin, op.cout, OCNN_BF16, st));
+          break;
+        }
         case ExecOp::kPool: {
           // OctreeMaxPool: max over sibling groups, then pad to every node of depth - 1
           const int h = m.nnum[op.depth], top = h / 8;
@@ -1728,6 +1784,7 @@ class NetExecutor {
       ++index;
     }
     const ExecOp& last = ops_.back();
+    if (last.kind == ExecOp::kHead) return head_out;
     auto opts = octree.options().dtype(torch::kBFloat16);
     return torch::from_blob(slot(last.out), {1, chans[last.out], rows[last.out], 1},
                             {chans[last.out] * rows[last.out], 1, chans[last.out], chans[last.out]},
@@ -1904,6 +1961,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("packed"), py::arg("num_output"), py::arg("scale") = py::none(),
         py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("relu") = false,
         py::arg("status"));
+  m.def("global_pool_fc", &global_pool_fc, py::arg("data_in"), py::arg("weights"),
+        py::arg("bias") = py::none(), py::arg("batch"));
   m.def("octree_encode_key", &octree_encode_key, "encode xyz-id to octree key");
   m.def("octree_decode_key", &octree_decode_key, "decode octree key to xyz-id");
   m.def("octree_xyz2key", &octree_xyz2key, "convert key from xyz order");
@@ -1937,6 +1996,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("output") = 0, py::arg("residual") = -1, py::arg("pointwise_above") = -1)
       .def("add_conv_pair", &NetExecutor::add_conv_pair)
       .def("add_pool", &NetExecutor::add_pool)
+      .def("add_head", &NetExecutor::add_head)
       .def("set_trace", &NetExecutor::set_trace)
       .def("forward", &NetExecutor::forward, py::call_guard<py::gil_scoped_release>())
       .def("trace_ms", &NetExecutor::trace_ms)

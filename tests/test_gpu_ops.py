@@ -212,3 +212,24 @@ def test_octree2col_matches_oracle(ocnn, batch):
         hc = H if stride == 1 else H // 8
         got = ocnn.octree2col(gu.data_cuda(x), octree, d, ks, stride, False)
         assert np.array_equal(got.cpu().numpy(), oc.octree2col(x, v.prop('neigh', d), ks, stride, hc))
+
+
+@pytest.mark.parametrize('half', [False, True], ids=['bf16', 'fp16'])
+@pytest.mark.parametrize('shape', [(32, 64, 512, 40), (3, 8, 32, 7), (1, 512, 96, 20)])
+def test_global_pool_fc(shape, half):
+  """FullOctreeGlobalPool + Linear (pytorch/ocnn/octree_pool.py:106-115, resnet.py:18-21) in one launch
+  against the mean over each shape's rows and a float64 matrix product."""
+  import ocnn
+  batch, per, C, nout = shape
+  rng = np.random.default_rng(batch + C)
+  rnd = gu.half_round if half else gu.bf16_round
+  x = rnd(rng.uniform(-1, 1, size=(C, batch * per)).astype(np.float32))
+  w = rng.normal(size=(nout, C)).astype(np.float32)
+  b = rng.normal(size=nout).astype(np.float32)
+  want = x.reshape(C, batch, per).astype(np.float64).mean(axis=2).T @ w.T.astype(np.float64) + b
+  got = ocnn.nn.global_pool_fc(gu.data_cuda(x, True, not half, half), torch.from_numpy(w).cuda(),
+                               torch.from_numpy(b).cuda(), batch)
+  assert got.shape == (batch, nout) and got.dtype == torch.float32
+  assert np.abs(got.cpu().numpy() - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+  with pytest.raises(RuntimeError, match='rows'):
+    ocnn.nn.global_pool_fc(gu.data_cuda(x, True, not half, half), torch.from_numpy(w).cuda(), None, batch * per + 1)
