@@ -508,6 +508,18 @@ int ocnn_points_bbox(const float* xyz_dev, int64_t n, float* out6_dev, void* wor
 int ocnn_feature_to_node_major(const float* feature_dev, void* out_dev, int channels, int c_pad,
                                int nnum, int dtype, void* stream);
 
+/* A 1x1x1 convolution with its epilogue followed by OctreeMaxPool (octree_max_pool, then octree_pad
+ * with 0 at depth - 1: pytorch/ocnn/octree_pool.py, OctreeMaxPool.forward) in one pass: the
+ * convolution's own output is never written.  x: [h, cin] rows of level `depth`, 16-bit node-major;
+ * weights fp32 [cout, cin]; epilogue as in ocnn_octree_conv (a residual has h rows of cout
+ * channels); top: [top_h, cout] rows of level depth - 1; child_parent_dev: the Child block of level
+ * depth - 1; group_parent_dev: scratch of h / 8 ints.  cin, cout in {8, 16, 32, 64} (not 64 -> 64),
+ * OCNN_ERR_UNSUPPORTED otherwise: the caller then runs the two operators. */
+int ocnn_octree_conv1x1_max_pool_pad(const void* x_dev, const float* weights_dev, void* top_dev,
+                                     const int32_t* child_parent_dev, int h, int top_h, int cin,
+                                     int cout, int dtype, const ocnn_conv_epilogue* epilogue,
+                                     int32_t* group_parent_dev, void* stream);
+
 /* The classification header of the reference's networks in one launch: FullOctreeGlobalPool (the
  * mean over the 8^d cells of each shape's full level, pytorch/ocnn/octree_pool.py:106-115) followed
  * by the Linear layer (pytorch/ocnn/resnet.py:18-21, lenet.py).  x: 16-bit node-major

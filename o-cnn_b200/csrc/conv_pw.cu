@@ -23,6 +23,10 @@ struct PwArgs {
   int relu;
   int f16;                 // the 16-bit elements are fp16 instead of bf16
   int wide;                // x, y and the residual start on 32-byte boundaries
+  // conv_pw_mma_kernel<.., POOL = true>: the layer's output is max-pooled over sibling groups (8
+  // consecutive rows) and the group's row written to row pool_inv[group] of y (OctreeMaxPool's
+  // pad: the parent node of the group); the un-pooled output is not stored at all
+  const int* pool_inv;
 };
 
 // CIN > 0: the channel count is a compile-time constant and a thread requests its whole rows
@@ -290,7 +294,7 @@ __device__ __forceinline__ void store_words(uint32_t* p, const uint32_t (&v)[W])
 // (+ 2), logical column 2q + e of accumulator tile j is output channel q*COUT/4 + 2j + e.  A
 // lane then reads its CIN/4 input channels and writes its COUT/4 output channels (and reads the
 // shortcut's) of a row as one vector each, and a warp instruction covers 8 whole consecutive rows.
-template <int CIN, int COUT, bool HALF>
+template <int CIN, int COUT, bool HALF, bool POOL = false>
 __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   constexpr int KS = CIN >= 16 ? CIN / 16 : 1;     // 16-wide (8-wide for CIN = 8) K slices
   constexpr int NT = COUT / 8;                      // 8-column accumulator tiles
@@ -384,11 +388,28 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
         v0 += fa.x; v1 += fa.y; v2 += fb.x; v3 += fb.y;
       }
       if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
+      if constexpr (POOL) {
+        // rows g = 0..7 of the tile are one sibling group, rows 8..15 the next: the maximum over g
+        // (lane bits 2..4); fmaxf drops a NaN operand, like the pool kernel
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+          v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, d));
+          v1 = fmaxf(v1, __shfl_xor_sync(0xffffffffu, v1, d));
+          v2 = fmaxf(v2, __shfl_xor_sync(0xffffffffu, v2, d));
+          v3 = fmaxf(v3, __shfl_xor_sync(0xffffffffu, v3, d));
+        }
+      }
       oa[j] = pack2(v0, v1, HALF);
       ob[j] = pack2(v2, v3, HALF);
     }
-    if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
-    if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
+    if constexpr (POOL) {
+      // (a level holds whole sibling groups: a group's rows exist together)
+      if (g == 0 && ok0) store_words<YW>(y32 + (long long)a.pool_inv[2 * tile] * (COUT / 2), oa);
+      if (g == 0 && ok1) store_words<YW>(y32 + (long long)a.pool_inv[2 * tile + 1] * (COUT / 2), ob);
+    } else {
+      if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
+      if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
+    }
 #pragma unroll
     for (int i = 0; i < XW; ++i) { xa[i] = nxa[i]; xb[i] = nxb[i]; }
 #pragma unroll
@@ -534,12 +555,35 @@ int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
   const long long want = (warps + 47) / 48;
   const long long cap = (long long)sm_count() * 8;
   const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-  if (a.f16)
+  if (a.pool_inv != nullptr) {
+    if (a.f16)
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, true, true>, dim3(grid), dim3(256), 0, st, a));
+    else
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, false, true>, dim3(grid), dim3(256), 0, st, a));
+  } else if (a.f16) {
     OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, true>, dim3(grid), dim3(256), 0, st, a));
-  else
+  } else {
     OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, false>, dim3(grid), dim3(256), 0, st, a));
+  }
   OCNN_LAUNCH_OK("conv_pw_mma_kernel");
   return OCNN_OK;
+}
+
+// Before the pooled layer: for every node p of the parent level, inv[child[p]] = p for a non-empty
+// node (its sibling group's pooled row goes to row p), a zero row p for a leaf.  One thread per
+// (node, 16-byte piece of the row).
+__global__ void __launch_bounds__(256) pool_prepare_kernel(const int* __restrict__ child, int top_h,
+                                                           int* __restrict__ inv, uint4* __restrict__ top,
+                                                           int chunks) {
+  grid_dependency_wait();
+  const long long total = (long long)top_h * chunks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(i / chunks), c = (int)(i % chunks);
+    const int ch = child[p];
+    if (ch < 0) top[i] = make_uint4(0, 0, 0, 0);
+    else if (c == 0) inv[ch] = p;
+  }
 }
 
 // -1: not a shape the mma kernel is built for
@@ -576,6 +620,7 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
   a.relu = ep ? ep->relu : 0;
   a.f16 = f16 ? 1 : 0;
+  a.pool_inv = nullptr;
   a.wide = (((uintptr_t)x % 32) == 0 && ((uintptr_t)y % 32) == 0 &&
             (!(ep && ep->residual_dev) || ((uintptr_t)ep->residual_dev % 32) == 0)) ? 1 : 0;
   {
@@ -598,6 +643,41 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
     }
     default: return -1;
   }
+}
+
+// 1x1x1 convolution + OctreeMaxPool (max over sibling groups, pad to the parent level) in one pass
+// over the data: the streaming kernel's 16-row tiles are two sibling groups.  -1: not a shape that
+// kernel takes.
+int conv_pointwise_pool_bf16(const void* x, const float* w, void* top, const int* child_parent, int h,
+                             int top_h, int cin, int cout, const ocnn_conv_epilogue* ep, int* inv,
+                             cudaStream_t st, bool f16) {
+  if (h % 8 != 0 || cout % 8 != 0) return -1;
+  if (((uintptr_t)x % 16) != 0 || ((uintptr_t)top % 16) != 0) return -1;
+  if (ep && ep->residual_dev && ((uintptr_t)ep->residual_dev % 16) != 0) return -1;
+  PwArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.w = w;
+  a.y = static_cast<__nv_bfloat16*>(top);
+  a.h = h; a.cin = cin;
+  a.y_stride = cout; a.co_base = 0;
+  a.scale = ep ? ep->scale_dev : nullptr;
+  a.bias = ep ? ep->bias_dev : nullptr;
+  a.residual = ep ? static_cast<const __nv_bfloat16*>(ep->residual_dev) : nullptr;
+  a.relu = ep ? ep->relu : 0;
+  a.f16 = f16 ? 1 : 0;
+  a.wide = 0;
+  a.pool_inv = inv;
+  // is it a shape of the mma kernel?  (decided before anything is launched)
+  bool known = false;
+  for (int ci : {8, 16, 32, 64})
+    for (int co : {8, 16, 32, 64})
+      if (cin == ci && cout == co && !(ci == 64 && co == 64)) known = true;
+  if (!known || (uintptr_t)w % 8 != 0) return -1;
+  const int chunks = cout / 8;
+  OCNN_CUDA_OK(launch_chained(pool_prepare_kernel, dim3(grid_for((long long)top_h * chunks, 256, 8)), dim3(256), 0,
+                              st, child_parent, top_h, inv, static_cast<uint4*>(top), chunks));
+  OCNN_LAUNCH_OK("pool_prepare_kernel");
+  return try_pw_mma(a, cout, st);
 }
 
 // The two-input 1x1x1 layer on the streaming kernel, for the shapes and sizes where it beats the

@@ -16,6 +16,9 @@ namespace ocnn {
 
 int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, int cout,
                         const ocnn_conv_epilogue* ep, cudaStream_t st, bool f16);   // conv_pw.cu
+int conv_pointwise_pool_bf16(const void* x, const float* w, void* top, const int* child_parent, int h,
+                             int top_h, int cin, int cout, const ocnn_conv_epilogue* ep, int* inv,
+                             cudaStream_t st, bool f16);                            // conv_pw.cu
 
 namespace {
 
@@ -312,6 +315,25 @@ extern "C" int ocnn_octree_conv(const void* x, const float* w, void* y, const in
   }
   return conv_simt_launch(x, w, y, neigh, nullptr, nullptr, h_in, h_out, cin, cout, tl, stride, dtype,
                           layout, ep, stream);
+}
+
+extern "C" int ocnn_octree_conv1x1_max_pool_pad(const void* x, const float* w, void* top,
+                                                const int32_t* child_parent, int h, int top_h, int cin,
+                                                int cout, int dtype, const ocnn_conv_epilogue* ep,
+                                                int32_t* group_parent, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(x && w && top && child_parent && group_parent, "ocnn_octree_conv1x1_max_pool_pad: null pointer");
+  OCNN_REQUIRE(dtype == OCNN_BF16 || dtype == OCNN_F16,
+               "ocnn_octree_conv1x1_max_pool_pad: bf16 or fp16 node-major data");
+  OCNN_REQUIRE(h >= 0 && h % 8 == 0 && top_h >= h / 8,
+               "ocnn_octree_conv1x1_max_pool_pad: %d rows are not whole sibling groups of %d parents", h, top_h);
+  if (top_h == 0) return OCNN_OK;
+  const int s = conv_pointwise_pool_bf16(x, w, top, child_parent, h, top_h, cin, cout, ep, group_parent,
+                                         static_cast<cudaStream_t>(stream), dtype == OCNN_F16);
+  if (s >= 0) return s;
+  return fail(OCNN_ERR_UNSUPPORTED,
+              "ocnn_octree_conv1x1_max_pool_pad: %d -> %d channels (8, 16, 32 or 64 each, not 64 -> 64; "
+              "16-byte aligned data)", cin, cout);
 }
 
 extern "C" int ocnn_octree_ichild(const int32_t* child, int nnum, int32_t* ichild, void* stream) {

@@ -21,6 +21,8 @@ PW_MIN_NODES = int(os.environ.get('OCNN_PW_MIN_NODES', '100000'))
 BLOCK_PAIR = int(os.environ.get('OCNN_BLOCK_PAIR', '1'))
 # global pool + FC of the classification networks as one launch of the executor (0: torch ops)
 HEAD_FUSED = int(os.environ.get('OCNN_HEAD_FUSED', '1'))
+# a level's last 1x1x1 layer and its max-pool as one pass on big levels (0: two launches)
+POOL_FUSED = int(os.environ.get('OCNN_POOL_FUSED', '1'))
 
 BN_EPS = 0.001   # pytorch/ocnn/modules.py:5
 
@@ -294,9 +296,11 @@ class GpuNet:
     else:
       conv(net['conv1'], net['depth'], cur, other, True)
       cur, other = other, cur
+      spare = 5          # third slot of the block input / output rotation (see the pooled layer below)
       for lv in net['levels']:
         d = lv['depth']
-        for blk in lv['blocks']:
+        pooled = False
+        for bi, blk in enumerate(lv['blocks']):
           conv(blk['a'], d, cur, 2, True)
           conv(blk['conv'], d, 2, 3, True)
           skip = cur
@@ -310,9 +314,23 @@ class GpuNet:
           if blk['c'] is not None:
             conv(blk['c'], d, cur, 4, False)
             skip = 4
-          conv(blk['b'], d, 3, other, True, skip)
+          p = blk['b']
+          if (POOL_FUSED and lv['pool'] and bi == len(lv['blocks']) - 1 and p['_pointwise'] and
+              p['_cout'] <= 32):
+            # (with 64 output channels the reduction over the eight rows -- three shuffles per
+            # accumulator value -- costs what the saved traffic gains: depth 5 stays on two launches)
+            # the level's last layer and its max-pool: one pass on big levels (the executor falls
+            # back to the two operators through slot `other` elsewhere); the pooled rows go to the
+            # rotation's spare slot, the block input `skip` is still being read as the shortcut
+            ex.add_conv_pool(p['name'], d, p['_cin'], p['_cout'], p['_w'], p['_packed'], p['_scale'],
+                             p['_bias'], True, 3, other, skip, spare, PW_MIN_NODES)
+            self.exec_layers.append(p['name'] + '+pool')
+            cur, spare = spare, cur
+            pooled = True
+            continue
+          conv(p, d, 3, other, True, skip)
           cur, other = other, cur
-        if lv['pool']:
+        if lv['pool'] and not pooled:
           ex.add_pool(d, lv['blocks'][-1]['b']['cout'], cur, other)
           self.exec_layers.append('pool%d' % d)
           cur, other = other, cur

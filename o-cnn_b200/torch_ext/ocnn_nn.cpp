@@ -1587,11 +1587,12 @@ Tensor feature_node_major(Tensor octree, int c_pad, bool bf16, bool half) {
 // from C++, with every activation carved out of one arena that is reused across calls.
 // Activations are bf16 node-major ([H, C]); slot s at depth d holds nnum[d] rows.
 struct ExecOp {
-  enum Kind { kFeature, kConvTc, kConv, kPool, kHead } kind;
+  enum Kind { kFeature, kConvTc, kConv, kPool, kHead, kConvPool } kind;
   std::string name;
   int depth = 0, cin = 0, cout = 0, stride = 1, relu = 0;
   int in = -1, out = -1, res = -1;
   int in2 = -1, cin2 = 0;         // second input of a two-input 1x1x1 layer (cin = the first one's)
+  int tmp = -1;                   // kConvPool: slot of the un-pooled output when the two run apart
   int64_t pointwise_above = -1;   // >= 0: prefer the streaming pointwise kernel from this many nodes
   std::vector<int> ks;
   Tensor weights, packed, scale, bias;     // kept alive here
@@ -1641,6 +1642,28 @@ class NetExecutor {
     op.cin = op.cout = channels; op.in = in; op.out = out;
     return push(op);
   }
+  // A 1x1x1 layer followed by OctreeMaxPool.  From `fused_above` nodes on (and for the channel
+  // counts the streaming kernel takes) the two run as one pass that never writes the un-pooled
+  // tensor; otherwise the layer writes slot `tmp` and the pool reads it.  `out` holds level
+  // depth - 1 and must differ from `in`, `res` and `tmp`.
+  int add_conv_pool(string name, int depth, int cin, int cout, Tensor weights,
+                    c10::optional<Tensor> packed, c10::optional<Tensor> scale,
+                    c10::optional<Tensor> bias, bool relu, int in, int tmp, int res, int out,
+                    int64_t fused_above) {
+    ExecOp op;
+    op.kind = ExecOp::kConvPool;
+    op.name = name; op.depth = depth; op.cin = cin; op.cout = cout; op.ks = {1, 1, 1};
+    op.relu = relu ? 1 : 0; op.in = in; op.tmp = tmp; op.res = res; op.out = out;
+    op.pointwise_above = fused_above;
+    TORCH_CHECK(out != in && out != tmp && out != res && tmp != in && tmp != res,
+                "add_conv_pool: the slots must be distinct");
+    TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32, "weights: float32 CUDA");
+    op.weights = weights.contiguous();
+    if (packed.has_value() && packed->defined()) op.packed = *packed;
+    if (scale.has_value() && scale->defined()) op.scale = scale->contiguous();
+    if (bias.has_value() && bias->defined()) op.bias = bias->contiguous();
+    return push(op);
+  }
   // global average pool over the full level `depth` + Linear: the output is fp32 [batch, nout]
   int add_head(int depth, int channels, int nout, Tensor weights, c10::optional<Tensor> bias, int in,
                int out) {
@@ -1665,10 +1688,12 @@ class NetExecutor {
       status_ = torch::zeros({1}, octree.options().dtype(torch::kInt32));
     // slot capacity = the largest tensor any op writes into it (slots are reused along the net)
     int nslots = 0;
-    for (auto& op : ops_) nslots = std::max(nslots, op.out + 1);
+    for (auto& op : ops_) nslots = std::max(nslots, std::max(op.out, op.tmp) + 1);
     vector<int64_t> rows(nslots, 0), chans(nslots, 0), offs(nslots, 0), cap(nslots, 0);
     for (auto& op : ops_) {
-      const int d = op.kind == ExecOp::kPool ? op.depth - 1 : op.depth;
+      const int d = (op.kind == ExecOp::kPool || op.kind == ExecOp::kConvPool) ? op.depth - 1 : op.depth;
+      if (op.kind == ExecOp::kConvPool)
+        cap[op.tmp] = std::max<int64_t>(cap[op.tmp], (int64_t)o.meta.nnum[op.depth] * op.cout * 2);
       TORCH_CHECK(d >= 1 && d <= o.meta.depth, "NetExecutor: op ", op.name, " outside the octree depth");
       cap[op.out] = std::max<int64_t>(cap[op.out], (int64_t)o.meta.nnum[d] * op.cout * (op.kind == ExecOp::kHead ? 4 : 2));
     }
@@ -1677,6 +1702,8 @@ class NetExecutor {
     for (auto& op : ops_)
       if (op.kind == ExecOp::kPool)
         pool_tmp = std::max<int64_t>(pool_tmp, (int64_t)o.meta.nnum[op.depth] / 8 * op.cin * 6);
+      else if (op.kind == ExecOp::kConvPool)
+        pool_tmp = std::max<int64_t>(pool_tmp, (int64_t)o.meta.nnum[op.depth] / 8 * 4);
     const int64_t tmp_off = total;
     total += (pool_tmp + 255) / 256 * 256;
     if (!arena_.defined() || arena_.numel() < total || arena_.device() != octree.device())
@@ -1740,6 +1767,40 @@ class NetExecutor {
           }
           break;
         }
+        case ExecOp::kConvPool: {
+          const int h = m.nnum[op.depth], top_h = m.nnum[op.depth - 1];
+          TORCH_CHECK(op.in >= 0 && rows[op.in] == h && chans[op.in] == op.cin, "NetExecutor: ", op.name,
+                      " input slot does not match");
+          TORCH_CHECK(op.res < 0 || (rows[op.res] == h && chans[op.res] == op.cout), "NetExecutor: ",
+                      op.name, " residual slot does not match");
+          ocnn_conv_epilogue ep;
+          ep.scale_dev = op.scale.defined() ? op.scale.data_ptr<float>() : nullptr;
+          ep.bias_dev = op.bias.defined() ? op.bias.data_ptr<float>() : nullptr;
+          ep.residual_dev = slot(op.res);
+          ep.relu = op.relu;
+          const int32_t* child_parent = level_ptr(o, OCNN_PROP_CHILD, op.depth - 1, "pool");
+          int rc = OCNN_ERR_UNSUPPORTED;
+          if (op.pointwise_above >= 0 && h >= op.pointwise_above)
+            rc = ocnn_octree_conv1x1_max_pool_pad(slot(op.in), op.weights.data_ptr<float>(), slot(op.out),
+                                                  child_parent, h, top_h, op.cin, op.cout, OCNN_BF16, &ep,
+                                                  reinterpret_cast<int32_t*>(base + tmp_off), st);
+          if (rc == OCNN_ERR_UNSUPPORTED) {
+            if (op.packed.defined()) {
+              OCNN_CALL(ocnn_octree_conv_tc(slot(op.in), op.packed.data_ptr(), slot(op.tmp), nullptr, h, h,
+                                            op.cin, op.cout, op.ks.data(), 1, &ep,
+                                            status_.data_ptr<int32_t>(), st));
+            } else {
+              OCNN_CALL(ocnn_octree_conv(slot(op.in), op.weights.data_ptr<float>(), slot(op.tmp), nullptr, h,
+                                         h, op.cin, op.cout, op.ks.data(), 1, OCNN_BF16, OCNN_NODE_MAJOR,
+                                         &ep, st));
+            }
+            OCNN_CALL(ocnn_octree_max_pool_pad(slot(op.tmp), slot(op.out), child_parent, op.cout, h, top_h,
+                                               OCNN_BF16, OCNN_NODE_MAJOR, st));
+          } else {
+            OCNN_CALL(rc);
+          }
+          break;
+        }
         case ExecOp::kHead: {
           const int h = m.nnum[op.depth], batch = m.batch_size;
           TORCH_CHECK(rows[op.in] == h && chans[op.in] == op.cin && batch > 0 &&
@@ -1775,7 +1836,7 @@ class NetExecutor {
           break;
         }
       }
-      rows[op.out] = m.nnum[op.kind == ExecOp::kPool ? op.depth - 1 : op.depth];
+      rows[op.out] = m.nnum[(op.kind == ExecOp::kPool || op.kind == ExecOp::kConvPool) ? op.depth - 1 : op.depth];
       chans[op.out] = op.cout;
       if (traced) {
         cudaEventRecord(e1, st);
@@ -1997,6 +2058,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("add_conv_pair", &NetExecutor::add_conv_pair)
       .def("add_pool", &NetExecutor::add_pool)
       .def("add_head", &NetExecutor::add_head)
+      .def("add_conv_pool", &NetExecutor::add_conv_pool)
       .def("set_trace", &NetExecutor::set_trace)
       .def("forward", &NetExecutor::forward, py::call_guard<py::gil_scoped_release>())
       .def("trace_ms", &NetExecutor::trace_ms)
