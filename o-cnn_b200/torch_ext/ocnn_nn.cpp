@@ -276,6 +276,47 @@ Tensor octree_max_pool_pad(Tensor data_in, Tensor octree, int depth) {
   return top;
 }
 
+ocnn_conv_epilogue make_epilogue(const c10::optional<Tensor>& scale, const c10::optional<Tensor>& bias,
+                                 const c10::optional<Tensor>& residual, bool relu, int cout,
+                                 const Tensor& y);
+
+// A 1x1x1 convolution (with scale / bias / residual / ReLU) followed by OctreeMaxPool, one pass:
+// data [1, Cin, nnum[depth], 1] 16-bit channels_last -> [1, Cout, nnum[depth - 1], 1].
+Tensor conv1x1_max_pool_pad(Tensor data_in, Tensor weights, Tensor octree, int depth,
+                            c10::optional<Tensor> scale, c10::optional<Tensor> bias,
+                            c10::optional<Tensor> residual, bool relu) {
+  OctreeRef o = get_octree(octree);
+  TORCH_CHECK(depth > 1 && depth <= o.meta.depth, "conv1x1_max_pool_pad: depth ", depth, " out of range");
+  need_cuda(data_in, "conv1x1_max_pool_pad");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "conv1x1_max_pool_pad");
+  TORCH_CHECK(x.dtype != OCNN_F32 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
+              "conv1x1_max_pool_pad takes bfloat16 or float16 channels_last data");
+  x.layout = OCNN_NODE_MAJOR;
+  TORCH_CHECK(o.meta.nnum[depth] == x.H, "conv1x1_max_pool_pad: data height ", x.H, " != node number ",
+              o.meta.nnum[depth]);
+  TORCH_CHECK(weights.is_cuda() && weights.scalar_type() == torch::kFloat32 && weights.dim() == 2 &&
+                  weights.size(1) == x.C, "conv1x1_max_pool_pad: weights float32 [Cout, Cin]");
+  Tensor w = weights.contiguous();
+  const int cout = (int)w.size(0), top_h = o.meta.nnum[depth - 1];
+  Tensor top = new_data(cout, top_h, x);
+  ocnn_conv_epilogue ep = make_epilogue(scale, bias, c10::nullopt, relu, cout, top);
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_cuda() && residual->dim() == 4 && residual->size(0) == 1 &&
+                    residual->size(1) == cout && residual->size(2) == x.H && residual->size(3) == 1 &&
+                    residual->scalar_type() == data_in.scalar_type() &&
+                    residual->is_contiguous(at::MemoryFormat::ChannelsLast),
+                "residual must be [1, Cout, H, 1] channels_last of the data's dtype");
+    ep.residual_dev = residual->data_ptr();
+  }
+  Tensor inv = torch::empty({std::max(x.H / 8, 1)}, data_in.options().dtype(torch::kInt32).memory_format(c10::MemoryFormat::Contiguous));
+  OCNN_CALL(ocnn_octree_conv1x1_max_pool_pad(x.t.data_ptr(), w.data_ptr<float>(), top.data_ptr(),
+                                             level_ptr(o, OCNN_PROP_CHILD, depth - 1, "conv1x1_max_pool_pad"),
+                                             x.H, top_h, x.C, cout, x.dtype, &ep, inv.data_ptr<int32_t>(),
+                                             current_stream()));
+  return top;
+}
+
 // ---- octree2col / col2octree ---------------------------------------------------------------------
 // ichild of a level (node of the i-th non-empty node), as pytorch/cpp/octree2col.cpp:8-18 builds it.
 Tensor make_ichild(const OctreeRef& o, int depth, const torch::TensorOptions& like, const char* what) {
@@ -2022,6 +2063,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("packed"), py::arg("num_output"), py::arg("scale") = py::none(),
         py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("relu") = false,
         py::arg("status"));
+  m.def("conv1x1_max_pool_pad", &conv1x1_max_pool_pad, py::arg("data_in"), py::arg("weights"),
+        py::arg("octree"), py::arg("depth"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("relu") = false);
   m.def("global_pool_fc", &global_pool_fc, py::arg("data_in"), py::arg("weights"),
         py::arg("bias") = py::none(), py::arg("batch"));
   m.def("octree_encode_key", &octree_encode_key, "encode xyz-id to octree key");

@@ -286,6 +286,32 @@ def test_pointwise_pair_rejects_what_it_cannot_run(ocnn):
     ocnn.nn.pointwise_conv_tc_pair(xa, xc, packed, 16, None, None, None, False, status)
 
 
+@pytest.mark.parametrize('half', [False, True], ids=['bf16', 'fp16'])
+@pytest.mark.parametrize('shape', [(6, 8, 32), (5, 16, 64), (4, 32, 8), (6, 64, 16), (3, 16, 16)])
+def test_conv1x1_max_pool_pad_is_the_two_operators(ocnn, batch, shape, half):
+  """A 1x1x1 layer + OctreeMaxPool (pytorch/ocnn/octree_pool.py: octree_max_pool, octree_pad) in one
+  pass against the two operators run one after the other on the same 16-bit data."""
+  merged, octree, v = batch
+  d, cin, cout = shape
+  H = int(v.nnum[d])
+  rng = np.random.default_rng(d * 100 + cin)
+  rnd = gu.half_round if half else gu.bf16_round
+  x = gu.data_cuda(rnd(rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)), True, not half, half)
+  res = gu.data_cuda(rnd(rng.normal(size=(cout, H)).astype(np.float32)), True, not half, half)
+  w = torch.from_numpy(rng.normal(scale=0.3, size=(cout, cin)).astype(np.float32)).cuda()
+  scale = torch.from_numpy(rng.uniform(0.5, 1.5, size=cout).astype(np.float32)).cuda()
+  bias = torch.from_numpy(rng.normal(size=cout).astype(np.float32)).cuda()
+  for relu, r in ((True, res), (False, None)):
+    got = ocnn.nn.conv1x1_max_pool_pad(x, w, octree, d, scale, bias, r, relu)
+    y = ocnn.nn.octree_conv_fused(x, w, octree, d, cout, [1, 1, 1], 1, scale, bias, r, relu)
+    want = ocnn.nn.octree_max_pool_pad(y, octree, d)
+    assert got.shape == want.shape == (1, cout, int(v.nnum[d - 1]), 1)
+    assert torch.equal(got, want)
+  with pytest.raises(RuntimeError, match='channels'):
+    ocnn.nn.conv1x1_max_pool_pad(gu.data_cuda(np.zeros((24, H), np.float32), True, True),
+                                 torch.zeros(8, 24, device='cuda'), octree, d)
+
+
 def test_bounded_wait_runs_out_and_reports(ocnn, batch):
   """A wait that nothing completes ends by itself: the waiter writes its code to the status word
   and raises the abort flag, a second waiter is told to stop, the kernel returns, and the next
