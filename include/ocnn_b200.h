@@ -520,6 +520,17 @@ int ocnn_octree_conv1x1_max_pool_pad(const void* x_dev, const float* weights_dev
                                      int cout, int dtype, const ocnn_conv_epilogue* epilogue,
                                      int32_t* group_parent_dev, void* stream);
 
+/* Two 1x1x1 layers in a row in one pass: y1 = epilogue1(w1 * x) is written as usual and
+ * y2 = epilogue2(w2 * y1) is computed from the rows of y1 while they are in registers (a residual
+ * block's conv1x1b + shortcut followed by the next block's conv1x1a: pytorch/ocnn/modules.py,
+ * OctreeResBlock.forward of two consecutive blocks).  16-bit node-major data of h rows; w1 fp32
+ * [cmid, cin], w2 fp32 [cout2, cmid]; epilogue2 without residual.  Built for the channel triples
+ * 8-32-8, 16-64-16, 16-32-8 and 8-16-8; OCNN_ERR_UNSUPPORTED otherwise (run the two layers). */
+int ocnn_octree_conv1x1_chain(const void* x_dev, const float* w1_dev, void* y1_dev,
+                              const ocnn_conv_epilogue* epilogue1, const float* w2_dev, void* y2_dev,
+                              const ocnn_conv_epilogue* epilogue2, int h, int cin, int cmid, int cout2,
+                              int dtype, void* stream);
+
 /* The classification header of the reference's networks in one launch: FullOctreeGlobalPool (the
  * mean over the 8^d cells of each shape's full level, pytorch/ocnn/octree_pool.py:106-115) followed
  * by the Linear layer (pytorch/ocnn/resnet.py:18-21, lenet.py).  x: 16-bit node-major

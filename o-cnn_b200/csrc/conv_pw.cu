@@ -27,6 +27,14 @@ struct PwArgs {
   // consecutive rows) and the group's row written to row pool_inv[group] of y (OctreeMaxPool's
   // pad: the parent node of the group); the un-pooled output is not stored at all
   const int* pool_inv;
+  // conv_pw_mma_kernel<.., C2 > 0>: a second 1x1x1 layer (the next block's conv1x1a) applied to the
+  // rows this one has just produced, while they are still in registers: y2 = act(scale2 * (w2 * y)
+  // + bias2), w2 fp32 [C2, COUT]
+  const float* w2;
+  const float* scale2;
+  const float* bias2;
+  __nv_bfloat16* y2;
+  int relu2;
 };
 
 // CIN > 0: the channel count is a compile-time constant and a thread requests its whole rows
@@ -294,8 +302,13 @@ __device__ __forceinline__ void store_words(uint32_t* p, const uint32_t (&v)[W])
 // (+ 2), logical column 2q + e of accumulator tile j is output channel q*COUT/4 + 2j + e.  A
 // lane then reads its CIN/4 input channels and writes its COUT/4 output channels (and reads the
 // shortcut's) of a row as one vector each, and a warp instruction covers 8 whole consecutive rows.
-template <int CIN, int COUT, bool HALF, bool POOL = false>
+template <int CIN, int COUT, bool HALF, bool POOL = false, int C2 = 0>
 __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
+  static_assert(C2 == 0 || (!POOL && COUT % 16 == 0 && C2 % 8 == 0), "second layer: whole K slices");
+  constexpr int KS2 = C2 > 0 ? COUT / 16 : 1, NT2 = C2 > 0 ? C2 / 8 : 1;   // second layer's slices, tiles
+  constexpr int CQ2 = C2 > 0 ? C2 / 4 : 2, YW2 = CQ2 / 2;
+  constexpr int PAIRS2 = C2 > 0 ? C2 * COUT / 2 : 1;
+  __shared__ uint32_t s2_hi[PAIRS2], s2_lo[PAIRS2];
   constexpr int KS = CIN >= 16 ? CIN / 16 : 1;     // 16-wide (8-wide for CIN = 8) K slices
   constexpr int NT = COUT / 8;                      // 8-column accumulator tiles
   constexpr int BR = CIN >= 16 ? 2 : 1;             // B registers per (slice, tile)
@@ -309,6 +322,12 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
   for (int p = threadIdx.x; p < PAIRS; p += blockDim.x) {
     const float2 w2 = *reinterpret_cast<const float2*>(a.w + 2 * p);
     split2(w2.x, w2.y, HALF, s_hi[p], s_lo[p]);
+  }
+  if constexpr (C2 > 0) {
+    for (int p = threadIdx.x; p < PAIRS2; p += blockDim.x) {
+      const float2 w2 = *reinterpret_cast<const float2*>(a.w2 + 2 * p);
+      split2(w2.x, w2.y, HALF, s2_hi[p], s2_lo[p]);
+    }
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
@@ -334,6 +353,33 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
       sc[j][e] = a.scale ? a.scale[q * CQ + 2 * j + e] : 1.f;
       bi[j][e] = a.bias ? a.bias[q * CQ + 2 * j + e] : 0.f;
     }
+  // The second layer's A operand is this layer's packed output: the pair (2q, 2q + 1) of
+  // accumulator tile 2s is K pair 2q of slice s, that of tile 2s + 1 is K pair 2q + 8, i.e. logical
+  // k of (slice s, register r) is output channel q*CQ + 2*(2s + r) + {0, 1}; its B fragments and
+  // its own output follow the same lane-contiguous scheme.
+  uint32_t b2h[KS2][NT2][2], b2l[KS2][NT2][2];
+  float sc2[NT2][2], bi2[NT2][2];
+  if constexpr (C2 > 0) {
+#pragma unroll
+    for (int s = 0; s < KS2; ++s)
+#pragma unroll
+      for (int j = 0; j < NT2; ++j)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int co = (g >> 1) * CQ2 + 2 * j + (g & 1);
+          const int ci = q * CQ + 2 * (2 * s + r);
+          const int p = (co * COUT + ci) >> 1;
+          b2h[s][j][r] = s2_hi[p];
+          b2l[s][j][r] = s2_lo[p];
+        }
+#pragma unroll
+    for (int j = 0; j < NT2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sc2[j][e] = a.scale2 ? a.scale2[q * CQ2 + 2 * j + e] : 1.f;
+        bi2[j][e] = a.bias2 ? a.bias2[q * CQ2 + 2 * j + e] : 0.f;
+      }
+  }
   const long long tiles = ((long long)a.h + 15) >> 4;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -409,6 +455,27 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
     } else {
       if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
       if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
+    }
+    if constexpr (C2 > 0) {
+      uint32_t* y2 = reinterpret_cast<uint32_t*>(a.y2) + q * YW2;
+      uint32_t pa[YW2], pb[YW2];
+#pragma unroll
+      for (int j = 0; j < NT2; ++j) {
+        float c2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < KS2; ++s) {
+          const uint32_t af[4] = {oa[2 * s], ob[2 * s], oa[2 * s + 1], ob[2 * s + 1]};
+          mma_16816(c2, af, b2l[s][j][0], b2l[s][j][1], HALF);
+          mma_16816(c2, af, b2h[s][j][0], b2h[s][j][1], HALF);
+        }
+        float u0 = fmaf(c2[0], sc2[j][0], bi2[j][0]), u1 = fmaf(c2[1], sc2[j][1], bi2[j][1]);
+        float u2 = fmaf(c2[2], sc2[j][0], bi2[j][0]), u3 = fmaf(c2[3], sc2[j][1], bi2[j][1]);
+        if (a.relu2) { u0 = fmaxf(u0, 0.f); u1 = fmaxf(u1, 0.f); u2 = fmaxf(u2, 0.f); u3 = fmaxf(u3, 0.f); }
+        pa[j] = pack2(u0, u1, HALF);
+        pb[j] = pack2(u2, u3, HALF);
+      }
+      if (ok0) store_words<YW2>(y2 + r0 * (C2 / 2), pa);
+      if (ok1) store_words<YW2>(y2 + r1 * (C2 / 2), pb);
     }
 #pragma unroll
     for (int i = 0; i < XW; ++i) { xa[i] = nxa[i]; xb[i] = nxb[i]; }
@@ -621,6 +688,7 @@ int conv_pointwise_bf16(const void* x, const float* w, void* y, int h, int cin, 
   a.relu = ep ? ep->relu : 0;
   a.f16 = f16 ? 1 : 0;
   a.pool_inv = nullptr;
+  a.w2 = nullptr; a.scale2 = nullptr; a.bias2 = nullptr; a.y2 = nullptr; a.relu2 = 0;
   a.wide = (((uintptr_t)x % 32) == 0 && ((uintptr_t)y % 32) == 0 &&
             (!(ep && ep->residual_dev) || ((uintptr_t)ep->residual_dev % 32) == 0)) ? 1 : 0;
   {
@@ -667,6 +735,7 @@ int conv_pointwise_pool_bf16(const void* x, const float* w, void* top, const int
   a.f16 = f16 ? 1 : 0;
   a.wide = 0;
   a.pool_inv = inv;
+  a.w2 = nullptr; a.scale2 = nullptr; a.bias2 = nullptr; a.y2 = nullptr; a.relu2 = 0;
   // is it a shape of the mma kernel?  (decided before anything is launched)
   bool known = false;
   for (int ci : {8, 16, 32, 64})
@@ -678,6 +747,53 @@ int conv_pointwise_pool_bf16(const void* x, const float* w, void* top, const int
                               st, child_parent, top_h, inv, static_cast<uint4*>(top), chunks));
   OCNN_LAUNCH_OK("pool_prepare_kernel");
   return try_pw_mma(a, cout, st);
+}
+
+// Two 1x1x1 layers in a row (a block's conv1x1b with its shortcut, then the next block's conv1x1a)
+// as one pass: the second reads the first's rows from registers.  -1: not a shape it is built for.
+int conv_pointwise_chain_bf16(const void* x, const float* w1, void* y1, int h, int cin, int cmid,
+                              const ocnn_conv_epilogue* ep1, const float* w2, void* y2, int cout2,
+                              const ocnn_conv_epilogue* ep2, cudaStream_t st, bool f16) {
+  if (((uintptr_t)x % 16) || ((uintptr_t)y1 % 16) || ((uintptr_t)y2 % 16)) return -1;
+  if (((uintptr_t)w1 % 8) || ((uintptr_t)w2 % 8)) return -1;
+  if (ep1 && ep1->residual_dev && ((uintptr_t)ep1->residual_dev % 16) != 0) return -1;
+  if (ep2 && ep2->residual_dev) return -1;
+  PwArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.w = w1;
+  a.y = static_cast<__nv_bfloat16*>(y1);
+  a.h = h; a.cin = cin;
+  a.y_stride = cmid; a.co_base = 0;
+  a.scale = ep1 ? ep1->scale_dev : nullptr;
+  a.bias = ep1 ? ep1->bias_dev : nullptr;
+  a.residual = ep1 ? static_cast<const __nv_bfloat16*>(ep1->residual_dev) : nullptr;
+  a.relu = ep1 ? ep1->relu : 0;
+  a.f16 = f16 ? 1 : 0;
+  a.wide = 0;
+  a.pool_inv = nullptr;
+  a.w2 = w2;
+  a.scale2 = ep2 ? ep2->scale_dev : nullptr;
+  a.bias2 = ep2 ? ep2->bias_dev : nullptr;
+  a.y2 = static_cast<__nv_bfloat16*>(y2);
+  a.relu2 = ep2 ? ep2->relu : 0;
+  const long long warps = ((long long)h + 15) / 16;
+  const long long want = (warps + 47) / 48;
+  const long long cap = (long long)sm_count() * 8;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+#define OCNN_CHAIN_CASE(CI, CM, CO)                                                                     \
+  if (cin == CI && cmid == CM && cout2 == CO) {                                                         \
+    if (f16)                                                                                            \
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CI, CM, true, false, CO>, dim3(grid), dim3(256), 0, \
+                                  st, a));                                                              \
+    else                                                                                                \
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CI, CM, false, false, CO>, dim3(grid), dim3(256), 0, \
+                                  st, a));                                                              \
+    OCNN_LAUNCH_OK("conv_pw_mma_kernel");                                                               \
+    return OCNN_OK;                                                                                     \
+  }
+  OCNN_CHAIN_CASE(8, 32, 8) OCNN_CHAIN_CASE(16, 64, 16) OCNN_CHAIN_CASE(16, 32, 8) OCNN_CHAIN_CASE(8, 16, 8)
+#undef OCNN_CHAIN_CASE
+  return -1;
 }
 
 // The two-input 1x1x1 layer on the streaming kernel, for the shapes and sizes where it beats the

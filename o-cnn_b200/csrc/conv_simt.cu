@@ -20,6 +20,10 @@ int conv_pointwise_pool_bf16(const void* x, const float* w, void* top, const int
                              int top_h, int cin, int cout, const ocnn_conv_epilogue* ep, int* inv,
                              cudaStream_t st, bool f16);                            // conv_pw.cu
 
+int conv_pointwise_chain_bf16(const void* x, const float* w1, void* y1, int h, int cin, int cmid,
+                              const ocnn_conv_epilogue* ep1, const float* w2, void* y2, int cout2,
+                              const ocnn_conv_epilogue* ep2, cudaStream_t st, bool f16);   // conv_pw.cu
+
 namespace {
 
 constexpr int BK = 16;
@@ -334,6 +338,23 @@ extern "C" int ocnn_octree_conv1x1_max_pool_pad(const void* x, const float* w, v
   return fail(OCNN_ERR_UNSUPPORTED,
               "ocnn_octree_conv1x1_max_pool_pad: %d -> %d channels (8, 16, 32 or 64 each, not 64 -> 64; "
               "16-byte aligned data)", cin, cout);
+}
+
+extern "C" int ocnn_octree_conv1x1_chain(const void* x, const float* w1, void* y1,
+                                         const ocnn_conv_epilogue* ep1, const float* w2, void* y2,
+                                         const ocnn_conv_epilogue* ep2, int h, int cin, int cmid,
+                                         int cout2, int dtype, void* stream) {
+  using namespace ocnn;
+  OCNN_REQUIRE(x && w1 && y1 && w2 && y2, "ocnn_octree_conv1x1_chain: null pointer");
+  OCNN_REQUIRE(dtype == OCNN_BF16 || dtype == OCNN_F16, "ocnn_octree_conv1x1_chain: bf16 or fp16 node-major data");
+  OCNN_REQUIRE(h >= 0, "ocnn_octree_conv1x1_chain: negative height");
+  OCNN_REQUIRE(!(ep2 && ep2->residual_dev), "ocnn_octree_conv1x1_chain: no residual on the second layer");
+  if (h == 0) return OCNN_OK;
+  const int s = conv_pointwise_chain_bf16(x, w1, y1, h, cin, cmid, ep1, w2, y2, cout2, ep2,
+                                          static_cast<cudaStream_t>(stream), dtype == OCNN_F16);
+  if (s >= 0) return s;
+  return fail(OCNN_ERR_UNSUPPORTED, "ocnn_octree_conv1x1_chain: %d -> %d -> %d channels is not one of "
+              "8-32-8, 16-64-16, 16-32-8, 8-16-8 (16-byte aligned data)", cin, cmid, cout2);
 }
 
 extern "C" int ocnn_octree_ichild(const int32_t* child, int nnum, int32_t* ichild, void* stream) {

@@ -23,6 +23,8 @@ BLOCK_PAIR = int(os.environ.get('OCNN_BLOCK_PAIR', '1'))
 HEAD_FUSED = int(os.environ.get('OCNN_HEAD_FUSED', '1'))
 # a level's last 1x1x1 layer and its max-pool as one pass on big levels (0: two launches)
 POOL_FUSED = int(os.environ.get('OCNN_POOL_FUSED', '1'))
+# a block's conv1x1b and the next block's conv1x1a as one pass on big levels (0: two launches)
+CHAIN_FUSED = int(os.environ.get('OCNN_CHAIN_FUSED', '1'))
 
 BN_EPS = 0.001   # pytorch/ocnn/modules.py:5
 
@@ -300,8 +302,11 @@ class GpuNet:
       for lv in net['levels']:
         d = lv['depth']
         pooled = False
+        a_done = False       # this block's conv1x1a was chained onto the previous block's conv1x1b
         for bi, blk in enumerate(lv['blocks']):
-          conv(blk['a'], d, cur, 2, True)
+          if not a_done:
+            conv(blk['a'], d, cur, 2, True)
+          a_done = False
           conv(blk['conv'], d, 2, 3, True)
           skip = cur
           pr = blk.get('_pair')
@@ -329,6 +334,15 @@ class GpuNet:
             pooled = True
             continue
           conv(p, d, 3, other, True, skip)
+          nxt = lv['blocks'][bi + 1]['a'] if bi + 1 < len(lv['blocks']) else None
+          if (CHAIN_FUSED and nxt is not None and p['_pointwise'] and nxt['_pointwise'] and
+              (p['_cin'], p['_cout'], nxt['_cout']) in ((8, 32, 8), (16, 64, 16), (16, 32, 8), (8, 16, 8))):
+            # the next block's first layer reads exactly the rows this one writes: on big levels
+            # both run as one pass (slot 2 is free again: the 3x3x3 layer has consumed it)
+            ex.add_chain(nxt['name'], nxt['_cout'], nxt['_w'], nxt['_packed'], nxt['_scale'], nxt['_bias'],
+                         True, 2, PW_MIN_NODES, PW_MIN_NODES if nxt['_pointwise'] else -1)
+            self.exec_layers[-1] = p['name'] + '+' + nxt['name'].split('.', 1)[1]
+            a_done = True
           cur, other = other, cur
         if lv['pool'] and not pooled:
           ex.add_pool(d, lv['blocks'][-1]['b']['cout'], cur, other)

@@ -317,6 +317,34 @@ Tensor conv1x1_max_pool_pad(Tensor data_in, Tensor weights, Tensor octree, int d
   return top;
 }
 
+// Two 1x1x1 layers in one pass: y1 = act1(scale1 * (w1 * x) + bias1 + residual1), y2 = act2(scale2 *
+// (w2 * y1) + bias2), 16-bit channels_last data; returns (y1, y2).
+std::tuple<Tensor, Tensor> conv1x1_chain(Tensor data_in, Tensor w1, c10::optional<Tensor> scale1,
+                                         c10::optional<Tensor> bias1, c10::optional<Tensor> residual1,
+                                         bool relu1, Tensor w2, c10::optional<Tensor> scale2,
+                                         c10::optional<Tensor> bias2, bool relu2) {
+  need_cuda(data_in, "conv1x1_chain");
+  c10::cuda::CUDAGuard guard(data_in.device());
+  DataRef x = get_data(data_in, "conv1x1_chain");
+  TORCH_CHECK(x.dtype != OCNN_F32 && (x.layout == OCNN_NODE_MAJOR || x.C == 1 || x.H == 1),
+              "conv1x1_chain takes bfloat16 or float16 channels_last data");
+  x.layout = OCNN_NODE_MAJOR;
+  TORCH_CHECK(w1.is_cuda() && w1.scalar_type() == torch::kFloat32 && w1.dim() == 2 && w1.size(1) == x.C,
+              "conv1x1_chain: w1 float32 [Cmid, Cin]");
+  const int cmid = (int)w1.size(0);
+  TORCH_CHECK(w2.is_cuda() && w2.scalar_type() == torch::kFloat32 && w2.dim() == 2 && w2.size(1) == cmid,
+              "conv1x1_chain: w2 float32 [Cout2, Cmid]");
+  const int cout2 = (int)w2.size(0);
+  Tensor a = w1.contiguous(), b = w2.contiguous();
+  Tensor y1 = new_data(cmid, x.H, x), y2 = new_data(cout2, x.H, x);
+  ocnn_conv_epilogue ep1 = make_epilogue(scale1, bias1, residual1, relu1, cmid, y1);
+  ocnn_conv_epilogue ep2 = make_epilogue(scale2, bias2, c10::nullopt, relu2, cout2, y2);
+  OCNN_CALL(ocnn_octree_conv1x1_chain(x.t.data_ptr(), a.data_ptr<float>(), y1.data_ptr(), &ep1,
+                                      b.data_ptr<float>(), y2.data_ptr(), &ep2, x.H, x.C, cmid, cout2,
+                                      x.dtype, current_stream()));
+  return std::make_tuple(y1, y2);
+}
+
 // ---- octree2col / col2octree ---------------------------------------------------------------------
 // ichild of a level (node of the i-th non-empty node), as pytorch/cpp/octree2col.cpp:8-18 builds it.
 Tensor make_ichild(const OctreeRef& o, int depth, const torch::TensorOptions& like, const char* what) {
@@ -1629,6 +1657,11 @@ Tensor feature_node_major(Tensor octree, int c_pad, bool bf16, bool half) {
 // Activations are bf16 node-major ([H, C]); slot s at depth d holds nnum[d] rows.
 struct ExecOp {
   enum Kind { kFeature, kConvTc, kConv, kPool, kHead, kConvPool } kind;
+  // a second 1x1x1 layer chained onto this (1x1x1) one: see add_chain
+  int out2 = -1, cout2 = 0, relu2 = 0;
+  Tensor weights2, packed2, scale2, bias2;
+  int64_t pointwise_above2 = -1, chain_above = -1;
+  std::string name2;
   std::string name;
   int depth = 0, cin = 0, cout = 0, stride = 1, relu = 0;
   int in = -1, out = -1, res = -1;
@@ -1683,6 +1716,26 @@ class NetExecutor {
     op.cin = op.cout = channels; op.in = in; op.out = out;
     return push(op);
   }
+  // Chains a second 1x1x1 layer (`name2`: cout -> cout2, no residual) onto the 1x1x1 layer recorded
+  // last: from `fused_above` nodes on, and for the channel triples the streaming kernel is built
+  // for, the two run as one pass; otherwise one after the other, exactly as recorded separately.
+  void add_chain(string name2, int cout2, Tensor weights2, c10::optional<Tensor> packed2,
+                 c10::optional<Tensor> scale2, c10::optional<Tensor> bias2, bool relu2, int out2,
+                 int64_t fused_above, int64_t pointwise_above2) {
+    TORCH_CHECK(!ops_.empty(), "add_chain: nothing recorded");
+    ExecOp& op = ops_.back();
+    TORCH_CHECK((op.kind == ExecOp::kConvTc || op.kind == ExecOp::kConv) && op.in2 < 0 &&
+                    op.ks[0] * op.ks[1] * op.ks[2] == 1, "add_chain: the last op must be a plain 1x1x1 layer");
+    TORCH_CHECK(out2 != op.out && out2 != op.in && out2 != op.res, "add_chain: out2 must be a slot of its own");
+    TORCH_CHECK(weights2.is_cuda() && weights2.scalar_type() == torch::kFloat32, "weights2: float32 CUDA");
+    op.name2 = name2; op.cout2 = cout2; op.relu2 = relu2 ? 1 : 0; op.out2 = out2;
+    op.weights2 = weights2.contiguous();
+    if (packed2.has_value() && packed2->defined()) op.packed2 = *packed2;
+    if (scale2.has_value() && scale2->defined()) op.scale2 = scale2->contiguous();
+    if (bias2.has_value() && bias2->defined()) op.bias2 = bias2->contiguous();
+    op.chain_above = fused_above;
+    op.pointwise_above2 = pointwise_above2;
+  }
   // A 1x1x1 layer followed by OctreeMaxPool.  From `fused_above` nodes on (and for the channel
   // counts the streaming kernel takes) the two run as one pass that never writes the un-pooled
   // tensor; otherwise the layer writes slot `tmp` and the pool reads it.  `out` holds level
@@ -1729,12 +1782,14 @@ class NetExecutor {
       status_ = torch::zeros({1}, octree.options().dtype(torch::kInt32));
     // slot capacity = the largest tensor any op writes into it (slots are reused along the net)
     int nslots = 0;
-    for (auto& op : ops_) nslots = std::max(nslots, std::max(op.out, op.tmp) + 1);
+    for (auto& op : ops_) nslots = std::max(nslots, std::max(std::max(op.out, op.tmp), op.out2) + 1);
     vector<int64_t> rows(nslots, 0), chans(nslots, 0), offs(nslots, 0), cap(nslots, 0);
     for (auto& op : ops_) {
       const int d = (op.kind == ExecOp::kPool || op.kind == ExecOp::kConvPool) ? op.depth - 1 : op.depth;
       if (op.kind == ExecOp::kConvPool)
         cap[op.tmp] = std::max<int64_t>(cap[op.tmp], (int64_t)o.meta.nnum[op.depth] * op.cout * 2);
+      if (op.out2 >= 0)
+        cap[op.out2] = std::max<int64_t>(cap[op.out2], (int64_t)o.meta.nnum[op.depth] * op.cout2 * 2);
       TORCH_CHECK(d >= 1 && d <= o.meta.depth, "NetExecutor: op ", op.name, " outside the octree depth");
       cap[op.out] = std::max<int64_t>(cap[op.out], (int64_t)o.meta.nnum[d] * op.cout * (op.kind == ExecOp::kHead ? 4 : 2));
     }
@@ -1791,7 +1846,25 @@ class NetExecutor {
           const bool identity = op.ks[0] * op.ks[1] * op.ks[2] == 1;
           const int32_t* neigh = identity ? nullptr : level_ptr(o, OCNN_PROP_NEIGH, op.depth, "conv");
           const bool stream_pw = identity && op.pointwise_above >= 0 && h >= op.pointwise_above;
-          if (op.in2 >= 0) {
+          bool chained = false;
+          if (op.out2 >= 0) {
+            ocnn_conv_epilogue ep2;
+            ep2.scale_dev = op.scale2.defined() ? op.scale2.data_ptr<float>() : nullptr;
+            ep2.bias_dev = op.bias2.defined() ? op.bias2.data_ptr<float>() : nullptr;
+            ep2.residual_dev = nullptr;
+            ep2.relu = op.relu2;
+            if (op.chain_above >= 0 && h >= op.chain_above) {
+              const int rc = ocnn_octree_conv1x1_chain(slot(op.in), op.weights.data_ptr<float>(), slot(op.out),
+                                                       &ep, op.weights2.data_ptr<float>(), slot(op.out2), &ep2,
+                                                       h, op.cin, op.cout, op.cout2, OCNN_BF16, st);
+              if (rc == OCNN_OK) chained = true;
+              else TORCH_CHECK(rc == OCNN_ERR_UNSUPPORTED, "ocnn_b200: ", ocnn_last_error());
+            }
+          }
+          if (chained) {
+            rows[op.out2] = h;
+            chans[op.out2] = op.cout2;
+          } else if (op.in2 >= 0) {
             TORCH_CHECK(op.in2 != op.out && rows[op.in2] == h && chans[op.in2] == op.cin2,
                         "NetExecutor: ", op.name, " second input slot does not match");
             OCNN_CALL(ocnn_octree_conv_tc_pair(slot(op.in), op.cin, slot(op.in2), op.cin2,
@@ -1805,6 +1878,25 @@ class NetExecutor {
             OCNN_CALL(ocnn_octree_conv(slot(op.in), op.weights.data_ptr<float>(), slot(op.out), neigh,
                                        h, h, op.cin, op.cout, op.ks.data(), 1, OCNN_BF16,
                                        OCNN_NODE_MAJOR, &ep, st));
+          }
+          if (op.out2 >= 0 && !chained) {
+            ocnn_conv_epilogue ep2;
+            ep2.scale_dev = op.scale2.defined() ? op.scale2.data_ptr<float>() : nullptr;
+            ep2.bias_dev = op.bias2.defined() ? op.bias2.data_ptr<float>() : nullptr;
+            ep2.residual_dev = nullptr;
+            ep2.relu = op.relu2;
+            const bool stream2 = op.pointwise_above2 >= 0 && h >= op.pointwise_above2;
+            if (op.packed2.defined() && !stream2) {
+              OCNN_CALL(ocnn_octree_conv_tc(slot(op.out), op.packed2.data_ptr(), slot(op.out2), nullptr, h, h,
+                                            op.cout, op.cout2, op.ks.data(), 1, &ep2,
+                                            status_.data_ptr<int32_t>(), st));
+            } else {
+              OCNN_CALL(ocnn_octree_conv(slot(op.out), op.weights2.data_ptr<float>(), slot(op.out2), nullptr,
+                                         h, h, op.cout, op.cout2, op.ks.data(), 1, OCNN_BF16,
+                                         OCNN_NODE_MAJOR, &ep2, st));
+            }
+            rows[op.out2] = h;
+            chans[op.out2] = op.cout2;
           }
           break;
         }
@@ -2066,6 +2158,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("conv1x1_max_pool_pad", &conv1x1_max_pool_pad, py::arg("data_in"), py::arg("weights"),
         py::arg("octree"), py::arg("depth"), py::arg("scale") = py::none(), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("relu") = false);
+  m.def("conv1x1_chain", &conv1x1_chain, py::arg("data_in"), py::arg("w1"), py::arg("scale1") = py::none(),
+        py::arg("bias1") = py::none(), py::arg("residual1") = py::none(), py::arg("relu1") = false,
+        py::arg("w2"), py::arg("scale2") = py::none(), py::arg("bias2") = py::none(),
+        py::arg("relu2") = false);
   m.def("global_pool_fc", &global_pool_fc, py::arg("data_in"), py::arg("weights"),
         py::arg("bias") = py::none(), py::arg("batch"));
   m.def("octree_encode_key", &octree_encode_key, "encode xyz-id to octree key");
@@ -2103,6 +2199,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("add_pool", &NetExecutor::add_pool)
       .def("add_head", &NetExecutor::add_head)
       .def("add_conv_pool", &NetExecutor::add_conv_pool)
+      .def("add_chain", &NetExecutor::add_chain)
       .def("set_trace", &NetExecutor::set_trace)
       .def("forward", &NetExecutor::forward, py::call_guard<py::gil_scoped_release>())
       .def("trace_ms", &NetExecutor::trace_ms)

@@ -443,3 +443,31 @@ def test_conv_tensor_core_nempty(ocnn, batch, case):
   assert int(status.item()) == 0
   full = np.maximum(want * scale[:, None] + bias[:, None] + res, 0)
   assert gu.rel_err(gu.to_np(got), full) < BF16_TOL
+
+
+@pytest.mark.parametrize('half', [False, True], ids=['bf16', 'fp16'])
+@pytest.mark.parametrize('triple', [(8, 32, 8), (16, 64, 16), (16, 32, 8), (8, 16, 8)])
+def test_conv1x1_chain_is_the_two_layers(ocnn, batch, triple, half):
+  """conv1x1b (+ shortcut, ReLU) of one block and conv1x1a of the next in one pass (two consecutive
+  OctreeResBlock.forward calls of pytorch/ocnn/modules.py) against the two layers run separately."""
+  merged, octree, v = batch
+  cin, cmid, cout2 = triple
+  d = 6
+  H = int(v.nnum[d])
+  rng = np.random.default_rng(cin * 7 + cmid)
+  rnd = gu.half_round if half else gu.bf16_round
+  x = gu.data_cuda(rnd(rng.uniform(-1, 1, size=(cin, H)).astype(np.float32)), True, not half, half)
+  res = gu.data_cuda(rnd(rng.normal(size=(cmid, H)).astype(np.float32)), True, not half, half)
+  w1 = torch.from_numpy(rng.normal(scale=0.3, size=(cmid, cin)).astype(np.float32)).cuda()
+  w2 = torch.from_numpy(rng.normal(scale=0.3, size=(cout2, cmid)).astype(np.float32)).cuda()
+  s1 = torch.from_numpy(rng.uniform(0.5, 1.5, size=cmid).astype(np.float32)).cuda()
+  b1 = torch.from_numpy(rng.normal(size=cmid).astype(np.float32)).cuda()
+  s2 = torch.from_numpy(rng.uniform(0.5, 1.5, size=cout2).astype(np.float32)).cuda()
+  b2 = torch.from_numpy(rng.normal(size=cout2).astype(np.float32)).cuda()
+  y1, y2 = ocnn.nn.conv1x1_chain(x, w1, s1, b1, res, True, w2, s2, b2, True)
+  want1 = ocnn.nn.octree_conv_fused(x, w1, octree, d, cmid, [1, 1, 1], 1, s1, b1, res, True)
+  want2 = ocnn.nn.octree_conv_fused(want1, w2, octree, d, cout2, [1, 1, 1], 1, s2, b2, None, True)
+  assert torch.equal(y1, want1)
+  # the same products summed in another order: equal to fp32 rounding, i.e. at most one 16-bit ulp
+  err = float((y2.float() - want2.float()).abs().max()) / max(1.0, float(want2.float().abs().max()))
+  assert err < (1e-3 if half else 8e-3)
