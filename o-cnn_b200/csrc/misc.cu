@@ -54,7 +54,20 @@ __global__ void __launch_bounds__(256) global_pool_fc_kernel(const uint16_t* __r
   const float inv = 1.f / (float)per;
   for (int c2 = threadIdx.x; 2 * c2 < C; c2 += blockDim.x) {
     float s0 = 0.f, s1 = 0.f;
-    for (int i = 0; i < per; ++i) {
+    // (eight rows requested at a time: one load per iteration left the sum waiting on each)
+    int i = 0;
+    for (; i + 8 <= per; i += 8) {
+      uint32_t r[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) r[k] = *reinterpret_cast<const uint32_t*>(xb + (long long)(i + k) * C + 2 * c2);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float2 v = unpack2(r[k], HALF);
+        s0 += v.x;
+        s1 += v.y;
+      }
+    }
+    for (; i < per; ++i) {
       const float2 v = unpack2(*reinterpret_cast<const uint32_t*>(xb + (long long)i * C + 2 * c2), HALF);
       s0 += v.x;
       s1 += v.y;
@@ -66,7 +79,16 @@ __global__ void __launch_bounds__(256) global_pool_fc_kernel(const uint16_t* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int o = warp; o < nout; o += blockDim.x >> 5) {
     float acc = 0.f;
-    for (int c = lane; c < C; c += 32) acc = fmaf(w[(long long)o * C + c], s_mean[c], acc);
+    const float* wr = w + (long long)o * C;
+    int c = lane;
+    for (; c + 7 * 32 < C; c += 8 * 32) {        // eight weight reads in flight
+      float wv[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) wv[k] = wr[c + 32 * k];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc = fmaf(wv[k], s_mean[c + 32 * k], acc);
+    }
+    for (; c < C; c += 32) acc = fmaf(wr[c], s_mean[c], acc);
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
     if (lane == 0) out[(long long)b * nout + o] = acc + (bias ? bias[o] : 0.f);
