@@ -224,16 +224,37 @@ class ClockSampler:
                                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     except OSError:
       self.proc = None
+    self.first = ''
+    self._reader = None
+
+  def wait_first_sample(self, timeout=20.0):
+    """Blocks until nvidia-smi has printed its first line.  Its start-up (loading NVML, enumerating
+    the box's GPUs) takes a second or two, and kernel launches issued meanwhile stalled for tens of
+    milliseconds at a time: on some boxes that landed in the first timed regions (39, 88, 28, 39 and
+    46 ms for five regions that take 28 ms each).  Sampling itself goes on until stop()."""
+    if self.proc is None:
+      return
+    import threading
+    got = []
+    self._reader = threading.Thread(target=lambda: got.append(self.proc.stdout.readline()), daemon=True)
+    self._reader.start()
+    self._reader.join(timeout)
+    self.first = got[0] if got else ''
+    time.sleep(0.3)
 
   def stop(self):
     if self.proc is None:
       return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
     self.proc.terminate()
+    if self._reader is not None and self._reader.is_alive():      # never produced a line
+      self.proc.kill()
+      return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples'], 'samples': 0}
     try:
       out, _ = self.proc.communicate(timeout=5)
     except subprocess.TimeoutExpired:
       self.proc.kill()
       out, _ = self.proc.communicate()
+    out = self.first + out
     sm, smax, reasons = [], [], set()
     for row in out.splitlines():
       f = [x.strip() for x in row.split(',')]
@@ -366,6 +387,8 @@ def run_ours(args):
     return octree, net.forward(octree)
 
   sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+  if sampler is not None:
+    sampler.wait_first_sample()
 
   # ---- warm-up; one warm-up step is instrumented per layer to find the dominant kernel ----
   layer_ms = {}

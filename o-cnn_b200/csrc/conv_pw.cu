@@ -23,9 +23,9 @@ struct PwArgs {
   int relu;
   int f16;                 // the 16-bit elements are fp16 instead of bf16
   int wide;                // x, y and the residual start on 32-byte boundaries
-  // conv_pw_mma_kernel<.., POOL = true>: the layer's output is max-pooled over sibling groups (8
-  // consecutive rows) and the group's row written to row pool_inv[group] of y (OctreeMaxPool's
-  // pad: the parent node of the group); the un-pooled output is not stored at all
+  // conv_pw_mma_pool_kernel: the layer's output is max-pooled over sibling groups (8 consecutive
+  // rows) and the group's row written to row pool_inv[group] of y (OctreeMaxPool's pad: the parent
+  // node of the group); the un-pooled output is not stored at all
   const int* pool_inv;
   // conv_pw_mma_kernel<.., C2 > 0>: a second 1x1x1 layer (the next block's conv1x1a) applied to the
   // rows this one has just produced, while they are still in registers: y2 = act(scale2 * (w2 * y)
@@ -302,9 +302,9 @@ __device__ __forceinline__ void store_words(uint32_t* p, const uint32_t (&v)[W])
 // (+ 2), logical column 2q + e of accumulator tile j is output channel q*COUT/4 + 2j + e.  A
 // lane then reads its CIN/4 input channels and writes its COUT/4 output channels (and reads the
 // shortcut's) of a row as one vector each, and a warp instruction covers 8 whole consecutive rows.
-template <int CIN, int COUT, bool HALF, bool POOL = false, int C2 = 0>
+template <int CIN, int COUT, bool HALF, int C2 = 0>
 __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
-  static_assert(C2 == 0 || (!POOL && COUT % 16 == 0 && C2 % 8 == 0), "second layer: whole K slices");
+  static_assert(C2 == 0 || (COUT % 16 == 0 && C2 % 8 == 0), "second layer: whole K slices");
   constexpr int KS2 = C2 > 0 ? COUT / 16 : 1, NT2 = C2 > 0 ? C2 / 8 : 1;   // second layer's slices, tiles
   constexpr int CQ2 = C2 > 0 ? C2 / 4 : 2, YW2 = CQ2 / 2;
   constexpr int PAIRS2 = C2 > 0 ? C2 * COUT / 2 : 1;
@@ -434,28 +434,11 @@ __global__ void __launch_bounds__(256) conv_pw_mma_kernel(const PwArgs a) {
         v0 += fa.x; v1 += fa.y; v2 += fb.x; v3 += fb.y;
       }
       if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
-      if constexpr (POOL) {
-        // rows g = 0..7 of the tile are one sibling group, rows 8..15 the next: the maximum over g
-        // (lane bits 2..4); fmaxf drops a NaN operand, like the pool kernel
-#pragma unroll
-        for (int d = 4; d < 32; d <<= 1) {
-          v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, d));
-          v1 = fmaxf(v1, __shfl_xor_sync(0xffffffffu, v1, d));
-          v2 = fmaxf(v2, __shfl_xor_sync(0xffffffffu, v2, d));
-          v3 = fmaxf(v3, __shfl_xor_sync(0xffffffffu, v3, d));
-        }
-      }
       oa[j] = pack2(v0, v1, HALF);
       ob[j] = pack2(v2, v3, HALF);
     }
-    if constexpr (POOL) {
-      // (a level holds whole sibling groups: a group's rows exist together)
-      if (g == 0 && ok0) store_words<YW>(y32 + (long long)a.pool_inv[2 * tile] * (COUT / 2), oa);
-      if (g == 0 && ok1) store_words<YW>(y32 + (long long)a.pool_inv[2 * tile + 1] * (COUT / 2), ob);
-    } else {
-      if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
-      if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
-    }
+    if (ok0) store_words<YW>(y32 + r0 * (COUT / 2), oa);
+    if (ok1) store_words<YW>(y32 + r1 * (COUT / 2), ob);
     if constexpr (C2 > 0) {
       uint32_t* y2 = reinterpret_cast<uint32_t*>(a.y2) + q * YW2;
       uint32_t pa[YW2], pb[YW2];
@@ -614,6 +597,125 @@ __global__ void __launch_bounds__(256) conv_pw_pair_kernel(const PwPairArgs a) {
   }
 }
 
+// The pooled form without any exchange between lanes.  Which NODE an MMA row stands for is free
+// too: a warp takes 16 sibling groups at a time and runs eight MMA passes over them, pass t on
+// sibling t of every group (row g of the pass = node 8*(G0 + g) + t, row g + 8 = node
+// 8*(G0 + g + 8) + t).  A lane then sees all eight siblings of its two groups one after the other
+// and keeps a running maximum of its accumulator values; after the eighth pass it writes its
+// quarter of the two pooled rows.  The next sibling's rows are requested before the current
+// ones are multiplied.
+template <int CIN, int COUT, bool HALF>
+__global__ void __launch_bounds__(256) conv_pw_mma_pool_kernel(const PwArgs a) {
+  constexpr int KS = CIN >= 16 ? CIN / 16 : 1;
+  constexpr int NT = COUT / 8;
+  constexpr int BR = CIN >= 16 ? 2 : 1;
+  constexpr int KQ = CIN / 4, CQ = COUT / 4;
+  constexpr int XW = KQ / 2, YW = CQ / 2;
+  constexpr int PAIRS = COUT * CIN / 2;
+  __shared__ uint32_t s_hi[PAIRS], s_lo[PAIRS];
+  grid_dependency_trigger();
+  grid_dependency_wait();
+  for (int p = threadIdx.x; p < PAIRS; p += blockDim.x) {
+    const float2 w2 = *reinterpret_cast<const float2*>(a.w + 2 * p);
+    split2(w2.x, w2.y, HALF, s_hi[p], s_lo[p]);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  uint32_t bh[KS][NT][BR], bl[KS][NT][BR];
+#pragma unroll
+  for (int s = 0; s < KS; ++s)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int r = 0; r < BR; ++r) {
+        const int co = (g >> 1) * CQ + 2 * j + (g & 1);
+        const int ci = q * KQ + (CIN >= 16 ? 4 * s + 2 * r : 0);
+        const int p = (co * CIN + ci) >> 1;
+        bh[s][j][r] = s_hi[p];
+        bl[s][j][r] = s_lo[p];
+      }
+  float sc[NT][2], bi[NT][2];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      sc[j][e] = a.scale ? a.scale[q * CQ + 2 * j + e] : 1.f;
+      bi[j][e] = a.bias ? a.bias[q * CQ + 2 * j + e] : 0.f;
+    }
+  const long long groups = (long long)a.h >> 3;
+  const long long supers = (groups + 15) >> 4;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const uint32_t* x32 = reinterpret_cast<const uint32_t*>(a.x) + q * XW;
+  const uint32_t* r32 = a.residual ? reinterpret_cast<const uint32_t*>(a.residual) + q * YW : nullptr;
+  uint32_t* y32 = reinterpret_cast<uint32_t*>(a.y) + q * YW;
+  for (long long sup = warp0; sup < supers; sup += nwarps) {
+    const long long ga = (sup << 4) + g, gb = ga + 8;          // this lane's two groups
+    const bool oka = ga < groups, okb = gb < groups;
+    auto load_pass = [&](int t, uint32_t (&pa)[XW], uint32_t (&pb)[XW], uint32_t (&qa)[YW],
+                         uint32_t (&qb)[YW]) {
+#pragma unroll
+      for (int i = 0; i < XW; ++i) pa[i] = pb[i] = 0u;
+#pragma unroll
+      for (int i = 0; i < YW; ++i) qa[i] = qb[i] = 0u;
+      if (t >= 8) return;
+      const long long ra = (ga << 3) + t, rb = (gb << 3) + t;
+      if (oka) load_words<XW>(x32 + ra * (CIN / 2), pa);
+      if (okb) load_words<XW>(x32 + rb * (CIN / 2), pb);
+      if (r32 && oka) load_words<YW>(r32 + ra * (COUT / 2), qa);
+      if (r32 && okb) load_words<YW>(r32 + rb * (COUT / 2), qb);
+    };
+    uint32_t xa[XW], xb[XW], ra_[YW], rb_[YW];
+    load_pass(0, xa, xb, ra_, rb_);
+    float m[NT][4];
+#pragma unroll(NT >= 8 ? 1 : 8)
+    for (int t = 0; t < 8; ++t) {
+      uint32_t nxa[XW], nxb[XW], nra[YW], nrb[YW];
+      load_pass(t + 1, nxa, nxb, nra, nrb);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+          if constexpr (CIN >= 16) {
+            const uint32_t af[4] = {xa[2 * s], xb[2 * s], xa[2 * s + 1], xb[2 * s + 1]};
+            mma_16816(acc, af, bl[s][j][0], bl[s][j][BR - 1], HALF);
+            mma_16816(acc, af, bh[s][j][0], bh[s][j][BR - 1], HALF);
+          } else {
+            mma_1688(acc, xa[0], xb[0], bl[s][j][0], HALF);
+            mma_1688(acc, xa[0], xb[0], bh[s][j][0], HALF);
+          }
+        }
+        float v0 = fmaf(acc[0], sc[j][0], bi[j][0]), v1 = fmaf(acc[1], sc[j][1], bi[j][1]);
+        float v2 = fmaf(acc[2], sc[j][0], bi[j][0]), v3 = fmaf(acc[3], sc[j][1], bi[j][1]);
+        if (r32) {
+          const float2 fa = unpack2(ra_[j], HALF), fb = unpack2(rb_[j], HALF);
+          v0 += fa.x; v1 += fa.y; v2 += fb.x; v3 += fb.y;
+        }
+        if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
+        if (t == 0) {
+          m[j][0] = v0; m[j][1] = v1; m[j][2] = v2; m[j][3] = v3;
+        } else {                       // fmaxf drops a NaN operand, like the pool kernel
+          m[j][0] = fmaxf(m[j][0], v0); m[j][1] = fmaxf(m[j][1], v1);
+          m[j][2] = fmaxf(m[j][2], v2); m[j][3] = fmaxf(m[j][3], v3);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < XW; ++i) { xa[i] = nxa[i]; xb[i] = nxb[i]; }
+#pragma unroll
+      for (int i = 0; i < YW; ++i) { ra_[i] = nra[i]; rb_[i] = nrb[i]; }
+    }
+    uint32_t oa[YW], ob[YW];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      oa[j] = pack2(m[j][0], m[j][1], HALF);
+      ob[j] = pack2(m[j][2], m[j][3], HALF);
+    }
+    if (oka) store_words<YW>(y32 + (long long)a.pool_inv[ga] * (COUT / 2), oa);
+    if (okb) store_words<YW>(y32 + (long long)a.pool_inv[gb] * (COUT / 2), ob);
+  }
+}
+
 template <int CIN, int COUT>
 int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
   const long long warps = ((long long)a.h + 15) / 16;
@@ -623,10 +725,14 @@ int launch_pw_mma(const PwArgs& a, cudaStream_t st) {
   const long long cap = (long long)sm_count() * 8;
   const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
   if (a.pool_inv != nullptr) {
+    // one pass over 16 sibling groups (eight MMA passes) per warp and iteration
+    const long long supers = ((long long)a.h / 8 + 15) / 16;
+    const long long pwant = (supers + 7) / 8;
+    const int pgrid = (int)(pwant < 1 ? 1 : (pwant > cap ? cap : pwant));
     if (a.f16)
-      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, true, true>, dim3(grid), dim3(256), 0, st, a));
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_pool_kernel<CIN, COUT, true>, dim3(pgrid), dim3(256), 0, st, a));
     else
-      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, false, true>, dim3(grid), dim3(256), 0, st, a));
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_pool_kernel<CIN, COUT, false>, dim3(pgrid), dim3(256), 0, st, a));
   } else if (a.f16) {
     OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CIN, COUT, true>, dim3(grid), dim3(256), 0, st, a));
   } else {
@@ -783,10 +889,10 @@ int conv_pointwise_chain_bf16(const void* x, const float* w1, void* y1, int h, i
 #define OCNN_CHAIN_CASE(CI, CM, CO)                                                                     \
   if (cin == CI && cmid == CM && cout2 == CO) {                                                         \
     if (f16)                                                                                            \
-      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CI, CM, true, false, CO>, dim3(grid), dim3(256), 0, \
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CI, CM, true, CO>, dim3(grid), dim3(256), 0,        \
                                   st, a));                                                              \
     else                                                                                                \
-      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CI, CM, false, false, CO>, dim3(grid), dim3(256), 0, \
+      OCNN_CUDA_OK(launch_chained(conv_pw_mma_kernel<CI, CM, false, CO>, dim3(grid), dim3(256), 0,       \
                                   st, a));                                                              \
     OCNN_LAUNCH_OK("conv_pw_mma_kernel");                                                               \
     return OCNN_OK;                                                                                     \

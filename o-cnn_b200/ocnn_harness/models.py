@@ -22,7 +22,8 @@ BLOCK_PAIR = int(os.environ.get('OCNN_BLOCK_PAIR', '1'))
 # global pool + FC of the classification networks as one launch of the executor (0: torch ops)
 HEAD_FUSED = int(os.environ.get('OCNN_HEAD_FUSED', '1'))
 # a level's last 1x1x1 layer and its max-pool as one pass on big levels (0: two launches)
-POOL_FUSED = int(os.environ.get('OCNN_POOL_FUSED', '1'))
+# (the value is the largest output channel count that is fused)
+POOL_FUSED = int(os.environ.get('OCNN_POOL_FUSED', '64'))
 # a block's conv1x1b and the next block's conv1x1a as one pass on big levels (0: two launches)
 CHAIN_FUSED = int(os.environ.get('OCNN_CHAIN_FUSED', '1'))
 
@@ -321,9 +322,7 @@ class GpuNet:
             skip = 4
           p = blk['b']
           if (POOL_FUSED and lv['pool'] and bi == len(lv['blocks']) - 1 and p['_pointwise'] and
-              p['_cout'] <= 32):
-            # (with 64 output channels the reduction over the eight rows -- three shuffles per
-            # accumulator value -- costs what the saved traffic gains: depth 5 stays on two launches)
+              p['_cout'] <= POOL_FUSED):
             # the level's last layer and its max-pool: one pass on big levels (the executor falls
             # back to the two operators through slot `other` elsewhere); the pooled rows go to the
             # rotation's spare slot, the block input `skip` is still being read as the shortcut
