@@ -224,8 +224,22 @@ class ClockSampler:
                                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     except OSError:
       self.proc = None
+    # every line the tool prints, collected by a reader thread for the sampler's whole life
+    self.lines = []
     self.first = ''
+    self._have_line = None
     self._reader = None
+    if self.proc is not None:
+      import threading
+      self._have_line = threading.Event()
+
+      def pump():
+        for row in self.proc.stdout:
+          self.lines.append(row)
+          self._have_line.set()
+
+      self._reader = threading.Thread(target=pump, daemon=True)
+      self._reader.start()
 
   def wait_first_sample(self, timeout=20.0):
     """Blocks until nvidia-smi has printed its first line.  Its start-up (loading NVML, enumerating
@@ -234,27 +248,20 @@ class ClockSampler:
     46 ms for five regions that take 28 ms each).  Sampling itself goes on until stop()."""
     if self.proc is None:
       return
-    import threading
-    got = []
-    self._reader = threading.Thread(target=lambda: got.append(self.proc.stdout.readline()), daemon=True)
-    self._reader.start()
-    self._reader.join(timeout)
-    self.first = got[0] if got else ''
-    time.sleep(0.3)
+    if self._have_line.wait(timeout):
+      self.first = self.lines[0]
+      time.sleep(0.3)
 
   def stop(self):
     if self.proc is None:
       return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
     self.proc.terminate()
-    if self._reader is not None and self._reader.is_alive():      # never produced a line
-      self.proc.kill()
-      return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples'], 'samples': 0}
     try:
-      out, _ = self.proc.communicate(timeout=5)
+      self.proc.wait(timeout=5)
     except subprocess.TimeoutExpired:
       self.proc.kill()
-      out, _ = self.proc.communicate()
-    out = self.first + out
+    self._reader.join(2.0)          # (a grandchild holding the pipe open must not hold the bench)
+    out = ''.join(list(self.lines))
     sm, smax, reasons = [], [], set()
     for row in out.splitlines():
       f = [x.strip() for x in row.split(',')]
