@@ -61,3 +61,22 @@ def test_clock_sampler_ignores_other_gpus_and_reports_slowdown(bench, tmp_path, 
   time.sleep(0.1)
   out = s.stop()
   assert out['sm_mhz'] == 1500.0 and out['reasons'] == ['hw_slowdown'] and out['samples'] == 1
+
+
+def test_physical_gpu_index_follows_cuda_visible_devices(bench, monkeypatch):
+  monkeypatch.delenv('CUDA_VISIBLE_DEVICES', raising=False)
+  assert bench.physical_gpu_index(2) == 2
+  monkeypatch.setenv('CUDA_VISIBLE_DEVICES', '5,7')
+  assert bench.physical_gpu_index(0) == 5 and bench.physical_gpu_index(1) == 7
+  assert bench.physical_gpu_index(3) == 3            # beyond the list: the local index itself
+  monkeypatch.setenv('CUDA_VISIBLE_DEVICES', 'GPU-8f2c,GPU-11aa')
+  assert bench.physical_gpu_index(1) == 1            # UUIDs: nothing to translate
+
+
+def test_conv_work_counts_the_reference_dense_flops(bench):
+  # octree/octree/octree_conv.cpp:287-289: a GEMM of [Cout, Cin*K] x [Cin*K, H]
+  flops, byts = bench.conv_work({'ks': [3, 3, 3], 'cin': 8, 'cout': 32}, 1000)
+  assert flops == 2.0 * 32 * 8 * 27 * 1000
+  assert byts == (8 + 32) * 1000 * 2 + 32 * 1000 + 32 * 8 * 27 * 2
+  flops, byts = bench.conv_work({'ks': [1, 1, 1], 'cin': 16, 'cout': 64}, 10)
+  assert flops == 2.0 * 64 * 16 * 10 and byts == (16 + 64) * 10 * 2 + 64 * 16 * 2
